@@ -1,0 +1,16 @@
+"""A Llama 4 text inference engine for one B200: config.json + safetensors -> paged cache ->
+one step function -> scheduler and sampling -> generated tokens.  CUDA kernels for sm_100a only."""
+
+from .cache import CacheManager, OutOfPages, Retention
+from .config import ConfigError, Llama4Config, known_architectures, preset, register_architecture, resolve
+from .engine import Engine, EngineError, Generator, Request, Scheduler, StepEntry, generate
+from .loading import load_model, model_from_tensors, random_model
+from .sampling import Sampler, SamplingParams
+from .weights import WeightError, write_random_model
+
+__all__ = [
+    "CacheManager", "ConfigError", "Engine", "EngineError", "Generator", "Llama4Config", "OutOfPages", "Request",
+    "Retention", "Sampler", "SamplingParams", "Scheduler", "StepEntry", "WeightError", "generate",
+    "known_architectures", "load_model", "model_from_tensors", "preset", "random_model", "register_architecture",
+    "resolve", "write_random_model",
+]

@@ -1,0 +1,156 @@
+// Routing of tokens to experts: router scores, top-k, sigmoid weights, the expert-sorted row order,
+// the scaled gather of rows into that order, and the sum of expert outputs back per token.
+//
+// Reference: llama4/llama4_jax/model.py:958-972 (scores = h W_router in 32-bit, top-k on the raw
+// scores, sigmoid of the chosen), model.py:1049-1073 (sort pairs by expert, gather rows, scale the
+// INPUT row by its router weight, group sizes), model.py:1109-1111 (unsort, sum over k),
+// model.py:1139 (add the shared expert).  Ties go to the lower expert index (jax.lax.top_k order).
+#include "common.cuh"
+
+#define ROUTER_MAX_E 256
+#define ROUTER_MAX_K 16
+
+// One block per token.  Warp w computes the scores of experts w, w + nwarp, ...: a fixed order of
+// the D products per (token, expert), so a token's routing does not depend on the batch.
+__global__ void router_kernel(const float* __restrict__ h, const float* __restrict__ w_router, int* __restrict__ topk_idx,
+                              float* __restrict__ topk_w, float* __restrict__ scores_out, int D, int E, int k) {
+  __shared__ float scores[ROUTER_MAX_E];
+  const int n = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  const float* hr = h + (size_t)n * D;
+  for (int e = warp; e < E; e += nwarp) {
+    const float* wr = w_router + (size_t)e * D;
+    float s = 0.f;
+    for (int d = lane; d < D; d += 32) s = fmaf(hr[d], wr[d], s);
+    s = warp_sum(s);
+    if (lane == 0) scores[e] = s;
+  }
+  __syncthreads();
+  if (scores_out)
+    for (int e = threadIdx.x; e < E; e += blockDim.x) scores_out[(size_t)n * E + e] = scores[e];
+  if (threadIdx.x == 0) {
+    for (int j = 0; j < k; ++j) {
+      int best = -1;
+      float bv = 0.f;
+      for (int e = 0; e < E; ++e) {
+        const float v = scores[e];
+        if (isnan(v)) continue;
+        if (best < 0 || v > bv) {  // strict: the lower index wins a tie
+          best = e;
+          bv = v;
+        }
+      }
+      if (best < 0) best = j;  // all NaN: still a valid expert index
+      topk_idx[(size_t)n * k + j] = best;
+      topk_w[(size_t)n * k + j] = 1.f / (1.f + expf(-bv));
+      scores[best] = NAN;  // taken
+    }
+  }
+}
+
+JLX_API int jlx_router(const float* h, const float* w_router, int* topk_idx, float* topk_w, float* scores_out, int N,
+                       int D, int E, int k, cudaStream_t stream) {
+  JLX_REQUIRE(N >= 0 && D > 0, "router: bad sizes N=%d D=%d", N, D);
+  JLX_REQUIRE(E >= 1 && E <= ROUTER_MAX_E, "router: %d experts; supported 1..%d", E, ROUTER_MAX_E);
+  JLX_REQUIRE(k >= 1 && k <= E && k <= ROUTER_MAX_K, "router: top-%d of %d experts; supported k in 1..min(E, %d)", k, E, ROUTER_MAX_K);
+  if (N == 0) return 0;
+  router_kernel<<<N, 256, 0, stream>>>(h, w_router, topk_idx, topk_w, scores_out, D, E, k);
+  JLX_LAUNCH_CHECK("router");
+  return 0;
+}
+
+// Counting sort of the P = N * k (token, choice) pairs by expert, stable in pair order.  One block;
+// warp w owns experts w, w + nwarp, ...  Writes offsets[E + 1], sorted_pair[P] (pair id at each sorted
+// row) and sorted_pos[P] (sorted row of each pair).
+__global__ void expert_sort_kernel(const int* __restrict__ topk_idx, int* __restrict__ offsets,
+                                   int* __restrict__ sorted_pair, int* __restrict__ sorted_pos, int P, int E, int* status) {
+  __shared__ int counts[ROUTER_MAX_E + 1];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  for (int e = warp; e < E; e += nwarp) {
+    int c = 0;
+    for (int base = 0; base < P; base += 32) {
+      const int i = base + lane;
+      const int v = i < P ? topk_idx[i] : -1;
+      c += __popc(__ballot_sync(0xffffffffu, v == e));
+    }
+    if (lane == 0) counts[e] = c;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int run = 0;
+    for (int e = 0; e < E; ++e) {
+      const int c = counts[e];
+      counts[e] = run;
+      offsets[e] = run;
+      run += c;
+    }
+    counts[E] = run;
+    offsets[E] = run;
+    if (run != P) atomicOr(status, JLX_STATUS_BAD_EXPERT);
+  }
+  __syncthreads();
+  for (int e = warp; e < E; e += nwarp) {
+    int at = counts[e];
+    for (int base = 0; base < P; base += 32) {
+      const int i = base + lane;
+      const int v = i < P ? topk_idx[i] : -1;
+      const unsigned mask = __ballot_sync(0xffffffffu, v == e);
+      if (v == e) {
+        const int dst = at + __popc(mask & ((1u << lane) - 1u));
+        sorted_pair[dst] = i;
+        sorted_pos[i] = dst;
+      }
+      at += __popc(mask);
+    }
+  }
+}
+
+JLX_API int jlx_expert_sort(const int* topk_idx, int* offsets, int* sorted_pair, int* sorted_pos, int P, int E,
+                            int* status, cudaStream_t stream) {
+  JLX_REQUIRE(P >= 0 && E >= 1 && E <= ROUTER_MAX_E, "expert_sort: bad sizes P=%d E=%d", P, E);
+  const int warps = E < 32 ? E : 32;
+  expert_sort_kernel<<<1, warps * 32, 0, stream>>>(topk_idx, offsets, sorted_pair, sorted_pos, P, E, status);
+  JLX_LAUNCH_CHECK("expert_sort");
+  return 0;
+}
+
+// a_sorted[i, :] = weight(pair) * h[token(pair), :]  with pair = sorted_pair[i], token = pair / k
+template <typename T>
+__global__ void permute_scale_kernel(const float* __restrict__ h, const int* __restrict__ sorted_pair,
+                                     const float* __restrict__ topk_w, T* __restrict__ a_sorted, int D, int k) {
+  const int i = blockIdx.x;
+  const int pair = sorted_pair[i];
+  const float w = topk_w[pair];
+  const float* src = h + (size_t)(pair / k) * D;
+  T* dst = a_sorted + (size_t)i * D;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) dst[d] = from_f32<T>(w * src[d]);
+}
+
+JLX_API int jlx_permute_scale(const float* h, const int* sorted_pair, const float* topk_w, void* a_sorted, int dtype,
+                              int P, int D, int k, cudaStream_t stream) {
+  JLX_REQUIRE(P >= 0 && D > 0 && k >= 1, "permute_scale: bad sizes");
+  if (P == 0) return 0;
+  JLX_DISPATCH_DTYPE(dtype, T, (permute_scale_kernel<T><<<P, 256, 0, stream>>>(h, sorted_pair, topk_w, (T*)a_sorted, D, k)));
+  JLX_LAUNCH_CHECK("permute_scale");
+  return 0;
+}
+
+// delta[n, :] = shared[n, :] + sum_j y_sorted[sorted_pos[n * k + j], :]   (j ascending: fixed order)
+__global__ void moe_combine_kernel(const float* __restrict__ y_sorted, const float* __restrict__ shared,
+                                   const int* __restrict__ sorted_pos, float* __restrict__ delta, int D, int k) {
+  const int n = blockIdx.x;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float s = shared ? shared[(size_t)n * D + d] : 0.f;
+    for (int j = 0; j < k; ++j) s += y_sorted[(size_t)sorted_pos[(size_t)n * k + j] * D + d];
+    delta[(size_t)n * D + d] = s;
+  }
+}
+
+JLX_API int jlx_moe_combine(const float* y_sorted, const float* shared, const int* sorted_pos, float* delta, int N,
+                            int D, int k, cudaStream_t stream) {
+  JLX_REQUIRE(N >= 0 && D > 0 && k >= 1, "moe_combine: bad sizes");
+  if (N == 0) return 0;
+  moe_combine_kernel<<<N, 256, 0, stream>>>(y_sorted, shared, sorted_pos, delta, D, k);
+  JLX_LAUNCH_CHECK("moe_combine");
+  return 0;
+}

@@ -1,0 +1,189 @@
+"""The step function: one batch of (request, its next tokens) through the model, from the cache.
+
+The reference runs prompts and decoding as two separate programs over padded rectangular
+batches (llama4/llama4_jax/model.py:1243-1277: ``prefill`` pads to a power of two, ``decode_step``
+takes [B, 1]) on a ring-buffer cache.  Here one ``step`` takes any mixture: portions of prompts
+of any length beside single decoded tokens, flattened to N token rows without padding.  It runs
+only those tokens, reads everything earlier from the paged cache, writes their keys and values
+into pages, and returns float32 logits at the places asked for.
+"""
+
+from __future__ import annotations
+
+import dataclasses
+from typing import Sequence
+
+import numpy as np
+import torch
+
+from ..cache.manager import CacheManager, OutOfPages
+from ..kernels import api as K
+from ..parts.base import StepContext
+from ..parts.decoder import DecoderModel
+
+
+class EngineError(RuntimeError):
+    pass
+
+
+@dataclasses.dataclass
+class StepEntry:
+    """A request's share of a step: its next tokens and the places among them whose logits are wanted."""
+
+    slot: int
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+class _HostRing:
+    """Pinned host buffers for step descriptors; a buffer is reused only after its copy has run."""
+
+    def __init__(self, n: int = 3):
+        self.bufs: list[torch.Tensor | None] = [None] * n
+        self.events: list[torch.cuda.Event | None] = [None] * n
+        self.i = 0
+
+    def next(self, size: int) -> tuple[torch.Tensor, int]:
+        i = self.i
+        self.i = (self.i + 1) % len(self.bufs)
+        if self.events[i] is not None:
+            self.events[i].synchronize()
+        if self.bufs[i] is None or self.bufs[i].numel() < size:
+            self.bufs[i] = torch.empty(max(size, 4096), dtype=torch.int32, pin_memory=True)
+        return self.bufs[i], i
+
+    def mark(self, i: int) -> None:
+        ev = self.events[i] or torch.cuda.Event()
+        ev.record()
+        self.events[i] = ev
+
+
+class Engine:
+    """Owns the cache (manager, pages, state slabs) of one model on one GPU and steps batches through it.
+
+    ``max_tokens``: tokens that all live requests may hold together (each request's count rounded
+    up to whole pages); every group's pool has ``ceil(max_tokens / page_size)`` pages.
+    ``max_seq_len``: longest request (sets the block-table width); default ``max_tokens``.
+    """
+
+    def __init__(self, model: DecoderModel, *, max_tokens: int, page_size: int = 64, max_slots: int = 64,
+                 max_seq_len: int | None = None):
+        if not torch.cuda.is_available():
+            raise EngineError("no CUDA device: this engine runs on a GPU only and has no CPU path")
+        if page_size <= 0 or max_tokens <= 0:
+            raise EngineError("page_size and max_tokens must be positive")
+        self.model, self.runtime = model, model.runtime
+        self.page_size, self.max_slots = page_size, max_slots
+        self.num_pages = -(-max_tokens // page_size)
+        self.max_seq_len = max_seq_len or max_tokens
+        self.max_pages_per_request = -(-self.max_seq_len // page_size)
+        plan = model.plan
+        K.preload(model.required_libraries())
+        self.manager = CacheManager(page_size, max_slots, self.max_pages_per_request)
+        for r in plan.groups:
+            self.manager.add_group(r, self.num_pages)
+        dev, dt = self.runtime.device, self.runtime.dtype
+        self.kv = [torch.zeros((self.num_pages, 2, c.num_kv_heads, page_size, c.head_dim), dtype=dt, device=dev)
+                   for c in plan.caches]
+        self.states = [torch.zeros((max_slots, *s.shape), dtype=s.dtype, device=dev) for s in plan.states]
+        self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+        self._ring = _HostRing()
+        self._dev_desc: torch.Tensor | None = None
+        self.steps_run = 0
+        self.record_routing = False  # True: keep each routed layer's expert choices of the last step
+        self.last_routing: list[torch.Tensor] = []
+
+    # ------------------------------------------------------------------ requests
+    def new_request(self) -> int:
+        """Takes a slot (raises OutOfSlots) and clears its per-request state."""
+        slot = self.manager.alloc_slot()
+        for s in self.states:
+            s[slot].zero_()
+        return slot
+
+    def finish(self, slot: int) -> int:
+        """Gives back everything the request holds; returns the number of pages given back."""
+        return self.manager.release(slot)
+
+    def length(self, slot: int) -> int:
+        return self.manager.committed(slot)
+
+    def cache_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in self.kv + self.states)
+
+    # ---------------------------------------------------------------------- step
+    def reserve(self, entries: Sequence[StepEntry]) -> None:
+        """Takes the pages the entries need; raises OutOfPages (pages taken for earlier entries stay reserved)."""
+        for e in entries:
+            self.manager.reserve(e.slot, self.manager.committed(e.slot) + len(e.tokens))
+
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Runs one batch.  Returns float32 logits [M, vocab] on the device, M = all wanted places in
+        the order of the entries and of each entry's ``want``."""
+        if not entries:
+            raise EngineError("a step needs at least one entry")
+        R = len(entries)
+        n_tok = np.fromiter((len(e.tokens) for e in entries), dtype=np.int32, count=R)
+        if (n_tok <= 0).any():
+            raise EngineError("every entry of a step needs at least one token")
+        if len({e.slot for e in entries}) != R:
+            raise EngineError("a request may appear only once in a step")
+        tokens = np.concatenate([np.asarray(e.tokens, dtype=np.int64) for e in entries])
+        if tokens.min() < 0 or tokens.max() >= self.model.vocab_size:
+            raise EngineError(f"token id outside the vocabulary [0, {self.model.vocab_size})")
+        tokens = tokens.astype(np.int32)
+        want_off = np.zeros(R + 1, dtype=np.int32)
+        np.cumsum([len(e.want) for e in entries], out=want_off[1:])
+        want = np.fromiter((w for e in entries for w in e.want), dtype=np.int32, count=int(want_off[-1]))
+        slots = np.fromiter((e.slot for e in entries), dtype=np.int32, count=R)
+        N, M = int(n_tok.sum()), int(want_off[-1])
+
+        self.reserve(entries)
+        starts = [self.manager.committed(e.slot) for e in entries]
+        max_kv = max(s + int(n) for s, n in zip(starts, n_tok))
+        width = -(-max_kv // self.page_size)
+        G = len(self.manager.groups)
+        size = CacheManager.packed_size(G, N, R, M, width)
+        host, ring_i = self._ring.next(size)
+        self.manager.pack_step(slots, n_tok, tokens, want_off, want, width, N, R, M, host.numpy())
+        if self._dev_desc is None or self._dev_desc.numel() < size:
+            self._dev_desc = torch.empty(max(size, 4096), dtype=torch.int32, device=self.runtime.device)
+        desc = self._dev_desc[:size]
+        desc.copy_(host[:size], non_blocking=True)
+        self._ring.mark(ring_i)
+
+        o = 0
+
+        def cut(n: int) -> torch.Tensor:
+            nonlocal o
+            v = desc[o:o + n]
+            o += n
+            return v
+
+        ctx = StepContext(
+            runtime=self.runtime, n_tokens=N, n_requests=R,
+            token_ids=cut(N), positions=cut(N), req_of_token=cut(N), cu_q=cut(R + 1), q_start=cut(R), kv_len=cut(R),
+            slot_ids=cut(R), logit_rows=cut(M), n_logit_rows=M, status=self.status,
+            host_q_lens=[int(n) for n in n_tok], host_q_start=starts, host_slot_ids=[int(s) for s in slots],
+            max_q_len=int(n_tok.max()), max_kv_len=max_kv,
+        )
+        block_tables = [cut(R * width).view(R, width) for _ in range(G)]
+        if self.record_routing:
+            ctx.scratch["record_routing"] = []
+        logits = self.model.forward(ctx, self.kv, self.states, block_tables)
+        self.last_routing = ctx.scratch.get("record_routing", [])
+        for e, s, n in zip(entries, starts, n_tok):
+            self.manager.commit(e.slot, s + int(n))
+        self.steps_run += 1
+        return logits
+
+    def check_status(self) -> None:
+        """Reads the kernels' status word (synchronises) and raises if any kernel refused something."""
+        bits = int(self.status.item())
+        if bits:
+            self.status.zero_()
+            why = [text for bit, text in K.STATUS_BITS.items() if bits & bit]
+            raise EngineError("a kernel reported: " + "; ".join(why))
+
+
+__all__ = ["Engine", "EngineError", "OutOfPages", "StepEntry"]

@@ -1,0 +1,82 @@
+"""The Python entry point for generation: host token ids in, host token ids out.
+
+The reference's offline path is ``prefill`` then a loop of ``decode_step`` over a fixed batch
+(llama4/main.py:68-75, llama4/llama4_jax/model.py:1243-1277), greedy.  Here requests of any
+lengths go through the scheduler and the one step function; tokens are sampled on the GPU and
+only the chosen ids come back to the host each step.
+"""
+
+from __future__ import annotations
+
+from typing import Sequence
+
+import torch
+
+from ..parts.decoder import DecoderModel
+from ..sampling.sampler import Sampler, SamplingParams
+from .engine import Engine, StepEntry
+from .scheduler import PlannedEntry, Request, Scheduler
+
+
+class Generator:
+    """An engine, a scheduler and a sampler around one model."""
+
+    def __init__(self, model: DecoderModel, *, max_tokens: int, page_size: int = 64, max_slots: int = 64,
+                 max_tokens_per_step: int = 2048, max_live: int | None = None, max_seq_len: int | None = None,
+                 seed: int = 0):
+        self.engine = Engine(model, max_tokens=max_tokens, page_size=page_size, max_slots=max_slots,
+                             max_seq_len=max_seq_len)
+        self.sampler = Sampler(seed)
+        self.scheduler = Scheduler(self.engine.manager, self._run, max_tokens_per_step=max_tokens_per_step,
+                                   max_live=max_live, max_seq_len=self.engine.max_seq_len, on_admit=self._admit)
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
+        self._next_id = 0
+
+    def _admit(self, r: Request) -> None:
+        for s in self.engine.states:
+            s[r.slot].zero_()
+
+    def _run(self, entries: Sequence[PlannedEntry]) -> list[int]:
+        batch = [StepEntry(e.request.slot, e.tokens, [len(e.tokens) - 1] if e.wants_logits else []) for e in entries]
+        logits = self.engine.step(batch)
+        self.h2d_bytes += 4 * sum(len(e.tokens) for e in entries)
+        want = [e.request for e in entries if e.wants_logits]
+        if not want:
+            return []
+        toks = self.sampler.sample(
+            logits, [r.params.temperature for r in want], [r.params.top_k for r in want],
+            [r.request_id for r in want], [len(r.output) for r in want])
+        host = toks.cpu()
+        self.d2h_bytes += 4 * host.numel()
+        self.engine.check_status()
+        return host.tolist()
+
+    def submit(self, prompt: Sequence[int], params: SamplingParams | None = None) -> Request:
+        r = Request(self._next_id, list(prompt), params or SamplingParams())
+        self._next_id += 1
+        self.scheduler.add(r)
+        return r
+
+    def generate(self, prompts: Sequence[Sequence[int]], params: SamplingParams | Sequence[SamplingParams] | None = None) -> list[list[int]]:
+        """Generates for every prompt (token ids); returns the new token ids of each, in order."""
+        if params is None or isinstance(params, SamplingParams):
+            params = [params or SamplingParams()] * len(prompts)
+        reqs = [self.submit(p, q) for p, q in zip(prompts, params)]
+        self.scheduler.run()
+        for r in reqs:
+            if r.finish_reason == "too_long":
+                raise ValueError(f"request {r.request_id} ({len(r.prompt)} prompt tokens) does not fit the cache "
+                                 f"({self.engine.num_pages} pages of {self.engine.page_size} tokens)")
+        return [r.output for r in reqs]
+
+
+def generate(model: DecoderModel, prompts: Sequence[Sequence[int]], params: SamplingParams | None = None, *,
+             page_size: int = 64, max_tokens: int | None = None, max_tokens_per_step: int = 2048, seed: int = 0) -> list[list[int]]:
+    """One call: builds a Generator sized for these prompts and runs them."""
+    params = params or SamplingParams()
+    if max_tokens is None:
+        max_tokens = sum(-(-(len(p) + params.max_new_tokens) // page_size) * page_size for p in prompts)
+    gen = Generator(model, max_tokens=max_tokens, page_size=page_size, max_slots=max(len(prompts), 1),
+                    max_tokens_per_step=max_tokens_per_step, seed=seed)
+    return gen.generate(prompts, params)

@@ -1,0 +1,233 @@
+"""Python face of the CUDA kernel libraries: loads them with ctypes and launches on torch's
+current stream.  There is no fallback: a missing compiler, a failed build or a missing GPU
+raises.  Every launch through this module is counted (``launch_count``)."""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_ulonglong, c_void_p
+
+import torch
+
+from . import build
+
+F32, BF16 = 0, 1
+_DTYPE_CODE = {torch.float32: F32, torch.bfloat16: BF16}
+
+STATUS_BITS = {
+    1: "a block-table entry pointed outside the page pool",
+    2: "a token id was outside the vocabulary",
+    4: "a routed expert index was outside the expert count",
+    8: "a bounded wait inside a kernel gave up",
+}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_libs: dict[str, ctypes.CDLL] = {}
+_launches = 0
+
+
+def launch_count() -> int:
+    return _launches
+
+
+def library(name: str) -> ctypes.CDLL:
+    lib = _libs.get(name)
+    if lib is None:
+        path = build.ensure_built([name])[name]
+        lib = ctypes.CDLL(str(path))
+        lib.jlx_last_error.restype = ctypes.c_char_p
+        _libs[name] = lib
+    return lib
+
+
+def preload(names) -> None:
+    """Builds (in parallel) and loads the named libraries."""
+    build.ensure_built(list(names))
+    for n in names:
+        library(n)
+
+
+def loaded_libraries() -> list[str]:
+    return sorted(_libs)
+
+
+def code(dtype: torch.dtype) -> int:
+    try:
+        return _DTYPE_CODE[dtype]
+    except KeyError:
+        raise KernelError(f"element type {dtype} is not supported by the kernels (float32, bfloat16)") from None
+
+
+def _ptr(t: torch.Tensor | None):
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise KernelError("a kernel was given a tensor that is not on the GPU; there is no CPU path")
+    return c_void_p(t.data_ptr())
+
+
+def _stream():
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _run(libname: str, fn: str, *args) -> None:
+    global _launches
+    lib = library(libname)
+    rc = getattr(lib, fn)(*args)
+    if rc != 0:
+        raise KernelError(f"{fn}: {lib.jlx_last_error().decode()}")
+    _launches += 1
+
+
+def _contig(*ts: torch.Tensor | None) -> None:
+    for t in ts:
+        if t is not None and not t.is_contiguous():
+            raise KernelError("a kernel was given a tensor that is not contiguous")
+
+
+# ------------------------------------------------------------------------------ elementwise
+def embed(ids: torch.Tensor, table: torch.Tensor, x_out: torch.Tensor, status: torch.Tensor) -> None:
+    _contig(ids, table, x_out)
+    V, D = table.shape
+    _run("elementwise", "jlx_embed", _ptr(ids), _ptr(table), c_int(code(table.dtype)), _ptr(x_out),
+         c_int(ids.numel()), c_int(D), c_int(V), _ptr(status), _stream())
+
+
+def add_rmsnorm(x: torch.Tensor, delta: torch.Tensor | None, gamma: torch.Tensor | None, eps: float,
+                out: torch.Tensor | None, out32: torch.Tensor | None = None,
+                row_index: torch.Tensor | None = None) -> None:
+    """x (+= delta); out = gamma * x / sqrt(mean(x^2) + eps).  With row_index, row n reads source
+    row row_index[n] and x is not written back."""
+    _contig(x, delta, gamma, out, out32, row_index)
+    D = x.shape[-1]
+    n = row_index.numel() if row_index is not None else x.numel() // D
+    if x.dtype != torch.float32 or (delta is not None and delta.dtype != torch.float32):
+        raise KernelError("add_rmsnorm: the residual stream must be float32")
+    if gamma is not None and gamma.dtype != torch.float32:
+        raise KernelError("add_rmsnorm: the norm weight must be float32")
+    _run("elementwise", "jlx_add_rmsnorm", _ptr(x), _ptr(delta), _ptr(gamma), c_float(eps), _ptr(out),
+         c_int(code(out.dtype) if out is not None else F32), _ptr(out32), _ptr(row_index), c_int(n), c_int(D), _stream())
+
+
+def silu_mul(gu: torch.Tensor, out: torch.Tensor, n_rows_dev: torch.Tensor | None = None) -> None:
+    _contig(gu, out)
+    rows, F2 = gu.shape
+    _run("elementwise", "jlx_silu_mul", _ptr(gu), _ptr(out), c_int(code(gu.dtype)), _ptr(n_rows_dev), c_int(rows),
+         c_int(F2 // 2), _stream())
+
+
+def convert(src: torch.Tensor, dst: torch.Tensor) -> None:
+    _contig(src, dst)
+    _run("elementwise", "jlx_convert", _ptr(src), c_int(code(src.dtype)), _ptr(dst), c_int(code(dst.dtype)),
+         c_longlong(src.numel()), _stream())
+
+
+# ------------------------------------------------------------------- position encoding + cache
+def rope_kv_store(qkv: torch.Tensor, q_out: torch.Tensor, pages: torch.Tensor | None, block_table: torch.Tensor | None,
+                  req_of_token: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor | None, l2norm: bool,
+                  eps: float, Hq: int, Hkv: int, dh: int, status: torch.Tensor) -> None:
+    """pages: [num_pages, 2, Hkv, page_size, dh] or None (a layer that writes no cache: Hkv heads of
+    k and v are still expected in qkv only if Hkv > 0)."""
+    _contig(qkv, q_out, pages, block_table, inv_freq)
+    store = pages is not None
+    N = qkv.shape[0]
+    _run("rope_kv", "jlx_rope_kv_store", _ptr(qkv), _ptr(q_out), _ptr(pages), c_int(code(qkv.dtype)),
+         _ptr(block_table), c_int(block_table.shape[1] if store else 0), _ptr(req_of_token), _ptr(positions),
+         _ptr(inv_freq), c_int(int(l2norm)), c_float(eps), c_int(N), c_int(Hq), c_int(Hkv), c_int(dh),
+         c_int(pages.shape[3] if store else 0), c_int(pages.shape[0] if store else 0), c_int(int(store)),
+         _ptr(status), _stream())
+
+
+def kv_store(k: torch.Tensor, v: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor,
+             req_of_token: torch.Tensor, positions: torch.Tensor, status: torch.Tensor) -> None:
+    _contig(k, v, pages, block_table)
+    N, Hkv, dh = k.shape
+    _run("rope_kv", "jlx_kv_store", _ptr(k), _ptr(v), _ptr(pages), c_int(code(k.dtype)), _ptr(block_table),
+         c_int(block_table.shape[1]), _ptr(req_of_token), _ptr(positions), c_int(N), c_int(Hkv), c_int(dh),
+         c_int(pages.shape[3]), c_int(pages.shape[0]), _ptr(status), _stream())
+
+
+# ---------------------------------------------------------------------------------- attention
+def attention_generic(q: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor, req_of_token: torch.Tensor,
+                      positions: torch.Tensor, out: torch.Tensor, scale: float, chunk: int, window: int,
+                      attn_scale: float, floor_scale: float, status: torch.Tensor) -> None:
+    """q: [N, Hq, dh]; pages: [P, 2, Hkv, page, dh]; out: [N, Hq, dh]."""
+    _contig(q, pages, block_table, out)
+    N, Hq, dh = q.shape
+    P, _, Hkv, page_size, dh2 = pages.shape
+    if dh2 != dh or pages.dtype != q.dtype:
+        raise KernelError("attention: cache pages and queries disagree in head size or element type")
+    _run("attention_generic", "jlx_attention_generic", _ptr(q), _ptr(pages), c_int(code(q.dtype)), _ptr(block_table),
+         c_int(block_table.shape[1]), _ptr(req_of_token), _ptr(positions), _ptr(out), c_int(N), c_int(Hq), c_int(Hkv),
+         c_int(dh), c_int(page_size), c_int(P), c_float(scale), c_int(chunk), c_int(window), c_float(attn_scale),
+         c_float(floor_scale), _ptr(status), _stream())
+
+
+# ------------------------------------------------------------------------------------- GEMMs
+def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, offsets: torch.Tensor | None = None) -> None:
+    """out = a @ w^T.  a: [M, K]; w: [N, K], or [E, N, K] with row-group offsets [E + 1] on the device."""
+    _contig(a, w, out, offsets)
+    M, K = a.shape
+    if offsets is None:
+        N, E, stride = w.shape[0], 0, 0
+    else:
+        E, N = w.shape[0], w.shape[1]
+        stride = N * K
+    if w.shape[-1] != K or out.shape[0] != M or out.shape[1] != N:
+        raise KernelError(f"gemm: shapes do not fit: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    _run("gemm_simt", "jlx_gemm_simt", _ptr(a), c_int(code(a.dtype)), _ptr(w), c_int(code(w.dtype)), _ptr(out),
+         c_int(code(out.dtype)), c_int(M), c_int(N), c_int(K), c_longlong(K), c_longlong(K), c_longlong(N),
+         _ptr(offsets), c_int(E), c_longlong(stride), _stream())
+
+
+# --------------------------------------------------------------------------------------- MoE
+def router(h32: torch.Tensor, w_router: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tensor,
+           scores_out: torch.Tensor | None = None) -> None:
+    _contig(h32, w_router, topk_idx, topk_w, scores_out)
+    N, D = h32.shape
+    E, k = w_router.shape[0], topk_idx.shape[1]
+    if h32.dtype != torch.float32 or w_router.dtype != torch.float32:
+        raise KernelError("router: scores are computed from float32 input and weight")
+    _run("moe", "jlx_router", _ptr(h32), _ptr(w_router), _ptr(topk_idx), _ptr(topk_w), _ptr(scores_out), c_int(N),
+         c_int(D), c_int(E), c_int(k), _stream())
+
+
+def expert_sort(topk_idx: torch.Tensor, offsets: torch.Tensor, sorted_pair: torch.Tensor, sorted_pos: torch.Tensor,
+                E: int, status: torch.Tensor) -> None:
+    _contig(topk_idx, offsets, sorted_pair, sorted_pos)
+    _run("moe", "jlx_expert_sort", _ptr(topk_idx), _ptr(offsets), _ptr(sorted_pair), _ptr(sorted_pos),
+         c_int(topk_idx.numel()), c_int(E), _ptr(status), _stream())
+
+
+def permute_scale(h32: torch.Tensor, sorted_pair: torch.Tensor, topk_w: torch.Tensor, a_sorted: torch.Tensor, k: int) -> None:
+    _contig(h32, sorted_pair, topk_w, a_sorted)
+    _run("moe", "jlx_permute_scale", _ptr(h32), _ptr(sorted_pair), _ptr(topk_w), _ptr(a_sorted),
+         c_int(code(a_sorted.dtype)), c_int(a_sorted.shape[0]), c_int(h32.shape[1]), c_int(k), _stream())
+
+
+def moe_combine(y_sorted: torch.Tensor, shared: torch.Tensor | None, sorted_pos: torch.Tensor, delta: torch.Tensor, k: int) -> None:
+    _contig(y_sorted, shared, sorted_pos, delta)
+    N, D = delta.shape
+    _run("moe", "jlx_moe_combine", _ptr(y_sorted), _ptr(shared), _ptr(sorted_pos), _ptr(delta), c_int(N), c_int(D),
+         c_int(k), _stream())
+
+
+# ---------------------------------------------------------------------------------- sampling
+def sample_max_top_k() -> int:
+    return int(library("sampling").jlx_sample_max_top_k())
+
+
+def sample(logits: torch.Tensor, out: torch.Tensor, temperature: torch.Tensor | None = None,
+           top_k: torch.Tensor | None = None, streams: torch.Tensor | None = None,
+           counters: torch.Tensor | None = None, seed: int = 0) -> None:
+    """out[m] = argmax (temperature None or <= 1e-3) or a draw from softmax(logits / temperature)."""
+    _contig(logits, out, temperature, top_k, streams, counters)
+    if logits.dtype != torch.float32:
+        raise KernelError("sample: logits must be float32")
+    M, V = logits.shape
+    _run("sampling", "jlx_sample", _ptr(logits), c_int(M), c_int(V), c_longlong(V), _ptr(temperature), _ptr(top_k),
+         _ptr(streams), _ptr(counters), c_ulonglong(seed & 0xFFFFFFFFFFFFFFFF), _ptr(out), _stream())

@@ -1,0 +1,68 @@
+"""Attention mixer over the paged cache."""
+
+from __future__ import annotations
+
+import torch
+
+from ..cache.manager import Retention
+from ..kernels import api as K
+from .base import KVNeed, LayerCache, Mixer, PositionEncoding, Runtime, StepContext, register_part
+from .linear import linear
+
+
+class PagedAttention(Mixer):
+    """Grouped-query attention (llama4/llama4_jax/model.py:891-955, 745-794).
+
+    ``w_qkv``: [(Hq + 2 Hkv) * dh, D], the q, k and v projections stacked in that order, each head a
+    block of dh rows (HF orientation, chkpt_utils.py:84-89).  ``w_o``: [D, Hq * dh].
+    ``chunk``: query and key must lie in the same chunk of that many positions (model.py:738-740);
+    ``window``: keys within the last that many positions; None = no such limit.
+    ``qk_norm_eps``: eps of the weightless norm of q and k, None = no norm.
+    A layer with ``shares_cache`` projects only q and reads pages that another layer wrote.
+    """
+
+    kernel_libraries = ("attention_generic", "rope_kv", "gemm_simt")
+
+    def __init__(self, w_qkv: torch.Tensor, w_o: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
+                 position: PositionEncoding, qk_norm_eps: float | None = None, chunk: int | None = None,
+                 window: int | None = None, scale: float | None = None):
+        if n_heads % n_kv_heads:
+            raise ValueError(f"{n_heads} query heads are no multiple of {n_kv_heads} KV heads")
+        rows = (n_heads + 2 * n_kv_heads) * head_dim
+        if w_qkv.shape[0] != rows or w_o.shape[1] != n_heads * head_dim or w_o.shape[0] != w_qkv.shape[1]:
+            raise ValueError(f"attention weights do not fit: w_qkv {tuple(w_qkv.shape)}, w_o {tuple(w_o.shape)} for "
+                             f"{n_heads}/{n_kv_heads} heads of {head_dim}")
+        self.w_qkv, self.w_o = w_qkv, w_o
+        self.n_heads, self.n_kv_heads, self.head_dim = n_heads, n_kv_heads, head_dim
+        self.position = position
+        self.qk_norm_eps = qk_norm_eps
+        self.chunk, self.window = chunk, window
+        self.scale = float(head_dim) ** -0.5 if scale is None else float(scale)  # model.py:774
+
+    def required_libraries(self, runtime: Runtime):
+        return tuple(dict.fromkeys(self.kernel_libraries + self.position.required_libraries(runtime)))
+
+    def kv_need(self) -> KVNeed:
+        if self.chunk is not None and self.window is None:
+            keep = Retention.chunk(self.chunk)
+        elif self.window is not None and self.chunk is None:
+            keep = Retention.window(self.window)
+        else:
+            keep = Retention.all()  # both limits at once: keep everything (correct, not minimal)
+        return KVNeed(self.n_kv_heads, self.head_dim, keep)
+
+    def forward(self, ctx: StepContext, h: torch.Tensor, cache: LayerCache) -> torch.Tensor:
+        rt = ctx.runtime
+        qkv = linear(h, self.w_qkv, rt.dtype)
+        q = self.position.encode_and_store(ctx, qkv, self.n_heads, self.n_kv_heads, self.head_dim, cache, self.qk_norm_eps)
+        attn_scale, floor_scale = self.position.query_temperature()
+        out = torch.empty_like(q)
+        self.attend(ctx, q, cache, out, attn_scale, floor_scale)
+        return linear(out.view(q.shape[0], -1), self.w_o, torch.float32)
+
+    def attend(self, ctx: StepContext, q, cache: LayerCache, out, attn_scale: float, floor_scale: float) -> None:
+        K.attention_generic(q, cache.pages, cache.block_table, ctx.req_of_token, ctx.positions, out, self.scale,
+                            self.chunk or 0, self.window or 0, attn_scale, floor_scale, ctx.status)
+
+
+register_part("mixer", "paged_attention", PagedAttention)

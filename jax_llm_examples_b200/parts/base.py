@@ -1,0 +1,173 @@
+"""Interfaces of the parts a decoder is put together from, and the step context they all see.
+
+A part gets its sizes and constants as constructor arguments and never learns which model it
+is in.  The kinds of part:
+
+* :class:`Norm` — normalises rows of the residual stream.
+* :class:`PositionEncoding` — turns projected q and k rows into position-aware ones and hands
+  k and v to the cache.
+* :class:`Mixer` — mixes information across a request's tokens (attention here); it says what it
+  needs of the cache manager: pages of keys and values (:class:`KVNeed`) and/or per-request state
+  of fixed size (:class:`StateNeed`).
+* :class:`FeedForward` — acts on each token alone (dense, or routed experts).
+* :class:`Block` — arranges the above (pre-norm residual block here).
+
+All of them work on the *flattened* batch of a step: N token rows from R requests, described by
+:class:`StepContext`.  The residual stream is float32 [N, D]; parts return a float32 ``delta`` that
+the next norm adds to it (the sum is fused into the norm kernel).
+"""
+
+from __future__ import annotations
+
+import dataclasses
+from typing import Any, Callable
+
+import torch
+
+from ..cache.manager import Retention
+
+
+@dataclasses.dataclass
+class Runtime:
+    """Where and in which precision a model runs."""
+
+    dtype: torch.dtype  # activations and cache: torch.bfloat16, or torch.float32 for the true 32-bit path
+    device: torch.device
+
+    def __post_init__(self):
+        if self.dtype not in (torch.float32, torch.bfloat16):
+            raise ValueError(f"dtype must be float32 or bfloat16, not {self.dtype}")
+
+
+@dataclasses.dataclass(frozen=True)
+class KVNeed:
+    """Pages of keys and values: heads, head size, and which keys stay readable."""
+
+    num_kv_heads: int
+    head_dim: int
+    retention: Retention
+
+
+@dataclasses.dataclass(frozen=True)
+class StateNeed:
+    """Per-request state of fixed size (zeroed when a request is admitted)."""
+
+    shape: tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+@dataclasses.dataclass
+class LayerCache:
+    """What one run of a layer sees of the cache in this step."""
+
+    pages: torch.Tensor | None  # [num_pages, 2, Hkv, page_size, dh]
+    block_table: torch.Tensor | None  # int32 [R, width], rows in the order of the step's requests
+    writes: bool  # False: the layer reads a cache that another layer fills
+    state: torch.Tensor | None  # [max_slots, *StateNeed.shape]
+
+
+@dataclasses.dataclass
+class StepContext:
+    """One step's batch: N tokens of R requests, portions of prompts beside single decoded tokens."""
+
+    runtime: Runtime
+    n_tokens: int
+    n_requests: int
+    token_ids: torch.Tensor  # int32 [N]
+    positions: torch.Tensor  # int32 [N] absolute position in the request
+    req_of_token: torch.Tensor  # int32 [N] index into this step's requests
+    cu_q: torch.Tensor  # int32 [R + 1] token offsets of the requests
+    q_start: torch.Tensor  # int32 [R] tokens the request held before this step
+    kv_len: torch.Tensor  # int32 [R] tokens it holds after this step
+    slot_ids: torch.Tensor  # int32 [R] cache-manager slot (indexes per-request state)
+    logit_rows: torch.Tensor  # int32 [M] token rows whose logits are wanted
+    n_logit_rows: int
+    status: torch.Tensor  # int32 [1] error bits raised by kernels
+    # host copies, for parts that plan on the host
+    host_q_lens: list[int] = dataclasses.field(default_factory=list)
+    host_q_start: list[int] = dataclasses.field(default_factory=list)
+    host_slot_ids: list[int] = dataclasses.field(default_factory=list)
+    max_q_len: int = 0
+    max_kv_len: int = 0
+    scratch: dict[str, Any] = dataclasses.field(default_factory=dict)  # per-step memo shared by parts
+
+
+class Part:
+    """Base of all parts.  ``tensors()`` lists device tensors for memory accounting."""
+
+    kernel_libraries: tuple[str, ...] = ()  # kernel libraries this part launches (built on first use)
+
+    def required_libraries(self, runtime: Runtime) -> tuple[str, ...]:
+        return self.kernel_libraries
+
+
+class Norm(Part):
+    def forward(self, ctx: StepContext, x: torch.Tensor, delta: torch.Tensor | None, *, out_dtype: torch.dtype,
+                want_f32: bool = False, row_index: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor | None]:
+        """x += delta (if given); returns (normed rows in out_dtype, the same in float32 if asked)."""
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    def encode_and_store(self, ctx: StepContext, qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
+                         cache: LayerCache, qk_norm_eps: float | None) -> torch.Tensor:
+        """qkv: [N, (Hq + 2 Hkv) * dh] projected rows.  Returns q [N, Hq, dh] ready for the score
+        product; writes k and v into the cache pages when ``cache.writes``."""
+        raise NotImplementedError
+
+    def query_temperature(self) -> tuple[float, float]:
+        """(attn_scale, floor_scale) of the position-dependent query scale; (0, 1) = none."""
+        return (0.0, 1.0)
+
+
+class Mixer(Part):
+    def kv_need(self) -> KVNeed | None:
+        return None
+
+    def state_need(self) -> StateNeed | None:
+        return None
+
+    def forward(self, ctx: StepContext, h: torch.Tensor, cache: LayerCache) -> torch.Tensor:
+        """h: normed rows [N, D] in the runtime's dtype.  Returns delta [N, D] float32."""
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    needs_f32_input: bool = False  # True: forward() also gets the normed rows unrounded
+
+    def forward(self, ctx: StepContext, h: torch.Tensor, h32: torch.Tensor | None) -> torch.Tensor:
+        """Returns delta [N, D] float32."""
+        raise NotImplementedError
+
+
+class Block(Part):
+    mixer: Mixer
+
+    def forward(self, ctx: StepContext, x: torch.Tensor, delta: torch.Tensor | None, cache: LayerCache) -> torch.Tensor:
+        """Runs the block on residual x with a pending ``delta`` not yet added; returns the new pending delta."""
+        raise NotImplementedError
+
+
+# ------------------------------------------------------------------------------ part registry
+_PARTS: dict[tuple[str, str], Callable[..., Part]] = {}
+KINDS = ("norm", "position", "mixer", "feed_forward", "block")
+
+
+def register_part(kind: str, name: str, factory: Callable[..., Part]) -> None:
+    """Makes a part available to model builders under (kind, name)."""
+    if kind not in KINDS:
+        raise ValueError(f"unknown kind of part {kind!r}; kinds: {KINDS}")
+    _PARTS[(kind, name)] = factory
+
+
+def make_part(kind: str, name: str, **kwargs: Any) -> Part:
+    try:
+        factory = _PARTS[(kind, name)]
+    except KeyError:
+        known = sorted(n for k, n in _PARTS if k == kind)
+        raise KeyError(f"no {kind} part named {name!r}; known: {known}") from None
+    return factory(**kwargs)
+
+
+def known_parts(kind: str) -> list[str]:
+    return sorted(n for k, n in _PARTS if k == kind)

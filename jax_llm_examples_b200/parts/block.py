@@ -1,0 +1,34 @@
+"""The arrangement of parts in a layer."""
+
+from __future__ import annotations
+
+import torch
+
+from .base import Block, FeedForward, LayerCache, Mixer, Norm, Runtime, StepContext, register_part
+
+
+class PreNormBlock(Block):
+    """x += mixer(norm1(x)); x += feed_forward(norm2(x))  (llama4/llama4_jax/model.py:1156-1183).
+
+    The residual sums are done in float32 inside the following norm's kernel: a block returns its
+    last delta unadded, and the next block's first norm (or the model's final norm) adds it."""
+
+    def __init__(self, norm1: Norm, mixer: Mixer, norm2: Norm, feed_forward: FeedForward):
+        self.norm1, self.mixer, self.norm2, self.feed_forward = norm1, mixer, norm2, feed_forward
+
+    def required_libraries(self, runtime: Runtime):
+        libs: list[str] = []
+        for p in (self.norm1, self.mixer, self.norm2, self.feed_forward):
+            libs.extend(p.required_libraries(runtime))
+        return tuple(dict.fromkeys(libs))
+
+    def forward(self, ctx: StepContext, x: torch.Tensor, delta, cache: LayerCache) -> torch.Tensor:
+        dt = ctx.runtime.dtype
+        h, _ = self.norm1.forward(ctx, x, delta, out_dtype=dt)
+        a = self.mixer.forward(ctx, h, cache)
+        want32 = self.feed_forward.needs_f32_input
+        h, h32 = self.norm2.forward(ctx, x, a, out_dtype=dt, want_f32=want32)
+        return self.feed_forward.forward(ctx, h, h32)
+
+
+register_part("block", "pre_norm", PreNormBlock)

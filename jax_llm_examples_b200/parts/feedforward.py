@@ -1,0 +1,86 @@
+"""Feed-forward parts: dense SwiGLU and routed experts with a shared expert."""
+
+from __future__ import annotations
+
+import torch
+
+from ..kernels import api as K
+from .base import FeedForward, StepContext, register_part
+from .linear import grouped_linear, linear
+
+
+class DenseSwiGLU(FeedForward):
+    """down(silu(h gate) * (h up)) (llama4/llama4_jax/model.py:1142-1153).
+    ``w_gate_up``: [2F, D], gate rows then up rows; ``w_down``: [D, F]."""
+
+    kernel_libraries = ("elementwise", "gemm_simt")
+
+    def __init__(self, w_gate_up: torch.Tensor, w_down: torch.Tensor):
+        if w_gate_up.shape[0] != 2 * w_down.shape[1] or w_gate_up.shape[1] != w_down.shape[0]:
+            raise ValueError(f"SwiGLU weights do not fit: gate_up {tuple(w_gate_up.shape)}, down {tuple(w_down.shape)}")
+        self.w_gate_up, self.w_down = w_gate_up, w_down
+
+    def forward(self, ctx: StepContext, h, h32=None):
+        gu = linear(h, self.w_gate_up, ctx.runtime.dtype)
+        act = torch.empty((gu.shape[0], gu.shape[1] // 2), dtype=gu.dtype, device=gu.device)
+        K.silu_mul(gu, act)
+        return linear(act, self.w_down, torch.float32)
+
+
+class RoutedExperts(FeedForward):
+    """Sigmoid-routed top-k experts plus an optional shared expert (model.py:958-972, 999-1139).
+
+    scores = h W_router in float32 from the unrounded normed rows; top-k of the raw scores (lower
+    index wins ties); weight = sigmoid(score); each chosen expert runs SwiGLU on weight * h (the
+    INPUT is scaled, model.py:1071); expert outputs are summed per token in choice order and the
+    shared expert's output on the unscaled h is added (model.py:1111, 1137-1139).
+    ``w_router``: [E, D]; ``we_gate_up``: [E, 2F, D] (gate rows then up rows); ``we_down``: [E, D, F]."""
+
+    kernel_libraries = ("moe", "elementwise", "gemm_simt")
+    needs_f32_input = True
+
+    def __init__(self, w_router: torch.Tensor, we_gate_up: torch.Tensor, we_down: torch.Tensor, top_k: int,
+                 shared: DenseSwiGLU | None = None):
+        E = w_router.shape[0]
+        if we_gate_up.shape[0] != E or we_down.shape[0] != E or we_gate_up.shape[1] != 2 * we_down.shape[2] \
+                or we_gate_up.shape[2] != we_down.shape[1] or w_router.shape[1] != we_down.shape[1]:
+            raise ValueError(f"expert weights do not fit: router {tuple(w_router.shape)}, gate_up "
+                             f"{tuple(we_gate_up.shape)}, down {tuple(we_down.shape)}")
+        if not 1 <= top_k <= E:
+            raise ValueError(f"top-{top_k} of {E} experts")
+        self.w_router = w_router.to(torch.float32).contiguous()
+        self.we_gate_up, self.we_down, self.top_k, self.shared = we_gate_up, we_down, top_k, shared
+        self.num_experts = E
+
+    def route(self, ctx: StepContext, h32: torch.Tensor):
+        n, k, dev = h32.shape[0], self.top_k, h32.device
+        topk_idx = torch.empty((n, k), dtype=torch.int32, device=dev)
+        topk_w = torch.empty((n, k), dtype=torch.float32, device=dev)
+        K.router(h32, self.w_router, topk_idx, topk_w)
+        offsets = torch.empty(self.num_experts + 1, dtype=torch.int32, device=dev)
+        sorted_pair = torch.empty(n * k, dtype=torch.int32, device=dev)
+        sorted_pos = torch.empty(n * k, dtype=torch.int32, device=dev)
+        K.expert_sort(topk_idx, offsets, sorted_pair, sorted_pos, self.num_experts, ctx.status)
+        return topk_idx, topk_w, offsets, sorted_pair, sorted_pos
+
+    def forward(self, ctx: StepContext, h, h32):
+        rt = ctx.runtime
+        n, D = h32.shape
+        k = self.top_k
+        topk_idx, topk_w, offsets, sorted_pair, sorted_pos = self.route(ctx, h32)
+        if "record_routing" in ctx.scratch:  # tests compare the choices with a plain router's
+            ctx.scratch["record_routing"].append(topk_idx)
+        a_sorted = torch.empty((n * k, D), dtype=rt.dtype, device=h.device)
+        K.permute_scale(h32, sorted_pair, topk_w, a_sorted, k)
+        gu = grouped_linear(a_sorted, self.we_gate_up, offsets, rt.dtype)
+        act = torch.empty((n * k, gu.shape[1] // 2), dtype=rt.dtype, device=h.device)
+        K.silu_mul(gu, act)
+        y = grouped_linear(act, self.we_down, offsets, torch.float32)
+        shared = self.shared.forward(ctx, h, None) if self.shared is not None else None
+        delta = torch.empty((n, D), dtype=torch.float32, device=h.device)
+        K.moe_combine(y, shared, sorted_pos, delta, k)
+        return delta
+
+
+register_part("feed_forward", "dense_swiglu", DenseSwiGLU)
+register_part("feed_forward", "routed_experts", RoutedExperts)

@@ -1,0 +1,183 @@
+"""Shared by the tests: tiny model folders, the plain implementation's logits, trace families."""
+
+from __future__ import annotations
+
+import functools
+import json
+import random
+from pathlib import Path
+
+import numpy as np
+import torch
+
+from tests.plain import llama4_plain as plain
+
+
+def make_model_dir(path: Path, preset_name: str, seed: int, norm_noise: float = 0.0, dtype=torch.bfloat16, **overrides) -> Path:
+    from jax_llm_examples_b200 import preset, write_random_model
+
+    return write_random_model(path, preset(preset_name, **overrides), seed, dtype=dtype, norm_noise=norm_noise)
+
+
+@functools.lru_cache(maxsize=64)
+def _plain_model(model_dir: str):
+    return plain.load_config(model_dir), plain.load_weights(model_dir, torch.float32)
+
+
+def moe_layer_indices(model_dir) -> list[int]:
+    cfg, _ = _plain_model(str(model_dir))
+    return [i for i in range(cfg["num_hidden_layers"]) if plain.layer_is_moe(cfg, i)]
+
+
+def plain_logits(model_dir, tokens, routing: dict[int, np.ndarray] | None = None) -> tuple[np.ndarray, float]:
+    """Logits [T, V] of the plain implementation in float32.  With ``routing`` ({layer: experts
+    [T, k]}) it takes those experts instead of its own choice and also returns by how much, at
+    worst, a taken expert's score lay below the score it needed to be chosen (0 = same choice)."""
+    cfg, w = _plain_model(str(model_dir))
+    stats: dict = {}
+    with torch.no_grad():
+        out = plain.forward(cfg, w, list(tokens), stats, routing).numpy()
+    worst = max((float(g.max()) for g in stats.get("router_shortfall", {}).values()), default=0.0)
+    return out, worst
+
+
+def rel_err(a: np.ndarray, b: np.ndarray) -> float:
+    """Largest difference of a row, relative to that row's largest reference logit; max over rows."""
+    a, b = np.atleast_2d(a), np.atleast_2d(b)
+    return float(np.max(np.max(np.abs(a - b), axis=-1) / np.maximum(np.max(np.abs(b), axis=-1), 1e-6)))
+
+
+# Tolerances follow the precisions: float32 has eps 6e-8 and a few thousand roundings per logit;
+# bfloat16 rounds activations (eps 4e-3) a few times per layer.
+TOL = {"float32": 2e-5, "bfloat16": 4e-2}
+
+
+def random_requests(rng: random.Random, vocab: int, lengths: list[int]) -> dict[str, list[int]]:
+    return {f"r{i}": [rng.randrange(vocab) for _ in range(n)] for i, n in enumerate(lengths)}
+
+
+# ------------------------------------------------------------------------------------ traces
+def trace_whole(requests):
+    """Each request alone, whole, in one step."""
+    steps = []
+    for rid, toks in requests.items():
+        steps.append({"entries": [{"id": rid, "tokens": toks, "want": list(range(len(toks)))}], "end": [rid]})
+    return steps
+
+
+def trace_tail_decode(requests, tail=32):
+    """Most of a request in one step, then its last `tail` tokens one by one."""
+    steps = []
+    for rid, toks in requests.items():
+        head = max(len(toks) - tail, 0)
+        if head:
+            steps.append({"entries": [{"id": rid, "tokens": toks[:head], "want": list(range(head))}], "end": []})
+        for i in range(head, len(toks)):
+            steps.append({"entries": [{"id": rid, "tokens": [toks[i]], "want": [0]}], "end": [rid] if i == len(toks) - 1 else []})
+    return steps
+
+
+def trace_portions(requests, rng: random.Random):
+    """Portions of changing size, down to two tokens."""
+    steps = []
+    sizes = [7, 2, 19, 3, 2, 11, 5, 2, 13, 4]
+    for rid, toks in requests.items():
+        at, k = 0, rng.randrange(len(sizes))
+        while at < len(toks):
+            n = min(sizes[k % len(sizes)], len(toks) - at)
+            k += 1
+            steps.append({"entries": [{"id": rid, "tokens": toks[at:at + n], "want": list(range(n))}],
+                          "end": [rid] if at + n == len(toks) else []})
+            at += n
+    return steps
+
+
+def trace_mixed(requests, rng: random.Random, max_live=4):
+    """Up to `max_live` live requests: portions of some beside single tokens of others; a request
+    may sit out a step; finished requests make room (and pages) for the next ones."""
+    pending = list(requests.items())
+    live: dict[str, int] = {}
+    steps = []
+    while pending or live:
+        while pending and len(live) < max_live and (not live or rng.random() < 0.7):
+            rid, _ = pending.pop(0)
+            live[rid] = 0
+        entries, end = [], []
+        for rid in list(live):
+            if len(live) > 1 and rng.random() < 0.2:
+                continue  # sits this step out
+            toks, at = requests[rid], live[rid]
+            left = len(toks) - at
+            if rng.random() < 0.5 or left == 1:
+                n = 1
+            else:
+                n = min(left, rng.choice([2, 2, 3, 5, 8, 17, 33]))
+            entries.append({"id": rid, "tokens": toks[at:at + n], "want": list(range(n))})
+            live[rid] = at + n
+            if live[rid] == len(toks):
+                end.append(rid)
+                del live[rid]
+        if entries:
+            steps.append({"entries": entries, "end": end})
+    return steps
+
+
+def run_trace(engine, steps):
+    """Drives the engine's step function with a trace.  Returns (logits by (request, position),
+    expert choices by (request, position): one array [k] per routed layer, in layer order)."""
+    from jax_llm_examples_b200 import StepEntry
+
+    engine.record_routing = True
+    slots: dict[str, int] = {}
+    at: dict[str, int] = {}
+    out: dict[tuple[str, int], np.ndarray] = {}
+    routing: dict[tuple[str, int], list[np.ndarray]] = {}
+    for st in steps:
+        entries, places, fed = [], [], []
+        for e in st["entries"]:
+            rid = e["id"]
+            if rid not in slots:
+                slots[rid] = engine.new_request()
+                at[rid] = 0
+            entries.append(StepEntry(slots[rid], e["tokens"], e["want"]))
+            places += [(rid, at[rid] + w) for w in e["want"]]
+            fed += [(rid, at[rid] + i) for i in range(len(e["tokens"]))]
+            at[rid] += len(e["tokens"])
+        logits = engine.step(entries).cpu().numpy()
+        engine.check_status()
+        assert logits.shape[0] == len(places)
+        for row, key in zip(logits, places):
+            out[key] = row
+        choices = [t.cpu().numpy() for t in engine.last_routing]
+        for n, key in enumerate(fed):
+            routing[key] = [c[n] for c in choices]
+        for rid in st["end"]:
+            engine.finish(slots.pop(rid))
+        engine.manager.check()
+    return out, routing
+
+
+# A router score difference below this is a tie that either precision may break either way:
+# float32 sums of D products differ by ~1e-6; bfloat16 rounds the layer inputs to 3 digits.
+TIE = {"float32": 1e-5, "bfloat16": 5e-3}
+
+
+def compare_with_plain(model_dir, requests, got, routing, dtype: str):
+    """Every logit row the trace produced against the plain implementation's row at that place.
+    The plain implementation takes the engine's experts; they must be its own choice too, except
+    where the scores tie."""
+    worst = 0.0
+    layers = moe_layer_indices(model_dir)
+    for rid, toks in requests.items():
+        forced = None
+        if layers:
+            forced = {L: np.stack([routing[(rid, p)][j] for p in range(len(toks))]) for j, L in enumerate(layers)}
+        ref, shortfall = plain_logits(model_dir, toks, forced)
+        assert shortfall < TIE[dtype], f"{dtype}: request {rid}: an expert was chosen whose score is {shortfall:.2e} too low"
+        for pos in range(len(toks)):
+            if (rid, pos) not in got:
+                continue
+            err = rel_err(got[(rid, pos)], ref[pos])
+            assert err < TOL[dtype], f"{dtype}: request {rid} position {pos}: relative error {err:.3e}"
+            worst = max(worst, err)
+    return worst

@@ -1,0 +1,88 @@
+"""The engine against the plain implementation, on a GPU, in 32-bit and in bfloat16: the same
+requests whole; most of each in one step and the last 32 tokens one by one; in portions of changing
+size; and mixed, with so few pages that they are used again."""
+
+import random
+
+import pytest
+import torch
+
+from tests import helpers as H
+
+pytestmark = pytest.mark.gpu
+
+LENGTHS = {"tiny_a": [80, 1, 33, 47, 64, 17], "tiny_b": [130, 49, 2, 97, 48, 75]}
+VOCAB = {"tiny_a": 256, "tiny_b": 384}
+
+
+def _engine(model_dir, dtype, max_tokens, page_size=16, max_slots=8):
+    import jax_llm_examples_b200 as J
+
+    model = J.load_model(model_dir, dtype, "cuda")
+    return J.Engine(model, max_tokens=max_tokens, page_size=page_size, max_slots=max_slots)
+
+
+def _requests(name, seed=0):
+    return H.random_requests(random.Random(seed), VOCAB[name], LENGTHS[name])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
+def test_whole_requests(model_dirs, name, dtype):
+    reqs = _requests(name)
+    eng = _engine(model_dirs[name], dtype, max_tokens=160)
+    got, routing = H.run_trace(eng, H.trace_whole(reqs))
+    worst = H.compare_with_plain(model_dirs[name], reqs, got, routing, dtype)
+    print(f"{name} {dtype} whole: worst relative error {worst:.2e}")
+    assert all(eng.manager.free_pages(g) == eng.num_pages for g in range(len(eng.manager.groups)))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
+def test_last_32_tokens_one_by_one(model_dirs, name, dtype):
+    reqs = _requests(name)
+    eng = _engine(model_dirs[name], dtype, max_tokens=160)
+    got, routing = H.run_trace(eng, H.trace_tail_decode(reqs, 32))
+    worst = H.compare_with_plain(model_dirs[name], reqs, got, routing, dtype)
+    print(f"{name} {dtype} tail decode: worst relative error {worst:.2e}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
+def test_portions_of_changing_size(model_dirs, name, dtype):
+    reqs = _requests(name)
+    eng = _engine(model_dirs[name], dtype, max_tokens=160)
+    got, routing = H.run_trace(eng, H.trace_portions(reqs, random.Random(3)))
+    worst = H.compare_with_plain(model_dirs[name], reqs, got, routing, dtype)
+    print(f"{name} {dtype} portions: worst relative error {worst:.2e}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
+def test_mixed_batches_reusing_pages(model_dirs, name, dtype):
+    rng = random.Random(7)
+    lengths = LENGTHS[name] + [rng.randrange(1, max(LENGTHS[name])) for _ in range(6)]
+    reqs = H.random_requests(rng, VOCAB[name], lengths)
+    # four live requests of the longest length fit, nothing more: every page is handed out many times
+    longest = -(-max(lengths) // 16) * 16
+    eng = _engine(model_dirs[name], dtype, max_tokens=4 * longest)
+    steps = H.trace_mixed(reqs, rng, max_live=4)
+    assert any(len(s["entries"]) >= 3 for s in steps)
+    got, routing = H.run_trace(eng, steps)
+    worst = H.compare_with_plain(model_dirs[name], reqs, got, routing, dtype)
+    print(f"{name} {dtype} mixed: worst relative error {worst:.2e}")
+    total_pages_needed = sum(-(-n // 16) for n in lengths)
+    assert total_pages_needed > eng.num_pages, "the trace must need more pages than the pool has"
+
+
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
+def test_cutting_does_not_change_float32_logits(model_dirs, name):
+    """In 32-bit every reduction has a fixed order per position, so whole, decoded and portioned runs
+    agree far more closely than any of them agrees with another implementation."""
+    reqs = _requests(name, seed=5)
+    eng = _engine(model_dirs[name], "float32", max_tokens=160)
+    whole, _ = H.run_trace(eng, H.trace_whole(reqs))
+    cut, _ = H.run_trace(eng, H.trace_portions(reqs, random.Random(1)))
+    worst = max(H.rel_err(cut[k], whole[k]) for k in whole)
+    print(f"{name}: whole vs portions, float32: {worst:.2e}")
+    assert worst < 2e-6
