@@ -1,0 +1,380 @@
+// Weight-streaming GEMM for sm_100a: C = A * W^T in bfloat16 with 32-bit accumulation, on the
+// 5th-generation tensor cores (tcgen05.mma, accumulator in tensor memory), operands staged by TMA.
+//
+// It is built for the products whose cost is reading the weights once: every product of a decode
+// step (few token rows), and the routed experts at any batch (llama4/llama4_jax/model.py:975-996 is
+// the reference's ragged product; its decode kernel, decode_ragged_dot.py:26-116, is the TPU
+// counterpart).  The operands are swapped with respect to the usual tiling: a tile of 128 weight rows
+// is the MMA's M side (one row per tensor-memory lane) and the token rows are its N side (BT columns,
+// 16..256), so that a handful of tokens still fills the instruction.  K advances in stages of 64
+// elements (one 128-byte swizzled row per operand row).
+//
+//   A: [rows, K] row-major (tokens).  W: [E * N, K] row-major ([out, in] weights of E groups).
+//   C: [rows, N].  Grouped: token rows [offsets[e], offsets[e+1]) use weight rows [e*N, (e+1)*N).
+//   split-K: blockIdx.z takes a K range and writes a 32-bit partial [z][rows][N]; a second kernel
+//   adds the partials in a fixed order.
+//
+// One block = one (weight tile, token tile, K range).  Warp 0 issues TMA loads, warp 1 allocates tensor
+// memory and issues the MMAs, warps 2..5 read the accumulator back (each its own 32-lane quarter) and
+// store it transposed (for a fixed token, 32 consecutive outputs per warp: coalesced).
+// Every wait on a barrier is bounded; on a timeout the block raises JLX_STATUS_WAIT_TIMEOUT, drains its
+// own copies, frees its tensor memory and returns.
+#include <cuda.h>
+
+#include "common.cuh"
+
+#define WN 128          // weight rows per tile (MMA M)
+#define BK 64           // K elements per stage (128 bytes of bfloat16)
+#define UMMA_K 16
+#define NTHREADS 192
+#define WAIT_LIMIT (1u << 22)
+
+// ------------------------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: false after WAIT_LIMIT polls (each poll itself waits a bounded time in hardware).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, stored with the
+// 128-byte swizzle (as TMA writes it): 8-row groups are 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFF) >> 4);   // start address
+  d |= (uint64_t)0 << 16;                   // leading byte offset: unused for swizzled K-major
+  d |= (uint64_t)(1024 >> 4) << 32;         // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;                   // descriptor version of sm_100
+  d |= (uint64_t)2 << 61;                   // layout: 128-byte swizzle
+  return d;
+}
+
+// Instruction descriptor: bfloat16 x bfloat16 -> float32, both operands K-major, M = 128, N = bt.
+__host__ __device__ constexpr uint32_t make_idesc(int bt) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bt >> 3) << 17) | ((uint32_t)(WN >> 4) << 24);
+}
+
+// ------------------------------------------------------------------------------------------ kernel
+struct StreamArgs {
+  int N;                 // outputs per group
+  int K;
+  int rows;              // token rows in A (upper bound of offsets[E])
+  const int* offsets;    // null: one group over all rows
+  int E;
+  void* out;             // [rows, N] (bf16 or f32), or partials [splits][rows][N] f32 when splits > 1
+  int out_is_f32;
+  int splits;
+  int k_per_split;       // multiple of BK
+  int* status;
+};
+
+template <int BT, int STAGES>
+__global__ void __launch_bounds__(NTHREADS)
+gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a, const StreamArgs args) {
+  constexpr uint32_t W_BYTES = WN * BK * 2, A_BYTES = BT * BK * 2, STAGE_BYTES = W_BYTES + A_BYTES;
+  constexpr uint32_t TMEM_COLS = BT < 32 ? 32 : BT;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  __shared__ __align__(8) uint64_t bars[2 * STAGES + 1];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int failed;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // ---- which tile
+  int row_lo, row_hi, group = 0;
+  if (args.offsets) {
+    int t = blockIdx.y, found = 0;
+    for (int e = 0; e < args.E; ++e) {
+      const int lo = args.offsets[e], hi = args.offsets[e + 1];
+      const int tiles = (hi - lo + BT - 1) / BT;
+      if (t < tiles) { row_lo = lo + t * BT; row_hi = hi; group = e; found = 1; break; }
+      t -= tiles;
+    }
+    if (!found) return;
+  } else {
+    row_lo = blockIdx.y * BT;
+    row_hi = args.rows;
+    if (row_lo >= row_hi) return;
+  }
+  const int n0 = blockIdx.x * WN;
+  const int k_begin = blockIdx.z * args.k_per_split;
+  const int k_end = min(args.K, k_begin + args.k_per_split);
+  const int k_iters = (k_end - k_begin + BK - 1) / BK;
+
+  const uint32_t bar_full = smem_u32(&bars[0]), bar_empty = smem_u32(&bars[STAGES]), bar_acc = smem_u32(&bars[2 * STAGES]);
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    mbar_init(bar_acc, 1);
+    failed = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(smem_u32(&tmem_slot), TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_acc = tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int issued = 0;
+      bool ok = true;
+      for (int it = 0; it < k_iters && ok; ++it) {
+        const int s = it % STAGES;
+        ok = mbar_wait(bar_empty + 8 * s, ((it / STAGES) & 1) ^ 1);
+        if (!ok || *(volatile int*)&failed) { ok = false; break; }
+        const uint32_t dst = smem_base + s * STAGE_BYTES;
+        mbar_expect_tx(bar_full + 8 * s, STAGE_BYTES);
+        tma_load_2d(dst, &map_w, k_begin + it * BK, group * args.N + n0, bar_full + 8 * s);
+        tma_load_2d(dst + W_BYTES, &map_a, k_begin + it * BK, row_lo, bar_full + 8 * s);
+        issued = it + 1;
+      }
+      if (!ok) {
+        atomicOr(args.status, JLX_STATUS_WAIT_TIMEOUT);
+        failed = 1;
+        // let this block's copies in flight land before its shared memory is given up
+        for (int it = max(0, issued - STAGES); it < issued; ++it) mbar_wait(bar_full + 8 * (it % STAGES), (it / STAGES) & 1);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(BT);
+      bool ok = true;
+      for (int it = 0; it < k_iters; ++it) {
+        const int s = it % STAGES;
+        ok = mbar_wait(bar_full + 8 * s, (it / STAGES) & 1);
+        if (!ok || *(volatile int*)&failed) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t w_addr = smem_base + s * STAGE_BYTES, a_addr = w_addr + W_BYTES;
+        const uint64_t wdesc = smem_desc_sw128(w_addr), adesc = smem_desc_sw128(a_addr);
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k) {
+          // 16 elements = 32 bytes further along K inside the swizzled row: +2 in the address field
+          umma_bf16(tmem_acc, wdesc + 2 * k, adesc + 2 * k, idesc, (it | k) != 0);
+        }
+        umma_commit(bar_empty + 8 * s);  // frees the stage when these MMAs have read it
+      }
+      if (ok) {
+        umma_commit(bar_acc);  // accumulator complete
+      } else {
+        atomicOr(args.status, JLX_STATUS_WAIT_TIMEOUT);
+        failed = 1;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int quarter = warp & 3;  // tensor-memory lanes [32 * quarter, 32 * quarter + 32)
+    bool ok = mbar_wait(bar_acc, 0);
+    if (*(volatile int*)&failed) ok = false;
+    ok = __all_sync(0xffffffffu, ok);  // the tensor-memory loads below need the whole warp
+    if (ok) {
+      tc_fence_after();
+      const int n = n0 + quarter * 32 + lane;
+      const bool n_ok = n < args.N;
+      const size_t split_off = args.splits > 1 ? (size_t)blockIdx.z * args.rows * args.N : 0;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BT; c0 += 16) {
+        if (row_lo + c0 >= row_hi) break;  // uniform across the warp
+        uint32_t r[16];
+        tmem_ld16(tmem_acc + ((uint32_t)(quarter * 32) << 16) + c0, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int m = row_lo + c0 + j;
+          if (m < row_hi && n_ok) {
+            const float v = __uint_as_float(r[j]);
+            if (args.out_is_f32 || args.splits > 1)
+              ((float*)args.out)[split_off + (size_t)m * args.N + n] = v;
+            else
+              ((bf16*)args.out)[(size_t)m * args.N + n] = __float2bfloat16_rn(v);
+          }
+        }
+      }
+    } else if (lane == 0) {
+      atomicOr(args.status, JLX_STATUS_WAIT_TIMEOUT);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_acc, TMEM_COLS);
+  }
+}
+
+// out[m, n] = sum over splits (ascending) of partial[z][m][n]
+template <typename TO>
+__global__ void splitk_reduce_kernel(const float* __restrict__ partial, TO* __restrict__ out, long long total, int splits) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    float s = 0.f;
+    for (int z = 0; z < splits; ++z) s += partial[(size_t)z * total + i];
+    out[i] = from_f32<TO>(s);
+  }
+}
+
+// -------------------------------------------------------------------------------------------- host
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+// 2-D bfloat16 tensor [rows, K] row-major, boxes of [box_rows, 64] with the 128-byte swizzle; reads
+// outside the tensor give zeros.
+static int make_map(CUtensorMap* map, const void* base, long long rows, long long K, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  JLX_REQUIRE(fn != nullptr, "gemm_stream: the driver does not offer cuTensorMapEncodeTiled");
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+  cuuint32_t box[2] = {BK, (cuuint32_t)box_rows};
+  cuuint32_t elem[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  JLX_REQUIRE(r == CUDA_SUCCESS, "gemm_stream: cuTensorMapEncodeTiled failed (%d) for a [%lld, %lld] tensor", (int)r, rows, K);
+  return 0;
+}
+
+template <int BT, int STAGES>
+static int launch(const CUtensorMap& mw, const CUtensorMap& ma, const StreamArgs& a, int row_tiles, cudaStream_t stream) {
+  constexpr size_t smem = (size_t)STAGES * (WN * BK * 2 + BT * BK * 2) + 1024;
+  static bool configured = false;
+  if (!configured) {
+    JLX_CUDA(cudaFuncSetAttribute(gemm_stream_kernel<BT, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = true;
+  }
+  dim3 grid((a.N + WN - 1) / WN, row_tiles, a.splits);
+  gemm_stream_kernel<BT, STAGES><<<grid, NTHREADS, smem, stream>>>(mw, ma, a);
+  JLX_LAUNCH_CHECK("gemm_stream");
+  return 0;
+}
+
+// Token-tile width for a product whose largest group has about `rows_hint` rows.
+static int pick_bt(int rows_hint) {
+  if (rows_hint <= 16) return 16;
+  if (rows_hint <= 32) return 32;
+  if (rows_hint <= 64) return 64;
+  if (rows_hint <= 128) return 128;
+  return 256;
+}
+
+JLX_API int jlx_gemm_stream_supported(int K) { return K % 8 == 0 && K >= 8; }
+
+// rows: token rows of A (grouped: an upper bound of offsets[E]); rows_hint: typical rows per group
+// (chooses the token-tile width).  scratch: float32 [splits * rows * N] when splits > 1.
+JLX_API int jlx_gemm_stream(const void* A, const void* W, void* out, int out_is_f32, int rows, int N, int K,
+                            const int* offsets, int E, int rows_hint, int splits, float* scratch, int* status,
+                            cudaStream_t stream) {
+  JLX_REQUIRE(rows >= 0 && N > 0 && K > 0, "gemm_stream: bad sizes rows=%d N=%d K=%d", rows, N, K);
+  JLX_REQUIRE(K % 8 == 0, "gemm_stream: K = %d is no multiple of 8 (TMA needs 16-byte row strides); use the SIMT product", K);
+  JLX_REQUIRE(((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0, "gemm_stream: operands must be 16-byte aligned");
+  JLX_REQUIRE(!offsets || E > 0, "gemm_stream: a grouped product needs a group count");
+  JLX_REQUIRE(splits >= 1 && (splits == 1 || scratch), "gemm_stream: split-K needs scratch memory");
+  JLX_REQUIRE(splits == 1 || !offsets, "gemm_stream: split-K is for ungrouped products");
+  if (rows == 0) return 0;
+  const int groups = offsets ? E : 1;
+  const int bt = pick_bt(rows_hint > 0 ? rows_hint : rows);
+  CUtensorMap mw, ma;
+  if (make_map(&mw, W, (long long)groups * N, K, WN)) return 1;
+  if (make_map(&ma, A, rows, K, bt)) return 1;
+  int kps = K;
+  if (splits > 1) {
+    kps = ((K + splits - 1) / splits + BK - 1) / BK * BK;
+    splits = (K + kps - 1) / kps;
+  }
+  StreamArgs a;
+  a.N = N; a.K = K; a.rows = rows; a.offsets = offsets; a.E = E;
+  a.out = splits > 1 ? (void*)scratch : out;
+  a.out_is_f32 = out_is_f32; a.splits = splits; a.k_per_split = kps; a.status = status;
+  const int row_tiles = (rows + bt - 1) / bt + (offsets ? E : 0);
+  JLX_REQUIRE(row_tiles <= 65535, "gemm_stream: too many row tiles");
+  int rc;
+  switch (bt) {
+    // stages sized so that two blocks share an SM (about 100 KB each), except for the widest tile
+    case 16: rc = launch<16, 5>(mw, ma, a, row_tiles, stream); break;
+    case 32: rc = launch<32, 5>(mw, ma, a, row_tiles, stream); break;
+    case 64: rc = launch<64, 4>(mw, ma, a, row_tiles, stream); break;
+    case 128: rc = launch<128, 3>(mw, ma, a, row_tiles, stream); break;
+    default: rc = launch<256, 4>(mw, ma, a, row_tiles, stream); break;
+  }
+  if (rc) return rc;
+  if (splits > 1) {
+    const long long total = (long long)rows * N;
+    const int blocks = (int)((total + 255) / 256 < 4096 ? (total + 255) / 256 : 4096);
+    if (out_is_f32)
+      splitk_reduce_kernel<float><<<blocks, 256, 0, stream>>>(scratch, (float*)out, total, splits);
+    else
+      splitk_reduce_kernel<bf16><<<blocks, 256, 0, stream>>>(scratch, (bf16*)out, total, splits);
+    JLX_LAUNCH_CHECK("splitk_reduce");
+  }
+  return 0;
+}

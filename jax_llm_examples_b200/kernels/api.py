@@ -184,6 +184,32 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, offsets: torc
          _ptr(offsets), c_int(E), c_longlong(stride), _stream())
 
 
+def gemm_stream_supported(a: torch.Tensor, w: torch.Tensor) -> bool:
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.shape[-1] % 8 == 0
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_stream(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: torch.Tensor,
+                offsets: torch.Tensor | None = None, rows_hint: int = 0, splits: int = 1,
+                scratch: torch.Tensor | None = None) -> None:
+    """out = a @ w^T on the tcgen05 tensor cores (bfloat16 in, float32 accumulate).  a: [M, K];
+    w: [N, K] or, with row-group offsets [E + 1], [E, N, K]; out: [M, N] bfloat16 or float32.
+    splits > 1 cuts K across blocks; scratch: float32 [splits * M * N]."""
+    _contig(a, w, out, offsets, scratch)
+    M, K = a.shape
+    E = w.shape[0] if offsets is not None else 0
+    N = w.shape[-2]
+    if w.shape[-1] != K or tuple(out.shape) != (M, N) or (offsets is None) != (w.dim() == 2):
+        raise KernelError(f"gemm_stream: shapes do not fit: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or out.dtype not in (torch.bfloat16, torch.float32):
+        raise KernelError("gemm_stream: bfloat16 operands and a bfloat16 or float32 result are supported")
+    if splits > 1 and (scratch is None or scratch.numel() < splits * M * N or scratch.dtype != torch.float32):
+        raise KernelError("gemm_stream: split-K needs float32 scratch of splits * M * N elements")
+    _run("gemm_stream", "jlx_gemm_stream", _ptr(a), _ptr(w), _ptr(out), c_int(int(out.dtype == torch.float32)), c_int(M),
+         c_int(N), c_int(K), _ptr(offsets), c_int(E), c_int(rows_hint), c_int(splits), _ptr(scratch), _ptr(status),
+         _stream())
+
+
 # --------------------------------------------------------------------------------------- MoE
 def router(h32: torch.Tensor, w_router: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tensor,
            scores_out: torch.Tensor | None = None) -> None:

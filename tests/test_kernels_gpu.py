@@ -1,0 +1,348 @@
+"""Each CUDA kernel alone against a plain float32 torch reference of the same operation, at sizes
+other than the engine's: odd widths, head sizes in steps of 16, any head and group counts."""
+
+import math
+import random
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+def K():
+    from jax_llm_examples_b200.kernels import api
+
+    return api
+
+
+def status():
+    return torch.zeros(1, dtype=torch.int32, device=DEV)
+
+
+def close(a, b, tol):
+    err = float((a.float() - b.float()).abs().max() / b.float().abs().max().clamp_min(1e-6))
+    assert err < tol, f"relative error {err:.3e} (tolerance {tol})"
+    return err
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("V, D, N", [(1000, 72, 5), (257, 1030, 33)])
+def test_embed(dtype, V, D, N):
+    table = torch.randn(V, D, device=DEV).to(dtype)
+    ids = torch.randint(0, V, (N,), device=DEV, dtype=torch.int32)
+    x, st = torch.empty(N, D, device=DEV), status()
+    K().embed(ids, table, x, st)
+    assert torch.equal(x, table[ids.long()].float()) and int(st) == 0
+    ids[0] = V  # outside the vocabulary: flagged, not read
+    K().embed(ids, table, x, st)
+    assert int(st) == 2
+
+
+@pytest.mark.parametrize("out_dtype, tol", [(torch.float32, 2e-6), (torch.bfloat16, 5e-3)])
+@pytest.mark.parametrize("N, D, eps", [(7, 96, 1e-6), (3, 5120, 1e-5), (130, 1000, 1e-3)])
+def test_add_rmsnorm(out_dtype, tol, N, D, eps):
+    x, delta, g = torch.randn(N, D, device=DEV), torch.randn(N, D, device=DEV), 1 + 0.1 * torch.randn(D, device=DEV)
+    s = x + delta
+    ref = g * s / torch.sqrt((s * s).mean(-1, keepdim=True) + eps)
+    xc, out, out32 = x.clone(), torch.empty(N, D, device=DEV, dtype=out_dtype), torch.empty(N, D, device=DEV)
+    K().add_rmsnorm(xc, delta, g, eps, out, out32)
+    close(out, ref, tol), close(out32, ref, 2e-6)
+    assert torch.equal(xc, s)  # the residual sum is written back
+    # weightless, no delta, gathered rows
+    rows = torch.tensor([N - 1, 0, N // 2], device=DEV, dtype=torch.int32)
+    out2 = torch.empty(3, D, device=DEV, dtype=out_dtype)
+    xc2 = x.clone()
+    K().add_rmsnorm(xc2, delta, None, eps, out2, None, rows)
+    sr = s[rows.long()]
+    close(out2, sr / torch.sqrt((sr * sr).mean(-1, keepdim=True) + eps), tol)
+    assert torch.equal(xc2, x)  # gathered rows are not written back
+
+
+@pytest.mark.parametrize("dtype, tol", [(torch.float32, 1e-6), (torch.bfloat16, 1e-2)])
+def test_silu_mul(dtype, tol):
+    gu = torch.randn(9, 2 * 200, device=DEV).to(dtype)
+    out = torch.empty(9, 200, device=DEV, dtype=dtype)
+    K().silu_mul(gu, out)
+    g, u = gu.float()[:, :200], gu.float()[:, 200:]
+    close(out, torch.nn.functional.silu(g) * u, tol)
+
+
+def _rope_ref(x, pos, inv_freq):
+    ang = pos.float()[:, None] * inv_freq[None]
+    s, c = torch.sin(ang)[:, None], torch.cos(ang)[:, None]
+    a, b = x[..., 0::2], x[..., 1::2]
+    return torch.stack([a * c - b * s, b * c + a * s], -1).reshape(x.shape)
+
+
+@pytest.mark.parametrize("dtype, tol", [(torch.float32, 3e-6), (torch.bfloat16, 8e-3)])
+@pytest.mark.parametrize("Hq, Hkv, dh, page, rope, l2", [(6, 3, 48, 8, True, True), (5, 1, 16, 4, True, False),
+                                                         (4, 4, 112, 16, False, False), (8, 2, 256, 32, True, True)])
+def test_rope_kv_store(dtype, tol, Hq, Hkv, dh, page, rope, l2):
+    N, P, eps = 11, 9, 1e-5
+    qkv = torch.randn(N, (Hq + 2 * Hkv) * dh, device=DEV).to(dtype)
+    # two requests: tokens 0..5 at positions 20..25 of request 0; tokens 6..10 at positions 0..4 of request 1
+    pos = torch.tensor(list(range(20, 26)) + list(range(5)), device=DEV, dtype=torch.int32)
+    req = torch.tensor([0] * 6 + [1] * 5, device=DEV, dtype=torch.int32)
+    width = 26 // page + 1
+    perm = torch.randperm(P)[: 2 * width].to(torch.int32).reshape(2, width) if 2 * width <= P else None
+    if perm is None:
+        P = 2 * width
+        perm = torch.randperm(P).to(torch.int32).reshape(2, width)
+    bt = perm.to(DEV)
+    pages = torch.zeros(P, 2, Hkv, page, dh, device=DEV, dtype=dtype)
+    inv_freq = (1.0 / (10000.0 ** (torch.arange(0, dh, 2, device=DEV).float() / dh))) if rope else None
+    q_out, st = torch.empty(N, Hq, dh, device=DEV, dtype=dtype), status()
+    K().rope_kv_store(qkv, q_out, pages, bt, req, pos, inv_freq, l2, eps, Hq, Hkv, dh, st)
+    assert int(st) == 0
+    x = qkv.float().reshape(N, Hq + 2 * Hkv, dh)
+    q, k, v = x[:, :Hq], x[:, Hq:Hq + Hkv], x[:, Hq + Hkv:]
+    if rope:
+        q, k = _rope_ref(q, pos, inv_freq), _rope_ref(k, pos, inv_freq)
+    if l2:
+        q = q / torch.sqrt((q * q).mean(-1, keepdim=True) + eps)
+        k = k / torch.sqrt((k * k).mean(-1, keepdim=True) + eps)
+    close(q_out, q, tol)
+    for n in range(N):
+        pg = int(bt[int(req[n]), int(pos[n]) // page])
+        slot = int(pos[n]) % page
+        close(pages[pg, 0, :, slot], k[n], tol)
+        assert torch.equal(pages[pg, 1, :, slot].float(), v[n])
+    # a block-table entry outside the pool is flagged and nothing is written there
+    bt2 = bt.clone()
+    bt2[0, 20 // page] = P + 3
+    K().rope_kv_store(qkv, q_out, pages, bt2, req, pos, inv_freq, l2, eps, Hq, Hkv, dh, st)
+    assert int(st) == 1
+
+
+def _attention_ref(q, k_all, v_all, q_pos, chunk, window, scale, attn_scale, floor_scale):
+    """q: [n, Hq, dh] at positions q_pos of one request; k_all, v_all: [S, Hkv, dh] for positions 0..S-1."""
+    n, Hq, dh = q.shape
+    Hkv = k_all.shape[1]
+    G = Hq // Hkv
+    S = k_all.shape[0]
+    kp = torch.arange(S, device=q.device)
+    mask = q_pos[:, None] >= kp[None]
+    if chunk:
+        mask &= (q_pos[:, None] // chunk) == (kp[None] // chunk)
+    if window:
+        mask &= (q_pos[:, None] - kp[None]) < window
+    qs = q.float()
+    if attn_scale:
+        qs = qs * (1 + attn_scale * torch.log1p(torch.floor((q_pos.float() + 1) / floor_scale)))[:, None, None]
+    s = torch.einsum("nhgd,shd->hgns", qs.reshape(n, Hkv, G, dh), k_all.float()) * scale
+    s = s.masked_fill(~mask[None, None], float("-inf"))
+    return torch.einsum("hgns,shd->nhgd", torch.softmax(s, -1), v_all.float()).reshape(n, Hq, dh)
+
+
+def _paged_case(dtype, Hq, Hkv, dh, page, lens, q_lens, seed=0):
+    """Requests with `lens` tokens in the cache, the last `q_lens` of them being this step's queries."""
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    R = len(lens)
+    width = max(-(-L // page) for L in lens)
+    P = R * width + 3
+    ids = torch.randperm(P, generator=torch.Generator().manual_seed(seed))[: R * width].to(torch.int32).reshape(R, width)
+    pages = torch.randn(P, 2, Hkv, page, dh, device=DEV, generator=g).to(dtype)
+    ks, vs = [], []
+    for r, L in enumerate(lens):
+        k = torch.stack([pages[int(ids[r, p // page]), 0, :, p % page] for p in range(L)])
+        v = torch.stack([pages[int(ids[r, p // page]), 1, :, p % page] for p in range(L)])
+        ks.append(k), vs.append(v)
+    pos = torch.tensor([p for L, n in zip(lens, q_lens) for p in range(L - n, L)], device=DEV, dtype=torch.int32)
+    req = torch.tensor([r for r, n in enumerate(q_lens) for _ in range(n)], device=DEV, dtype=torch.int32)
+    q = torch.randn(len(pos), Hq, dh, device=DEV, generator=g).to(dtype)
+    return q, pages, ids.to(DEV), req, pos, ks, vs
+
+
+@pytest.mark.parametrize("dtype, tol", [(torch.float32, 5e-6), (torch.bfloat16, 1.5e-2)])
+@pytest.mark.parametrize("Hq, Hkv, dh, page, chunk, window, temp", [
+    (6, 2, 48, 8, 0, 0, False), (5, 5, 16, 4, 24, 0, False), (12, 1, 80, 16, 0, 13, True), (8, 2, 128, 64, 64, 0, True),
+    (3, 3, 272, 16, 0, 0, False)])
+def test_attention_generic(dtype, tol, Hq, Hkv, dh, page, chunk, window, temp):
+    lens, q_lens = [150, 37, 1, 66], [40, 1, 1, 66]
+    q, pages, bt, req, pos, ks, vs = _paged_case(dtype, Hq, Hkv, dh, page, lens, q_lens)
+    out, st = torch.empty_like(q), status()
+    attn_scale, floor_scale = (0.1, 16.0) if temp else (0.0, 1.0)
+    K().attention_generic(q, pages, bt, req, pos, out, dh ** -0.5, chunk, window, attn_scale, floor_scale, st)
+    assert int(st) == 0
+    at = 0
+    for r, n in enumerate(q_lens):
+        ref = _attention_ref(q[at:at + n], ks[r], vs[r], pos[at:at + n].long(), chunk, window, dh ** -0.5, attn_scale, floor_scale)
+        close(out[at:at + n], ref, tol)
+        at += n
+
+
+def test_attention_finds_one_far_key_among_hundreds():
+    """Random keys would hide a key that is skipped or read from the wrong page: here one key far back
+    matches the query strongly, so almost all of the output is that key's value."""
+    Hq, Hkv, dh, page = 4, 2, 64, 16
+    for dtype in (torch.float32, torch.bfloat16):
+        for far in (0, 15, 16, 17, 255, 256, 511):
+            q, pages, bt, req, pos, ks, vs = _paged_case(dtype, Hq, Hkv, dh, page, [600], [1], seed=far)
+            pg, slot = int(bt[0, far // page]), far % page
+            pages[pg, 0, :, slot] = 0
+            pages[pg, 0, :, slot, 0] = 40.0
+            q[:] = 0
+            q[..., 0] = 40.0  # score 1600 / 8 = 200 for that key, ~0 for the others
+            out, st = torch.empty_like(q), status()
+            K().attention_generic(q, pages, bt, req, pos, out, dh ** -0.5, 0, 0, 0.0, 1.0, st)
+            want = pages[pg, 1, :, slot].float().repeat_interleave(Hq // Hkv, 0)
+            close(out[0], want, 1e-5 if dtype == torch.float32 else 1e-2)
+
+
+@pytest.mark.parametrize("ta, tw, tc", [(torch.float32,) * 3, (torch.bfloat16, torch.float32, torch.float32),
+                                        (torch.bfloat16, torch.bfloat16, torch.bfloat16), (torch.float32, torch.bfloat16, torch.float32)])
+@pytest.mark.parametrize("M, N, Kd", [(1, 130, 70), (65, 64, 16), (200, 333, 257)])
+def test_gemm_simt(ta, tw, tc, M, N, Kd):
+    a, w = torch.randn(M, Kd, device=DEV).to(ta), torch.randn(N, Kd, device=DEV).to(tw)
+    out = torch.empty(M, N, device=DEV, dtype=tc)
+    K().gemm_simt(a, w, out)
+    close(out, a.double() @ w.double().T, 1e-2 if tc == torch.bfloat16 else 2e-6)
+
+
+def _groups(E, sizes_seed, total):
+    rng = random.Random(sizes_seed)
+    cuts = sorted(rng.randrange(total + 1) for _ in range(E - 1))
+    return torch.tensor([0] + cuts + [total], dtype=torch.int32)
+
+
+@pytest.mark.parametrize("E, rows, N, Kd", [(4, 37, 70, 50), (8, 300, 130, 64), (3, 5, 64, 129)])
+def test_gemm_simt_grouped(E, rows, N, Kd):
+    a, w = torch.randn(rows, Kd, device=DEV), torch.randn(E, N, Kd, device=DEV)
+    off = _groups(E, rows, rows)
+    out = torch.full((rows, N), float("nan"), device=DEV)
+    K().gemm_simt(a, w, out, off.to(DEV))
+    for e in range(E):
+        lo, hi = int(off[e]), int(off[e + 1])
+        if hi > lo:
+            close(out[lo:hi], a[lo:hi].double() @ w[e].double().T, 2e-6)
+
+
+@pytest.mark.parametrize("M, N, Kd, out_dtype, splits", [
+    (1, 128, 64, torch.float32, 1), (8, 384, 512, torch.bfloat16, 1), (5, 200, 136, torch.float32, 1),
+    (64, 1000, 1024, torch.float32, 1), (130, 256, 320, torch.bfloat16, 1), (300, 130, 72, torch.float32, 1),
+    (8, 640, 2048, torch.float32, 4), (33, 130, 1000, torch.bfloat16, 3)])
+def test_gemm_stream_dense(M, N, Kd, out_dtype, splits):
+    """The tcgen05 product against float64 of the same bfloat16 operands."""
+    a = torch.randn(M, Kd, device=DEV).bfloat16()
+    w = torch.randn(N, Kd, device=DEV).bfloat16()
+    out = torch.full((M, N), float("nan"), device=DEV, dtype=out_dtype)
+    scratch = torch.empty(splits * M * N, device=DEV) if splits > 1 else None
+    st = status()
+    K().gemm_stream(a, w, out, st, splits=splits, scratch=scratch)
+    torch.cuda.synchronize()
+    assert int(st) == 0
+    close(out, a.double() @ w.double().T, 1e-2 if out_dtype == torch.bfloat16 else 1e-5)
+
+
+@pytest.mark.parametrize("E, rows, N, Kd, hint", [(4, 37, 256, 128, 0), (16, 64, 384, 512, 4), (8, 700, 130, 200, 88),
+                                                  (5, 9, 128, 64, 16)])
+def test_gemm_stream_grouped(E, rows, N, Kd, hint):
+    a = torch.randn(rows, Kd, device=DEV).bfloat16()
+    w = torch.randn(E, N, Kd, device=DEV).bfloat16()
+    off = _groups(E, rows + 1, rows)
+    out = torch.full((rows, N), float("nan"), device=DEV)
+    st = status()
+    K().gemm_stream(a, w, out, st, offsets=off.to(DEV), rows_hint=hint)
+    torch.cuda.synchronize()
+    assert int(st) == 0
+    for e in range(E):
+        lo, hi = int(off[e]), int(off[e + 1])
+        if hi > lo:
+            close(out[lo:hi], a[lo:hi].double() @ w[e].double().T, 1e-5)
+
+
+def test_gemm_stream_refuses_what_it_cannot_take():
+    a, w = torch.randn(4, 70, device=DEV).bfloat16(), torch.randn(128, 70, device=DEV).bfloat16()
+    with pytest.raises(K().KernelError, match="multiple of 8"):
+        K().gemm_stream(a, w, torch.empty(4, 128, device=DEV), status())
+
+
+@pytest.mark.parametrize("N, D, E, k", [(33, 96, 8, 2), (5, 5120, 16, 1), (64, 200, 128, 4), (1, 64, 3, 3)])
+def test_router_and_sort(N, D, E, k):
+    h, w = torch.randn(N, D, device=DEV), torch.randn(E, D, device=DEV)
+    idx = torch.empty(N, k, device=DEV, dtype=torch.int32)
+    wt, scores = torch.empty(N, k, device=DEV), torch.empty(N, E, device=DEV)
+    K().router(h, w, idx, wt, scores)
+    ref = h.double() @ w.double().T
+    close(scores, ref, 5e-6)
+    order = torch.sort(scores, dim=-1, descending=True, stable=True)
+    assert torch.equal(idx.long(), order.indices[:, :k])
+    close(wt, torch.sigmoid(order.values[:, :k]), 1e-6)
+    off = torch.empty(E + 1, device=DEV, dtype=torch.int32)
+    pair, pos, st = torch.empty(N * k, device=DEV, dtype=torch.int32), torch.empty(N * k, device=DEV, dtype=torch.int32), status()
+    K().expert_sort(idx, off, pair, pos, E, st)
+    flat = idx.flatten().long()
+    counts = torch.bincount(flat, minlength=E)
+    assert torch.equal(off.long(), torch.cat([torch.zeros(1, device=DEV, dtype=torch.long), counts.cumsum(0)]))
+    assert torch.equal(pair.long(), torch.sort(flat, stable=True).indices)
+    assert torch.equal(pos.long()[pair.long()], torch.arange(N * k, device=DEV)) and int(st) == 0
+
+
+def test_router_tie_goes_to_the_lower_expert():
+    h = torch.zeros(2, 32, device=DEV)
+    h[:, 0] = 1
+    w = torch.zeros(6, 32, device=DEV)
+    w[:, 0] = torch.tensor([0.5, 2.0, 2.0, -1.0, 2.0, 0.0])
+    idx, wt = torch.empty(2, 2, device=DEV, dtype=torch.int32), torch.empty(2, 2, device=DEV)
+    K().router(h, w, idx, wt)
+    assert idx.tolist() == [[1, 2], [1, 2]]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_permute_scale_and_combine(dtype):
+    N, D, k, E = 21, 72, 2, 5
+    h = torch.randn(N, D, device=DEV)
+    idx = torch.stack([torch.randperm(E)[:k] for _ in range(N)]).to(DEV).to(torch.int32)
+    wt = torch.rand(N, k, device=DEV)
+    off, pair, pos, st = (torch.empty(E + 1, device=DEV, dtype=torch.int32), torch.empty(N * k, device=DEV, dtype=torch.int32),
+                          torch.empty(N * k, device=DEV, dtype=torch.int32), status())
+    K().expert_sort(idx, off, pair, pos, E, st)
+    a = torch.empty(N * k, D, device=DEV, dtype=dtype)
+    K().permute_scale(h, pair, wt, a, k)
+    ref = (wt.flatten()[pair.long()][:, None] * h[pair.long() // k])
+    close(a, ref, 1e-6 if dtype == torch.float32 else 5e-3)
+    y, shared, delta = torch.randn(N * k, D, device=DEV), torch.randn(N, D, device=DEV), torch.empty(N, D, device=DEV)
+    K().moe_combine(y, shared, pos, delta, k)
+    close(delta, shared + y[pos.long()].reshape(N, k, D).sum(1), 1e-6)
+
+
+def test_sampling_argmax_and_draws():
+    from tests.plain import llama4_plain as plain
+
+    M, V = 6, 1003
+    logits = torch.randn(M, V, device=DEV) * 3
+    logits[2, 77] = logits[2, 500] = 50.0  # a tie: the lower index wins
+    out = torch.empty(M, device=DEV, dtype=torch.int32)
+    K().sample(logits, out)
+    want = logits.argmax(-1).tolist()
+    want[2] = 77
+    assert out.tolist() == want
+    temps = torch.tensor([0.0, 0.8, 0.8, 1.5, 0.3, 0.8], device=DEV)
+    ks = torch.tensor([0, 0, 16, 64, 5, 1], device=DEV, dtype=torch.int32)
+    streams = torch.tensor([3, 3, 9, 2 ** 40 + 5, 0, 7], device=DEV, dtype=torch.int64)
+    for step in range(12):
+        counters = torch.full((M,), step, device=DEV, dtype=torch.int64)
+        K().sample(logits, out, temps, ks, streams, counters, seed=1234)
+        got = out.tolist()
+        for m in range(M):
+            s, c = int(streams[m]), step
+            bits = plain.philox4x32((c & 0xFFFFFFFF, c >> 32, s & 0xFFFFFFFF, s >> 32), (1234, 0))
+            u = plain.uniform_from_bits(bits[0])
+            ref = plain.sample_top(logits[m].cpu(), float(temps[m]), int(ks[m]), u)
+            if got[m] != ref:  # allowed only when u sits on the boundary between the two tokens (float32 vs float64 sums)
+                p = torch.softmax(logits[m].double().cpu() / float(temps[m]), -1)
+                assert abs(got[m] - ref) >= 1 and min(float(p[got[m]]), float(p[ref])) > 0
+                us = [plain.sample_top(logits[m].cpu(), float(temps[m]), int(ks[m]), min(max(u + d, 0.0), 0.999999)) for d in (-2e-6, 2e-6)]
+                assert got[m] in us, (m, step, got[m], ref)
+    # draws follow the distribution: 4000 draws over 3 tokens
+    small = torch.tensor([[2.0, 1.0, 0.0]], device=DEV)
+    n = 4000
+    big = small.expand(n, 3).contiguous()
+    o = torch.empty(n, device=DEV, dtype=torch.int32)
+    K().sample(big, o, torch.ones(n, device=DEV), torch.zeros(n, device=DEV, dtype=torch.int32),
+               torch.arange(n, device=DEV, dtype=torch.int64), torch.zeros(n, device=DEV, dtype=torch.int64), seed=5)
+    freq = torch.bincount(o.long(), minlength=3).float() / n
+    assert (freq - torch.softmax(small[0], -1)).abs().max() < 0.03
