@@ -237,7 +237,7 @@ def run_ours(args) -> dict:
     clocks.start()
     main = decode_run(batch, args.steps, args.warmup, e2e=False)
     clock_rec = clocks.stop()
-    e2e = e2e_run(batch, args.steps, args.warmup)
+    e2e = e2e_run(batch, args.steps, args.warmup) if not args.skip_e2e else {"ms": float("nan"), "h2d": 0, "d2h": 0}
 
     points = {}
     if not args.skip_points:
@@ -252,7 +252,7 @@ def run_ours(args) -> dict:
     eng = g.engine
     prompt = [rng.randrange(cfg.vocab_size) for _ in range(T)]
     pre_ms = []
-    for it in range(3 + 3):
+    for it in range(0 if args.skip_prefill else 3 + 3):
         s = eng.new_request()
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         ev0.record()
@@ -262,7 +262,7 @@ def run_ours(args) -> dict:
         if it >= 3:
             pre_ms.append(ev0.elapsed_time(ev1))
         eng.finish(s)
-    pre = sorted(pre_ms)[len(pre_ms) // 2]
+    pre = sorted(pre_ms)[len(pre_ms) // 2] if pre_ms else float("nan")
     flops = _prefill_flops(cfg, T)
 
     tok_s = batch / (main["ms"] / 1e3)
@@ -305,6 +305,8 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=8192)
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--skip-points", action="store_true", help="skip the batch 1 and 64 points")
+    ap.add_argument("--skip-e2e", action="store_true", help="skip the end-to-end run (for profiling captures)")
+    ap.add_argument("--skip-prefill", action="store_true", help="skip the prefill measurement (for profiling captures)")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "the reference (llama4_jax) installs offline only with --no-deps and "

@@ -1,0 +1,525 @@
+// Paged attention on the tensor cores for bfloat16, head sizes 64 and 128: a split-KV decode
+// kernel (one query token per request) and a flash prefill kernel (portions of prompts, also mixed
+// with single tokens), both aware of chunks, windows and the attention temperature.
+//
+// Reference: the reference's decode kernel (llama4/llama4_jax/ragged_attention.py:17-118) keeps
+// running max / sum / output in 32-bit over blocks of keys with a per-row [start, length) range; its
+// prefill goes to a TPU library (llama4/llama4_jax/model.py:842-864).  Mask, scale and softmax are
+// those of model.py:731-794.  Here:
+//
+//  * rows of the score tile are (query token, query head of the group); all G query heads of a KV head
+//    share each key/value tile in shared memory (a tile is read from HBM once per group, not per head);
+//  * keys and values come by cp.async in 64-key tiles, found row by row through the block table, so any
+//    page size works; shared-memory rows are XOR-swizzled for conflict-free ldmatrix;
+//  * scores, softmax statistics and the output accumulator are 32-bit; probabilities are rounded to
+//    bfloat16 only as the operand of the P*V product;
+//  * key tiles and decode splits are aligned to absolute positions (multiples of 64 / 256), so the order
+//    of a position's sums does not depend on the batch or on how the prompt was cut.
+//
+// A query at position p reads keys [start(p), p], start(p) = max(chunk ? p - p % chunk : 0,
+// window ? p - window + 1 : 0).  Temperature: scores of a layer with attn_scale != 0 are multiplied by
+// 1 + attn_scale * ln(1 + floor((p + 1) / floor_scale)).
+#include "common.cuh"
+
+#define KT 64            // keys per tile
+#define SPLIT 256        // keys per decode split (4 tiles), aligned to absolute positions
+#define NEG_BIG (-1.0e30f)
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+  const int n = valid ? 16 : 0;  // 0 bytes read: the 16 bytes are filled with zeros
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+struct AttnParams {
+  const bf16* q;        // [N, Hq, DH]
+  const bf16* pages;    // [P, 2, Hkv, page, DH]
+  const int* block_table;
+  int bt_stride;
+  const int* req_of_token;
+  const int* positions;
+  bf16* out;            // [N, Hq, DH]
+  int Hq, Hkv, page_size, num_pages;
+  float scale_log2;     // dh^-0.5 * log2(e)
+  int chunk, window;
+  float attn_scale, floor_scale;
+  int* status;
+  // prefill: tiles of up to 16 consecutive tokens of one request
+  const int* tiles;     // [n_tiles][2] = (first token row, token count)
+  // decode: partial results
+  float* part_o;        // [N, Hq, max_splits, DH]
+  float* part_ml;       // [N, Hq, max_splits, 2]
+  int max_splits;
+};
+
+__device__ __forceinline__ int first_key(int p, int chunk, int window) {
+  int s = 0;
+  if (chunk > 0) s = p - p % chunk;
+  if (window > 0) s = max(s, p - window + 1);
+  return s;
+}
+
+__device__ __forceinline__ float temperature(int p, float attn_scale, float floor_scale) {
+  return attn_scale != 0.f ? 1.f + attn_scale * log1pf(floorf(((float)p + 1.f) / floor_scale)) : 1.f;
+}
+
+// Loads keys [key0, key0 + KT) of request r, KV head hk, into ks / vs (each [KT][DH], swizzled).
+// Keys outside [lo, hi] or without a page become zeros.
+template <int DH>
+__device__ __forceinline__ void load_kv_tile(const AttnParams& P, int r, int hk, int key0, int lo, int hi, bf16* ks, bf16* vs,
+                                             int NT) {
+  constexpr int CH = DH / 8;              // 16-byte chunks per row
+  constexpr int TOTAL = KT * CH;          // chunks per tile and tensor
+  const size_t v_off = (size_t)P.Hkv * P.page_size * DH;
+  for (int idx = threadIdx.x; idx < TOTAL; idx += NT) {
+    const int j = idx / CH, c = idx % CH;
+    const int pos = key0 + j;
+    bool valid = pos >= lo && pos <= hi;
+    const bf16* src = P.pages;
+    if (valid) {
+      const int page = P.block_table[(size_t)r * P.bt_stride + pos / P.page_size];
+      if (page < 0 || page >= P.num_pages) {
+        atomicOr(P.status, JLX_STATUS_BAD_PAGE);
+        valid = false;
+      } else {
+        src = P.pages + (size_t)page * 2 * v_off + ((size_t)hk * P.page_size + pos % P.page_size) * DH + c * 8;
+      }
+    }
+    const int sw = (j * CH + (c ^ (j & 7))) * 8;
+    cp_async16(smem_u32(ks + sw), src, valid);
+    cp_async16(smem_u32(vs + sw), valid ? src + v_off : src, valid);
+  }
+}
+
+// ------------------------------------------------------------------------------------ decode
+// grid (max_splits, Hkv, R); 128 threads.  Rows of the score tile = the G query heads (G <= 16).
+// Warp w takes keys [16 w, 16 w + 16) of every 64-key tile; the four warps' results are merged in
+// shared memory and written as one partial (unnormalised output, max, sum) per (token, head, split).
+template <int DH>
+__global__ void __launch_bounds__(128) attention_decode_kernel(const AttnParams P) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  constexpr int TILES = SPLIT / KT;
+  constexpr int CH = DH / 8;
+  bf16* ks = reinterpret_cast<bf16*>(smem);                  // [TILES][KT][DH]
+  bf16* vs = ks + TILES * KT * DH;                           // [TILES][KT][DH]
+  const int n = blockIdx.z, hk = blockIdx.y, split = blockIdx.x;
+  const int G = P.Hq / P.Hkv;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int p = P.positions[n], r = P.req_of_token[n];
+  const int lo = first_key(p, P.chunk, P.window);
+  const int key_begin = (lo / SPLIT + split) * SPLIT;
+  if (key_begin > p) return;
+
+  // all four tiles of the split are requested at once; they are consumed as they land
+#pragma unroll
+  for (int t = 0; t < TILES; ++t) {
+    load_kv_tile<DH>(P, r, hk, key_begin + t * KT, lo, p, ks + t * KT * DH, vs + t * KT * DH, 128);
+    cp_async_commit();
+  }
+
+  // Q fragments: row = head g (rows >= G are zero)
+  uint32_t qf[DH / 16][4];
+  {
+    const int g0 = lane >> 2, g1 = g0 + 8, kk = (lane & 3) * 2;
+    const bf16* q0 = P.q + ((size_t)n * P.Hq + hk * G + g0) * DH;
+    const bf16* q1 = P.q + ((size_t)n * P.Hq + hk * G + g1) * DH;
+#pragma unroll
+    for (int s = 0; s < DH / 16; ++s) {
+      qf[s][0] = g0 < G ? *reinterpret_cast<const uint32_t*>(q0 + s * 16 + kk) : 0u;
+      qf[s][1] = g1 < G ? *reinterpret_cast<const uint32_t*>(q1 + s * 16 + kk) : 0u;
+      qf[s][2] = g0 < G ? *reinterpret_cast<const uint32_t*>(q0 + s * 16 + kk + 8) : 0u;
+      qf[s][3] = g1 < G ? *reinterpret_cast<const uint32_t*>(q1 + s * 16 + kk + 8) : 0u;
+    }
+  }
+  const float sc = P.scale_log2 * temperature(p, P.attn_scale, P.floor_scale);
+  float m[2] = {NEG_BIG, NEG_BIG}, l[2] = {0.f, 0.f};
+  float o[DH / 8][4];
+#pragma unroll
+  for (int i = 0; i < DH / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+
+#pragma unroll
+  for (int t = 0; t < TILES; ++t) {
+    if (t == 0) cp_async_wait<TILES - 1>();
+    else if (t == 1) cp_async_wait<TILES - 2>();
+    else if (t == 2) cp_async_wait<TILES - 3>();
+    else cp_async_wait<0>();
+    __syncthreads();
+    const int tile_key = key_begin + t * KT;
+    if (tile_key > p) break;  // uniform
+    const bf16* kt = ks + t * KT * DH;
+    const bf16* vt = vs + t * KT * DH;
+    // S = Q K^T for this warp's 16 keys: two n-tiles of 8 keys
+    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+    for (int kstep = 0; kstep < DH / 16; ++kstep) {
+      const int key = warp * 16 + (lane >> 4) * 8 + (lane & 7);
+      const int c = kstep * 2 + ((lane >> 3) & 1);
+      uint32_t b0, b1, b2, b3;
+      ldmatrix_x4(smem_u32(kt + (key * CH + (c ^ (key & 7))) * 8), b0, b1, b2, b3);
+      mma_bf16(s[0], qf[kstep], b0, b1);
+      mma_bf16(s[1], qf[kstep], b2, b3);
+    }
+    // mask, online softmax (rows lane/4 and lane/4 + 8)
+    float mx[2] = {m[0], m[1]};
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int key = tile_key + warp * 16 + nt * 8 + (lane & 3) * 2 + (e & 1);
+        const bool ok = key >= lo && key <= p;
+        s[nt][e] = ok ? s[nt][e] * sc : NEG_BIG;
+        mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
+      }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+    }
+    float corr[2], rs[2] = {0.f, 0.f};
+#pragma unroll
+    for (int h = 0; h < 2; ++h) corr[h] = exp2f(m[h] - mx[h]);
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float pv = s[nt][e] > 0.5f * NEG_BIG ? exp2f(s[nt][e] - mx[e >> 1]) : 0.f;
+        s[nt][e] = pv;
+        rs[e >> 1] += pv;
+      }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      rs[h] += __shfl_xor_sync(0xffffffffu, rs[h], 1);
+      rs[h] += __shfl_xor_sync(0xffffffffu, rs[h], 2);
+      l[h] = l[h] * corr[h] + rs[h];
+      m[h] = mx[h];
+    }
+#pragma unroll
+    for (int i = 0; i < DH / 8; ++i) {
+      o[i][0] *= corr[0]; o[i][1] *= corr[0]; o[i][2] *= corr[1]; o[i][3] *= corr[1];
+    }
+    // O += P V over this warp's 16 keys
+    uint32_t pa[4] = {pack_bf16(s[0][0], s[0][1]), pack_bf16(s[0][2], s[0][3]), pack_bf16(s[1][0], s[1][1]), pack_bf16(s[1][2], s[1][3])};
+#pragma unroll
+    for (int np = 0; np < DH / 16; ++np) {
+      const int key = warp * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+      const int c = np * 2 + (lane >> 4);
+      uint32_t b0, b1, b2, b3;
+      ldmatrix_x4_trans(smem_u32(vt + (key * CH + (c ^ (key & 7))) * 8), b0, b1, b2, b3);
+      mma_bf16(o[np * 2], pa, b0, b1);
+      mma_bf16(o[np * 2 + 1], pa, b2, b3);
+    }
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+  // merge the four warps: shared memory is reused as float [4][16][DH + 2]
+  float* red = reinterpret_cast<float*>(smem);
+  constexpr int LD = DH + 2;
+  {
+    const int r0 = lane >> 2, r1 = r0 + 8, col = (lane & 3) * 2;
+    float* w0 = red + (warp * 16 + r0) * LD;
+    float* w1 = red + (warp * 16 + r1) * LD;
+#pragma unroll
+    for (int i = 0; i < DH / 8; ++i) {
+      w0[i * 8 + col] = o[i][0]; w0[i * 8 + col + 1] = o[i][1];
+      w1[i * 8 + col] = o[i][2]; w1[i * 8 + col + 1] = o[i][3];
+    }
+    if ((lane & 3) == 0) {
+      w0[DH] = m[0]; w0[DH + 1] = l[0];
+      w1[DH] = m[1]; w1[DH + 1] = l[1];
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < G * DH; idx += 128) {
+    const int g = idx / DH, d = idx % DH;
+    float mm = NEG_BIG;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) mm = fmaxf(mm, red[(w * 16 + g) * LD + DH]);
+    float acc = 0.f, ll = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float f = exp2f(red[(w * 16 + g) * LD + DH] - mm);
+      acc += red[(w * 16 + g) * LD + d] * f;
+      ll += red[(w * 16 + g) * LD + DH + 1] * f;
+    }
+    const size_t row = ((size_t)n * P.Hq + hk * G + g) * P.max_splits + split;
+    P.part_o[row * DH + d] = acc;
+    if (d == 0) {
+      P.part_ml[row * 2] = mm;
+      P.part_ml[row * 2 + 1] = ll;
+    }
+  }
+}
+
+// out[n, h, :] = sum_s o_s 2^(m_s - m) / sum_s l_s 2^(m_s - m), splits in ascending order.
+template <int DH>
+__global__ void attention_combine_kernel(const AttnParams P) {
+  const int n = blockIdx.x, h = blockIdx.y;
+  const int p = P.positions[n];
+  const int lo = first_key(p, P.chunk, P.window);
+  const int splits = p / SPLIT - lo / SPLIT + 1;
+  const size_t row = ((size_t)n * P.Hq + h) * P.max_splits;
+  float mm = NEG_BIG;
+  for (int s = 0; s < splits; ++s) mm = fmaxf(mm, P.part_ml[(row + s) * 2]);
+  float ll = 0.f;
+  for (int s = 0; s < splits; ++s) ll += P.part_ml[(row + s) * 2 + 1] * exp2f(P.part_ml[(row + s) * 2] - mm);
+  for (int d = threadIdx.x; d < DH; d += blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < splits; ++s) acc += P.part_o[(row + s) * DH + d] * exp2f(P.part_ml[(row + s) * 2] - mm);
+    P.out[((size_t)n * P.Hq + h) * DH + d] = __float2bfloat16_rn(acc / ll);
+  }
+}
+
+// ----------------------------------------------------------------------------------- prefill
+// grid (n_tiles, Hkv); G warps.  A tile is up to 16 consecutive tokens of one request; warp g owns the
+// 16 x DH rows of query head g.  Key tiles of 64 are double-buffered.
+template <int DH>
+__global__ void __launch_bounds__(256) attention_prefill_kernel(const AttnParams P) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  constexpr int CH = DH / 8;
+  constexpr int STAGES = 2;
+  bf16* ks = reinterpret_cast<bf16*>(smem);          // [STAGES][KT][DH]
+  bf16* vs = ks + STAGES * KT * DH;
+  const int tile = blockIdx.x, hk = blockIdx.y;
+  const int G = P.Hq / P.Hkv;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = P.tiles[2 * tile], cnt = P.tiles[2 * tile + 1];
+  const int r = P.req_of_token[n0];
+  const int p_first = P.positions[n0], p_last = p_first + cnt - 1;
+  const int lo_tile = first_key(p_first, P.chunk, P.window);  // start(p) grows with p: the tile's lowest
+  const int key_begin = lo_tile / KT * KT;
+  const int n_tiles = (p_last - key_begin) / KT + 1;
+  const int NT = blockDim.x;
+
+  // this thread's two rows: tokens lane/4 and lane/4 + 8 of head `warp`
+  const int t0 = lane >> 2, t1 = t0 + 8;
+  const int p0 = p_first + min(t0, cnt - 1), p1 = p_first + min(t1, cnt - 1);
+  const int lo0 = first_key(p0, P.chunk, P.window), lo1 = first_key(p1, P.chunk, P.window);
+  const bool row0 = t0 < cnt, row1 = t1 < cnt;
+  uint32_t qf[DH / 16][4];
+  {
+    const int kk = (lane & 3) * 2;
+    const bf16* q0 = P.q + ((size_t)(n0 + min(t0, cnt - 1)) * P.Hq + hk * G + warp) * DH;
+    const bf16* q1 = P.q + ((size_t)(n0 + min(t1, cnt - 1)) * P.Hq + hk * G + warp) * DH;
+#pragma unroll
+    for (int s = 0; s < DH / 16; ++s) {
+      qf[s][0] = row0 ? *reinterpret_cast<const uint32_t*>(q0 + s * 16 + kk) : 0u;
+      qf[s][1] = row1 ? *reinterpret_cast<const uint32_t*>(q1 + s * 16 + kk) : 0u;
+      qf[s][2] = row0 ? *reinterpret_cast<const uint32_t*>(q0 + s * 16 + kk + 8) : 0u;
+      qf[s][3] = row1 ? *reinterpret_cast<const uint32_t*>(q1 + s * 16 + kk + 8) : 0u;
+    }
+  }
+  const float sc0 = P.scale_log2 * temperature(p0, P.attn_scale, P.floor_scale);
+  const float sc1 = P.scale_log2 * temperature(p1, P.attn_scale, P.floor_scale);
+  float m[2] = {NEG_BIG, NEG_BIG}, l[2] = {0.f, 0.f};
+  float o[DH / 8][4];
+#pragma unroll
+  for (int i = 0; i < DH / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+
+  // prologue: first tile
+  load_kv_tile<DH>(P, r, hk, key_begin, lo_tile, p_last, ks, vs, NT);
+  cp_async_commit();
+
+  for (int t = 0; t < n_tiles; ++t) {
+    const int buf = t & 1;
+    // request the next tile into the other buffer (free since the barrier at the end of the last round)
+    if (t + 1 < n_tiles)
+      load_kv_tile<DH>(P, r, hk, key_begin + (t + 1) * KT, lo_tile, p_last, ks + (buf ^ 1) * KT * DH, vs + (buf ^ 1) * KT * DH, NT);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    const int tile_key = key_begin + t * KT;
+    const bf16* kt = ks + buf * KT * DH;
+    const bf16* vt = vs + buf * KT * DH;
+    if (warp < G) {
+      float s[KT / 8][4];
+#pragma unroll
+      for (int i = 0; i < KT / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+#pragma unroll
+      for (int kstep = 0; kstep < DH / 16; ++kstep) {
+#pragma unroll
+        for (int np = 0; np < KT / 16; ++np) {
+          const int key = np * 16 + (lane >> 4) * 8 + (lane & 7);
+          const int c = kstep * 2 + ((lane >> 3) & 1);
+          uint32_t b0, b1, b2, b3;
+          ldmatrix_x4(smem_u32(kt + (key * CH + (c ^ (key & 7))) * 8), b0, b1, b2, b3);
+          mma_bf16(s[np * 2], qf[kstep], b0, b1);
+          mma_bf16(s[np * 2 + 1], qf[kstep], b2, b3);
+        }
+      }
+      float mx[2] = {m[0], m[1]};
+#pragma unroll
+      for (int nt = 0; nt < KT / 8; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int key = tile_key + nt * 8 + (lane & 3) * 2 + (e & 1);
+          const bool ok = (e < 2) ? (row0 && key >= lo0 && key <= p0) : (row1 && key >= lo1 && key <= p1);
+          s[nt][e] = ok ? s[nt][e] * ((e < 2) ? sc0 : sc1) : NEG_BIG;
+          mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
+        }
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+      }
+      float corr[2], rs[2] = {0.f, 0.f};
+#pragma unroll
+      for (int h = 0; h < 2; ++h) corr[h] = exp2f(m[h] - mx[h]);
+#pragma unroll
+      for (int nt = 0; nt < KT / 8; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float pv = s[nt][e] > 0.5f * NEG_BIG ? exp2f(s[nt][e] - mx[e >> 1]) : 0.f;
+          s[nt][e] = pv;
+          rs[e >> 1] += pv;
+        }
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        rs[h] += __shfl_xor_sync(0xffffffffu, rs[h], 1);
+        rs[h] += __shfl_xor_sync(0xffffffffu, rs[h], 2);
+        l[h] = l[h] * corr[h] + rs[h];
+        m[h] = mx[h];
+      }
+#pragma unroll
+      for (int i = 0; i < DH / 8; ++i) {
+        o[i][0] *= corr[0]; o[i][1] *= corr[0]; o[i][2] *= corr[1]; o[i][3] *= corr[1];
+      }
+#pragma unroll
+      for (int kp = 0; kp < KT / 16; ++kp) {
+        uint32_t pa[4] = {pack_bf16(s[kp * 2][0], s[kp * 2][1]), pack_bf16(s[kp * 2][2], s[kp * 2][3]),
+                          pack_bf16(s[kp * 2 + 1][0], s[kp * 2 + 1][1]), pack_bf16(s[kp * 2 + 1][2], s[kp * 2 + 1][3])};
+#pragma unroll
+        for (int np = 0; np < DH / 16; ++np) {
+          const int key = kp * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+          const int c = np * 2 + (lane >> 4);
+          uint32_t b0, b1, b2, b3;
+          ldmatrix_x4_trans(smem_u32(vt + (key * CH + (c ^ (key & 7))) * 8), b0, b1, b2, b3);
+          mma_bf16(o[np * 2], pa, b0, b1);
+          mma_bf16(o[np * 2 + 1], pa, b2, b3);
+        }
+      }
+    }
+    __syncthreads();  // everyone is done with this buffer before the next round overwrites it
+  }
+  cp_async_wait<0>();
+  if (warp < G) {
+    const int col = (lane & 3) * 2;
+    const float i0 = 1.f / l[0], i1 = 1.f / l[1];
+    bf16* o0 = P.out + ((size_t)(n0 + t0) * P.Hq + hk * G + warp) * DH;
+    bf16* o1 = P.out + ((size_t)(n0 + t1) * P.Hq + hk * G + warp) * DH;
+#pragma unroll
+    for (int i = 0; i < DH / 8; ++i) {
+      if (row0) *reinterpret_cast<__nv_bfloat162*>(o0 + i * 8 + col) = __floats2bfloat162_rn(o[i][0] * i0, o[i][1] * i0);
+      if (row1) *reinterpret_cast<__nv_bfloat162*>(o1 + i * 8 + col) = __floats2bfloat162_rn(o[i][2] * i1, o[i][3] * i1);
+    }
+  }
+}
+
+// --------------------------------------------------------------------------------------- host
+static int fill_params(AttnParams& P, const void* q, const void* pages, const int* block_table, int bt_stride,
+                       const int* req_of_token, const int* positions, void* out, int Hq, int Hkv, int dh, int page_size,
+                       int num_pages, float scale, int chunk, int window, float attn_scale, float floor_scale, int* status) {
+  JLX_REQUIRE(Hq > 0 && Hkv > 0 && Hq % Hkv == 0, "attention: %d query heads are no multiple of %d KV heads", Hq, Hkv);
+  JLX_REQUIRE(dh == 64 || dh == 128, "attention_mma: head size %d is not built (64 and 128 are); use the generic kernel", dh);
+  JLX_REQUIRE(page_size > 0 && num_pages > 0 && bt_stride > 0, "attention: bad cache sizes");
+  JLX_REQUIRE(attn_scale == 0.f || floor_scale > 0.f, "attention: floor_scale must be positive");
+  JLX_REQUIRE(((uintptr_t)q & 15) == 0 && ((uintptr_t)pages & 15) == 0, "attention: q and pages must be 16-byte aligned");
+  P.q = (const bf16*)q; P.pages = (const bf16*)pages; P.block_table = block_table; P.bt_stride = bt_stride;
+  P.req_of_token = req_of_token; P.positions = positions; P.out = (bf16*)out; P.Hq = Hq; P.Hkv = Hkv;
+  P.page_size = page_size; P.num_pages = num_pages; P.scale_log2 = scale * 1.4426950408889634f;
+  P.chunk = chunk; P.window = window; P.attn_scale = attn_scale; P.floor_scale = floor_scale; P.status = status;
+  P.tiles = nullptr; P.part_o = nullptr; P.part_ml = nullptr; P.max_splits = 0;
+  return 0;
+}
+
+JLX_API int jlx_attention_mma_supported(int Hq, int Hkv, int dh, int decode) {
+  if (Hkv <= 0 || Hq % Hkv) return 0;
+  const int G = Hq / Hkv;
+  return (dh == 64 || dh == 128) && G <= (decode ? 16 : 8);
+}
+
+// Splits a decode launch needs for requests of up to max_kv_len keys.
+JLX_API int jlx_attention_decode_splits(int max_kv_len, int chunk, int window) {
+  int span = max_kv_len;
+  if (chunk > 0 && chunk < span) span = chunk;
+  if (window > 0 && window < span) span = window;
+  return (span + SPLIT - 1) / SPLIT + 1;
+}
+
+// One query token per request.  part_o: float [N * Hq * max_splits * dh]; part_ml: float [N * Hq * max_splits * 2].
+JLX_API int jlx_attention_decode(const void* q, const void* pages, const int* block_table, int bt_stride,
+                                 const int* req_of_token, const int* positions, void* out, int N, int Hq, int Hkv, int dh,
+                                 int page_size, int num_pages, float scale, int chunk, int window, float attn_scale,
+                                 float floor_scale, float* part_o, float* part_ml, int max_splits, int* status,
+                                 cudaStream_t stream) {
+  AttnParams P;
+  if (fill_params(P, q, pages, block_table, bt_stride, req_of_token, positions, out, Hq, Hkv, dh, page_size, num_pages,
+                  scale, chunk, window, attn_scale, floor_scale, status)) return 1;
+  JLX_REQUIRE(Hq / Hkv <= 16, "attention_decode: %d query heads per KV head; up to 16 are supported", Hq / Hkv);
+  JLX_REQUIRE(part_o && part_ml && max_splits > 0, "attention_decode: scratch for the partial results is missing");
+  JLX_REQUIRE(N <= 65535 && Hkv <= 65535, "attention_decode: too many rows");
+  if (N == 0) return 0;
+  P.part_o = part_o; P.part_ml = part_ml; P.max_splits = max_splits;
+  const size_t smem = (size_t)2 * SPLIT * dh * 2;
+  dim3 grid(max_splits, Hkv, N);
+  if (dh == 128) {
+    static bool cfg = false;
+    if (!cfg) { JLX_CUDA(cudaFuncSetAttribute(attention_decode_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); cfg = true; }
+    attention_decode_kernel<128><<<grid, 128, smem, stream>>>(P);
+    JLX_LAUNCH_CHECK("attention_decode");
+    attention_combine_kernel<128><<<dim3(N, Hq), 128, 0, stream>>>(P);
+  } else {
+    static bool cfg = false;
+    if (!cfg) { JLX_CUDA(cudaFuncSetAttribute(attention_decode_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); cfg = true; }
+    attention_decode_kernel<64><<<grid, 128, smem, stream>>>(P);
+    JLX_LAUNCH_CHECK("attention_decode");
+    attention_combine_kernel<64><<<dim3(N, Hq), 64, 0, stream>>>(P);
+  }
+  JLX_LAUNCH_CHECK("attention_combine");
+  return 0;
+}
+
+// tiles: int32 [n_tiles][2] on the device: (first token row, count <= 16), tokens of one request each.
+JLX_API int jlx_attention_prefill(const void* q, const void* pages, const int* block_table, int bt_stride,
+                                  const int* req_of_token, const int* positions, void* out, const int* tiles, int n_tiles,
+                                  int Hq, int Hkv, int dh, int page_size, int num_pages, float scale, int chunk, int window,
+                                  float attn_scale, float floor_scale, int* status, cudaStream_t stream) {
+  AttnParams P;
+  if (fill_params(P, q, pages, block_table, bt_stride, req_of_token, positions, out, Hq, Hkv, dh, page_size, num_pages,
+                  scale, chunk, window, attn_scale, floor_scale, status)) return 1;
+  const int G = Hq / Hkv;
+  JLX_REQUIRE(G <= 8, "attention_prefill: %d query heads per KV head; up to 8 are supported", G);
+  JLX_REQUIRE(Hkv <= 65535, "attention_prefill: too many KV heads");
+  if (n_tiles == 0) return 0;
+  P.tiles = tiles;
+  const size_t smem = (size_t)2 * 2 * KT * dh * 2;
+  dim3 grid(n_tiles, Hkv);
+  if (dh == 128) {
+    static bool cfg = false;
+    if (!cfg) { JLX_CUDA(cudaFuncSetAttribute(attention_prefill_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); cfg = true; }
+    attention_prefill_kernel<128><<<grid, G * 32, smem, stream>>>(P);
+  } else {
+    attention_prefill_kernel<64><<<grid, G * 32, smem, stream>>>(P);
+  }
+  JLX_LAUNCH_CHECK("attention_prefill");
+  return 0;
+}

@@ -18,7 +18,7 @@ import torch
 
 from ..cache.manager import CacheManager, OutOfPages
 from ..kernels import api as K
-from ..parts.base import StepContext
+from ..parts.base import StepContext, Workspace
 from ..parts.decoder import DecoderModel
 
 
@@ -88,6 +88,7 @@ class Engine:
         self.states = [torch.zeros((max_slots, *s.shape), dtype=s.dtype, device=dev) for s in plan.states]
         self.status = torch.zeros(1, dtype=torch.int32, device=dev)
         self._ring = _HostRing()
+        self.workspace = Workspace(dev)
         self._dev_desc: torch.Tensor | None = None
         self.steps_run = 0
         self.record_routing = False  # True: keep each routed layer's expert choices of the last step
@@ -143,9 +144,18 @@ class Engine:
         max_kv = max(s + int(n) for s, n in zip(starts, n_tok))
         width = -(-max_kv // self.page_size)
         G = len(self.manager.groups)
-        size = CacheManager.packed_size(G, N, R, M, width)
+        packed = CacheManager.packed_size(G, N, R, M, width)
+        # query tiles for the flash kernel: up to 16 consecutive tokens of one request
+        tiles = None
+        if int(n_tok.max()) > 1:
+            firsts = np.concatenate([[0], np.cumsum(n_tok)[:-1]])
+            tiles = np.array([(f + t, min(16, n - t)) for f, n in zip(firsts, n_tok) for t in range(0, n, 16)], dtype=np.int32)
+        size = packed + (tiles.size if tiles is not None else 0)
         host, ring_i = self._ring.next(size)
-        self.manager.pack_step(slots, n_tok, tokens, want_off, want, width, N, R, M, host.numpy())
+        host_np = host.numpy()
+        self.manager.pack_step(slots, n_tok, tokens, want_off, want, width, N, R, M, host_np)
+        if tiles is not None:
+            host_np[packed:size] = tiles.reshape(-1)
         if self._dev_desc is None or self._dev_desc.numel() < size:
             self._dev_desc = torch.empty(max(size, 4096), dtype=torch.int32, device=self.runtime.device)
         desc = self._dev_desc[:size]
@@ -165,9 +175,11 @@ class Engine:
             token_ids=cut(N), positions=cut(N), req_of_token=cut(N), cu_q=cut(R + 1), q_start=cut(R), kv_len=cut(R),
             slot_ids=cut(R), logit_rows=cut(M), n_logit_rows=M, status=self.status,
             host_q_lens=[int(n) for n in n_tok], host_q_start=starts, host_slot_ids=[int(s) for s in slots],
-            max_q_len=int(n_tok.max()), max_kv_len=max_kv,
+            max_q_len=int(n_tok.max()), max_kv_len=max_kv, workspace=self.workspace,
         )
         block_tables = [cut(R * width).view(R, width) for _ in range(G)]
+        if tiles is not None:
+            ctx.attn_tiles, ctx.n_attn_tiles = cut(tiles.size).view(-1, 2), tiles.shape[0]
         if self.record_routing:
             ctx.scratch["record_routing"] = []
         logits = self.model.forward(ctx, self.kv, self.states, block_tables)

@@ -167,6 +167,47 @@ def attention_generic(q: torch.Tensor, pages: torch.Tensor, block_table: torch.T
          c_float(floor_scale), _ptr(status), _stream())
 
 
+def attention_mma_supported(q_dtype: torch.dtype, Hq: int, Hkv: int, dh: int, decode: bool) -> bool:
+    if q_dtype != torch.bfloat16:
+        return False
+    return bool(library("attention_mma").jlx_attention_mma_supported(c_int(Hq), c_int(Hkv), c_int(dh), c_int(int(decode))))
+
+
+def attention_decode_splits(max_kv_len: int, chunk: int, window: int) -> int:
+    return int(library("attention_mma").jlx_attention_decode_splits(c_int(max_kv_len), c_int(chunk), c_int(window)))
+
+
+def attention_decode(q: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor, req_of_token: torch.Tensor,
+                     positions: torch.Tensor, out: torch.Tensor, scale: float, chunk: int, window: int, attn_scale: float,
+                     floor_scale: float, part_o: torch.Tensor, part_ml: torch.Tensor, max_splits: int,
+                     status: torch.Tensor) -> None:
+    """Split-KV attention for one query token per request (tensor cores, bfloat16).
+    part_o: float32 [N * Hq * max_splits * dh]; part_ml: float32 [N * Hq * max_splits * 2]."""
+    _contig(q, pages, block_table, out, part_o, part_ml)
+    N, Hq, dh = q.shape
+    P, _, Hkv, page_size, _ = pages.shape
+    if part_o.numel() < N * Hq * max_splits * dh or part_ml.numel() < N * Hq * max_splits * 2:
+        raise KernelError("attention_decode: scratch for the partial results is too small")
+    _run("attention_mma", "jlx_attention_decode", _ptr(q), _ptr(pages), _ptr(block_table), c_int(block_table.shape[1]),
+         _ptr(req_of_token), _ptr(positions), _ptr(out), c_int(N), c_int(Hq), c_int(Hkv), c_int(dh), c_int(page_size),
+         c_int(P), c_float(scale), c_int(chunk), c_int(window), c_float(attn_scale), c_float(floor_scale), _ptr(part_o),
+         _ptr(part_ml), c_int(max_splits), _ptr(status), _stream())
+
+
+def attention_prefill(q: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor, req_of_token: torch.Tensor,
+                      positions: torch.Tensor, out: torch.Tensor, tiles: torch.Tensor, n_tiles: int, scale: float,
+                      chunk: int, window: int, attn_scale: float, floor_scale: float, status: torch.Tensor) -> None:
+    """Flash attention over the paged cache for prompt portions (tensor cores, bfloat16).
+    tiles: int32 [n_tiles, 2] = (first token row, count <= 16), each within one request."""
+    _contig(q, pages, block_table, out, tiles)
+    N, Hq, dh = q.shape
+    P, _, Hkv, page_size, _ = pages.shape
+    _run("attention_mma", "jlx_attention_prefill", _ptr(q), _ptr(pages), _ptr(block_table), c_int(block_table.shape[1]),
+         _ptr(req_of_token), _ptr(positions), _ptr(out), _ptr(tiles), c_int(n_tiles), c_int(Hq), c_int(Hkv), c_int(dh),
+         c_int(page_size), c_int(P), c_float(scale), c_int(chunk), c_int(window), c_float(attn_scale),
+         c_float(floor_scale), _ptr(status), _stream())
+
+
 # ------------------------------------------------------------------------------------- GEMMs
 def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, offsets: torch.Tensor | None = None) -> None:
     """out = a @ w^T.  a: [M, K]; w: [N, K], or [E, N, K] with row-group offsets [E + 1] on the device."""

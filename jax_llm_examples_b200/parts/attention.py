@@ -21,7 +21,7 @@ class PagedAttention(Mixer):
     A layer with ``shares_cache`` projects only q and reads pages that another layer wrote.
     """
 
-    kernel_libraries = ("attention_generic", "rope_kv", "gemm_simt")
+    kernel_libraries = ("attention_generic", "attention_mma", "rope_kv", "gemm_simt", "gemm_stream")
 
     def __init__(self, w_qkv: torch.Tensor, w_o: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
                  position: PositionEncoding, qk_norm_eps: float | None = None, chunk: int | None = None,
@@ -40,7 +40,7 @@ class PagedAttention(Mixer):
         self.scale = float(head_dim) ** -0.5 if scale is None else float(scale)  # model.py:774
 
     def required_libraries(self, runtime: Runtime):
-        return tuple(dict.fromkeys(self.kernel_libraries + self.position.required_libraries(runtime)))
+        return tuple(dict.fromkeys(super().required_libraries(runtime) + self.position.required_libraries(runtime)))
 
     def kv_need(self) -> KVNeed:
         if self.chunk is not None and self.window is None:
@@ -53,14 +53,32 @@ class PagedAttention(Mixer):
 
     def forward(self, ctx: StepContext, h: torch.Tensor, cache: LayerCache) -> torch.Tensor:
         rt = ctx.runtime
-        qkv = linear(h, self.w_qkv, rt.dtype)
+        qkv = linear(ctx, h, self.w_qkv, rt.dtype)
         q = self.position.encode_and_store(ctx, qkv, self.n_heads, self.n_kv_heads, self.head_dim, cache, self.qk_norm_eps)
         attn_scale, floor_scale = self.position.query_temperature()
         out = torch.empty_like(q)
         self.attend(ctx, q, cache, out, attn_scale, floor_scale)
-        return linear(out.view(q.shape[0], -1), self.w_o, torch.float32)
+        return linear(ctx, out.view(q.shape[0], -1), self.w_o, torch.float32)
 
     def attend(self, ctx: StepContext, q, cache: LayerCache, out, attn_scale: float, floor_scale: float) -> None:
+        """Tensor-core kernels where they are built (bfloat16, head size 64 or 128, small groups): split-KV
+        when every request brings one token, flash tiles otherwise; the generic kernel for the rest."""
+        chunk, window = self.chunk or 0, self.window or 0
+        decode = ctx.max_q_len == 1
+        if K.attention_mma_supported(q.dtype, self.n_heads, self.n_kv_heads, self.head_dim, decode):
+            if decode:
+                splits = K.attention_decode_splits(ctx.max_kv_len, chunk, window)
+                n = q.shape[0] * self.n_heads * splits
+                part_o = ctx.workspace.get("attn_part_o", n * self.head_dim, torch.float32)
+                part_ml = ctx.workspace.get("attn_part_ml", n * 2, torch.float32)
+                K.attention_decode(q, cache.pages, cache.block_table, ctx.req_of_token, ctx.positions, out, self.scale,
+                                   chunk, window, attn_scale, floor_scale, part_o, part_ml, splits, ctx.status)
+                return
+            if ctx.attn_tiles is not None:
+                K.attention_prefill(q, cache.pages, cache.block_table, ctx.req_of_token, ctx.positions, out,
+                                    ctx.attn_tiles, ctx.n_attn_tiles, self.scale, chunk, window, attn_scale,
+                                    floor_scale, ctx.status)
+                return
         K.attention_generic(q, cache.pages, cache.block_table, ctx.req_of_token, ctx.positions, out, self.scale,
                             self.chunk or 0, self.window or 0, attn_scale, floor_scale, ctx.status)
 

@@ -56,6 +56,22 @@ class StateNeed:
     dtype: torch.dtype = torch.float32
 
 
+class Workspace:
+    """Named device buffers that live across steps (scratch of kernels, e.g. split-K partials).
+    Kernels of one stream run in order, so a buffer can serve every layer in turn."""
+
+    def __init__(self, device: torch.device):
+        self.device = device
+        self._bufs: dict[str, torch.Tensor] = {}
+
+    def get(self, name: str, numel: int, dtype: torch.dtype) -> torch.Tensor:
+        t = self._bufs.get(name)
+        if t is None or t.numel() < numel or t.dtype != dtype:
+            t = torch.empty(max(numel, 1), dtype=dtype, device=self.device)
+            self._bufs[name] = t
+        return t[:numel]
+
+
 @dataclasses.dataclass
 class LayerCache:
     """What one run of a layer sees of the cache in this step."""
@@ -90,6 +106,12 @@ class StepContext:
     max_q_len: int = 0
     max_kv_len: int = 0
     scratch: dict[str, Any] = dataclasses.field(default_factory=dict)  # per-step memo shared by parts
+    workspace: Workspace | None = None  # buffers that outlive the step
+    attn_tiles: torch.Tensor | None = None  # int32 [n, 2]: (first token row, count <= 16) tiles of one request each
+    n_attn_tiles: int = 0
+
+
+BF16_ONLY_LIBRARIES = ("gemm_stream", "attention_mma")
 
 
 class Part:
@@ -98,6 +120,9 @@ class Part:
     kernel_libraries: tuple[str, ...] = ()  # kernel libraries this part launches (built on first use)
 
     def required_libraries(self, runtime: Runtime) -> tuple[str, ...]:
+        """What this part launches in this precision (the 32-bit path needs no tensor-core kernels)."""
+        if runtime.dtype == torch.float32:
+            return tuple(n for n in self.kernel_libraries if n not in BF16_ONLY_LIBRARIES)
         return self.kernel_libraries
 
 

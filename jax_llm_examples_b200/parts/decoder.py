@@ -96,7 +96,7 @@ class DecoderModel:
                          tuple(states[s] for s in range(len(states))))
 
     def required_libraries(self) -> tuple[str, ...]:
-        libs = ["elementwise", "gemm_simt"]
+        libs = ["elementwise", "gemm_simt"] + ([] if self.runtime.dtype == torch.float32 else ["gemm_stream"])
         for b in self.blocks:
             libs.extend(b.required_libraries(self.runtime))
         libs.extend(self.final_norm.required_libraries(self.runtime))
@@ -138,4 +138,4 @@ class DecoderModel:
         if ctx.n_logit_rows == 0:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=rt.device)
         h, _ = self.final_norm.forward(ctx, x, delta, out_dtype=rt.dtype, row_index=ctx.logit_rows)
-        return linear(h, self.lm_head, torch.float32)
+        return linear(ctx, h, self.lm_head, torch.float32)

@@ -13,7 +13,7 @@ class DenseSwiGLU(FeedForward):
     """down(silu(h gate) * (h up)) (llama4/llama4_jax/model.py:1142-1153).
     ``w_gate_up``: [2F, D], gate rows then up rows; ``w_down``: [D, F]."""
 
-    kernel_libraries = ("elementwise", "gemm_simt")
+    kernel_libraries = ("elementwise", "gemm_simt", "gemm_stream")
 
     def __init__(self, w_gate_up: torch.Tensor, w_down: torch.Tensor):
         if w_gate_up.shape[0] != 2 * w_down.shape[1] or w_gate_up.shape[1] != w_down.shape[0]:
@@ -21,10 +21,10 @@ class DenseSwiGLU(FeedForward):
         self.w_gate_up, self.w_down = w_gate_up, w_down
 
     def forward(self, ctx: StepContext, h, h32=None):
-        gu = linear(h, self.w_gate_up, ctx.runtime.dtype)
+        gu = linear(ctx, h, self.w_gate_up, ctx.runtime.dtype)
         act = torch.empty((gu.shape[0], gu.shape[1] // 2), dtype=gu.dtype, device=gu.device)
         K.silu_mul(gu, act)
-        return linear(act, self.w_down, torch.float32)
+        return linear(ctx, act, self.w_down, torch.float32)
 
 
 class RoutedExperts(FeedForward):
@@ -36,7 +36,7 @@ class RoutedExperts(FeedForward):
     shared expert's output on the unscaled h is added (model.py:1111, 1137-1139).
     ``w_router``: [E, D]; ``we_gate_up``: [E, 2F, D] (gate rows then up rows); ``we_down``: [E, D, F]."""
 
-    kernel_libraries = ("moe", "elementwise", "gemm_simt")
+    kernel_libraries = ("moe", "elementwise", "gemm_simt", "gemm_stream")
     needs_f32_input = True
 
     def __init__(self, w_router: torch.Tensor, we_gate_up: torch.Tensor, we_down: torch.Tensor, top_k: int,
@@ -72,10 +72,10 @@ class RoutedExperts(FeedForward):
             ctx.scratch["record_routing"].append(topk_idx)
         a_sorted = torch.empty((n * k, D), dtype=rt.dtype, device=h.device)
         K.permute_scale(h32, sorted_pair, topk_w, a_sorted, k)
-        gu = grouped_linear(a_sorted, self.we_gate_up, offsets, rt.dtype)
+        gu = grouped_linear(ctx, a_sorted, self.we_gate_up, offsets, rt.dtype)
         act = torch.empty((n * k, gu.shape[1] // 2), dtype=rt.dtype, device=h.device)
         K.silu_mul(gu, act)
-        y = grouped_linear(act, self.we_down, offsets, torch.float32)
+        y = grouped_linear(ctx, act, self.we_down, offsets, torch.float32)
         shared = self.shared.forward(ctx, h, None) if self.shared is not None else None
         delta = torch.empty((n, D), dtype=torch.float32, device=h.device)
         K.moe_combine(y, shared, sorted_pos, delta, k)

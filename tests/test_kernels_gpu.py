@@ -346,3 +346,69 @@ def test_sampling_argmax_and_draws():
                torch.arange(n, device=DEV, dtype=torch.int64), torch.zeros(n, device=DEV, dtype=torch.int64), seed=5)
     freq = torch.bincount(o.long(), minlength=3).float() / n
     assert (freq - torch.softmax(small[0], -1)).abs().max() < 0.03
+
+
+@pytest.mark.parametrize("Hq, Hkv, dh, page, chunk, window, temp", [
+    (40, 8, 128, 64, 0, 0, False), (6, 2, 64, 16, 512, 0, False), (16, 1, 128, 32, 0, 300, True), (4, 4, 64, 128, 0, 0, True),
+    (10, 2, 128, 16, 1024, 0, False)])
+def test_attention_decode_mma(Hq, Hkv, dh, page, chunk, window, temp):
+    lens = [1500, 257, 1, 256, 1024, 63]
+    q, pages, bt, req, pos, ks, vs = _paged_case(torch.bfloat16, Hq, Hkv, dh, page, lens, [1] * len(lens))
+    out, st = torch.empty_like(q), status()
+    attn_scale, floor_scale = (0.1, 256.0) if temp else (0.0, 1.0)
+    api = K()
+    assert api.attention_mma_supported(q.dtype, Hq, Hkv, dh, True)
+    splits = api.attention_decode_splits(max(lens), chunk, window)
+    n = q.shape[0] * Hq * splits
+    part_o, part_ml = torch.empty(n * dh, device=DEV), torch.empty(n * 2, device=DEV)
+    api.attention_decode(q, pages, bt, req, pos, out, dh ** -0.5, chunk, window, attn_scale, floor_scale, part_o, part_ml, splits, st)
+    assert int(st) == 0
+    for r in range(len(lens)):
+        ref = _attention_ref(q[r:r + 1], ks[r], vs[r], pos[r:r + 1].long(), chunk, window, dh ** -0.5, attn_scale, floor_scale)
+        close(out[r:r + 1], ref, 1.5e-2)
+
+
+@pytest.mark.parametrize("Hq, Hkv, dh, page, chunk, window, temp", [
+    (40, 8, 128, 64, 0, 0, False), (6, 2, 64, 16, 100, 0, False), (8, 1, 128, 32, 0, 70, True), (4, 4, 64, 128, 0, 0, True),
+    (10, 2, 128, 16, 64, 0, False)])
+def test_attention_prefill_mma(Hq, Hkv, dh, page, chunk, window, temp):
+    lens, q_lens = [300, 37, 1, 129, 64], [300, 5, 1, 17, 33]
+    q, pages, bt, req, pos, ks, vs = _paged_case(torch.bfloat16, Hq, Hkv, dh, page, lens, q_lens)
+    out, st = torch.full_like(q, float("nan")), status()
+    attn_scale, floor_scale = (0.1, 64.0) if temp else (0.0, 1.0)
+    api = K()
+    assert api.attention_mma_supported(q.dtype, Hq, Hkv, dh, False)
+    tiles, at = [], 0
+    for n in q_lens:
+        tiles += [(at + t, min(16, n - t)) for t in range(0, n, 16)]
+        at += n
+    tl = torch.tensor(tiles, device=DEV, dtype=torch.int32)
+    api.attention_prefill(q, pages, bt, req, pos, out, tl, len(tiles), dh ** -0.5, chunk, window, attn_scale, floor_scale, st)
+    assert int(st) == 0
+    at = 0
+    for r, n in enumerate(q_lens):
+        ref = _attention_ref(q[at:at + n], ks[r], vs[r], pos[at:at + n].long(), chunk, window, dh ** -0.5, attn_scale, floor_scale)
+        close(out[at:at + n], ref, 1.5e-2)
+        at += n
+
+
+def test_mma_attention_finds_one_far_key():
+    Hq, Hkv, dh, page = 10, 2, 128, 64
+    api = K()
+    for far in (0, 63, 64, 255, 256, 257, 1000, 1999):
+        q, pages, bt, req, pos, ks, vs = _paged_case(torch.bfloat16, Hq, Hkv, dh, page, [2000], [1], seed=far)
+        pg, slot = int(bt[0, far // page]), far % page
+        pages[pg, 0, :, slot] = 0
+        pages[pg, 0, :, slot, 0] = 40.0
+        q[:] = 0
+        q[..., 0] = 40.0
+        want = pages[pg, 1, :, slot].float().repeat_interleave(Hq // Hkv, 0)
+        out, st = torch.empty_like(q), status()
+        splits = api.attention_decode_splits(2000, 0, 0)
+        part_o, part_ml = torch.empty(Hq * splits * dh, device=DEV), torch.empty(Hq * splits * 2, device=DEV)
+        api.attention_decode(q, pages, bt, req, pos, out, dh ** -0.5, 0, 0, 0.0, 1.0, part_o, part_ml, splits, st)
+        close(out[0], want, 1e-2)
+        out2 = torch.empty_like(q)
+        api.attention_prefill(q, pages, bt, req, pos, out2, torch.tensor([[0, 1]], device=DEV, dtype=torch.int32), 1,
+                              dh ** -0.5, 0, 0, 0.0, 1.0, st)
+        close(out2[0], want, 1e-2)
