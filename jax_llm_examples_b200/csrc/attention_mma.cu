@@ -22,7 +22,7 @@
 #include "common.cuh"
 
 #define KT 64            // keys per tile
-#define SPLIT 256        // keys per decode split (4 tiles), aligned to absolute positions
+#define SPLIT 128        // keys per decode split (2 tiles, 64 KB of shared memory: three blocks per SM), aligned to absolute positions
 #define NEG_BIG (-1.0e30f)
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -84,35 +84,40 @@ __device__ __forceinline__ float temperature(int p, float attn_scale, float floo
 }
 
 // Loads keys [key0, key0 + KT) of request r, KV head hk, into ks / vs (each [KT][DH], swizzled).
-// Keys outside [lo, hi] or without a page become zeros.
+// Keys outside [lo, hi] or without a page become zeros.  A pair of threads takes one key row (one
+// block-table lookup per row and thread), half of its 16-byte chunks each.
 template <int DH>
 __device__ __forceinline__ void load_kv_tile(const AttnParams& P, int r, int hk, int key0, int lo, int hi, bf16* ks, bf16* vs,
                                              int NT) {
   constexpr int CH = DH / 8;              // 16-byte chunks per row
-  constexpr int TOTAL = KT * CH;          // chunks per tile and tensor
   const size_t v_off = (size_t)P.Hkv * P.page_size * DH;
-  for (int idx = threadIdx.x; idx < TOTAL; idx += NT) {
-    const int j = idx / CH, c = idx % CH;
+  const int half = threadIdx.x & 1;
+  for (int j = threadIdx.x >> 1; j < KT; j += NT >> 1) {
     const int pos = key0 + j;
     bool valid = pos >= lo && pos <= hi;
     const bf16* src = P.pages;
     if (valid) {
-      const int page = P.block_table[(size_t)r * P.bt_stride + pos / P.page_size];
+      const int pi = pos / P.page_size;
+      const int page = P.block_table[(size_t)r * P.bt_stride + pi];
       if (page < 0 || page >= P.num_pages) {
         atomicOr(P.status, JLX_STATUS_BAD_PAGE);
         valid = false;
       } else {
-        src = P.pages + (size_t)page * 2 * v_off + ((size_t)hk * P.page_size + pos % P.page_size) * DH + c * 8;
+        src = P.pages + (size_t)page * 2 * v_off + ((size_t)hk * P.page_size + (pos - pi * P.page_size)) * DH;
       }
     }
-    const int sw = (j * CH + (c ^ (j & 7))) * 8;
-    cp_async16(smem_u32(ks + sw), src, valid);
-    cp_async16(smem_u32(vs + sw), valid ? src + v_off : src, valid);
+#pragma unroll
+    for (int i = 0; i < CH / 2; ++i) {
+      const int c = half * (CH / 2) + i;
+      const int sw = (j * CH + (c ^ (j & 7))) * 8;
+      cp_async16(smem_u32(ks + sw), valid ? src + c * 8 : src, valid);
+      cp_async16(smem_u32(vs + sw), valid ? src + v_off + c * 8 : src, valid);
+    }
   }
 }
 
 // ------------------------------------------------------------------------------------ decode
-// grid (max_splits, Hkv, R); 128 threads.  Rows of the score tile = the G query heads (G <= 16).
+// grid (max_splits, Hkv, R); 128 threads, TILES = 2 key tiles per block.  Rows of the score tile = the G query heads (G <= 16).
 // Warp w takes keys [16 w, 16 w + 16) of every 64-key tile; the four warps' results are merged in
 // shared memory and written as one partial (unnormalised output, max, sum) per (token, head, split).
 template <int DH>
@@ -130,7 +135,7 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttnParams 
   const int key_begin = (lo / SPLIT + split) * SPLIT;
   if (key_begin > p) return;
 
-  // all four tiles of the split are requested at once; they are consumed as they land
+  // all tiles of the split are requested at once; they are consumed as they land
 #pragma unroll
   for (int t = 0; t < TILES; ++t) {
     load_kv_tile<DH>(P, r, hk, key_begin + t * KT, lo, p, ks + t * KT * DH, vs + t * KT * DH, 128);
@@ -160,8 +165,6 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttnParams 
 #pragma unroll
   for (int t = 0; t < TILES; ++t) {
     if (t == 0) cp_async_wait<TILES - 1>();
-    else if (t == 1) cp_async_wait<TILES - 2>();
-    else if (t == 2) cp_async_wait<TILES - 3>();
     else cp_async_wait<0>();
     __syncthreads();
     const int tile_key = key_begin + t * KT;

@@ -30,14 +30,22 @@ JLX_API int jlx_embed(const int* ids, const void* table, int table_dtype, float*
 }
 
 // Row n (source row r = row_index ? row_index[n] : n):
-//   s = x[r] + delta[r]            (delta optional; written back to x[r] unless rows are gathered)
-//   out[n] = gamma * s / sqrt(mean(s^2) + eps)      (gamma optional: weightless norm)
+//   s = x[r] + sum over splits of delta[z][r]   (delta optional; split-K partials are added in ascending
+//                                                 order; s is written back to x[r] unless rows are gathered)
+//   out[n] = gamma * s / sqrt(mean(s^2) + eps)   (gamma optional: weightless norm)
 // `out` in the activation type and/or `out32` in 32-bit (for the router, which wants unrounded input).
+// With w_router the same block also routes the token (llama4/llama4_jax/model.py:958-972): scores =
+// normed row . w_router[e] in 32-bit, top-k of the raw scores (lower index wins ties), weight = sigmoid.
+#define ROUTER_MAX_E 256
 template <typename TO>
-__global__ void add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta,
-                                   const float* __restrict__ gamma, float eps, TO* __restrict__ out,
-                                   float* __restrict__ out32, const int* __restrict__ row_index, int D) {
+__global__ void __launch_bounds__(256)
+add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, int delta_splits, long long delta_stride,
+                   const float* __restrict__ gamma, float eps, TO* __restrict__ out, float* __restrict__ out32,
+                   const int* __restrict__ row_index, int D, int row_in_smem, const float* __restrict__ w_router, int E,
+                   int k, int* __restrict__ topk_idx, float* __restrict__ topk_w) {
+  extern __shared__ float rowbuf[];  // [D] when row_in_smem
   __shared__ float scratch[33];
+  __shared__ float scores[ROUTER_MAX_E];
   const int n = blockIdx.x;
   const size_t r = row_index ? (size_t)row_index[n] : (size_t)n;
   float* xr = x + r * D;
@@ -46,53 +54,115 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const float* __restric
   for (int d = threadIdx.x; d < D; d += blockDim.x) {
     float s = xr[d];
     if (dr) {
-      s += dr[d];
+      for (int z = 0; z < delta_splits; ++z) s += dr[(size_t)z * delta_stride + d];
       if (!row_index) xr[d] = s;
     }
+    if (row_in_smem) rowbuf[d] = s;
     ss += s * s;
   }
   ss = block_sum(ss, scratch);
   const float rms = sqrtf(ss / (float)D + eps);
   for (int d = threadIdx.x; d < D; d += blockDim.x) {
-    float s = xr[d];
-    if (dr && row_index) s += dr[d];
-    float v = (gamma ? gamma[d] * s : s) / rms;
+    float s;
+    if (row_in_smem) {
+      s = rowbuf[d];
+    } else {
+      s = xr[d];
+      if (dr && row_index)
+        for (int z = 0; z < delta_splits; ++z) s += dr[(size_t)z * delta_stride + d];
+    }
+    const float v = (gamma ? gamma[d] * s : s) / rms;
     if (out) out[(size_t)n * D + d] = from_f32<TO>(v);
     if (out32) out32[(size_t)n * D + d] = v;
+    if (row_in_smem) rowbuf[d] = v;
+  }
+  if (!w_router) return;
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  for (int e = warp; e < E; e += nwarp) {
+    const float* wr = w_router + (size_t)e * D;
+    float s = 0.f;
+    for (int d = lane; d < D; d += 32) s = fmaf(rowbuf[d], wr[d], s);
+    s = warp_sum(s);
+    if (lane == 0) scores[e] = s;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int j = 0; j < k; ++j) {
+      int best = -1;
+      float bv = 0.f;
+      for (int e = 0; e < E; ++e) {
+        const float v = scores[e];
+        if (isnan(v)) continue;
+        if (best < 0 || v > bv) {
+          best = e;
+          bv = v;
+        }
+      }
+      if (best < 0) best = j;
+      topk_idx[(size_t)n * k + j] = best;
+      topk_w[(size_t)n * k + j] = 1.f / (1.f + expf(-bv));
+      scores[best] = NAN;
+    }
   }
 }
 
-JLX_API int jlx_add_rmsnorm(float* x, const float* delta, const float* gamma, float eps, void* out, int out_dtype,
-                            float* out32, const int* row_index, int N, int D, cudaStream_t stream) {
+JLX_API int jlx_add_rmsnorm(float* x, const float* delta, int delta_splits, long long delta_stride, const float* gamma,
+                            float eps, void* out, int out_dtype, float* out32, const int* row_index, int N, int D,
+                            const float* w_router, int E, int k, int* topk_idx, float* topk_w, cudaStream_t stream) {
   JLX_REQUIRE(N >= 0 && D > 0, "add_rmsnorm: bad sizes N=%d D=%d", N, D);
   JLX_REQUIRE(eps > 0.f, "add_rmsnorm: eps must be positive");
+  JLX_REQUIRE(!delta || delta_splits >= 1, "add_rmsnorm: bad split count");
   if (N == 0) return 0;
-  const int threads = D >= 1024 ? 256 : 128;
-  JLX_DISPATCH_DTYPE(out_dtype, TO,
-                     (add_rmsnorm_kernel<TO><<<N, threads, 0, stream>>>(x, delta, gamma, eps, (TO*)out, out32, row_index, D)));
+  const int row_in_smem = (size_t)D * 4 <= 64 * 1024;
+  if (w_router) {
+    JLX_REQUIRE(E >= 1 && E <= ROUTER_MAX_E, "router: %d experts; supported 1..%d", E, ROUTER_MAX_E);
+    JLX_REQUIRE(k >= 1 && k <= E && k <= 16, "router: top-%d of %d experts; supported k in 1..min(E, 16)", k, E);
+    JLX_REQUIRE(row_in_smem, "router fused with the norm needs width <= 16384 (got %d)", D);
+    JLX_REQUIRE(topk_idx && topk_w, "router: outputs missing");
+  }
+  const size_t smem = row_in_smem ? (size_t)D * 4 : 0;
+  JLX_DISPATCH_DTYPE(out_dtype, TO, {
+    if (smem > 48 * 1024) {
+      static bool cfg = false;
+      if (!cfg) { JLX_CUDA(cudaFuncSetAttribute(add_rmsnorm_kernel<TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024)); cfg = true; }
+    }
+    add_rmsnorm_kernel<TO><<<N, 256, smem, stream>>>(x, delta, delta_splits, delta_stride, gamma, eps, (TO*)out, out32,
+                                                     row_index, D, row_in_smem, w_router, E, k, topk_idx, topk_w);
+  });
   JLX_LAUNCH_CHECK("add_rmsnorm");
   return 0;
 }
 
-// out[i, f] = silu(gu[i, f]) * gu[i, F + f]                       (model.py:1146-1151)
-template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, const int* __restrict__ n_rows_dev,
-                                int rows, int F) {
+// out[i, f] = silu(gate) * up of row i (llama4/llama4_jax/model.py:1146-1151).  The input row holds 2F values,
+// either [gate(0..F), up(0..F)] or, interleaved, blocks of [16 gate, 16 up]; it may come as `splits` float32
+// split-K partials that are added first.
+template <typename TI, typename TO>
+__global__ void silu_mul_kernel(const TI* __restrict__ gu, int splits, long long split_stride, TO* __restrict__ out,
+                                int F, int interleaved) {
   const int i = blockIdx.x;
-  if (n_rows_dev && i >= *n_rows_dev) return;
-  const T* g = gu + (size_t)i * 2 * F;
+  const TI* g = gu + (size_t)i * 2 * F;
   for (int f = threadIdx.x; f < F; f += blockDim.x) {
-    float a = to_f32<T>(g[f]), b = to_f32<T>(g[F + f]);
-    float s = a / (1.f + expf(-a));
-    out[(size_t)i * F + f] = from_f32<T>(s * b);
+    const int gi = interleaved ? ((f >> 4) << 5) + (f & 15) : f;
+    const int ui = interleaved ? gi + 16 : F + f;
+    float a = 0.f, b = 0.f;
+    for (int z = 0; z < splits; ++z) {
+      a += to_f32<TI>(g[(size_t)z * split_stride + gi]);
+      b += to_f32<TI>(g[(size_t)z * split_stride + ui]);
+    }
+    const float s = a / (1.f + expf(-a));
+    out[(size_t)i * F + f] = from_f32<TO>(s * b);
   }
 }
 
-JLX_API int jlx_silu_mul(const void* gu, void* out, int dtype, const int* n_rows_dev, int rows, int F,
-                         cudaStream_t stream) {
-  JLX_REQUIRE(rows >= 0 && F > 0, "silu_mul: bad sizes rows=%d F=%d", rows, F);
+JLX_API int jlx_silu_mul(const void* gu, int in_dtype, int splits, long long split_stride, void* out, int out_dtype,
+                         int rows, int F, int interleaved, cudaStream_t stream) {
+  JLX_REQUIRE(rows >= 0 && F > 0 && splits >= 1, "silu_mul: bad sizes rows=%d F=%d splits=%d", rows, F, splits);
+  JLX_REQUIRE(!interleaved || F % 16 == 0, "silu_mul: the interleaved layout needs a width that is a multiple of 16");
+  JLX_REQUIRE(splits == 1 || in_dtype == JLX_F32, "silu_mul: split-K partials are float32");
   if (rows == 0) return 0;
-  JLX_DISPATCH_DTYPE(dtype, T, (silu_mul_kernel<T><<<rows, 256, 0, stream>>>((const T*)gu, (T*)out, n_rows_dev, rows, F)));
+  JLX_DISPATCH_DTYPE(in_dtype, TI, JLX_DISPATCH_DTYPE(out_dtype, TO,
+      (silu_mul_kernel<TI, TO><<<rows, 256, 0, stream>>>((const TI*)gu, splits, split_stride, (TO*)out, F, interleaved))));
   JLX_LAUNCH_CHECK("silu_mul");
   return 0;
 }

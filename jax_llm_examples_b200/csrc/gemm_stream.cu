@@ -117,6 +117,7 @@ struct StreamArgs {
   int E;
   void* out;             // [rows, N] (bf16 or f32), or partials [splits][rows][N] f32 when splits > 1
   int out_is_f32;
+  int silu;              // 1: rows come in blocks of [16 gate, 16 up]; out[m, j] = silu(gate_j) * up_j, [rows, N / 2]
   int splits;
   int k_per_split;       // multiple of BK
   int* status;
@@ -240,8 +241,17 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
           const int m = row_lo + c0 + j;
-          if (m < row_hi && n_ok) {
-            const float v = __uint_as_float(r[j]);
+          const float v = __uint_as_float(r[j]);
+          if (args.silu) {
+            // lanes 0..15 hold gate rows, lanes 16..31 the matching up rows of the same 32-row block
+            const float up = __shfl_down_sync(0xffffffffu, v, 16);
+            if (lane < 16 && m < row_hi && n_ok) {
+              const float act = v / (1.f + __expf(-v)) * up;
+              const size_t col = (size_t)((n0 + quarter * 32) >> 1) + lane;
+              if (args.out_is_f32) ((float*)args.out)[(size_t)m * (args.N >> 1) + col] = act;
+              else ((bf16*)args.out)[(size_t)m * (args.N >> 1) + col] = __float2bfloat16_rn(act);
+            }
+          } else if (m < row_hi && n_ok) {
             if (args.out_is_f32 || args.splits > 1)
               ((float*)args.out)[split_off + (size_t)m * args.N + n] = v;
             else
@@ -330,16 +340,26 @@ static int pick_bt(int rows_hint) {
 JLX_API int jlx_gemm_stream_supported(int K) { return K % 8 == 0 && K >= 8; }
 
 // rows: token rows of A (grouped: an upper bound of offsets[E]); rows_hint: typical rows per group
-// (chooses the token-tile width).  scratch: float32 [splits * rows * N] when splits > 1.
+// (chooses the token-tile width).
+// mode 0: out[rows, N] (bfloat16 or float32); with splits > 1 the partials go to `scratch` (float32
+//         [splits * rows * N]) and a second kernel adds them in ascending order.
+// mode 1: out receives the float32 partials themselves, [splits][rows][N], for a consumer that adds them.
+// mode 2: fused SwiGLU epilogue: weight rows are interleaved in blocks of [16 gate, 16 up], out is
+//         [rows, N / 2] = silu(gate) * up; no split-K.
+// Returns the split count used through *splits_used (it may be lower than asked).
 JLX_API int jlx_gemm_stream(const void* A, const void* W, void* out, int out_is_f32, int rows, int N, int K,
-                            const int* offsets, int E, int rows_hint, int splits, float* scratch, int* status,
-                            cudaStream_t stream) {
+                            const int* offsets, int E, int rows_hint, int splits, float* scratch, int mode,
+                            int* splits_used, int* status, cudaStream_t stream) {
   JLX_REQUIRE(rows >= 0 && N > 0 && K > 0, "gemm_stream: bad sizes rows=%d N=%d K=%d", rows, N, K);
   JLX_REQUIRE(K % 8 == 0, "gemm_stream: K = %d is no multiple of 8 (TMA needs 16-byte row strides); use the SIMT product", K);
   JLX_REQUIRE(((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0, "gemm_stream: operands must be 16-byte aligned");
   JLX_REQUIRE(!offsets || E > 0, "gemm_stream: a grouped product needs a group count");
-  JLX_REQUIRE(splits >= 1 && (splits == 1 || scratch), "gemm_stream: split-K needs scratch memory");
+  JLX_REQUIRE(mode >= 0 && mode <= 2, "gemm_stream: unknown mode %d", mode);
+  JLX_REQUIRE(splits >= 1 && (splits == 1 || mode == 1 || scratch), "gemm_stream: split-K needs scratch memory");
   JLX_REQUIRE(splits == 1 || !offsets, "gemm_stream: split-K is for ungrouped products");
+  JLX_REQUIRE(mode != 2 || (splits == 1 && N % 32 == 0), "gemm_stream: the SwiGLU epilogue needs N %% 32 == 0 and no split-K");
+  JLX_REQUIRE(mode != 1 || out_is_f32, "gemm_stream: partials are float32");
+  if (splits_used) *splits_used = 1;
   if (rows == 0) return 0;
   const int groups = offsets ? E : 1;
   const int bt = pick_bt(rows_hint > 0 ? rows_hint : rows);
@@ -351,10 +371,11 @@ JLX_API int jlx_gemm_stream(const void* A, const void* W, void* out, int out_is_
     kps = ((K + splits - 1) / splits + BK - 1) / BK * BK;
     splits = (K + kps - 1) / kps;
   }
+  if (splits_used) *splits_used = splits;
   StreamArgs a;
   a.N = N; a.K = K; a.rows = rows; a.offsets = offsets; a.E = E;
-  a.out = splits > 1 ? (void*)scratch : out;
-  a.out_is_f32 = out_is_f32; a.splits = splits; a.k_per_split = kps; a.status = status;
+  a.out = (splits > 1 && mode == 0) ? (void*)scratch : out;
+  a.out_is_f32 = out_is_f32; a.silu = mode == 2; a.splits = splits; a.k_per_split = kps; a.status = status;
   const int row_tiles = (rows + bt - 1) / bt + (offsets ? E : 0);
   JLX_REQUIRE(row_tiles <= 65535, "gemm_stream: too many row tiles");
   int rc;
@@ -367,7 +388,7 @@ JLX_API int jlx_gemm_stream(const void* A, const void* W, void* out, int out_is_
     default: rc = launch<256, 4>(mw, ma, a, row_tiles, stream); break;
   }
   if (rc) return rc;
-  if (splits > 1) {
+  if (splits > 1 && mode == 0) {
     const long long total = (long long)rows * N;
     const int blocks = (int)((total + 255) / 256 < 4096 ? (total + 255) / 256 : 4096);
     if (out_is_f32)

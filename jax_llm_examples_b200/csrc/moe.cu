@@ -135,22 +135,26 @@ JLX_API int jlx_permute_scale(const float* h, const int* sorted_pair, const floa
   return 0;
 }
 
-// delta[n, :] = shared[n, :] + sum_j y_sorted[sorted_pos[n * k + j], :]   (j ascending: fixed order)
-__global__ void moe_combine_kernel(const float* __restrict__ y_sorted, const float* __restrict__ shared,
-                                   const int* __restrict__ sorted_pos, float* __restrict__ delta, int D, int k) {
+// delta[n, :] = sum over splits of shared[z][n, :] + sum_j y_sorted[sorted_pos[n * k + j], :]
+// (splits and j ascending: a fixed order)
+__global__ void moe_combine_kernel(const float* __restrict__ y_sorted, const float* __restrict__ shared, int splits,
+                                   long long split_stride, const int* __restrict__ sorted_pos, float* __restrict__ delta,
+                                   int D, int k) {
   const int n = blockIdx.x;
   for (int d = threadIdx.x; d < D; d += blockDim.x) {
-    float s = shared ? shared[(size_t)n * D + d] : 0.f;
+    float s = 0.f;
+    if (shared)
+      for (int z = 0; z < splits; ++z) s += shared[(size_t)z * split_stride + (size_t)n * D + d];
     for (int j = 0; j < k; ++j) s += y_sorted[(size_t)sorted_pos[(size_t)n * k + j] * D + d];
     delta[(size_t)n * D + d] = s;
   }
 }
 
-JLX_API int jlx_moe_combine(const float* y_sorted, const float* shared, const int* sorted_pos, float* delta, int N,
-                            int D, int k, cudaStream_t stream) {
-  JLX_REQUIRE(N >= 0 && D > 0 && k >= 1, "moe_combine: bad sizes");
+JLX_API int jlx_moe_combine(const float* y_sorted, const float* shared, int splits, long long split_stride,
+                            const int* sorted_pos, float* delta, int N, int D, int k, cudaStream_t stream) {
+  JLX_REQUIRE(N >= 0 && D > 0 && k >= 1 && splits >= 1, "moe_combine: bad sizes");
   if (N == 0) return 0;
-  moe_combine_kernel<<<N, 256, 0, stream>>>(y_sorted, shared, sorted_pos, delta, D, k);
+  moe_combine_kernel<<<N, 256, 0, stream>>>(y_sorted, shared, splits, split_stride, sorted_pos, delta, D, k);
   JLX_LAUNCH_CHECK("moe_combine");
   return 0;
 }

@@ -9,18 +9,26 @@
 // Cache layout of one layer: pages[page][0 = K, 1 = V][kv head][slot in page][dh].
 #include "common.cuh"
 
-template <typename T>
-__global__ void rope_kv_store_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict__ pages,
-                                     const int* __restrict__ block_table, int bt_stride,
-                                     const int* __restrict__ req_of_token, const int* __restrict__ positions,
-                                     const float* __restrict__ inv_freq, int l2norm, float eps, int Hq, int Hkv,
-                                     int dh, int page_size, int num_pages, int store_kv, int* status) {
+// TI: element type of the projected rows (the activation type, or float32 split-K partials that are
+// added first); T: element type of q_out and of the cache.
+template <typename TI, typename T>
+__global__ void __launch_bounds__(256)
+rope_kv_store_kernel(const TI* __restrict__ qkv, int splits, long long split_stride, T* __restrict__ q_out,
+                     T* __restrict__ pages, const int* __restrict__ block_table, int bt_stride,
+                     const int* __restrict__ req_of_token, const int* __restrict__ positions,
+                     const float* __restrict__ inv_freq, int l2norm, float eps, int Hq, int Hkv, int dh, int page_size,
+                     int num_pages, int store_kv, int* status) {
+  extern __shared__ float sc[];  // [dh / 2][2]: sine and cosine of this token's angles
   const int n = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
   const int pos = positions[n];
   const int heads = Hq + 2 * Hkv;
   const int half = dh >> 1;
-  const T* row = qkv + (size_t)n * heads * dh;
+  const TI* row = qkv + (size_t)n * heads * dh;
+  if (inv_freq) {
+    for (int j = threadIdx.x; j < half; j += blockDim.x) sincosf((float)pos * inv_freq[j], &sc[2 * j], &sc[2 * j + 1]);
+    __syncthreads();
+  }
 
   T* kdst = nullptr;
   T* vdst = nullptr;
@@ -37,11 +45,15 @@ __global__ void rope_kv_store_kernel(const T* __restrict__ qkv, T* __restrict__ 
   }
 
   for (int h = warp; h < heads; h += nwarp) {
-    const T* src = row + (size_t)h * dh;
-    if (h >= Hq + Hkv) {  // value head: copy
+    const TI* src = row + (size_t)h * dh;
+    if (h >= Hq + Hkv) {  // value head: copy (sum of the partials)
       if (vdst) {
         T* dst = vdst + (size_t)(h - Hq - Hkv) * page_size * dh;
-        for (int d = lane; d < dh; d += 32) dst[d] = src[d];
+        for (int d = lane; d < dh; d += 32) {
+          float v = 0.f;
+          for (int z = 0; z < splits; ++z) v += to_f32<TI>(src[(size_t)z * split_stride + d]);
+          dst[d] = from_f32<T>(v);
+        }
       }
       continue;
     }
@@ -49,11 +61,14 @@ __global__ void rope_kv_store_kernel(const T* __restrict__ qkv, T* __restrict__ 
     // pass 1: rotate, accumulate the sum of squares
     float ss = 0.f;
     for (int j = lane; j < half; j += 32) {
-      float a = to_f32<T>(src[2 * j]), b = to_f32<T>(src[2 * j + 1]);
+      float a = 0.f, b = 0.f;
+      for (int z = 0; z < splits; ++z) {
+        a += to_f32<TI>(src[(size_t)z * split_stride + 2 * j]);
+        b += to_f32<TI>(src[(size_t)z * split_stride + 2 * j + 1]);
+      }
       if (inv_freq) {
-        float s, c;
-        sincosf((float)pos * inv_freq[j], &s, &c);
-        float ra = a * c - b * s, rb = b * c + a * s;
+        const float s = sc[2 * j], c = sc[2 * j + 1];
+        const float ra = a * c - b * s, rb = b * c + a * s;
         a = ra;
         b = rb;
       }
@@ -65,13 +80,16 @@ __global__ void rope_kv_store_kernel(const T* __restrict__ qkv, T* __restrict__ 
       inv = 1.f / sqrtf(ss / (float)dh + eps);
     }
     if (!dst) continue;
-    // pass 2: recompute the rotation (cheaper than keeping dh values live for any dh) and write
+    // pass 2: the same values again (cheaper than keeping dh of them live for any dh), scaled and written
     for (int j = lane; j < half; j += 32) {
-      float a = to_f32<T>(src[2 * j]), b = to_f32<T>(src[2 * j + 1]);
+      float a = 0.f, b = 0.f;
+      for (int z = 0; z < splits; ++z) {
+        a += to_f32<TI>(src[(size_t)z * split_stride + 2 * j]);
+        b += to_f32<TI>(src[(size_t)z * split_stride + 2 * j + 1]);
+      }
       if (inv_freq) {
-        float s, c;
-        sincosf((float)pos * inv_freq[j], &s, &c);
-        float ra = a * c - b * s, rb = b * c + a * s;
+        const float s = sc[2 * j], c = sc[2 * j + 1];
+        const float ra = a * c - b * s, rb = b * c + a * s;
         a = ra;
         b = rb;
       }
@@ -81,18 +99,21 @@ __global__ void rope_kv_store_kernel(const T* __restrict__ qkv, T* __restrict__ 
   }
 }
 
-JLX_API int jlx_rope_kv_store(const void* qkv, void* q_out, void* pages, int dtype, const int* block_table,
-                              int bt_stride, const int* req_of_token, const int* positions, const float* inv_freq,
-                              int l2norm, float eps, int N, int Hq, int Hkv, int dh, int page_size, int num_pages,
-                              int store_kv, int* status, cudaStream_t stream) {
+JLX_API int jlx_rope_kv_store(const void* qkv, int in_dtype, int splits, long long split_stride, void* q_out, void* pages,
+                              int dtype, const int* block_table, int bt_stride, const int* req_of_token,
+                              const int* positions, const float* inv_freq, int l2norm, float eps, int N, int Hq, int Hkv,
+                              int dh, int page_size, int num_pages, int store_kv, int* status, cudaStream_t stream) {
   JLX_REQUIRE(N >= 0 && Hq > 0 && Hkv >= 0 && dh > 0, "rope_kv_store: bad sizes N=%d Hq=%d Hkv=%d dh=%d", N, Hq, Hkv, dh);
   JLX_REQUIRE(dh % 2 == 0, "rope_kv_store: head size %d must be even (rotary pairs)", dh);
+  JLX_REQUIRE(dh <= 8192, "rope_kv_store: head size %d is above the supported maximum 8192", dh);
   JLX_REQUIRE(!store_kv || (page_size > 0 && num_pages > 0 && bt_stride > 0), "rope_kv_store: bad cache sizes");
+  JLX_REQUIRE(splits >= 1 && (splits == 1 || in_dtype == JLX_F32), "rope_kv_store: split-K partials are float32");
   if (N == 0) return 0;
-  JLX_DISPATCH_DTYPE(dtype, T,
-                     (rope_kv_store_kernel<T><<<N, 128, 0, stream>>>(
-                         (const T*)qkv, (T*)q_out, (T*)pages, block_table, bt_stride, req_of_token, positions, inv_freq,
-                         l2norm, eps, Hq, Hkv, dh, page_size, num_pages, store_kv, status)));
+  const size_t smem = (size_t)dh * sizeof(float);
+  JLX_DISPATCH_DTYPE(in_dtype, TI, JLX_DISPATCH_DTYPE(dtype, T,
+                     (rope_kv_store_kernel<TI, T><<<N, 256, smem, stream>>>(
+                         (const TI*)qkv, splits, split_stride, (T*)q_out, (T*)pages, block_table, bt_stride, req_of_token,
+                         positions, inv_freq, l2norm, eps, Hq, Hkv, dh, page_size, num_pages, store_kv, status))));
   JLX_LAUNCH_CHECK("rope_kv_store");
   return 0;
 }

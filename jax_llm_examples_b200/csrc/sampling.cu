@@ -169,6 +169,56 @@ sample_kernel(const float* __restrict__ logits, int V, long long ld, const float
   }
 }
 
+// Greedy choice in two stages so that a handful of rows still uses the whole GPU: each block finds the
+// best (value, index) of one chunk of a row; one block per row then picks among the chunks.  Ties go to
+// the lower index in both stages.
+#define ARGMAX_CHUNKS 32
+__global__ void __launch_bounds__(256)
+argmax_chunk_kernel(const float* __restrict__ logits, int V, long long ld, float* __restrict__ part_v, int* __restrict__ part_i) {
+  __shared__ ArgMax scratch[33];
+  const int m = blockIdx.y, c = blockIdx.x;
+  const int span = (V + ARGMAX_CHUNKS - 1) / ARGMAX_CHUNKS;
+  const int lo = c * span, hi = min(V, lo + span);
+  const float* row = logits + (size_t)m * ld;
+  ArgMax best{0.f, -1};
+  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+    const float v = row[i];
+    if (!isnan(v)) best = better(best, ArgMax{v, i});
+  }
+  best = block_argmax(best, scratch);
+  if (threadIdx.x == 0) {
+    part_v[m * ARGMAX_CHUNKS + c] = best.v;
+    part_i[m * ARGMAX_CHUNKS + c] = best.i;
+  }
+}
+
+__global__ void argmax_final_kernel(const float* __restrict__ part_v, const int* __restrict__ part_i, int* __restrict__ out) {
+  const int m = blockIdx.x, lane = threadIdx.x;
+  ArgMax a{part_v[m * ARGMAX_CHUNKS + lane], part_i[m * ARGMAX_CHUNKS + lane]};
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    ArgMax b;
+    b.v = __shfl_xor_sync(0xffffffffu, a.v, o);
+    b.i = __shfl_xor_sync(0xffffffffu, a.i, o);
+    a = better(a, b);
+  }
+  if (lane == 0) out[m] = a.i < 0 ? 0 : a.i;
+}
+
+// part_v: float [M * 32], part_i: int [M * 32] scratch.
+JLX_API int jlx_argmax(const float* logits, int M, int V, long long ld, float* part_v, int* part_i, int* out,
+                       cudaStream_t stream) {
+  JLX_REQUIRE(M >= 0 && V > 0 && ld >= V, "argmax: bad sizes M=%d V=%d", M, V);
+  JLX_REQUIRE(part_v && part_i, "argmax: scratch missing");
+  JLX_REQUIRE(M <= 65535, "argmax: too many rows");
+  if (M == 0) return 0;
+  argmax_chunk_kernel<<<dim3(ARGMAX_CHUNKS, M), 256, 0, stream>>>(logits, V, ld, part_v, part_i);
+  JLX_LAUNCH_CHECK("argmax_chunk");
+  argmax_final_kernel<<<M, 32, 0, stream>>>(part_v, part_i, out);
+  JLX_LAUNCH_CHECK("argmax_final");
+  return 0;
+}
+
 JLX_API int jlx_sample_max_top_k() { return SAMPLE_MAX_K; }
 
 JLX_API int jlx_sample(const float* logits, int M, int V, long long ld, const float* temperature, const int* top_k,

@@ -67,7 +67,7 @@ class Engine:
     """
 
     def __init__(self, model: DecoderModel, *, max_tokens: int, page_size: int = 64, max_slots: int = 64,
-                 max_seq_len: int | None = None):
+                 max_seq_len: int | None = None, use_graphs: bool | None = None):
         if not torch.cuda.is_available():
             raise EngineError("no CUDA device: this engine runs on a GPU only and has no CPU path")
         if page_size <= 0 or max_tokens <= 0:
@@ -93,6 +93,11 @@ class Engine:
         self.steps_run = 0
         self.record_routing = False  # True: keep each routed layer's expert choices of the last step
         self.last_routing: list[torch.Tensor] = []
+        # Decode-only steps (one token per request) are launch-bound: from the second step of a batch
+        # shape on, the step's kernels are captured once in a CUDA graph and replayed.
+        self.use_graphs = (self.runtime.dtype == torch.bfloat16) if use_graphs is None else use_graphs
+        self._graphs: dict[tuple[int, int], dict] = {}
+        self.graph_replays = 0
 
     # ------------------------------------------------------------------ requests
     def new_request(self) -> int:
@@ -142,8 +147,14 @@ class Engine:
         self.reserve(entries)
         starts = [self.manager.committed(e.slot) for e in entries]
         max_kv = max(s + int(n) for s, n in zip(starts, n_tok))
-        width = -(-max_kv // self.page_size)
         G = len(self.manager.groups)
+        graph = None
+        if self.use_graphs and N == R and not self.record_routing and not self.states:
+            graph = self._graphs.setdefault((R, M), {"seen": 0})
+            graph["seen"] += 1
+        static = graph is not None and graph["seen"] >= 2
+        # a graph's descriptor is laid out for the longest request the engine allows, so that it fits every replay
+        width = self.max_pages_per_request if static else -(-max_kv // self.page_size)
         packed = CacheManager.packed_size(G, N, R, M, width)
         # query tiles for the flash kernel: up to 16 consecutive tokens of one request
         tiles = None
@@ -156,34 +167,53 @@ class Engine:
         self.manager.pack_step(slots, n_tok, tokens, want_off, want, width, N, R, M, host_np)
         if tiles is not None:
             host_np[packed:size] = tiles.reshape(-1)
-        if self._dev_desc is None or self._dev_desc.numel() < size:
-            self._dev_desc = torch.empty(max(size, 4096), dtype=torch.int32, device=self.runtime.device)
-        desc = self._dev_desc[:size]
+        if static:
+            if "desc" not in graph:
+                graph["desc"] = torch.empty(size, dtype=torch.int32, device=self.runtime.device)
+            desc = graph["desc"]
+        else:
+            if self._dev_desc is None or self._dev_desc.numel() < size:
+                self._dev_desc = torch.empty(max(size, 4096), dtype=torch.int32, device=self.runtime.device)
+            desc = self._dev_desc[:size]
         desc.copy_(host[:size], non_blocking=True)
         self._ring.mark(ring_i)
 
-        o = 0
+        if static and "graph" in graph:
+            graph["graph"].replay()
+            self.graph_replays += 1
+            logits = graph["logits"]
+        else:
+            o = 0
 
-        def cut(n: int) -> torch.Tensor:
-            nonlocal o
-            v = desc[o:o + n]
-            o += n
-            return v
+            def cut(n: int) -> torch.Tensor:
+                nonlocal o
+                v = desc[o:o + n]
+                o += n
+                return v
 
-        ctx = StepContext(
-            runtime=self.runtime, n_tokens=N, n_requests=R,
-            token_ids=cut(N), positions=cut(N), req_of_token=cut(N), cu_q=cut(R + 1), q_start=cut(R), kv_len=cut(R),
-            slot_ids=cut(R), logit_rows=cut(M), n_logit_rows=M, status=self.status,
-            host_q_lens=[int(n) for n in n_tok], host_q_start=starts, host_slot_ids=[int(s) for s in slots],
-            max_q_len=int(n_tok.max()), max_kv_len=max_kv, workspace=self.workspace,
-        )
-        block_tables = [cut(R * width).view(R, width) for _ in range(G)]
-        if tiles is not None:
-            ctx.attn_tiles, ctx.n_attn_tiles = cut(tiles.size).view(-1, 2), tiles.shape[0]
-        if self.record_routing:
-            ctx.scratch["record_routing"] = []
-        logits = self.model.forward(ctx, self.kv, self.states, block_tables)
-        self.last_routing = ctx.scratch.get("record_routing", [])
+            ctx = StepContext(
+                runtime=self.runtime, n_tokens=N, n_requests=R,
+                token_ids=cut(N), positions=cut(N), req_of_token=cut(N), cu_q=cut(R + 1), q_start=cut(R), kv_len=cut(R),
+                slot_ids=cut(R), logit_rows=cut(M), n_logit_rows=M, status=self.status,
+                host_q_lens=[int(n) for n in n_tok], host_q_start=starts, host_slot_ids=[int(s) for s in slots],
+                max_q_len=int(n_tok.max()), max_kv_len=self.max_seq_len if static else max_kv, workspace=self.workspace,
+            )
+            block_tables = [cut(R * width).view(R, width) for _ in range(G)]
+            if tiles is not None:
+                ctx.attn_tiles, ctx.n_attn_tiles = cut(tiles.size).view(-1, 2), tiles.shape[0]
+            if self.record_routing:
+                ctx.scratch["record_routing"] = []
+            if static:
+                g = torch.cuda.CUDAGraph()
+                torch.cuda.synchronize()
+                with torch.cuda.graph(g):
+                    logits = self.model.forward(ctx, self.kv, self.states, block_tables)
+                graph["graph"], graph["logits"] = g, logits
+                g.replay()
+                self.graph_replays += 1
+            else:
+                logits = self.model.forward(ctx, self.kv, self.states, block_tables)
+            self.last_routing = ctx.scratch.get("record_routing", [])
         for e, s, n in zip(entries, starts, n_tok):
             self.manager.commit(e.slot, s + int(n))
         self.steps_run += 1

@@ -97,27 +97,47 @@ def embed(ids: torch.Tensor, table: torch.Tensor, x_out: torch.Tensor, status: t
          c_int(ids.numel()), c_int(D), c_int(V), _ptr(status), _stream())
 
 
+def _splits(t: torch.Tensor | None, splits: int) -> tuple[int, int]:
+    """(split count, elements between partials) of a tensor that may hold split-K partials [splits, ...]."""
+    if t is None or splits <= 1:
+        return 1, 0
+    return splits, t.numel() // splits
+
+
 def add_rmsnorm(x: torch.Tensor, delta: torch.Tensor | None, gamma: torch.Tensor | None, eps: float,
-                out: torch.Tensor | None, out32: torch.Tensor | None = None,
-                row_index: torch.Tensor | None = None) -> None:
-    """x (+= delta); out = gamma * x / sqrt(mean(x^2) + eps).  With row_index, row n reads source
-    row row_index[n] and x is not written back."""
-    _contig(x, delta, gamma, out, out32, row_index)
+                out: torch.Tensor | None, out32: torch.Tensor | None = None, row_index: torch.Tensor | None = None,
+                delta_splits: int = 1, w_router: torch.Tensor | None = None, topk_idx: torch.Tensor | None = None,
+                topk_w: torch.Tensor | None = None) -> None:
+    """x (+= delta); out = gamma * x / sqrt(mean(x^2) + eps).  ``delta`` may hold ``delta_splits`` split-K
+    partials [splits, N, D] that are added in order.  With row_index, row n reads source row row_index[n]
+    and x is not written back.  With w_router [E, D] the token is routed in the same kernel:
+    topk_idx / topk_w [N, k]."""
+    _contig(x, delta, gamma, out, out32, row_index, w_router, topk_idx, topk_w)
     D = x.shape[-1]
     n = row_index.numel() if row_index is not None else x.numel() // D
     if x.dtype != torch.float32 or (delta is not None and delta.dtype != torch.float32):
         raise KernelError("add_rmsnorm: the residual stream must be float32")
     if gamma is not None and gamma.dtype != torch.float32:
         raise KernelError("add_rmsnorm: the norm weight must be float32")
-    _run("elementwise", "jlx_add_rmsnorm", _ptr(x), _ptr(delta), _ptr(gamma), c_float(eps), _ptr(out),
-         c_int(code(out.dtype) if out is not None else F32), _ptr(out32), _ptr(row_index), c_int(n), c_int(D), _stream())
+    ds, dstride = _splits(delta, delta_splits)
+    E = k = 0
+    if w_router is not None:
+        if w_router.dtype != torch.float32 or topk_idx is None or topk_w is None:
+            raise KernelError("router: float32 weight and outputs are needed")
+        E, k = w_router.shape[0], topk_idx.shape[1]
+    _run("elementwise", "jlx_add_rmsnorm", _ptr(x), _ptr(delta), c_int(ds), c_longlong(dstride), _ptr(gamma), c_float(eps),
+         _ptr(out), c_int(code(out.dtype) if out is not None else F32), _ptr(out32), _ptr(row_index), c_int(n), c_int(D),
+         _ptr(w_router), c_int(E), c_int(k), _ptr(topk_idx), _ptr(topk_w), _stream())
 
 
-def silu_mul(gu: torch.Tensor, out: torch.Tensor, n_rows_dev: torch.Tensor | None = None) -> None:
+def silu_mul(gu: torch.Tensor, out: torch.Tensor, splits: int = 1, interleaved: bool = False) -> None:
+    """out = silu(gate) * up.  gu: [rows, 2F] (or ``splits`` float32 partials [splits, rows, 2F]), laid out
+    [gate, up] or, interleaved, in blocks of [16 gate, 16 up]."""
     _contig(gu, out)
-    rows, F2 = gu.shape
-    _run("elementwise", "jlx_silu_mul", _ptr(gu), _ptr(out), c_int(code(gu.dtype)), _ptr(n_rows_dev), c_int(rows),
-         c_int(F2 // 2), _stream())
+    rows, F = out.shape
+    sp, stride = _splits(gu, splits)
+    _run("elementwise", "jlx_silu_mul", _ptr(gu), c_int(code(gu.dtype)), c_int(sp), c_longlong(stride), _ptr(out),
+         c_int(code(out.dtype)), c_int(rows), c_int(F), c_int(int(interleaved)), _stream())
 
 
 def convert(src: torch.Tensor, dst: torch.Tensor) -> None:
@@ -129,17 +149,18 @@ def convert(src: torch.Tensor, dst: torch.Tensor) -> None:
 # ------------------------------------------------------------------- position encoding + cache
 def rope_kv_store(qkv: torch.Tensor, q_out: torch.Tensor, pages: torch.Tensor | None, block_table: torch.Tensor | None,
                   req_of_token: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor | None, l2norm: bool,
-                  eps: float, Hq: int, Hkv: int, dh: int, status: torch.Tensor) -> None:
-    """pages: [num_pages, 2, Hkv, page_size, dh] or None (a layer that writes no cache: Hkv heads of
-    k and v are still expected in qkv only if Hkv > 0)."""
+                  eps: float, Hq: int, Hkv: int, dh: int, status: torch.Tensor, splits: int = 1) -> None:
+    """qkv: [N, (Hq + 2 Hkv) * dh] projected rows, or ``splits`` float32 partials of them.
+    pages: [num_pages, 2, Hkv, page_size, dh] or None (a layer that writes no cache)."""
     _contig(qkv, q_out, pages, block_table, inv_freq)
     store = pages is not None
-    N = qkv.shape[0]
-    _run("rope_kv", "jlx_rope_kv_store", _ptr(qkv), _ptr(q_out), _ptr(pages), c_int(code(qkv.dtype)),
-         _ptr(block_table), c_int(block_table.shape[1] if store else 0), _ptr(req_of_token), _ptr(positions),
-         _ptr(inv_freq), c_int(int(l2norm)), c_float(eps), c_int(N), c_int(Hq), c_int(Hkv), c_int(dh),
-         c_int(pages.shape[3] if store else 0), c_int(pages.shape[0] if store else 0), c_int(int(store)),
-         _ptr(status), _stream())
+    N = q_out.shape[0]
+    sp, stride = _splits(qkv, splits)
+    _run("rope_kv", "jlx_rope_kv_store", _ptr(qkv), c_int(code(qkv.dtype)), c_int(sp), c_longlong(stride), _ptr(q_out),
+         _ptr(pages), c_int(code(q_out.dtype)), _ptr(block_table), c_int(block_table.shape[1] if store else 0),
+         _ptr(req_of_token), _ptr(positions), _ptr(inv_freq), c_int(int(l2norm)), c_float(eps), c_int(N), c_int(Hq),
+         c_int(Hkv), c_int(dh), c_int(pages.shape[3] if store else 0), c_int(pages.shape[0] if store else 0),
+         c_int(int(store)), _ptr(status), _stream())
 
 
 def kv_store(k: torch.Tensor, v: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor,
@@ -230,25 +251,36 @@ def gemm_stream_supported(a: torch.Tensor, w: torch.Tensor) -> bool:
             and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
+GEMM_PLAIN, GEMM_PARTIALS, GEMM_SWIGLU = 0, 1, 2
+
+
 def gemm_stream(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: torch.Tensor,
                 offsets: torch.Tensor | None = None, rows_hint: int = 0, splits: int = 1,
-                scratch: torch.Tensor | None = None) -> None:
-    """out = a @ w^T on the tcgen05 tensor cores (bfloat16 in, float32 accumulate).  a: [M, K];
-    w: [N, K] or, with row-group offsets [E + 1], [E, N, K]; out: [M, N] bfloat16 or float32.
-    splits > 1 cuts K across blocks; scratch: float32 [splits * M * N]."""
+                scratch: torch.Tensor | None = None, mode: int = GEMM_PLAIN) -> int:
+    """a @ w^T on the tcgen05 tensor cores (bfloat16 in, float32 accumulate).  a: [M, K]; w: [N, K] or,
+    with row-group offsets [E + 1], [E, N, K].
+    GEMM_PLAIN: out [M, N] bfloat16 or float32; splits > 1 cuts K across blocks (scratch: float32
+    [splits * M * N]) and adds the partials.  GEMM_PARTIALS: out is float32 [splits, M, N], left for the
+    consumer to add.  GEMM_SWIGLU: w's rows are interleaved [16 gate, 16 up]; out [M, N / 2] =
+    silu(gate) * up.  Returns the split count used."""
     _contig(a, w, out, offsets, scratch)
     M, K = a.shape
     E = w.shape[0] if offsets is not None else 0
     N = w.shape[-2]
-    if w.shape[-1] != K or tuple(out.shape) != (M, N) or (offsets is None) != (w.dim() == 2):
-        raise KernelError(f"gemm_stream: shapes do not fit: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    if w.shape[-1] != K or (offsets is None) != (w.dim() == 2):
+        raise KernelError(f"gemm_stream: shapes do not fit: a {tuple(a.shape)}, w {tuple(w.shape)}")
+    want = {GEMM_PLAIN: M * N, GEMM_PARTIALS: splits * M * N, GEMM_SWIGLU: M * (N // 2)}[mode]
+    if out.numel() < want:
+        raise KernelError(f"gemm_stream: out has {out.numel()} elements, {want} are needed")
     if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or out.dtype not in (torch.bfloat16, torch.float32):
         raise KernelError("gemm_stream: bfloat16 operands and a bfloat16 or float32 result are supported")
-    if splits > 1 and (scratch is None or scratch.numel() < splits * M * N or scratch.dtype != torch.float32):
+    if mode == GEMM_PLAIN and splits > 1 and (scratch is None or scratch.numel() < splits * M * N or scratch.dtype != torch.float32):
         raise KernelError("gemm_stream: split-K needs float32 scratch of splits * M * N elements")
+    used = c_int(1)
     _run("gemm_stream", "jlx_gemm_stream", _ptr(a), _ptr(w), _ptr(out), c_int(int(out.dtype == torch.float32)), c_int(M),
-         c_int(N), c_int(K), _ptr(offsets), c_int(E), c_int(rows_hint), c_int(splits), _ptr(scratch), _ptr(status),
-         _stream())
+         c_int(N), c_int(K), _ptr(offsets), c_int(E), c_int(rows_hint), c_int(splits), _ptr(scratch), c_int(mode),
+         ctypes.byref(used), _ptr(status), _stream())
+    return used.value
 
 
 # --------------------------------------------------------------------------------------- MoE
@@ -276,16 +308,31 @@ def permute_scale(h32: torch.Tensor, sorted_pair: torch.Tensor, topk_w: torch.Te
          c_int(code(a_sorted.dtype)), c_int(a_sorted.shape[0]), c_int(h32.shape[1]), c_int(k), _stream())
 
 
-def moe_combine(y_sorted: torch.Tensor, shared: torch.Tensor | None, sorted_pos: torch.Tensor, delta: torch.Tensor, k: int) -> None:
+def moe_combine(y_sorted: torch.Tensor, shared: torch.Tensor | None, sorted_pos: torch.Tensor, delta: torch.Tensor, k: int,
+                shared_splits: int = 1) -> None:
+    """delta = shared (or the sum of its split-K partials) + the sum of each token's expert rows."""
     _contig(y_sorted, shared, sorted_pos, delta)
     N, D = delta.shape
-    _run("moe", "jlx_moe_combine", _ptr(y_sorted), _ptr(shared), _ptr(sorted_pos), _ptr(delta), c_int(N), c_int(D),
-         c_int(k), _stream())
+    sp, stride = _splits(shared, shared_splits)
+    _run("moe", "jlx_moe_combine", _ptr(y_sorted), _ptr(shared), c_int(sp), c_longlong(stride), _ptr(sorted_pos),
+         _ptr(delta), c_int(N), c_int(D), c_int(k), _stream())
 
 
 # ---------------------------------------------------------------------------------- sampling
 def sample_max_top_k() -> int:
     return int(library("sampling").jlx_sample_max_top_k())
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor, part_v: torch.Tensor, part_i: torch.Tensor) -> None:
+    """out[m] = index of the largest logit (lowest index on ties).  part_v (float32), part_i (int32): [M * 32] scratch."""
+    _contig(logits, out, part_v, part_i)
+    if logits.dtype != torch.float32:
+        raise KernelError("argmax: logits must be float32")
+    M, V = logits.shape
+    if part_v.numel() < 32 * M or part_i.numel() < 32 * M:
+        raise KernelError("argmax: scratch too small")
+    _run("sampling", "jlx_argmax", _ptr(logits), c_int(M), c_int(V), c_longlong(V), _ptr(part_v), _ptr(part_i), _ptr(out),
+         _stream())
 
 
 def sample(logits: torch.Tensor, out: torch.Tensor, temperature: torch.Tensor | None = None,

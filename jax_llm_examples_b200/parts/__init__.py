@@ -1,16 +1,16 @@
 from .attention import PagedAttention
-from .base import (Block, FeedForward, KVNeed, LayerCache, Mixer, Norm, Part, PositionEncoding, Runtime, StateNeed,
-                   StepContext, known_parts, make_part, register_part)
+from .base import (Block, FeedForward, KVNeed, LayerCache, Mixer, Norm, Part, PositionEncoding, Rows, Runtime, StateNeed,
+                   StepContext, Workspace, as_rows, known_parts, make_part, register_part)
 from .block import PreNormBlock
 from .decoder import CachePlan, DecoderModel, LayerRun
 from .feedforward import DenseSwiGLU, RoutedExperts
-from .linear import grouped_linear, linear
+from .linear import grouped_linear, grouped_swiglu_linear, interleave_gate_up, linear, swiglu_linear
 from .norms import RMSNorm
 from .positions import InterleavedRope, NoPositionWithTemperature, UnfusedEncoding, llama3_scaled_frequencies
 
 __all__ = [
     "Block", "CachePlan", "DecoderModel", "DenseSwiGLU", "FeedForward", "InterleavedRope", "KVNeed", "LayerCache",
     "LayerRun", "Mixer", "NoPositionWithTemperature", "Norm", "PagedAttention", "Part", "PositionEncoding",
-    "PreNormBlock", "RMSNorm", "RoutedExperts", "Runtime", "StateNeed", "StepContext", "UnfusedEncoding",
+    "PreNormBlock", "RMSNorm", "RoutedExperts", "Rows", "Runtime", "Workspace", "as_rows", "grouped_swiglu_linear", "interleave_gate_up", "swiglu_linear", "StateNeed", "StepContext", "UnfusedEncoding",
     "grouped_linear", "known_parts", "linear", "llama3_scaled_frequencies", "make_part", "register_part",
 ]

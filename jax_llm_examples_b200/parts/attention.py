@@ -53,12 +53,12 @@ class PagedAttention(Mixer):
 
     def forward(self, ctx: StepContext, h: torch.Tensor, cache: LayerCache) -> torch.Tensor:
         rt = ctx.runtime
-        qkv = linear(ctx, h, self.w_qkv, rt.dtype)
+        qkv = linear(ctx, h, self.w_qkv, rt.dtype, partials=self.position.accepts_partials)
         q = self.position.encode_and_store(ctx, qkv, self.n_heads, self.n_kv_heads, self.head_dim, cache, self.qk_norm_eps)
         attn_scale, floor_scale = self.position.query_temperature()
         out = torch.empty_like(q)
         self.attend(ctx, q, cache, out, attn_scale, floor_scale)
-        return linear(ctx, out.view(q.shape[0], -1), self.w_o, torch.float32)
+        return linear(ctx, out.view(q.shape[0], -1), self.w_o, torch.float32, partials=True)
 
     def attend(self, ctx: StepContext, q, cache: LayerCache, out, attn_scale: float, floor_scale: float) -> None:
         """Tensor-core kernels where they are built (bfloat16, head size 64 or 128, small groups): split-KV

@@ -56,17 +56,36 @@ class StateNeed:
     dtype: torch.dtype = torch.float32
 
 
+@dataclasses.dataclass
+class Rows:
+    """Token rows that may still be split-K partials: ``data`` is [N, D], or float32 [splits, N, D] whose
+    slices the consumer adds in ascending order (saving the launch that would add them)."""
+
+    data: torch.Tensor
+    splits: int = 1
+
+
+def as_rows(x: "torch.Tensor | Rows | None") -> "Rows | None":
+    if x is None or isinstance(x, Rows):
+        return x
+    return Rows(x, 1)
+
+
 class Workspace:
     """Named device buffers that live across steps (scratch of kernels, e.g. split-K partials).
-    Kernels of one stream run in order, so a buffer can serve every layer in turn."""
+    Kernels of one stream run in order, so a buffer can serve every layer in turn.  A buffer that was
+    outgrown is kept, not freed: a captured CUDA graph may still hold its address."""
 
     def __init__(self, device: torch.device):
         self.device = device
         self._bufs: dict[str, torch.Tensor] = {}
+        self._outgrown: list[torch.Tensor] = []
 
     def get(self, name: str, numel: int, dtype: torch.dtype) -> torch.Tensor:
         t = self._bufs.get(name)
         if t is None or t.numel() < numel or t.dtype != dtype:
+            if t is not None:
+                self._outgrown.append(t)
             t = torch.empty(max(numel, 1), dtype=dtype, device=self.device)
             self._bufs[name] = t
         return t[:numel]
@@ -127,14 +146,20 @@ class Part:
 
 
 class Norm(Part):
-    def forward(self, ctx: StepContext, x: torch.Tensor, delta: torch.Tensor | None, *, out_dtype: torch.dtype,
-                want_f32: bool = False, row_index: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor | None]:
-        """x += delta (if given); returns (normed rows in out_dtype, the same in float32 if asked)."""
+    fuses_router: bool = False  # True: forward(router=...) also routes the tokens in its kernel
+
+    def forward(self, ctx: StepContext, x: torch.Tensor, delta: "torch.Tensor | Rows | None", *, out_dtype: torch.dtype,
+                want_f32: bool = False, row_index: torch.Tensor | None = None, router=None):
+        """x += delta (if given); returns (normed rows in out_dtype, the same in float32 if asked,
+        routing).  ``router`` = (w_router [E, D] float32, top_k) asks a norm with ``fuses_router`` to
+        route as well: routing = (expert indices [N, k] int32, weights [N, k] float32); else None."""
         raise NotImplementedError
 
 
 class PositionEncoding(Part):
-    def encode_and_store(self, ctx: StepContext, qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
+    accepts_partials: bool = False  # True: encode_and_store takes qkv as Rows with split-K partials
+
+    def encode_and_store(self, ctx: StepContext, qkv: "torch.Tensor | Rows", n_heads: int, n_kv_heads: int, head_dim: int,
                          cache: LayerCache, qk_norm_eps: float | None) -> torch.Tensor:
         """qkv: [N, (Hq + 2 Hkv) * dh] projected rows.  Returns q [N, Hq, dh] ready for the score
         product; writes k and v into the cache pages when ``cache.writes``."""
@@ -152,23 +177,27 @@ class Mixer(Part):
     def state_need(self) -> StateNeed | None:
         return None
 
-    def forward(self, ctx: StepContext, h: torch.Tensor, cache: LayerCache) -> torch.Tensor:
-        """h: normed rows [N, D] in the runtime's dtype.  Returns delta [N, D] float32."""
+    def forward(self, ctx: StepContext, h: torch.Tensor, cache: LayerCache) -> "torch.Tensor | Rows":
+        """h: normed rows [N, D] in the runtime's dtype.  Returns delta [N, D] float32 (or Rows of partials)."""
         raise NotImplementedError
 
 
 class FeedForward(Part):
     needs_f32_input: bool = False  # True: forward() also gets the normed rows unrounded
 
-    def forward(self, ctx: StepContext, h: torch.Tensor, h32: torch.Tensor | None) -> torch.Tensor:
-        """Returns delta [N, D] float32."""
+    def router_request(self):
+        """(w_router, top_k) if the preceding norm may route the tokens for this part, else None."""
+        return None
+
+    def forward(self, ctx: StepContext, h: torch.Tensor, h32: torch.Tensor | None, routing=None) -> "torch.Tensor | Rows":
+        """Returns delta [N, D] float32 (or Rows of partials).  ``routing``: what a fusing norm already chose."""
         raise NotImplementedError
 
 
 class Block(Part):
     mixer: Mixer
 
-    def forward(self, ctx: StepContext, x: torch.Tensor, delta: torch.Tensor | None, cache: LayerCache) -> torch.Tensor:
+    def forward(self, ctx: StepContext, x: torch.Tensor, delta: "torch.Tensor | Rows | None", cache: LayerCache):
         """Runs the block on residual x with a pending ``delta`` not yet added; returns the new pending delta."""
         raise NotImplementedError
 

@@ -24,11 +24,12 @@ class PreNormBlock(Block):
 
     def forward(self, ctx: StepContext, x: torch.Tensor, delta, cache: LayerCache) -> torch.Tensor:
         dt = ctx.runtime.dtype
-        h, _ = self.norm1.forward(ctx, x, delta, out_dtype=dt)
+        h = self.norm1.forward(ctx, x, delta, out_dtype=dt)[0]
         a = self.mixer.forward(ctx, h, cache)
         want32 = self.feed_forward.needs_f32_input
-        h, h32 = self.norm2.forward(ctx, x, a, out_dtype=dt, want_f32=want32)
-        return self.feed_forward.forward(ctx, h, h32)
+        router = self.feed_forward.router_request() if self.norm2.fuses_router else None
+        h, h32, routing = self.norm2.forward(ctx, x, a, out_dtype=dt, want_f32=want32, router=router)
+        return self.feed_forward.forward(ctx, h, h32, routing)
 
 
 register_part("block", "pre_norm", PreNormBlock)

@@ -137,5 +137,5 @@ class DecoderModel:
             delta = self.blocks[run.block].forward(ctx, x, delta, cache)
         if ctx.n_logit_rows == 0:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=rt.device)
-        h, _ = self.final_norm.forward(ctx, x, delta, out_dtype=rt.dtype, row_index=ctx.logit_rows)
+        h = self.final_norm.forward(ctx, x, delta, out_dtype=rt.dtype, row_index=ctx.logit_rows)[0]
         return linear(ctx, h, self.lm_head, torch.float32)

@@ -5,26 +5,31 @@ from __future__ import annotations
 import torch
 
 from ..kernels import api as K
-from .base import FeedForward, StepContext, register_part
-from .linear import grouped_linear, linear
+from .base import FeedForward, Rows, StepContext, as_rows, register_part
+from .linear import grouped_linear, grouped_swiglu_linear, interleave_gate_up, linear, swiglu_linear
+
+
+def _can_interleave(w_gate_up: torch.Tensor) -> bool:
+    return w_gate_up.dtype == torch.bfloat16 and (w_gate_up.shape[-2] // 2) % 16 == 0 and w_gate_up.shape[-1] % 8 == 0
 
 
 class DenseSwiGLU(FeedForward):
     """down(silu(h gate) * (h up)) (llama4/llama4_jax/model.py:1142-1153).
-    ``w_gate_up``: [2F, D], gate rows then up rows; ``w_down``: [D, F]."""
+    ``w_gate_up``: [2F, D], gate rows then up rows; ``w_down``: [D, F].  bfloat16 weights are re-laid in
+    blocks of [16 gate rows, 16 up rows] so that the product's epilogue can apply the activation."""
 
     kernel_libraries = ("elementwise", "gemm_simt", "gemm_stream")
 
     def __init__(self, w_gate_up: torch.Tensor, w_down: torch.Tensor):
         if w_gate_up.shape[0] != 2 * w_down.shape[1] or w_gate_up.shape[1] != w_down.shape[0]:
             raise ValueError(f"SwiGLU weights do not fit: gate_up {tuple(w_gate_up.shape)}, down {tuple(w_down.shape)}")
-        self.w_gate_up, self.w_down = w_gate_up, w_down
+        self.interleaved = _can_interleave(w_gate_up)
+        self.w_gate_up = interleave_gate_up(w_gate_up) if self.interleaved else w_gate_up
+        self.w_down = w_down
 
-    def forward(self, ctx: StepContext, h, h32=None):
-        gu = linear(ctx, h, self.w_gate_up, ctx.runtime.dtype)
-        act = torch.empty((gu.shape[0], gu.shape[1] // 2), dtype=gu.dtype, device=gu.device)
-        K.silu_mul(gu, act)
-        return linear(ctx, act, self.w_down, torch.float32)
+    def forward(self, ctx: StepContext, h, h32=None, routing=None):
+        act = swiglu_linear(ctx, h, self.w_gate_up, self.interleaved, ctx.runtime.dtype)
+        return linear(ctx, act, self.w_down, torch.float32, partials=True)
 
 
 class RoutedExperts(FeedForward):
@@ -49,36 +54,46 @@ class RoutedExperts(FeedForward):
         if not 1 <= top_k <= E:
             raise ValueError(f"top-{top_k} of {E} experts")
         self.w_router = w_router.to(torch.float32).contiguous()
-        self.we_gate_up, self.we_down, self.top_k, self.shared = we_gate_up, we_down, top_k, shared
+        self.interleaved = _can_interleave(we_gate_up)
+        self.we_gate_up = interleave_gate_up(we_gate_up) if self.interleaved else we_gate_up
+        self.we_down, self.top_k, self.shared = we_down, top_k, shared
         self.num_experts = E
 
+    def router_request(self):
+        return (self.w_router, self.top_k)
+
     def route(self, ctx: StepContext, h32: torch.Tensor):
+        """The router as a kernel of its own (when the norm before this part does not route)."""
         n, k, dev = h32.shape[0], self.top_k, h32.device
         topk_idx = torch.empty((n, k), dtype=torch.int32, device=dev)
         topk_w = torch.empty((n, k), dtype=torch.float32, device=dev)
         K.router(h32, self.w_router, topk_idx, topk_w)
+        return topk_idx, topk_w
+
+    def sort(self, ctx: StepContext, topk_idx: torch.Tensor):
+        n, k, dev = topk_idx.shape[0], self.top_k, topk_idx.device
         offsets = torch.empty(self.num_experts + 1, dtype=torch.int32, device=dev)
         sorted_pair = torch.empty(n * k, dtype=torch.int32, device=dev)
         sorted_pos = torch.empty(n * k, dtype=torch.int32, device=dev)
         K.expert_sort(topk_idx, offsets, sorted_pair, sorted_pos, self.num_experts, ctx.status)
-        return topk_idx, topk_w, offsets, sorted_pair, sorted_pos
+        return offsets, sorted_pair, sorted_pos
 
-    def forward(self, ctx: StepContext, h, h32):
+    def forward(self, ctx: StepContext, h, h32, routing=None):
         rt = ctx.runtime
         n, D = h32.shape
         k = self.top_k
-        topk_idx, topk_w, offsets, sorted_pair, sorted_pos = self.route(ctx, h32)
+        topk_idx, topk_w = routing if routing is not None else self.route(ctx, h32)
         if "record_routing" in ctx.scratch:  # tests compare the choices with a plain router's
             ctx.scratch["record_routing"].append(topk_idx)
+        offsets, sorted_pair, sorted_pos = self.sort(ctx, topk_idx)
         a_sorted = torch.empty((n * k, D), dtype=rt.dtype, device=h.device)
         K.permute_scale(h32, sorted_pair, topk_w, a_sorted, k)
-        gu = grouped_linear(ctx, a_sorted, self.we_gate_up, offsets, rt.dtype)
-        act = torch.empty((n * k, gu.shape[1] // 2), dtype=rt.dtype, device=h.device)
-        K.silu_mul(gu, act)
+        act = grouped_swiglu_linear(ctx, a_sorted, self.we_gate_up, offsets, self.interleaved, rt.dtype)
         y = grouped_linear(ctx, act, self.we_down, offsets, torch.float32)
-        shared = self.shared.forward(ctx, h, None) if self.shared is not None else None
+        shared = as_rows(self.shared.forward(ctx, h, None)) if self.shared is not None else None
         delta = torch.empty((n, D), dtype=torch.float32, device=h.device)
-        K.moe_combine(y, shared, sorted_pos, delta, k)
+        K.moe_combine(y, None if shared is None else shared.data, sorted_pos, delta, k,
+                      1 if shared is None else shared.splits)
         return delta
 
 

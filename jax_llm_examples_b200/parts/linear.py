@@ -5,7 +5,8 @@ Which kernel runs:
 * bfloat16 activations and weights, few rows (a decode step) or row groups (routed experts): this
   package's tcgen05 weight-streaming kernel (``csrc/gemm_stream.cu``), with K cut across blocks when
   the output is too narrow to fill the GPU.  The reference has its own kernel at exactly this place
-  (llama4/llama4_jax/decode_ragged_dot.py).
+  (llama4/llama4_jax/decode_ragged_dot.py).  Its consumers can take the split-K partials as they are
+  (:class:`Rows`) and it can apply SiLU(gate) * up in its epilogue.
 * bfloat16, many rows, one group (prompt portions through the dense projections): the library GEMM
   (cuBLAS through torch), as the reference leaves its dense products to its library (XLA dot_general,
   llama4/llama4_jax/model.py:907-909, 952-954, 1146-1152, 1204).
@@ -19,7 +20,7 @@ from __future__ import annotations
 import torch
 
 from ..kernels import api as K
-from .base import StepContext
+from .base import Rows, StepContext
 
 STREAM_MAX_ROWS = 256  # above this a dense product is compute-bound and goes to the library
 _SM_COUNT = 148
@@ -32,22 +33,56 @@ def _splits_for(n_out: int, k: int) -> int:
     return max(1, min(want, k // 512, 8))
 
 
-def linear(ctx: StepContext, a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
-    """a: [M, K]; w: [N, K]; returns [M, N] in out_dtype (float32 accumulation)."""
+def _streams(a: torch.Tensor, w: torch.Tensor, rows_limit: bool) -> bool:
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and K.gemm_stream_supported(a, w)
+            and (not rows_limit or a.shape[0] <= STREAM_MAX_ROWS))
+
+
+def interleave_gate_up(w_gate_up: torch.Tensor) -> torch.Tensor:
+    """[..., 2F, D] with gate rows then up rows -> the same rows in blocks of [16 gate, 16 up], the layout
+    whose product the SwiGLU epilogue can finish inside one warp.  F must be a multiple of 16."""
+    F = w_gate_up.shape[-2] // 2
+    g = w_gate_up[..., :F, :].unflatten(-2, (F // 16, 16))
+    u = w_gate_up[..., F:, :].unflatten(-2, (F // 16, 16))
+    return torch.stack([g, u], dim=-3).flatten(-4, -2).contiguous()
+
+
+def linear(ctx: StepContext, a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, partials: bool = False):
+    """a: [M, K]; w: [N, K]; returns [M, N] in out_dtype (float32 accumulation).  With ``partials`` the
+    result is :class:`Rows` in float32 whose split-K slices the consumer adds."""
     M, N = a.shape[0], w.shape[0]
+    if _streams(a, w, True):
+        splits = _splits_for(N, a.shape[1])
+        if partials:
+            out = torch.empty((splits, M, N), dtype=torch.float32, device=a.device)
+            used = K.gemm_stream(a, w, out, ctx.status, splits=splits, mode=K.GEMM_PARTIALS)
+            return Rows(out[:used], used)
+        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+        scratch = ctx.workspace.get("splitk", splits * M * N, torch.float32) if splits > 1 else None
+        K.gemm_stream(a, w, out, ctx.status, splits=splits, scratch=scratch)
+        return out
+    if partials:
+        out_dtype = torch.float32
     if a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
-        if M <= STREAM_MAX_ROWS and K.gemm_stream_supported(a, w):
-            out = torch.empty((M, N), dtype=out_dtype, device=a.device)
-            splits = _splits_for(N, a.shape[1])
-            scratch = ctx.workspace.get("splitk", splits * M * N, torch.float32) if splits > 1 else None
-            K.gemm_stream(a, w, out, ctx.status, splits=splits, scratch=scratch)
-            return out
-        if out_dtype == torch.bfloat16:
-            return torch.mm(a, w.t())
-        return torch.mm(a, w.t(), out_dtype=torch.float32)
-    out = torch.empty((M, N), dtype=out_dtype, device=a.device)
-    K.gemm_simt(a, w, out)
-    return out
+        out = torch.mm(a, w.t()) if out_dtype == torch.bfloat16 else torch.mm(a, w.t(), out_dtype=torch.float32)
+    else:
+        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+        K.gemm_simt(a, w, out)
+    return Rows(out, 1) if partials else out
+
+
+def swiglu_linear(ctx: StepContext, a: torch.Tensor, w_gate_up: torch.Tensor, interleaved: bool,
+                  out_dtype: torch.dtype) -> torch.Tensor:
+    """silu(a Wg^T) * (a Wu^T) for stacked [2F, K] weights: in the product's epilogue where the streaming
+    kernel runs and the rows are interleaved, else a product followed by the activation kernel."""
+    M, F = a.shape[0], w_gate_up.shape[0] // 2
+    act = torch.empty((M, F), dtype=out_dtype, device=a.device)
+    if interleaved and _streams(a, w_gate_up, True):
+        K.gemm_stream(a, w_gate_up, act, ctx.status, mode=K.GEMM_SWIGLU)
+        return act
+    gu = linear(ctx, a, w_gate_up, out_dtype)
+    K.silu_mul(gu, act, interleaved=interleaved)
+    return act
 
 
 def grouped_linear(ctx: StepContext, a_sorted: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor,
@@ -55,9 +90,22 @@ def grouped_linear(ctx: StepContext, a_sorted: torch.Tensor, w: torch.Tensor, of
     """Rows [offsets[e], offsets[e+1]) of a_sorted times w[e]^T.  w: [E, N, K]."""
     rows, E = a_sorted.shape[0], w.shape[0]
     out = torch.empty((rows, w.shape[1]), dtype=out_dtype, device=a_sorted.device)
-    if K.gemm_stream_supported(a_sorted, w):
+    if _streams(a_sorted, w, False):
         hint = min(rows, 2 * -(-rows // E))  # groups are uneven: tile for twice the mean
         K.gemm_stream(a_sorted, w, out, ctx.status, offsets=offsets, rows_hint=hint)
     else:
         K.gemm_simt(a_sorted, w, out, offsets)
     return out
+
+
+def grouped_swiglu_linear(ctx: StepContext, a_sorted: torch.Tensor, w_gate_up: torch.Tensor, offsets: torch.Tensor,
+                          interleaved: bool, out_dtype: torch.dtype) -> torch.Tensor:
+    rows, E, F = a_sorted.shape[0], w_gate_up.shape[0], w_gate_up.shape[1] // 2
+    act = torch.empty((rows, F), dtype=out_dtype, device=a_sorted.device)
+    if interleaved and _streams(a_sorted, w_gate_up, False):
+        hint = min(rows, 2 * -(-rows // E))
+        K.gemm_stream(a_sorted, w_gate_up, act, ctx.status, offsets=offsets, rows_hint=hint, mode=K.GEMM_SWIGLU)
+        return act
+    gu = grouped_linear(ctx, a_sorted, w_gate_up, offsets, out_dtype)
+    K.silu_mul(gu, act, interleaved=interleaved)
+    return act

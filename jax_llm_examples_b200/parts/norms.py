@@ -5,25 +5,37 @@ from __future__ import annotations
 import torch
 
 from ..kernels import api as K
-from .base import Norm, StepContext, register_part
+from .base import Norm, StepContext, as_rows, register_part
 
 
 class RMSNorm(Norm):
     """out = weight * x / sqrt(mean(x^2) + eps), mean and division in float32
-    (llama4/llama4_jax/model.py:885-888).  ``weight`` None = weightless."""
+    (llama4/llama4_jax/model.py:885-888).  ``weight`` None = weightless.  The residual sum x += delta
+    runs in the same kernel, and so can the router of a following routed feed-forward."""
 
     kernel_libraries = ("elementwise",)
+    fuses_router = True
 
     def __init__(self, weight: torch.Tensor | None, eps: float):
         self.weight = None if weight is None else weight.to(torch.float32).contiguous()
         self.eps = float(eps)
 
-    def forward(self, ctx: StepContext, x, delta, *, out_dtype, want_f32=False, row_index=None):
+    def forward(self, ctx: StepContext, x, delta, *, out_dtype, want_f32=False, row_index=None, router=None):
         n = x.shape[0] if row_index is None else row_index.numel()
-        out = torch.empty((n, x.shape[1]), dtype=out_dtype, device=x.device)
-        out32 = torch.empty((n, x.shape[1]), dtype=torch.float32, device=x.device) if want_f32 else None
-        K.add_rmsnorm(x, delta, self.weight, self.eps, out, out32, row_index)
-        return out, out32
+        dev = x.device
+        out = torch.empty((n, x.shape[1]), dtype=out_dtype, device=dev)
+        out32 = torch.empty((n, x.shape[1]), dtype=torch.float32, device=dev) if want_f32 else None
+        d = as_rows(delta)
+        routing = None
+        w_router = idx = wt = None
+        if router is not None and x.shape[1] <= 16384:
+            w_router, k = router
+            idx = torch.empty((n, k), dtype=torch.int32, device=dev)
+            wt = torch.empty((n, k), dtype=torch.float32, device=dev)
+            routing = (idx, wt)
+        K.add_rmsnorm(x, None if d is None else d.data, self.weight, self.eps, out, out32, row_index,
+                      1 if d is None else d.splits, w_router, idx, wt)
+        return out, out32, routing
 
 
 register_part("norm", "rms", RMSNorm)

@@ -7,7 +7,7 @@ import math
 import torch
 
 from ..kernels import api as K
-from .base import LayerCache, PositionEncoding, StepContext, register_part
+from .base import LayerCache, PositionEncoding, Rows, StepContext, as_rows, register_part
 
 
 def llama3_scaled_frequencies(head_dim: int, theta: float, scaling: dict | None) -> torch.Tensor:
@@ -34,14 +34,16 @@ def llama3_scaled_frequencies(head_dim: int, theta: float, scaling: dict | None)
 
 class _FusedEncoding(PositionEncoding):
     kernel_libraries = ("rope_kv",)
+    accepts_partials = True
     inv_freq: torch.Tensor | None = None
 
     def encode_and_store(self, ctx: StepContext, qkv, n_heads, n_kv_heads, head_dim, cache: LayerCache, qk_norm_eps):
-        q = torch.empty((qkv.shape[0], n_heads, head_dim), dtype=qkv.dtype, device=qkv.device)
+        rows = as_rows(qkv)
+        q = torch.empty((ctx.n_tokens, n_heads, head_dim), dtype=ctx.runtime.dtype, device=rows.data.device)
         l2 = qk_norm_eps is not None and self.norm_applies
-        K.rope_kv_store(qkv, q, cache.pages if cache.writes else None, cache.block_table if cache.writes else None,
+        K.rope_kv_store(rows.data, q, cache.pages if cache.writes else None, cache.block_table if cache.writes else None,
                         ctx.req_of_token, ctx.positions, self.inv_freq, l2, qk_norm_eps if l2 else 1.0, n_heads,
-                        n_kv_heads, head_dim, ctx.status)
+                        n_kv_heads, head_dim, ctx.status, rows.splits)
         return q
 
 

@@ -39,6 +39,7 @@ class Sampler:
     def __init__(self, seed: int = 0):
         self.seed = int(seed)
         self._max_k: int | None = None
+        self._part: tuple[torch.Tensor, torch.Tensor] | None = None
 
     def sample(self, logits: torch.Tensor, temperatures: list[float], top_ks: list[int], streams: list[int],
                counters: list[int]) -> torch.Tensor:
@@ -46,7 +47,10 @@ class Sampler:
         M = logits.shape[0]
         out = torch.empty(M, dtype=torch.int32, device=logits.device)
         if all(t <= 1e-3 for t in temperatures):
-            K.sample(logits, out)
+            if self._part is None or self._part[0].numel() < 32 * M or self._part[0].device != logits.device:
+                self._part = (torch.empty(32 * max(M, 64), dtype=torch.float32, device=logits.device),
+                              torch.empty(32 * max(M, 64), dtype=torch.int32, device=logits.device))
+            K.argmax(logits, out, *self._part)
             return out
         if self._max_k is None:
             self._max_k = K.sample_max_top_k()

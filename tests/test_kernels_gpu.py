@@ -412,3 +412,89 @@ def test_mma_attention_finds_one_far_key():
         api.attention_prefill(q, pages, bt, req, pos, out2, torch.tensor([[0, 1]], device=DEV, dtype=torch.int32), 1,
                               dh ** -0.5, 0, 0, 0.0, 1.0, st)
         close(out2[0], want, 1e-2)
+
+
+def test_gemm_stream_partials_and_swiglu_epilogue():
+    from jax_llm_examples_b200.parts.linear import interleave_gate_up
+
+    api = K()
+    M, N, Kd = 9, 256, 2048
+    a, w = torch.randn(M, Kd, device=DEV).bfloat16(), torch.randn(N, Kd, device=DEV).bfloat16()
+    parts, st = torch.full((4, M, N), float("nan"), device=DEV), status()
+    used = api.gemm_stream(a, w, parts, st, splits=4, mode=api.GEMM_PARTIALS)
+    assert used == 4 and int(st) == 0
+    close(parts.sum(0), a.double() @ w.double().T, 1e-5)
+    # SwiGLU epilogue on interleaved rows, dense and grouped
+    F = 160
+    wgu = (torch.randn(2 * F, Kd, device=DEV) * 0.05).bfloat16()
+    act = torch.full((M, F), float("nan"), device=DEV, dtype=torch.bfloat16)
+    api.gemm_stream(a, interleave_gate_up(wgu), act, st, mode=api.GEMM_SWIGLU)
+    g, u = a.double() @ wgu[:F].double().T, a.double() @ wgu[F:].double().T
+    close(act, torch.nn.functional.silu(g) * u, 1e-2)
+    E, rows = 5, 70
+    a2 = torch.randn(rows, Kd, device=DEV).bfloat16()
+    we = (torch.randn(E, 2 * F, Kd, device=DEV) * 0.05).bfloat16()
+    off = _groups(E, 3, rows)
+    act2 = torch.full((rows, F), float("nan"), device=DEV)
+    api.gemm_stream(a2, interleave_gate_up(we), act2, st, offsets=off.to(DEV), rows_hint=20, mode=api.GEMM_SWIGLU)
+    assert int(st) == 0
+    for e in range(E):
+        lo, hi = int(off[e]), int(off[e + 1])
+        if hi > lo:
+            g, u = a2[lo:hi].double() @ we[e, :F].double().T, a2[lo:hi].double() @ we[e, F:].double().T
+            close(act2[lo:hi], torch.nn.functional.silu(g) * u, 1e-4)
+    # the activation kernel reads the same interleaved layout and split partials
+    gu = torch.randn(3, 7, 2 * F, device=DEV)
+    out = torch.empty(7, F, device=DEV)
+    api.silu_mul(interleave_gate_up(gu.transpose(1, 2)).transpose(1, 2).contiguous(), out, splits=3, interleaved=True)
+    s = gu.sum(0)
+    close(out, torch.nn.functional.silu(s[:, :F]) * s[:, F:], 1e-5)
+
+
+def test_add_rmsnorm_with_partials_and_fused_router():
+    N, D, E, k, eps = 19, 1000, 12, 3, 1e-5
+    x, parts, g = torch.randn(N, D, device=DEV), torch.randn(3, N, D, device=DEV), 1 + 0.1 * torch.randn(D, device=DEV)
+    w = torch.randn(E, D, device=DEV)
+    s = x + parts[0] + parts[1] + parts[2]
+    ref = g * s / torch.sqrt((s * s).mean(-1, keepdim=True) + eps)
+    xc, out, out32 = x.clone(), torch.empty(N, D, device=DEV, dtype=torch.bfloat16), torch.empty(N, D, device=DEV)
+    idx, wt = torch.empty(N, k, device=DEV, dtype=torch.int32), torch.empty(N, k, device=DEV)
+    K().add_rmsnorm(xc, parts, g, eps, out, out32, None, 3, w, idx, wt)
+    close(out32, ref, 2e-6), close(out, ref, 5e-3)
+    assert torch.allclose(xc, s, atol=1e-6)
+    scores = out32.double() @ w.double().T
+    order = torch.sort(scores, dim=-1, descending=True, stable=True)
+    assert torch.equal(idx.long(), order.indices[:, :k])
+    close(wt, torch.sigmoid(order.values[:, :k]), 1e-5)
+
+
+def test_rope_kv_store_from_float32_partials():
+    N, Hq, Hkv, dh, page, P, eps = 5, 4, 2, 64, 16, 4, 1e-5
+    parts = torch.randn(2, N, (Hq + 2 * Hkv) * dh, device=DEV)
+    pos = torch.arange(7, 7 + N, device=DEV, dtype=torch.int32)
+    req = torch.zeros(N, device=DEV, dtype=torch.int32)
+    bt = torch.tensor([[2, 0, 3, 1]], device=DEV, dtype=torch.int32)
+    pages = torch.zeros(P, 2, Hkv, page, dh, device=DEV, dtype=torch.bfloat16)
+    inv_freq = 1.0 / (10000.0 ** (torch.arange(0, dh, 2, device=DEV).float() / dh))
+    q_out, st = torch.empty(N, Hq, dh, device=DEV, dtype=torch.bfloat16), status()
+    K().rope_kv_store(parts, q_out, pages, bt, req, pos, inv_freq, True, eps, Hq, Hkv, dh, st, splits=2)
+    x = parts.sum(0).reshape(N, Hq + 2 * Hkv, dh)
+    q = _rope_ref(x[:, :Hq], pos, inv_freq)
+    q = q / torch.sqrt((q * q).mean(-1, keepdim=True) + eps)
+    close(q_out, q, 8e-3)
+    v = x[:, Hq + Hkv:]
+    for n in range(N):
+        pg, slot = int(bt[0, int(pos[n]) // page]), int(pos[n]) % page
+        close(pages[pg, 1, :, slot], v[n], 8e-3)
+
+
+def test_two_stage_argmax():
+    M, V = 7, 202048
+    logits = torch.randn(M, V, device=DEV)
+    logits[3, 5000] = logits[3, 150000] = 99.0
+    logits[5, V - 1] = 100.0
+    out = torch.empty(M, device=DEV, dtype=torch.int32)
+    K().argmax(logits, out, torch.empty(32 * M, device=DEV), torch.empty(32 * M, device=DEV, dtype=torch.int32))
+    want = logits.argmax(-1).tolist()
+    want[3] = 5000
+    assert out.tolist() == want
