@@ -13,8 +13,9 @@
 //    page size works; shared-memory rows are XOR-swizzled for conflict-free ldmatrix;
 //  * scores, softmax statistics and the output accumulator are 32-bit; probabilities are rounded to
 //    bfloat16 only as the operand of the P*V product;
-//  * key tiles and decode splits are aligned to absolute positions (multiples of 64 / 256), so the order
-//    of a position's sums does not depend on the batch or on how the prompt was cut.
+//  * key tiles are aligned to absolute positions (multiples of 64), so the order of a position's sums in a
+//    prefill does not depend on the batch or on how the prompt was cut; decode splits are aligned multiples
+//    of 256 keys whose size follows the batch size (a difference of rounding only).
 //
 // A query at position p reads keys [start(p), p], start(p) = max(chunk ? p - p % chunk : 0,
 // window ? p - window + 1 : 0).  Temperature: scores of a layer with attn_scale != 0 are multiplied by
@@ -22,7 +23,8 @@
 #include "common.cuh"
 
 #define KT 64            // keys per tile
-#define SPLIT 128        // keys per decode split (2 tiles, 64 KB of shared memory: three blocks per SM), aligned to absolute positions
+#define SPLIT_UNIT 256   // decode splits are multiples of this many keys, aligned to absolute positions
+#define DEC_STAGES 3     // key/value tiles in flight per decode block (96 KB at head size 128: two blocks per SM)
 #define NEG_BIG (-1.0e30f)
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -70,6 +72,7 @@ struct AttnParams {
   float* part_o;        // [N, Hq, max_splits, DH]
   float* part_ml;       // [N, Hq, max_splits, 2]
   int max_splits;
+  int split_keys;       // keys per decode split (a multiple of SPLIT_UNIT)
 };
 
 __device__ __forceinline__ int first_key(int p, int chunk, int window) {
@@ -117,28 +120,30 @@ __device__ __forceinline__ void load_kv_tile(const AttnParams& P, int r, int hk,
 }
 
 // ------------------------------------------------------------------------------------ decode
-// grid (max_splits, Hkv, R); 128 threads, TILES = 2 key tiles per block.  Rows of the score tile = the G query heads (G <= 16).
-// Warp w takes keys [16 w, 16 w + 16) of every 64-key tile; the four warps' results are merged in
-// shared memory and written as one partial (unnormalised output, max, sum) per (token, head, split).
+// grid (max_splits, Hkv, R); 128 threads.  Rows of the score tile = the G query heads (G <= 16).  A block
+// walks the 64-key tiles of its split through a ring of DEC_STAGES shared-memory stages; warp w takes keys
+// [16 w, 16 w + 16) of every tile.  The four warps' results are merged in shared memory and written as one
+// partial (unnormalised output, max, sum) per (token, head, split).  The host sizes the splits so that a
+// few hundred blocks share the GPU: short-lived blocks would spend their time on set-up.
 template <int DH>
 __global__ void __launch_bounds__(128) attention_decode_kernel(const AttnParams P) {
   extern __shared__ __align__(128) uint8_t smem[];
-  constexpr int TILES = SPLIT / KT;
   constexpr int CH = DH / 8;
-  bf16* ks = reinterpret_cast<bf16*>(smem);                  // [TILES][KT][DH]
-  bf16* vs = ks + TILES * KT * DH;                           // [TILES][KT][DH]
+  bf16* ks = reinterpret_cast<bf16*>(smem);                  // [DEC_STAGES][KT][DH]
+  bf16* vs = ks + DEC_STAGES * KT * DH;                      // [DEC_STAGES][KT][DH]
   const int n = blockIdx.z, hk = blockIdx.y, split = blockIdx.x;
   const int G = P.Hq / P.Hkv;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int p = P.positions[n], r = P.req_of_token[n];
   const int lo = first_key(p, P.chunk, P.window);
-  const int key_begin = (lo / SPLIT + split) * SPLIT;
+  const int key_begin = (lo / P.split_keys + split) * P.split_keys;
   if (key_begin > p) return;
+  const int key_end = min(p + 1, key_begin + P.split_keys);
+  const int n_tiles = (key_end - key_begin + KT - 1) / KT;
 
-  // all tiles of the split are requested at once; they are consumed as they land
 #pragma unroll
-  for (int t = 0; t < TILES; ++t) {
-    load_kv_tile<DH>(P, r, hk, key_begin + t * KT, lo, p, ks + t * KT * DH, vs + t * KT * DH, 128);
+  for (int t = 0; t < DEC_STAGES - 1; ++t) {
+    if (t < n_tiles) load_kv_tile<DH>(P, r, hk, key_begin + t * KT, lo, p, ks + t * KT * DH, vs + t * KT * DH, 128);
     cp_async_commit();
   }
 
@@ -162,15 +167,17 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttnParams 
 #pragma unroll
   for (int i = 0; i < DH / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
 
-#pragma unroll
-  for (int t = 0; t < TILES; ++t) {
-    if (t == 0) cp_async_wait<TILES - 1>();
-    else cp_async_wait<0>();
-    __syncthreads();
+  for (int t = 0; t < n_tiles; ++t) {
+    cp_async_wait<DEC_STAGES - 2>();  // tile t has landed
+    __syncthreads();                  // ... for every thread, and the stage of tile t - 1 is free
+    {
+      const int nt = t + DEC_STAGES - 1, st = nt % DEC_STAGES;
+      if (nt < n_tiles) load_kv_tile<DH>(P, r, hk, key_begin + nt * KT, lo, p, ks + st * KT * DH, vs + st * KT * DH, 128);
+      cp_async_commit();
+    }
     const int tile_key = key_begin + t * KT;
-    if (tile_key > p) break;  // uniform
-    const bf16* kt = ks + t * KT * DH;
-    const bf16* vt = vs + t * KT * DH;
+    const bf16* kt = ks + (t % DEC_STAGES) * KT * DH;
+    const bf16* vt = vs + (t % DEC_STAGES) * KT * DH;
     // S = Q K^T for this warp's 16 keys: two n-tiles of 8 keys
     float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
@@ -276,19 +283,26 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttnParams 
 // out[n, h, :] = sum_s o_s 2^(m_s - m) / sum_s l_s 2^(m_s - m), splits in ascending order.
 template <int DH>
 __global__ void attention_combine_kernel(const AttnParams P) {
+  __shared__ float wgt[512];
   const int n = blockIdx.x, h = blockIdx.y;
   const int p = P.positions[n];
   const int lo = first_key(p, P.chunk, P.window);
-  const int splits = p / SPLIT - lo / SPLIT + 1;
+  const int splits = p / P.split_keys - lo / P.split_keys + 1;
   const size_t row = ((size_t)n * P.Hq + h) * P.max_splits;
   float mm = NEG_BIG;
   for (int s = 0; s < splits; ++s) mm = fmaxf(mm, P.part_ml[(row + s) * 2]);
   float ll = 0.f;
   for (int s = 0; s < splits; ++s) ll += P.part_ml[(row + s) * 2 + 1] * exp2f(P.part_ml[(row + s) * 2] - mm);
+  const bool cached = splits <= 512;
+  if (cached) {
+    for (int s = threadIdx.x; s < splits; s += blockDim.x) wgt[s] = exp2f(P.part_ml[(row + s) * 2] - mm) / ll;
+    __syncthreads();
+  }
   for (int d = threadIdx.x; d < DH; d += blockDim.x) {
     float acc = 0.f;
-    for (int s = 0; s < splits; ++s) acc += P.part_o[(row + s) * DH + d] * exp2f(P.part_ml[(row + s) * 2] - mm);
-    P.out[((size_t)n * P.Hq + h) * DH + d] = __float2bfloat16_rn(acc / ll);
+    for (int s = 0; s < splits; ++s)
+      acc += P.part_o[(row + s) * DH + d] * (cached ? wgt[s] : exp2f(P.part_ml[(row + s) * 2] - mm) / ll);
+    P.out[((size_t)n * P.Hq + h) * DH + d] = __float2bfloat16_rn(acc);
   }
 }
 
@@ -450,7 +464,7 @@ static int fill_params(AttnParams& P, const void* q, const void* pages, const in
   P.req_of_token = req_of_token; P.positions = positions; P.out = (bf16*)out; P.Hq = Hq; P.Hkv = Hkv;
   P.page_size = page_size; P.num_pages = num_pages; P.scale_log2 = scale * 1.4426950408889634f;
   P.chunk = chunk; P.window = window; P.attn_scale = attn_scale; P.floor_scale = floor_scale; P.status = status;
-  P.tiles = nullptr; P.part_o = nullptr; P.part_ml = nullptr; P.max_splits = 0;
+  P.tiles = nullptr; P.part_o = nullptr; P.part_ml = nullptr; P.max_splits = 0; P.split_keys = SPLIT_UNIT;
   return 0;
 }
 
@@ -460,29 +474,42 @@ JLX_API int jlx_attention_mma_supported(int Hq, int Hkv, int dh, int decode) {
   return (dh == 64 || dh == 128) && G <= (decode ? 16 : 8);
 }
 
-// Splits a decode launch needs for requests of up to max_kv_len keys.
-JLX_API int jlx_attention_decode_splits(int max_kv_len, int chunk, int window) {
+// Keys per decode split for `pairs` (request, KV head) pairs that read up to max_kv_len keys: a multiple
+// of SPLIT_UNIT chosen so that about four blocks per SM exist (two resident, two waiting).
+JLX_API int jlx_attention_decode_split_keys(int max_kv_len, int chunk, int window, int pairs) {
   int span = max_kv_len;
   if (chunk > 0 && chunk < span) span = chunk;
   if (window > 0 && window < span) span = window;
-  return (span + SPLIT - 1) / SPLIT + 1;
+  const int want_splits = (4 * 148 + pairs - 1) / (pairs > 0 ? pairs : 1);
+  int keys = (span + want_splits - 1) / (want_splits > 0 ? want_splits : 1);
+  keys = (keys + SPLIT_UNIT - 1) / SPLIT_UNIT * SPLIT_UNIT;
+  return keys < SPLIT_UNIT ? SPLIT_UNIT : keys;
+}
+
+// Splits a decode launch needs for requests of up to max_kv_len keys with that split size.
+JLX_API int jlx_attention_decode_splits(int max_kv_len, int chunk, int window, int split_keys) {
+  int span = max_kv_len;
+  if (chunk > 0 && chunk < span) span = chunk;
+  if (window > 0 && window < span) span = window;
+  return (span + split_keys - 1) / split_keys + 1;
 }
 
 // One query token per request.  part_o: float [N * Hq * max_splits * dh]; part_ml: float [N * Hq * max_splits * 2].
 JLX_API int jlx_attention_decode(const void* q, const void* pages, const int* block_table, int bt_stride,
                                  const int* req_of_token, const int* positions, void* out, int N, int Hq, int Hkv, int dh,
                                  int page_size, int num_pages, float scale, int chunk, int window, float attn_scale,
-                                 float floor_scale, float* part_o, float* part_ml, int max_splits, int* status,
-                                 cudaStream_t stream) {
+                                 float floor_scale, float* part_o, float* part_ml, int max_splits, int split_keys,
+                                 int* status, cudaStream_t stream) {
   AttnParams P;
   if (fill_params(P, q, pages, block_table, bt_stride, req_of_token, positions, out, Hq, Hkv, dh, page_size, num_pages,
                   scale, chunk, window, attn_scale, floor_scale, status)) return 1;
   JLX_REQUIRE(Hq / Hkv <= 16, "attention_decode: %d query heads per KV head; up to 16 are supported", Hq / Hkv);
   JLX_REQUIRE(part_o && part_ml && max_splits > 0, "attention_decode: scratch for the partial results is missing");
+  JLX_REQUIRE(split_keys > 0 && split_keys % SPLIT_UNIT == 0, "attention_decode: split size %d is no multiple of %d", split_keys, SPLIT_UNIT);
   JLX_REQUIRE(N <= 65535 && Hkv <= 65535, "attention_decode: too many rows");
   if (N == 0) return 0;
-  P.part_o = part_o; P.part_ml = part_ml; P.max_splits = max_splits;
-  const size_t smem = (size_t)2 * SPLIT * dh * 2;
+  P.part_o = part_o; P.part_ml = part_ml; P.max_splits = max_splits; P.split_keys = split_keys;
+  const size_t smem = (size_t)2 * DEC_STAGES * KT * dh * 2;
   dim3 grid(max_splits, Hkv, N);
   if (dh == 128) {
     static bool cfg = false;

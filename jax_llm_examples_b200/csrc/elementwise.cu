@@ -38,7 +38,7 @@ JLX_API int jlx_embed(const int* ids, const void* table, int table_dtype, float*
 // normed row . w_router[e] in 32-bit, top-k of the raw scores (lower index wins ties), weight = sigmoid.
 #define ROUTER_MAX_E 256
 template <typename TO>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, int delta_splits, long long delta_stride,
                    const float* __restrict__ gamma, float eps, TO* __restrict__ out, float* __restrict__ out32,
                    const int* __restrict__ row_index, int D, int row_in_smem, const float* __restrict__ w_router, int E,
@@ -81,9 +81,16 @@ add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, int d
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
   for (int e = warp; e < E; e += nwarp) {
     const float* wr = w_router + (size_t)e * D;
-    float s = 0.f;
-    for (int d = lane; d < D; d += 32) s = fmaf(rowbuf[d], wr[d], s);
-    s = warp_sum(s);
+    float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+    int d = lane;
+    for (; d + 96 < D; d += 128) {
+      s0 = fmaf(rowbuf[d], wr[d], s0);
+      s1 = fmaf(rowbuf[d + 32], wr[d + 32], s1);
+      s2 = fmaf(rowbuf[d + 64], wr[d + 64], s2);
+      s3 = fmaf(rowbuf[d + 96], wr[d + 96], s3);
+    }
+    for (; d < D; d += 32) s0 = fmaf(rowbuf[d], wr[d], s0);
+    const float s = warp_sum((s0 + s1) + (s2 + s3));
     if (lane == 0) scores[e] = s;
   }
   __syncthreads();
@@ -127,7 +134,9 @@ JLX_API int jlx_add_rmsnorm(float* x, const float* delta, int delta_splits, long
       static bool cfg = false;
       if (!cfg) { JLX_CUDA(cudaFuncSetAttribute(add_rmsnorm_kernel<TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024)); cfg = true; }
     }
-    add_rmsnorm_kernel<TO><<<N, 256, smem, stream>>>(x, delta, delta_splits, delta_stride, gamma, eps, (TO*)out, out32,
+    // wide rows with few tokens are latency-bound: more threads per row keep more loads in flight
+    const int threads = D >= 2048 ? 1024 : 256;
+    add_rmsnorm_kernel<TO><<<N, threads, smem, stream>>>(x, delta, delta_splits, delta_stride, gamma, eps, (TO*)out, out32,
                                                      row_index, D, row_in_smem, w_router, E, k, topk_idx, topk_w);
   });
   JLX_LAUNCH_CHECK("add_rmsnorm");

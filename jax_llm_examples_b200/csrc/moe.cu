@@ -123,14 +123,16 @@ __global__ void permute_scale_kernel(const float* __restrict__ h, const int* __r
   const float w = topk_w[pair];
   const float* src = h + (size_t)(pair / k) * D;
   T* dst = a_sorted + (size_t)i * D;
-  for (int d = threadIdx.x; d < D; d += blockDim.x) dst[d] = from_f32<T>(w * src[d]);
+  for (int d = blockIdx.y * blockDim.x + threadIdx.x; d < D; d += gridDim.y * blockDim.x) dst[d] = from_f32<T>(w * src[d]);
 }
 
 JLX_API int jlx_permute_scale(const float* h, const int* sorted_pair, const float* topk_w, void* a_sorted, int dtype,
                               int P, int D, int k, cudaStream_t stream) {
   JLX_REQUIRE(P >= 0 && D > 0 && k >= 1, "permute_scale: bad sizes");
   if (P == 0) return 0;
-  JLX_DISPATCH_DTYPE(dtype, T, (permute_scale_kernel<T><<<P, 256, 0, stream>>>(h, sorted_pair, topk_w, (T*)a_sorted, D, k)));
+  // few rows: spread each row over several blocks
+  const int ysplit = P >= 512 ? 1 : (D + 1023) / 1024;
+  JLX_DISPATCH_DTYPE(dtype, T, (permute_scale_kernel<T><<<dim3(P, ysplit), 256, 0, stream>>>(h, sorted_pair, topk_w, (T*)a_sorted, D, k)));
   JLX_LAUNCH_CHECK("permute_scale");
   return 0;
 }
@@ -141,7 +143,7 @@ __global__ void moe_combine_kernel(const float* __restrict__ y_sorted, const flo
                                    long long split_stride, const int* __restrict__ sorted_pos, float* __restrict__ delta,
                                    int D, int k) {
   const int n = blockIdx.x;
-  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+  for (int d = blockIdx.y * blockDim.x + threadIdx.x; d < D; d += gridDim.y * blockDim.x) {
     float s = 0.f;
     if (shared)
       for (int z = 0; z < splits; ++z) s += shared[(size_t)z * split_stride + (size_t)n * D + d];
@@ -154,7 +156,8 @@ JLX_API int jlx_moe_combine(const float* y_sorted, const float* shared, int spli
                             const int* sorted_pos, float* delta, int N, int D, int k, cudaStream_t stream) {
   JLX_REQUIRE(N >= 0 && D > 0 && k >= 1 && splits >= 1, "moe_combine: bad sizes");
   if (N == 0) return 0;
-  moe_combine_kernel<<<N, 256, 0, stream>>>(y_sorted, shared, splits, split_stride, sorted_pos, delta, D, k);
+  const int ysplit = N >= 512 ? 1 : (D + 1023) / 1024;
+  moe_combine_kernel<<<dim3(N, ysplit), 256, 0, stream>>>(y_sorted, shared, splits, split_stride, sorted_pos, delta, D, k);
   JLX_LAUNCH_CHECK("moe_combine");
   return 0;
 }

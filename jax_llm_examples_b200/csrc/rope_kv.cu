@@ -19,8 +19,9 @@ rope_kv_store_kernel(const TI* __restrict__ qkv, int splits, long long split_str
                      const float* __restrict__ inv_freq, int l2norm, float eps, int Hq, int Hkv, int dh, int page_size,
                      int num_pages, int store_kv, int* status) {
   extern __shared__ float sc[];  // [dh / 2][2]: sine and cosine of this token's angles
+  // grid (tokens, head groups): each block takes up to 8 heads of one token, one per warp
   const int n = blockIdx.x;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int pos = positions[n];
   const int heads = Hq + 2 * Hkv;
   const int half = dh >> 1;
@@ -44,7 +45,7 @@ rope_kv_store_kernel(const TI* __restrict__ qkv, int splits, long long split_str
     }
   }
 
-  for (int h = warp; h < heads; h += nwarp) {
+  for (int h = blockIdx.y * 8 + warp; h < min(heads, (int)blockIdx.y * 8 + 8); h += 8) {
     const TI* src = row + (size_t)h * dh;
     if (h >= Hq + Hkv) {  // value head: copy (sum of the partials)
       if (vdst) {
@@ -108,10 +109,11 @@ JLX_API int jlx_rope_kv_store(const void* qkv, int in_dtype, int splits, long lo
   JLX_REQUIRE(dh <= 8192, "rope_kv_store: head size %d is above the supported maximum 8192", dh);
   JLX_REQUIRE(!store_kv || (page_size > 0 && num_pages > 0 && bt_stride > 0), "rope_kv_store: bad cache sizes");
   JLX_REQUIRE(splits >= 1 && (splits == 1 || in_dtype == JLX_F32), "rope_kv_store: split-K partials are float32");
+  JLX_REQUIRE((Hq + 2 * Hkv + 7) / 8 <= 65535, "rope_kv_store: too many heads");
   if (N == 0) return 0;
   const size_t smem = (size_t)dh * sizeof(float);
   JLX_DISPATCH_DTYPE(in_dtype, TI, JLX_DISPATCH_DTYPE(dtype, T,
-                     (rope_kv_store_kernel<TI, T><<<N, 256, smem, stream>>>(
+                     (rope_kv_store_kernel<TI, T><<<dim3(N, (Hq + 2 * Hkv + 7) / 8), 256, smem, stream>>>(
                          (const TI*)qkv, splits, split_stride, (T*)q_out, (T*)pages, block_table, bt_stride, req_of_token,
                          positions, inv_freq, l2norm, eps, Hq, Hkv, dh, page_size, num_pages, store_kv, status))));
   JLX_LAUNCH_CHECK("rope_kv_store");

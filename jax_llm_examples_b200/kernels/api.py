@@ -194,13 +194,16 @@ def attention_mma_supported(q_dtype: torch.dtype, Hq: int, Hkv: int, dh: int, de
     return bool(library("attention_mma").jlx_attention_mma_supported(c_int(Hq), c_int(Hkv), c_int(dh), c_int(int(decode))))
 
 
-def attention_decode_splits(max_kv_len: int, chunk: int, window: int) -> int:
-    return int(library("attention_mma").jlx_attention_decode_splits(c_int(max_kv_len), c_int(chunk), c_int(window)))
+def attention_decode_plan(max_kv_len: int, chunk: int, window: int, pairs: int) -> tuple[int, int]:
+    """(keys per split, splits) for a decode launch over `pairs` (request, KV head) pairs."""
+    lib = library("attention_mma")
+    keys = int(lib.jlx_attention_decode_split_keys(c_int(max_kv_len), c_int(chunk), c_int(window), c_int(pairs)))
+    return keys, int(lib.jlx_attention_decode_splits(c_int(max_kv_len), c_int(chunk), c_int(window), c_int(keys)))
 
 
 def attention_decode(q: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor, req_of_token: torch.Tensor,
                      positions: torch.Tensor, out: torch.Tensor, scale: float, chunk: int, window: int, attn_scale: float,
-                     floor_scale: float, part_o: torch.Tensor, part_ml: torch.Tensor, max_splits: int,
+                     floor_scale: float, part_o: torch.Tensor, part_ml: torch.Tensor, max_splits: int, split_keys: int,
                      status: torch.Tensor) -> None:
     """Split-KV attention for one query token per request (tensor cores, bfloat16).
     part_o: float32 [N * Hq * max_splits * dh]; part_ml: float32 [N * Hq * max_splits * 2]."""
@@ -212,7 +215,7 @@ def attention_decode(q: torch.Tensor, pages: torch.Tensor, block_table: torch.Te
     _run("attention_mma", "jlx_attention_decode", _ptr(q), _ptr(pages), _ptr(block_table), c_int(block_table.shape[1]),
          _ptr(req_of_token), _ptr(positions), _ptr(out), c_int(N), c_int(Hq), c_int(Hkv), c_int(dh), c_int(page_size),
          c_int(P), c_float(scale), c_int(chunk), c_int(window), c_float(attn_scale), c_float(floor_scale), _ptr(part_o),
-         _ptr(part_ml), c_int(max_splits), _ptr(status), _stream())
+         _ptr(part_ml), c_int(max_splits), c_int(split_keys), _ptr(status), _stream())
 
 
 def attention_prefill(q: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor, req_of_token: torch.Tensor,

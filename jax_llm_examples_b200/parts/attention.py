@@ -67,12 +67,12 @@ class PagedAttention(Mixer):
         decode = ctx.max_q_len == 1
         if K.attention_mma_supported(q.dtype, self.n_heads, self.n_kv_heads, self.head_dim, decode):
             if decode:
-                splits = K.attention_decode_splits(ctx.max_kv_len, chunk, window)
+                split_keys, splits = K.attention_decode_plan(ctx.max_kv_len, chunk, window, q.shape[0] * self.n_kv_heads)
                 n = q.shape[0] * self.n_heads * splits
                 part_o = ctx.workspace.get("attn_part_o", n * self.head_dim, torch.float32)
                 part_ml = ctx.workspace.get("attn_part_ml", n * 2, torch.float32)
                 K.attention_decode(q, cache.pages, cache.block_table, ctx.req_of_token, ctx.positions, out, self.scale,
-                                   chunk, window, attn_scale, floor_scale, part_o, part_ml, splits, ctx.status)
+                                   chunk, window, attn_scale, floor_scale, part_o, part_ml, splits, split_keys, ctx.status)
                 return
             if ctx.attn_tiles is not None:
                 K.attention_prefill(q, cache.pages, cache.block_table, ctx.req_of_token, ctx.positions, out,

@@ -358,14 +358,17 @@ def test_attention_decode_mma(Hq, Hkv, dh, page, chunk, window, temp):
     attn_scale, floor_scale = (0.1, 256.0) if temp else (0.0, 1.0)
     api = K()
     assert api.attention_mma_supported(q.dtype, Hq, Hkv, dh, True)
-    splits = api.attention_decode_splits(max(lens), chunk, window)
-    n = q.shape[0] * Hq * splits
-    part_o, part_ml = torch.empty(n * dh, device=DEV), torch.empty(n * 2, device=DEV)
-    api.attention_decode(q, pages, bt, req, pos, out, dh ** -0.5, chunk, window, attn_scale, floor_scale, part_o, part_ml, splits, st)
-    assert int(st) == 0
-    for r in range(len(lens)):
-        ref = _attention_ref(q[r:r + 1], ks[r], vs[r], pos[r:r + 1].long(), chunk, window, dh ** -0.5, attn_scale, floor_scale)
-        close(out[r:r + 1], ref, 1.5e-2)
+    for pairs in (len(lens) * Hkv, 4000):  # few pairs: short splits; many pairs: one long split each
+        keys, splits = api.attention_decode_plan(max(lens), chunk, window, pairs)
+        n = q.shape[0] * Hq * splits
+        part_o, part_ml = torch.empty(n * dh, device=DEV), torch.empty(n * 2, device=DEV)
+        out.fill_(float("nan"))
+        api.attention_decode(q, pages, bt, req, pos, out, dh ** -0.5, chunk, window, attn_scale, floor_scale, part_o, part_ml,
+                             splits, keys, st)
+        assert int(st) == 0
+        for r in range(len(lens)):
+            ref = _attention_ref(q[r:r + 1], ks[r], vs[r], pos[r:r + 1].long(), chunk, window, dh ** -0.5, attn_scale, floor_scale)
+            close(out[r:r + 1], ref, 1.5e-2)
 
 
 @pytest.mark.parametrize("Hq, Hkv, dh, page, chunk, window, temp", [
@@ -404,9 +407,9 @@ def test_mma_attention_finds_one_far_key():
         q[..., 0] = 40.0
         want = pages[pg, 1, :, slot].float().repeat_interleave(Hq // Hkv, 0)
         out, st = torch.empty_like(q), status()
-        splits = api.attention_decode_splits(2000, 0, 0)
+        keys, splits = api.attention_decode_plan(2000, 0, 0, Hkv)
         part_o, part_ml = torch.empty(Hq * splits * dh, device=DEV), torch.empty(Hq * splits * 2, device=DEV)
-        api.attention_decode(q, pages, bt, req, pos, out, dh ** -0.5, 0, 0, 0.0, 1.0, part_o, part_ml, splits, st)
+        api.attention_decode(q, pages, bt, req, pos, out, dh ** -0.5, 0, 0, 0.0, 1.0, part_o, part_ml, splits, keys, st)
         close(out[0], want, 1e-2)
         out2 = torch.empty_like(q)
         api.attention_prefill(q, pages, bt, req, pos, out2, torch.tensor([[0, 1]], device=DEV, dtype=torch.int32), 1,
