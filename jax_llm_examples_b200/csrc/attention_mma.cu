@@ -20,10 +20,13 @@
 // A query at position p reads keys [start(p), p], start(p) = max(chunk ? p - p % chunk : 0,
 // window ? p - window + 1 : 0).  Temperature: scores of a layer with attn_scale != 0 are multiplied by
 // 1 + attn_scale * ln(1 + floor((p + 1) / floor_scale)).
+#include <cuda.h>
+
 #include "common.cuh"
 
 #define KT 64            // keys per tile
-#define SPLIT_UNIT 256   // decode splits are multiples of this many keys, aligned to absolute positions
+#define SPLIT_UNIT 64    // decode splits are multiples of this many keys (one tile), aligned to absolute positions
+#define SPLIT_MIN 256    // ... and at least this long: shorter blocks spend their time on set-up
 #define DEC_STAGES 3     // key/value tiles in flight per decode block (96 KB at head size 128: two blocks per SM)
 #define NEG_BIG (-1.0e30f)
 
@@ -51,6 +54,32 @@ __device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// ---- TMA and mbarrier (decode kernel: whole [rows, 64-element] boxes of a page per instruction)
+#define WAIT_LIMIT (1u << 22)
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {  // bounded: false = gave up
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
 }
 
 struct AttnParams {
@@ -87,35 +116,32 @@ __device__ __forceinline__ float temperature(int p, float attn_scale, float floo
 }
 
 // Loads keys [key0, key0 + KT) of request r, KV head hk, into ks / vs (each [KT][DH], swizzled).
-// Keys outside [lo, hi] or without a page become zeros.  A pair of threads takes one key row (one
-// block-table lookup per row and thread), half of its 16-byte chunks each.
+// Keys outside [lo, hi] or without a page become zeros.  Consecutive threads take consecutive 16-byte
+// chunks of a row, so a warp's copy covers whole rows: full 128-byte lines from L2.
 template <int DH>
 __device__ __forceinline__ void load_kv_tile(const AttnParams& P, int r, int hk, int key0, int lo, int hi, bf16* ks, bf16* vs,
                                              int NT) {
   constexpr int CH = DH / 8;              // 16-byte chunks per row
   const size_t v_off = (size_t)P.Hkv * P.page_size * DH;
-  const int half = threadIdx.x & 1;
-  for (int j = threadIdx.x >> 1; j < KT; j += NT >> 1) {
+  const int c = threadIdx.x % CH;
+  const int* table = P.block_table + (size_t)r * P.bt_stride;
+  for (int j = threadIdx.x / CH; j < KT; j += NT / CH) {
     const int pos = key0 + j;
     bool valid = pos >= lo && pos <= hi;
     const bf16* src = P.pages;
     if (valid) {
       const int pi = pos / P.page_size;
-      const int page = P.block_table[(size_t)r * P.bt_stride + pi];
+      const int page = table[pi];
       if (page < 0 || page >= P.num_pages) {
         atomicOr(P.status, JLX_STATUS_BAD_PAGE);
         valid = false;
       } else {
-        src = P.pages + (size_t)page * 2 * v_off + ((size_t)hk * P.page_size + (pos - pi * P.page_size)) * DH;
+        src = P.pages + (size_t)page * 2 * v_off + ((size_t)hk * P.page_size + (pos - pi * P.page_size)) * DH + c * 8;
       }
     }
-#pragma unroll
-    for (int i = 0; i < CH / 2; ++i) {
-      const int c = half * (CH / 2) + i;
-      const int sw = (j * CH + (c ^ (j & 7))) * 8;
-      cp_async16(smem_u32(ks + sw), valid ? src + c * 8 : src, valid);
-      cp_async16(smem_u32(vs + sw), valid ? src + v_off + c * 8 : src, valid);
-    }
+    const int sw = (j * CH + (c ^ (j & 7))) * 8;
+    cp_async16(smem_u32(ks + sw), src, valid);
+    cp_async16(smem_u32(vs + sw), valid ? src + v_off : src, valid);
   }
 }
 
@@ -243,6 +269,199 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttnParams 
   __syncthreads();
   // merge the four warps: shared memory is reused as float [4][16][DH + 2]
   float* red = reinterpret_cast<float*>(smem);
+  constexpr int LD = DH + 2;
+  {
+    const int r0 = lane >> 2, r1 = r0 + 8, col = (lane & 3) * 2;
+    float* w0 = red + (warp * 16 + r0) * LD;
+    float* w1 = red + (warp * 16 + r1) * LD;
+#pragma unroll
+    for (int i = 0; i < DH / 8; ++i) {
+      w0[i * 8 + col] = o[i][0]; w0[i * 8 + col + 1] = o[i][1];
+      w1[i * 8 + col] = o[i][2]; w1[i * 8 + col + 1] = o[i][3];
+    }
+    if ((lane & 3) == 0) {
+      w0[DH] = m[0]; w0[DH + 1] = l[0];
+      w1[DH] = m[1]; w1[DH + 1] = l[1];
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < G * DH; idx += 128) {
+    const int g = idx / DH, d = idx % DH;
+    float mm = NEG_BIG;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) mm = fmaxf(mm, red[(w * 16 + g) * LD + DH]);
+    float acc = 0.f, ll = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float f = exp2f(red[(w * 16 + g) * LD + DH] - mm);
+      acc += red[(w * 16 + g) * LD + d] * f;
+      ll += red[(w * 16 + g) * LD + DH + 1] * f;
+    }
+    const size_t row = ((size_t)n * P.Hq + hk * G + g) * P.max_splits + split;
+    P.part_o[row * DH + d] = acc;
+    if (d == 0) {
+      P.part_ml[row * 2] = mm;
+      P.part_ml[row * 2 + 1] = ll;
+    }
+  }
+}
+
+// The same decode kernel with the tiles brought in by TMA: the cache of one layer is a 2-D tensor
+// [pages * 2 * Hkv * page_size rows, DH] and a 64-key tile of one KV head is 64 / BOX_ROWS boxes of
+// [BOX_ROWS rows, 64 elements] per 128 bytes of head (BOX_ROWS = min(page_size, 64)), written to shared
+// memory with the 128-byte swizzle.  One thread issues the copies and the others wait on an mbarrier per
+// stage: no per-lane copy instructions, so the load/store units stay free and the queue stays deep.
+// Rows of keys outside [lo, p] are copied too (from page 0 where the block table has no page); their
+// scores are masked, and their values are finite numbers written by this engine, so 0 * value = 0.
+template <int DH>
+__global__ void __launch_bounds__(128)
+attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map, const AttnParams P, int box_rows) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  constexpr int HALVES = DH / 64;                 // 128-byte column blocks per row
+  constexpr uint32_t HALF_BYTES = KT * 128;       // one [64 keys][64 elements] block
+  constexpr uint32_t STAGE_BYTES = 2 * HALVES * HALF_BYTES;  // K and V
+  __shared__ __align__(8) uint64_t full_bar[DEC_STAGES];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const int n = blockIdx.z, hk = blockIdx.y, split = blockIdx.x;
+  const int G = P.Hq / P.Hkv;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int p = P.positions[n], r = P.req_of_token[n];
+  const int lo = first_key(p, P.chunk, P.window);
+  const int key_begin = (lo / P.split_keys + split) * P.split_keys;
+  if (key_begin > p) return;
+  const int key_end = min(p + 1, key_begin + P.split_keys);
+  const int n_tiles = (key_end - key_begin + KT - 1) / KT;
+  const int* table = P.block_table + (size_t)r * P.bt_stride;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < DEC_STAGES; ++s) mbar_init(smem_u32(&full_bar[s]), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  // producer: thread 0 issues all boxes of a tile
+  auto issue = [&](int t) {
+    const int st = t % DEC_STAGES;
+    const uint32_t bar = smem_u32(&full_bar[st]);
+    const uint32_t dst = base + st * STAGE_BYTES;
+    mbar_expect_tx(bar, STAGE_BYTES);
+    const int key0 = key_begin + t * KT;
+    for (int b = 0; b < KT / box_rows; ++b) {
+      const int pos = key0 + b * box_rows;
+      const int pi = pos / P.page_size;
+      int page = pi < P.bt_stride ? table[pi] : -1;
+      if (page >= P.num_pages) { atomicOr(P.status, JLX_STATUS_BAD_PAGE); page = 0; }
+      if (page < 0) page = 0;  // no page there: every key of the box is masked
+      const int row_k = ((page * 2 + 0) * P.Hkv + hk) * P.page_size + (pos - pi * P.page_size);
+      const int row_v = ((page * 2 + 1) * P.Hkv + hk) * P.page_size + (pos - pi * P.page_size);
+#pragma unroll
+      for (int h = 0; h < HALVES; ++h) {
+        tma_load_2d(dst + h * HALF_BYTES + b * box_rows * 128, &map, h * 64, row_k, bar);
+        tma_load_2d(dst + (HALVES + h) * HALF_BYTES + b * box_rows * 128, &map, h * 64, row_v, bar);
+      }
+    }
+  };
+  if (threadIdx.x == 0)
+    for (int t = 0; t < DEC_STAGES && t < n_tiles; ++t) issue(t);
+
+  uint32_t qf[DH / 16][4];
+  {
+    const int g0 = lane >> 2, g1 = g0 + 8, kk = (lane & 3) * 2;
+    const bf16* q0 = P.q + ((size_t)n * P.Hq + hk * G + g0) * DH;
+    const bf16* q1 = P.q + ((size_t)n * P.Hq + hk * G + g1) * DH;
+#pragma unroll
+    for (int s = 0; s < DH / 16; ++s) {
+      qf[s][0] = g0 < G ? *reinterpret_cast<const uint32_t*>(q0 + s * 16 + kk) : 0u;
+      qf[s][1] = g1 < G ? *reinterpret_cast<const uint32_t*>(q1 + s * 16 + kk) : 0u;
+      qf[s][2] = g0 < G ? *reinterpret_cast<const uint32_t*>(q0 + s * 16 + kk + 8) : 0u;
+      qf[s][3] = g1 < G ? *reinterpret_cast<const uint32_t*>(q1 + s * 16 + kk + 8) : 0u;
+    }
+  }
+  const float sc = P.scale_log2 * temperature(p, P.attn_scale, P.floor_scale);
+  float m[2] = {NEG_BIG, NEG_BIG}, l[2] = {0.f, 0.f};
+  float o[DH / 8][4];
+#pragma unroll
+  for (int i = 0; i < DH / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+
+  bool ok = true;
+  for (int t = 0; t < n_tiles; ++t) {
+    const int st = t % DEC_STAGES;
+    ok = __syncthreads_and(mbar_wait(smem_u32(&full_bar[st]), (t / DEC_STAGES) & 1));  // the same verdict for all
+    if (!ok) {
+      // a wait gave up: let the copies that are still under way land before the block leaves
+      if (threadIdx.x == 0) {
+        atomicOr(P.status, JLX_STATUS_WAIT_TIMEOUT);
+        for (int u = t + 1; u < n_tiles && u < t + DEC_STAGES; ++u) mbar_wait(smem_u32(&full_bar[u % DEC_STAGES]), (u / DEC_STAGES) & 1);
+      }
+      break;
+    }
+    const int tile_key = key_begin + t * KT;
+    const uint32_t kt = base + st * STAGE_BYTES, vt = kt + HALVES * HALF_BYTES;
+    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+    for (int kstep = 0; kstep < DH / 16; ++kstep) {
+      const int key = warp * 16 + (lane >> 4) * 8 + (lane & 7);
+      const int c = kstep * 2 + ((lane >> 3) & 1);  // 16-byte chunk of the row
+      uint32_t b0, b1, b2, b3;
+      ldmatrix_x4(kt + (c >> 3) * HALF_BYTES + key * 128 + (((c & 7) ^ (key & 7)) << 4), b0, b1, b2, b3);
+      mma_bf16(s[0], qf[kstep], b0, b1);
+      mma_bf16(s[1], qf[kstep], b2, b3);
+    }
+    float mx[2] = {m[0], m[1]};
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int key = tile_key + warp * 16 + nt * 8 + (lane & 3) * 2 + (e & 1);
+        const bool in = key >= lo && key <= p;
+        s[nt][e] = in ? s[nt][e] * sc : NEG_BIG;
+        mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
+      }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+    }
+    float corr[2], rs[2] = {0.f, 0.f};
+#pragma unroll
+    for (int h = 0; h < 2; ++h) corr[h] = exp2f(m[h] - mx[h]);
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float pv = s[nt][e] > 0.5f * NEG_BIG ? exp2f(s[nt][e] - mx[e >> 1]) : 0.f;
+        s[nt][e] = pv;
+        rs[e >> 1] += pv;
+      }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      rs[h] += __shfl_xor_sync(0xffffffffu, rs[h], 1);
+      rs[h] += __shfl_xor_sync(0xffffffffu, rs[h], 2);
+      l[h] = l[h] * corr[h] + rs[h];
+      m[h] = mx[h];
+    }
+#pragma unroll
+    for (int i = 0; i < DH / 8; ++i) {
+      o[i][0] *= corr[0]; o[i][1] *= corr[0]; o[i][2] *= corr[1]; o[i][3] *= corr[1];
+    }
+    uint32_t pa[4] = {pack_bf16(s[0][0], s[0][1]), pack_bf16(s[0][2], s[0][3]), pack_bf16(s[1][0], s[1][1]), pack_bf16(s[1][2], s[1][3])};
+#pragma unroll
+    for (int np = 0; np < DH / 16; ++np) {
+      const int key = warp * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+      const int c = np * 2 + (lane >> 4);
+      uint32_t b0, b1, b2, b3;
+      ldmatrix_x4_trans(vt + (c >> 3) * HALF_BYTES + key * 128 + (((c & 7) ^ (key & 7)) << 4), b0, b1, b2, b3);
+      mma_bf16(o[np * 2], pa, b0, b1);
+      mma_bf16(o[np * 2 + 1], pa, b2, b3);
+    }
+    __syncthreads();  // every warp is done reading this stage
+    if (threadIdx.x == 0 && t + DEC_STAGES < n_tiles) {
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // order those reads before the copy's writes
+      issue(t + DEC_STAGES);
+    }
+  }
+  if (!ok) return;
+  float* red = reinterpret_cast<float*>(smem_raw + (base - smem_u32(smem_raw)));
   constexpr int LD = DH + 2;
   {
     const int r0 = lane >> 2, r1 = r0 + 8, col = (lane & 3) * 2;
@@ -468,6 +687,37 @@ static int fill_params(AttnParams& P, const void* q, const void* pages, const in
   return 0;
 }
 
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+// The cache of one layer as rows of one head each: [num_pages * 2 * Hkv * page_size, dh], boxes of
+// [box_rows, 64 elements], 128-byte swizzle.
+static int make_cache_map(CUtensorMap* map, const void* pages, long long rows, int dh, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  JLX_REQUIRE(fn != nullptr, "attention_decode: the driver does not offer cuTensorMapEncodeTiled");
+  cuuint64_t dims[2] = {(cuuint64_t)dh, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)dh * 2};
+  cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+  cuuint32_t elem[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pages), dims, strides, box, elem,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  JLX_REQUIRE(r == CUDA_SUCCESS, "attention_decode: cuTensorMapEncodeTiled failed (%d)", (int)r);
+  return 0;
+}
+
 JLX_API int jlx_attention_mma_supported(int Hq, int Hkv, int dh, int decode) {
   if (Hkv <= 0 || Hq % Hkv) return 0;
   const int G = Hq / Hkv;
@@ -483,7 +733,7 @@ JLX_API int jlx_attention_decode_split_keys(int max_kv_len, int chunk, int windo
   const int want_splits = (4 * 148 + pairs - 1) / (pairs > 0 ? pairs : 1);
   int keys = (span + want_splits - 1) / (want_splits > 0 ? want_splits : 1);
   keys = (keys + SPLIT_UNIT - 1) / SPLIT_UNIT * SPLIT_UNIT;
-  return keys < SPLIT_UNIT ? SPLIT_UNIT : keys;
+  return keys < SPLIT_MIN ? SPLIT_MIN : keys;
 }
 
 // Splits a decode launch needs for requests of up to max_kv_len keys with that split size.
@@ -511,19 +761,36 @@ JLX_API int jlx_attention_decode(const void* q, const void* pages, const int* bl
   P.part_o = part_o; P.part_ml = part_ml; P.max_splits = max_splits; P.split_keys = split_keys;
   const size_t smem = (size_t)2 * DEC_STAGES * KT * dh * 2;
   dim3 grid(max_splits, Hkv, N);
-  if (dh == 128) {
+  // pages that hold whole 64-key tiles, or divide them, go through TMA; other page sizes through cp.async
+  const bool tma = (page_size % KT == 0 || KT % page_size == 0) && page_size >= 8 &&
+                   (long long)num_pages * 2 * Hkv * page_size < (1ll << 31);
+  if (tma) {
+    CUtensorMap map;
+    const int box_rows = page_size < KT ? page_size : KT;
+    if (make_cache_map(&map, pages, (long long)num_pages * 2 * Hkv * page_size, dh, box_rows)) return 1;
+    if (dh == 128) {
+      static bool cfg = false;
+      if (!cfg) { JLX_CUDA(cudaFuncSetAttribute(attention_decode_tma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem + 1024)); cfg = true; }
+      attention_decode_tma_kernel<128><<<grid, 128, smem + 1024, stream>>>(map, P, box_rows);
+    } else {
+      static bool cfg = false;
+      if (!cfg) { JLX_CUDA(cudaFuncSetAttribute(attention_decode_tma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem + 1024)); cfg = true; }
+      attention_decode_tma_kernel<64><<<grid, 128, smem + 1024, stream>>>(map, P, box_rows);
+    }
+    JLX_LAUNCH_CHECK("attention_decode_tma");
+  } else if (dh == 128) {
     static bool cfg = false;
     if (!cfg) { JLX_CUDA(cudaFuncSetAttribute(attention_decode_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); cfg = true; }
     attention_decode_kernel<128><<<grid, 128, smem, stream>>>(P);
     JLX_LAUNCH_CHECK("attention_decode");
-    attention_combine_kernel<128><<<dim3(N, Hq), 128, 0, stream>>>(P);
   } else {
     static bool cfg = false;
     if (!cfg) { JLX_CUDA(cudaFuncSetAttribute(attention_decode_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); cfg = true; }
     attention_decode_kernel<64><<<grid, 128, smem, stream>>>(P);
     JLX_LAUNCH_CHECK("attention_decode");
-    attention_combine_kernel<64><<<dim3(N, Hq), 64, 0, stream>>>(P);
   }
+  if (dh == 128) attention_combine_kernel<128><<<dim3(N, Hq), 128, 0, stream>>>(P);
+  else attention_combine_kernel<64><<<dim3(N, Hq), 64, 0, stream>>>(P);
   JLX_LAUNCH_CHECK("attention_combine");
   return 0;
 }

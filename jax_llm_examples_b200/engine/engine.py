@@ -98,6 +98,7 @@ class Engine:
         self.use_graphs = (self.runtime.dtype == torch.bfloat16) if use_graphs is None else use_graphs
         self._graphs: dict[tuple[int, int], dict] = {}
         self.graph_replays = 0
+        self.graph_kernel_launches = 0  # kernels of this package launched through graph replays
 
     # ------------------------------------------------------------------ requests
     def new_request(self) -> int:
@@ -181,6 +182,7 @@ class Engine:
         if static and "graph" in graph:
             graph["graph"].replay()
             self.graph_replays += 1
+            self.graph_kernel_launches += graph["kernels"]
             logits = graph["logits"]
         else:
             o = 0
@@ -206,11 +208,13 @@ class Engine:
             if static:
                 g = torch.cuda.CUDAGraph()
                 torch.cuda.synchronize()
+                before = K.launch_count()
                 with torch.cuda.graph(g):
                     logits = self.model.forward(ctx, self.kv, self.states, block_tables)
-                graph["graph"], graph["logits"] = g, logits
+                graph["graph"], graph["logits"], graph["kernels"] = g, logits, K.launch_count() - before
                 g.replay()
                 self.graph_replays += 1
+                self.graph_kernel_launches += graph["kernels"]
             else:
                 logits = self.model.forward(ctx, self.kv, self.states, block_tables)
             self.last_routing = ctx.scratch.get("record_routing", [])
