@@ -7,6 +7,7 @@
 // means argmax.  The draw here is Philox-4x32-10 keyed by (seed, request stream) with the request's
 // step as counter, so a request's tokens do not depend on what else is in the batch.
 #include "common.cuh"
+#include "sampling_noalloc.h"
 
 #define SAMPLE_MAX_K 64
 
@@ -212,6 +213,47 @@ JLX_API int jlx_argmax(const float* logits, int M, int V, long long ld, float* p
   JLX_REQUIRE(part_v && part_i, "argmax: scratch missing");
   JLX_REQUIRE(M <= 65535, "argmax: too many rows");
   if (M == 0) return 0;
+  argmax_chunk_kernel<<<dim3(ARGMAX_CHUNKS, M), 256, 0, stream>>>(logits, V, ld, part_v, part_i);
+  JLX_LAUNCH_CHECK("argmax_chunk");
+  argmax_final_kernel<<<M, 32, 0, stream>>>(part_v, part_i, out);
+  JLX_LAUNCH_CHECK("argmax_final");
+  return 0;
+}
+
+// ---- the variant for callers that cannot allocate: see sampling_noalloc.h for who they are and the rules.
+// Layout of the array: ARGMAX_CHUNKS * MAX_ROWS best values (float) followed by as many best indices (int).
+static __device__ __align__(256) unsigned char jlx_argmax_noalloc_scratch[JLX_ARGMAX_NOALLOC_MAX_ROWS * ARGMAX_CHUNKS * 8];
+
+// In host code the array's name stands for a host-side shadow, not for device memory: the device address
+// has to be asked for, once per device, while that device is current.
+static int noalloc_scratch_address(unsigned char** ptr) {
+  enum { MAX_DEVICES = 64 };
+  static unsigned char* cached[MAX_DEVICES] = {nullptr};
+  int dev = -1;
+  JLX_CUDA(cudaGetDevice(&dev));
+  JLX_REQUIRE(dev >= 0 && dev < MAX_DEVICES, "argmax_noalloc: device ordinal %d is outside 0..%d", dev, MAX_DEVICES - 1);
+  if (!cached[dev]) {
+    void* p = nullptr;
+    JLX_CUDA(cudaGetSymbolAddress(&p, jlx_argmax_noalloc_scratch));
+    JLX_REQUIRE(p != nullptr, "argmax_noalloc: the scratch array has no device address");
+    cached[dev] = static_cast<unsigned char*>(p);
+  }
+  *ptr = cached[dev];
+  return 0;
+}
+
+JLX_API int jlx_argmax_noalloc(const float* logits, int M, int V, long long ld, int* out, cudaStream_t stream) {
+  JLX_REQUIRE(M >= 0 && V > 0 && ld >= V, "argmax_noalloc: bad sizes M=%d V=%d", M, V);
+  JLX_REQUIRE(M <= JLX_ARGMAX_NOALLOC_MAX_ROWS,
+              "argmax_noalloc: %d rows, but the built-in scratch holds %d; use jlx_argmax with your own scratch", M,
+              JLX_ARGMAX_NOALLOC_MAX_ROWS);
+  JLX_REQUIRE(logits && out, "argmax_noalloc: null input or output");
+  if (M == 0) return 0;
+  unsigned char* base = nullptr;
+  if (noalloc_scratch_address(&base)) return 1;
+  float* part_v = reinterpret_cast<float*>(base);
+  int* part_i = reinterpret_cast<int*>(base + (size_t)JLX_ARGMAX_NOALLOC_MAX_ROWS * ARGMAX_CHUNKS * sizeof(float));
+  // every slot that the second kernel reads (M * ARGMAX_CHUNKS of each half) is written by the first
   argmax_chunk_kernel<<<dim3(ARGMAX_CHUNKS, M), 256, 0, stream>>>(logits, V, ld, part_v, part_i);
   JLX_LAUNCH_CHECK("argmax_chunk");
   argmax_final_kernel<<<M, 32, 0, stream>>>(part_v, part_i, out);
