@@ -32,4 +32,5 @@ def model_dirs(tmp_path_factory):
     return {
         "tiny_a": make_model_dir(root / "tiny_a", "tiny_a", seed=0, norm_noise=0.1),
         "tiny_b": make_model_dir(root / "tiny_b", "tiny_b", seed=1, norm_noise=0.0),
+        "tiny_c": make_model_dir(root / "tiny_c", "tiny_c", seed=2, norm_noise=0.05),
     }

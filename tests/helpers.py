@@ -4,6 +4,7 @@ from __future__ import annotations
 
 import functools
 import json
+import os
 import random
 from pathlib import Path
 
@@ -12,11 +13,29 @@ import torch
 
 from tests.plain import llama4_plain as plain
 
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+# A third tiny configuration, for the tensor-core kernels (head size 64, 3 query heads per KV head): the chunk
+# (80) is no multiple of the key tile (64) or of the test page size (16); MoE layers are given as a list;
+# llama3 scaling has equal low and high factors (no medium band).
+TINY_C = {
+    "architectures": ["Llama4ForCausalLM"], "model_type": "llama4_text",
+    "num_hidden_layers": 5, "hidden_size": 192, "num_attention_heads": 6, "num_key_value_heads": 2, "head_dim": 64,
+    "moe_layers": [0, 2, 3], "num_local_experts": 6, "num_experts_per_tok": 2, "intermediate_size": 96,
+    "intermediate_size_mlp": 160, "vocab_size": 320, "rope_theta": 50000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 4.0, "low_freq_factor": 2.0, "high_freq_factor": 2.0,
+                     "original_max_position_embeddings": 32},
+    "use_qk_norm": True, "attention_chunk_size": 80, "no_rope_layers": [1, 0, 1, 1, 0],
+    "attn_temperature_tuning": True, "floor_scale": 20.0, "attn_scale": 0.2, "rms_norm_eps": 1e-5,
+    "tie_word_embeddings": False,
+}
+
 
 def make_model_dir(path: Path, preset_name: str, seed: int, norm_noise: float = 0.0, dtype=torch.bfloat16, **overrides) -> Path:
     from jax_llm_examples_b200 import preset, write_random_model
 
-    return write_random_model(path, preset(preset_name, **overrides), seed, dtype=dtype, norm_noise=norm_noise)
+    cfg = dict(TINY_C, **overrides) if preset_name == "tiny_c" else preset(preset_name, **overrides)
+    return write_random_model(path, cfg, seed, dtype=dtype, norm_noise=norm_noise)
 
 
 @functools.lru_cache(maxsize=64)
@@ -39,6 +58,12 @@ def plain_logits(model_dir, tokens, routing: dict[int, np.ndarray] | None = None
         out = plain.forward(cfg, w, list(tokens), stats, routing).numpy()
     worst = max((float(g.max()) for g in stats.get("router_shortfall", {}).values()), default=0.0)
     return out, worst
+
+
+def as_rows_sum(x) -> torch.Tensor:
+    """What a part returned, as one tensor: split-K partials are added."""
+    data, splits = (x.data, x.splits) if hasattr(x, "splits") else (x, 1)
+    return data.sum(0) if splits > 1 or data.dim() == 3 else data
 
 
 def rel_err(a: np.ndarray, b: np.ndarray) -> float:
@@ -181,3 +206,13 @@ def compare_with_plain(model_dir, requests, got, routing, dtype: str):
             assert err < TOL[dtype], f"{dtype}: request {rid} position {pos}: relative error {err:.3e}"
             worst = max(worst, err)
     return worst
+
+
+def compare_plain_only(model_dir, requests, got, dtype: str):
+    """As compare_with_plain, with the plain implementation's own expert choices."""
+    for rid, toks in requests.items():
+        ref, _ = plain_logits(model_dir, toks)
+        for pos in range(len(toks)):
+            if (rid, pos) in got:
+                err = rel_err(got[(rid, pos)], ref[pos])
+                assert err < TOL[dtype], f"{dtype}: request {rid} position {pos}: relative error {err:.3e}"

@@ -11,8 +11,9 @@ from tests import helpers as H
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"tiny_a": [80, 1, 33, 47, 64, 17], "tiny_b": [130, 49, 2, 97, 48, 75]}
-VOCAB = {"tiny_a": 256, "tiny_b": 384}
+LENGTHS = {"tiny_a": [80, 1, 33, 47, 64, 17], "tiny_b": [130, 49, 2, 97, 48, 75], "tiny_c": [200, 81, 3, 160, 65, 129]}
+VOCAB = {"tiny_a": 256, "tiny_b": 384, "tiny_c": 320}
+NAMES = ["tiny_a", "tiny_b", "tiny_c"]
 
 
 def _engine(model_dir, dtype, max_tokens, page_size=16, max_slots=8):
@@ -27,10 +28,10 @@ def _requests(name, seed=0):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
+@pytest.mark.parametrize("name", NAMES)
 def test_whole_requests(model_dirs, name, dtype):
     reqs = _requests(name)
-    eng = _engine(model_dirs[name], dtype, max_tokens=160)
+    eng = _engine(model_dirs[name], dtype, max_tokens=208)
     got, routing = H.run_trace(eng, H.trace_whole(reqs))
     worst = H.compare_with_plain(model_dirs[name], reqs, got, routing, dtype)
     print(f"{name} {dtype} whole: worst relative error {worst:.2e}")
@@ -38,27 +39,27 @@ def test_whole_requests(model_dirs, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
+@pytest.mark.parametrize("name", NAMES)
 def test_last_32_tokens_one_by_one(model_dirs, name, dtype):
     reqs = _requests(name)
-    eng = _engine(model_dirs[name], dtype, max_tokens=160)
+    eng = _engine(model_dirs[name], dtype, max_tokens=208)
     got, routing = H.run_trace(eng, H.trace_tail_decode(reqs, 32))
     worst = H.compare_with_plain(model_dirs[name], reqs, got, routing, dtype)
     print(f"{name} {dtype} tail decode: worst relative error {worst:.2e}")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
+@pytest.mark.parametrize("name", NAMES)
 def test_portions_of_changing_size(model_dirs, name, dtype):
     reqs = _requests(name)
-    eng = _engine(model_dirs[name], dtype, max_tokens=160)
+    eng = _engine(model_dirs[name], dtype, max_tokens=208)
     got, routing = H.run_trace(eng, H.trace_portions(reqs, random.Random(3)))
     worst = H.compare_with_plain(model_dirs[name], reqs, got, routing, dtype)
     print(f"{name} {dtype} portions: worst relative error {worst:.2e}")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
+@pytest.mark.parametrize("name", NAMES)
 def test_mixed_batches_reusing_pages(model_dirs, name, dtype):
     rng = random.Random(7)
     lengths = LENGTHS[name] + [rng.randrange(1, max(LENGTHS[name])) for _ in range(6)]
@@ -75,12 +76,12 @@ def test_mixed_batches_reusing_pages(model_dirs, name, dtype):
     assert total_pages_needed > eng.num_pages, "the trace must need more pages than the pool has"
 
 
-@pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
+@pytest.mark.parametrize("name", NAMES)
 def test_cutting_does_not_change_float32_logits(model_dirs, name):
     """In 32-bit every reduction has a fixed order per position, so whole, decoded and portioned runs
     agree far more closely than any of them agrees with another implementation."""
     reqs = _requests(name, seed=5)
-    eng = _engine(model_dirs[name], "float32", max_tokens=160)
+    eng = _engine(model_dirs[name], "float32", max_tokens=208)
     whole, _ = H.run_trace(eng, H.trace_whole(reqs))
     cut, _ = H.run_trace(eng, H.trace_portions(reqs, random.Random(1)))
     worst = max(H.rel_err(cut[k], whole[k]) for k in whole)

@@ -1,0 +1,139 @@
+"""Generation through the Python entry point and the command line: greedy tokens against the plain
+implementation, long decoding (through the replayed CUDA graphs), the first tokens of a sequence,
+sampling with a temperature, and what happens when the cache is too small for everyone."""
+
+import random
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from tests import helpers as H
+from tests.plain import llama4_plain as plain
+
+pytestmark = pytest.mark.gpu
+
+
+def _plain_greedy_checked(folder, prompt, got, dtype):
+    """`got` must be the plain implementation's greedy continuation, except that a step whose two best
+    logits nearly tie (closer than the precision can tell apart) may go either way; after such a step the
+    comparison follows the engine's choice."""
+    cfg, w = plain.load_config(folder), plain.load_weights(folder)
+    toks = list(prompt)
+    tol = 1e-5 if dtype == "float32" else 2e-2
+    for step, g in enumerate(got):
+        logits = plain.forward(cfg, w, toks)[-1]
+        best = int(torch.argmax(logits))
+        if g != best:
+            gap = float(logits[best] - logits[g]) / float(logits.abs().max())
+            assert gap < tol, f"{dtype}: step {step}: engine chose {g}, plain {best}, relative logit gap {gap:.2e}"
+        toks.append(g)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_c"])
+def test_greedy_generation_through_the_entry_point(model_dirs, name, dtype):
+    import jax_llm_examples_b200 as J
+
+    model = J.load_model(model_dirs[name], dtype)
+    rng = random.Random(4)
+    prompts = [[rng.randrange(model.vocab_size) for _ in range(n)] for n in (1, 2, 31, 77)]
+    outs = J.generate(model, prompts, J.SamplingParams(max_new_tokens=12), page_size=16, max_tokens_per_step=48)
+    assert [len(o) for o in outs] == [12] * 4
+    for p, o in zip(prompts, outs):
+        _plain_greedy_checked(model_dirs[name], p, o, dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_stays_right(model_dirs, dtype):
+    """200 tokens decoded one by one (crossing chunks, pages and the temperature floor), batch of 3; in
+    bfloat16 the steps run as replayed CUDA graphs."""
+    import jax_llm_examples_b200 as J
+
+    folder = model_dirs["tiny_c"]
+    model = J.load_model(folder, dtype)
+    gen = J.Generator(model, max_tokens=3 * 240, page_size=16, max_slots=3, max_tokens_per_step=64)
+    prompts = [[5, 6, 7], [9] * 17, [200, 100]]
+    outs = gen.generate(prompts, J.SamplingParams(max_new_tokens=200))
+    if dtype == "bfloat16":
+        assert gen.engine.graph_replays > 150
+    for p, o in zip(prompts, outs):
+        assert len(o) == 200
+        _plain_greedy_checked(folder, p, o[:60], dtype)
+    # logits at the far end, teacher-forced through the engine's own tokens, against the plain implementation
+    eng = J.Engine(model, max_tokens=256, page_size=16, max_slots=1, use_graphs=False)
+    seq = prompts[0] + outs[0]
+    got, routing = H.run_trace(eng, H.trace_tail_decode({"r": seq}, 32))
+    H.compare_with_plain(folder, {"r": seq}, got, routing, dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c"])
+def test_first_tokens_of_a_sequence(model_dirs, name, dtype):
+    """Positions 0, 1, 2 alone and together: the shortest contexts (one key, a fresh page, no history)."""
+    import jax_llm_examples_b200 as J
+
+    model = J.load_model(model_dirs[name], dtype)
+    eng = J.Engine(model, max_tokens=64, page_size=16, max_slots=4)
+    reqs = {"a": [3], "b": [4, 5], "c": [6, 7, 8]}
+    steps = [{"entries": [{"id": "a", "tokens": [3], "want": [0]}, {"id": "b", "tokens": [4], "want": [0]},
+                          {"id": "c", "tokens": [6, 7, 8], "want": [0, 1, 2]}], "end": ["a", "c"]},
+             {"entries": [{"id": "b", "tokens": [5], "want": [0]}], "end": ["b"]}]
+    got, routing = H.run_trace(eng, steps)
+    H.compare_with_plain(model_dirs[name], reqs, got, routing, dtype)
+
+
+def test_temperature_sampling_is_reproducible_and_independent_of_the_batch(model_dirs):
+    import jax_llm_examples_b200 as J
+
+    model = J.load_model(model_dirs["tiny_b"], "float32")
+    params = J.SamplingParams(temperature=0.8, top_k=16, max_new_tokens=10)
+    prompts = [[1, 2, 3, 4], [7] * 30, [11, 12]]
+
+    def run(which, **kw):
+        gen = J.Generator(model, max_tokens=512, page_size=16, max_slots=4, seed=3, **kw)
+        reqs = [gen.submit(prompts[i], params) for i in which]
+        for r, i in zip(reqs, which):
+            r.request_id = i  # the request's random stream is its id: keep it whatever the batch
+        gen.scheduler.run()
+        return {i: r.output for r, i in zip(reqs, which)}
+
+    together = run([0, 1, 2])
+    assert together == run([0, 1, 2])
+    alone = {**run([0]), **run([1]), **run([2])}
+    assert alone == together
+    assert run([0, 1, 2], max_tokens_per_step=7) == together
+    greedy = J.generate(model, prompts, J.SamplingParams(max_new_tokens=10), page_size=16)
+    assert any(g != together[i] for i, g in enumerate(greedy))  # the draws are not just the argmax
+
+
+def test_too_few_pages_preempts_and_still_gives_the_same_tokens(model_dirs):
+    import jax_llm_examples_b200 as J
+
+    model = J.load_model(model_dirs["tiny_a"], "float32")
+    prompts = [[i + 1] * 20 for i in range(4)]
+    params = J.SamplingParams(max_new_tokens=40)
+    roomy = J.Generator(model, max_tokens=4 * 64, page_size=16, max_slots=4).generate(prompts, params)
+    tight_gen = J.Generator(model, max_tokens=7 * 16, page_size=16, max_slots=4)  # 7 pages for 4 x 60 tokens
+    tight = tight_gen.generate(prompts, params)
+    assert tight == roomy
+    assert sum(r.preemptions for r in tight_gen.scheduler.finished) > 0
+    tight_gen.engine.manager.check()
+    with pytest.raises(ValueError, match="does not fit the cache"):
+        J.Generator(model, max_tokens=32, page_size=16, max_slots=2).generate([[1] * 40], params)
+
+
+def test_command_line(model_dirs):
+    cmd = [sys.executable, "-m", "jax_llm_examples_b200.main", "--model", str(model_dirs["tiny_a"]), "--dtype", "float32",
+           "--prompt-ids", "5,6,7,8", "--prompt-ids", "9", "--max-new-tokens", "6", "--page-size", "16"]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, cwd=H.ROOT)
+    assert out.returncode == 0, out.stderr[-2000:]
+    lines = [ln for ln in out.stdout.splitlines() if ln and ln[0].isdigit()]
+    assert len(lines) == 2 and all(len(ln.split()) == 6 for ln in lines)
+    import jax_llm_examples_b200 as J
+
+    model = J.load_model(model_dirs["tiny_a"], "float32")
+    want = J.generate(model, [[5, 6, 7, 8], [9]], J.SamplingParams(max_new_tokens=6), page_size=16)
+    assert [list(map(int, ln.split())) for ln in lines] == want
