@@ -670,6 +670,195 @@ __global__ void __launch_bounds__(256) attention_prefill_kernel(const AttnParams
   }
 }
 
+// ---------------------------------------------------------------------------- prefill with TMA
+// The flash kernel with its key/value tiles brought in by TMA (one thread issues a tile's boxes, as in the
+// decode kernel) through a ring of PRE_STAGES stages, and with the 64-key tile scored in two halves of 32 keys
+// so that the score fragment takes 16 registers instead of 32: two blocks share an SM.
+#define PRE_STAGES 3
+
+template <int DH>
+__device__ __forceinline__ void tma_issue_tile(const CUtensorMap* map, const AttnParams& P, const int* table, int hk, int key0,
+                                               uint32_t dst, uint32_t bar, int box_rows) {
+  constexpr int HALVES = DH / 64;
+  constexpr uint32_t HALF_BYTES = KT * 128;
+  mbar_expect_tx(bar, 2 * HALVES * HALF_BYTES);
+  for (int b = 0; b < KT / box_rows; ++b) {
+    const int pos = key0 + b * box_rows;
+    const int pi = pos / P.page_size;
+    int page = pi < P.bt_stride ? table[pi] : -1;
+    if (page >= P.num_pages) { atomicOr(P.status, JLX_STATUS_BAD_PAGE); page = 0; }
+    if (page < 0) page = 0;  // no page there: every key of the box is masked
+    const int row_k = ((page * 2 + 0) * P.Hkv + hk) * P.page_size + (pos - pi * P.page_size);
+    const int row_v = ((page * 2 + 1) * P.Hkv + hk) * P.page_size + (pos - pi * P.page_size);
+#pragma unroll
+    for (int h = 0; h < HALVES; ++h) {
+      tma_load_2d(dst + h * HALF_BYTES + b * box_rows * 128, map, h * 64, row_k, bar);
+      tma_load_2d(dst + (HALVES + h) * HALF_BYTES + b * box_rows * 128, map, h * 64, row_v, bar);
+    }
+  }
+}
+
+template <int DH, int MAXW, int MINB>
+__global__ void __launch_bounds__(MAXW * 32, MINB)
+attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap map, const AttnParams P, int box_rows) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  constexpr int HALVES = DH / 64;
+  constexpr uint32_t HALF_BYTES = KT * 128;
+  constexpr uint32_t STAGE_BYTES = 2 * HALVES * HALF_BYTES;
+  __shared__ __align__(8) uint64_t full_bar[PRE_STAGES];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const int tile = blockIdx.x, hk = blockIdx.y;
+  const int G = P.Hq / P.Hkv;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = P.tiles[2 * tile], cnt = P.tiles[2 * tile + 1];
+  const int r = P.req_of_token[n0];
+  const int p_first = P.positions[n0], p_last = p_first + cnt - 1;
+  const int lo_tile = first_key(p_first, P.chunk, P.window);
+  const int key_begin = lo_tile / KT * KT;
+  const int n_tiles = (p_last - key_begin) / KT + 1;
+  const int* table = P.block_table + (size_t)r * P.bt_stride;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < PRE_STAGES; ++s) mbar_init(smem_u32(&full_bar[s]), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  if (threadIdx.x == 0)
+    for (int t = 0; t < PRE_STAGES && t < n_tiles; ++t)
+      tma_issue_tile<DH>(&map, P, table, hk, key_begin + t * KT, base + t * STAGE_BYTES, smem_u32(&full_bar[t]), box_rows);
+
+  const int t0 = lane >> 2, t1 = t0 + 8;
+  const int p0 = p_first + min(t0, cnt - 1), p1 = p_first + min(t1, cnt - 1);
+  const int lo0 = first_key(p0, P.chunk, P.window), lo1 = first_key(p1, P.chunk, P.window);
+  const bool row0 = t0 < cnt, row1 = t1 < cnt;
+  uint32_t qf[DH / 16][4];
+  {
+    const int kk = (lane & 3) * 2;
+    const bf16* q0 = P.q + ((size_t)(n0 + min(t0, cnt - 1)) * P.Hq + hk * G + warp) * DH;
+    const bf16* q1 = P.q + ((size_t)(n0 + min(t1, cnt - 1)) * P.Hq + hk * G + warp) * DH;
+#pragma unroll
+    for (int s = 0; s < DH / 16; ++s) {
+      qf[s][0] = row0 ? *reinterpret_cast<const uint32_t*>(q0 + s * 16 + kk) : 0u;
+      qf[s][1] = row1 ? *reinterpret_cast<const uint32_t*>(q1 + s * 16 + kk) : 0u;
+      qf[s][2] = row0 ? *reinterpret_cast<const uint32_t*>(q0 + s * 16 + kk + 8) : 0u;
+      qf[s][3] = row1 ? *reinterpret_cast<const uint32_t*>(q1 + s * 16 + kk + 8) : 0u;
+    }
+  }
+  const float sc0 = P.scale_log2 * temperature(p0, P.attn_scale, P.floor_scale);
+  const float sc1 = P.scale_log2 * temperature(p1, P.attn_scale, P.floor_scale);
+  float m[2] = {NEG_BIG, NEG_BIG}, l[2] = {0.f, 0.f};
+  float o[DH / 8][4];
+#pragma unroll
+  for (int i = 0; i < DH / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+
+  bool ok = true;
+  for (int t = 0; t < n_tiles; ++t) {
+    const int st = t % PRE_STAGES;
+    ok = __syncthreads_and(mbar_wait(smem_u32(&full_bar[st]), (t / PRE_STAGES) & 1));
+    if (!ok) {
+      if (threadIdx.x == 0) {
+        atomicOr(P.status, JLX_STATUS_WAIT_TIMEOUT);
+        for (int u = t + 1; u < n_tiles && u < t + PRE_STAGES; ++u) mbar_wait(smem_u32(&full_bar[u % PRE_STAGES]), (u / PRE_STAGES) & 1);
+      }
+      break;
+    }
+    const int tile_key = key_begin + t * KT;
+    const uint32_t kt = base + st * STAGE_BYTES, vt = kt + HALVES * HALF_BYTES;
+    // rows of this thread that see no key of the tile at all skip nothing: the masks below handle it
+    const bool need_mask = tile_key + KT - 1 > p_first || tile_key < first_key(p_last, P.chunk, P.window) || cnt < 16;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      float s[4][4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+#pragma unroll
+      for (int kstep = 0; kstep < DH / 16; ++kstep) {
+#pragma unroll
+        for (int np = 0; np < 2; ++np) {
+          const int key = half * 32 + np * 16 + (lane >> 4) * 8 + (lane & 7);
+          const int c = kstep * 2 + ((lane >> 3) & 1);
+          uint32_t b0, b1, b2, b3;
+          ldmatrix_x4(kt + (c >> 3) * HALF_BYTES + key * 128 + (((c & 7) ^ (key & 7)) << 4), b0, b1, b2, b3);
+          mma_bf16(s[np * 2], qf[kstep], b0, b1);
+          mma_bf16(s[np * 2 + 1], qf[kstep], b2, b3);
+        }
+      }
+      float mx[2] = {m[0], m[1]};
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          bool in = true;
+          if (need_mask) {
+            const int key = tile_key + half * 32 + nt * 8 + (lane & 3) * 2 + (e & 1);
+            in = (e < 2) ? (row0 && key >= lo0 && key <= p0) : (row1 && key >= lo1 && key <= p1);
+          }
+          s[nt][e] = in ? s[nt][e] * ((e < 2) ? sc0 : sc1) : NEG_BIG;
+          mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
+        }
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+      }
+      float corr[2], rs[2] = {0.f, 0.f};
+#pragma unroll
+      for (int h = 0; h < 2; ++h) corr[h] = exp2f(m[h] - mx[h]);
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float pv = s[nt][e] > 0.5f * NEG_BIG ? exp2f(s[nt][e] - mx[e >> 1]) : 0.f;
+          s[nt][e] = pv;
+          rs[e >> 1] += pv;
+        }
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        rs[h] += __shfl_xor_sync(0xffffffffu, rs[h], 1);
+        rs[h] += __shfl_xor_sync(0xffffffffu, rs[h], 2);
+        l[h] = l[h] * corr[h] + rs[h];
+        m[h] = mx[h];
+      }
+#pragma unroll
+      for (int i = 0; i < DH / 8; ++i) {
+        o[i][0] *= corr[0]; o[i][1] *= corr[0]; o[i][2] *= corr[1]; o[i][3] *= corr[1];
+      }
+#pragma unroll
+      for (int kp = 0; kp < 2; ++kp) {
+        uint32_t pa[4] = {pack_bf16(s[kp * 2][0], s[kp * 2][1]), pack_bf16(s[kp * 2][2], s[kp * 2][3]),
+                          pack_bf16(s[kp * 2 + 1][0], s[kp * 2 + 1][1]), pack_bf16(s[kp * 2 + 1][2], s[kp * 2 + 1][3])};
+#pragma unroll
+        for (int np = 0; np < DH / 16; ++np) {
+          const int key = half * 32 + kp * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+          const int c = np * 2 + (lane >> 4);
+          uint32_t b0, b1, b2, b3;
+          ldmatrix_x4_trans(vt + (c >> 3) * HALF_BYTES + key * 128 + (((c & 7) ^ (key & 7)) << 4), b0, b1, b2, b3);
+          mma_bf16(o[np * 2], pa, b0, b1);
+          mma_bf16(o[np * 2 + 1], pa, b2, b3);
+        }
+      }
+    }
+    __syncthreads();  // every warp is done reading this stage
+    if (threadIdx.x == 0 && t + PRE_STAGES < n_tiles) {
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      tma_issue_tile<DH>(&map, P, table, hk, key_begin + (t + PRE_STAGES) * KT, base + st * STAGE_BYTES,
+                         smem_u32(&full_bar[st]), box_rows);
+    }
+  }
+  if (!ok) return;
+  {
+    const int col = (lane & 3) * 2;
+    const float i0 = 1.f / l[0], i1 = 1.f / l[1];
+    bf16* o0 = P.out + ((size_t)(n0 + t0) * P.Hq + hk * G + warp) * DH;
+    bf16* o1 = P.out + ((size_t)(n0 + t1) * P.Hq + hk * G + warp) * DH;
+#pragma unroll
+    for (int i = 0; i < DH / 8; ++i) {
+      if (row0) *reinterpret_cast<__nv_bfloat162*>(o0 + i * 8 + col) = __floats2bfloat162_rn(o[i][0] * i0, o[i][1] * i0);
+      if (row1) *reinterpret_cast<__nv_bfloat162*>(o1 + i * 8 + col) = __floats2bfloat162_rn(o[i][2] * i1, o[i][3] * i1);
+    }
+  }
+}
+
 // --------------------------------------------------------------------------------------- host
 static int fill_params(AttnParams& P, const void* q, const void* pages, const int* block_table, int bt_stride,
                        const int* req_of_token, const int* positions, void* out, int Hq, int Hkv, int dh, int page_size,
@@ -808,8 +997,33 @@ JLX_API int jlx_attention_prefill(const void* q, const void* pages, const int* b
   JLX_REQUIRE(Hkv <= 65535, "attention_prefill: too many KV heads");
   if (n_tiles == 0) return 0;
   P.tiles = tiles;
-  const size_t smem = (size_t)2 * 2 * KT * dh * 2;
   dim3 grid(n_tiles, Hkv);
+  const bool tma = (page_size % KT == 0 || KT % page_size == 0) && page_size >= 8 &&
+                   (long long)num_pages * 2 * Hkv * page_size < (1ll << 31);
+  if (tma) {
+    CUtensorMap map;
+    const int box_rows = page_size < KT ? page_size : KT;
+    if (make_cache_map(&map, pages, (long long)num_pages * 2 * Hkv * page_size, dh, box_rows)) return 1;
+    const size_t smem = (size_t)PRE_STAGES * 2 * KT * dh * 2 + 1024;
+#define PREFILL_TMA(DHV, MAXW, MINB)                                                                                       \
+    do {                                                                                                                   \
+      static bool cfg = false;                                                                                             \
+      if (!cfg) {                                                                                                          \
+        JLX_CUDA(cudaFuncSetAttribute(attention_prefill_tma_kernel<DHV, MAXW, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        JLX_CUDA(cudaFuncSetAttribute(attention_prefill_tma_kernel<DHV, MAXW, MINB>, cudaFuncAttributePreferredSharedMemoryCarveout, 100));    \
+        cfg = true;                                                                                                        \
+      }                                                                                                                    \
+      attention_prefill_tma_kernel<DHV, MAXW, MINB><<<grid, G * 32, smem, stream>>>(map, P, box_rows);                      \
+    } while (0)
+    if (dh == 128 && G <= 5) PREFILL_TMA(128, 5, 2);
+    else if (dh == 128) PREFILL_TMA(128, 8, 1);
+    else if (G <= 5) PREFILL_TMA(64, 5, 2);
+    else PREFILL_TMA(64, 8, 1);
+#undef PREFILL_TMA
+    JLX_LAUNCH_CHECK("attention_prefill_tma");
+    return 0;
+  }
+  const size_t smem = (size_t)2 * 2 * KT * dh * 2;
   if (dh == 128) {
     static bool cfg = false;
     if (!cfg) { JLX_CUDA(cudaFuncSetAttribute(attention_prefill_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); cfg = true; }

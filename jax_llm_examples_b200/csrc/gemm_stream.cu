@@ -123,11 +123,13 @@ struct StreamArgs {
   int* status;
 };
 
-template <int BT, int STAGES>
+// WT: weight tiles of 128 rows per block.  With many token rows per group the token tile is the larger part of
+// a stage; two weight tiles (two accumulators in tensor memory) per token tile halve its traffic.
+template <int BT, int STAGES, int WT>
 __global__ void __launch_bounds__(NTHREADS)
 gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a, const StreamArgs args) {
-  constexpr uint32_t W_BYTES = WN * BK * 2, A_BYTES = BT * BK * 2, STAGE_BYTES = W_BYTES + A_BYTES;
-  constexpr uint32_t TMEM_COLS = BT < 32 ? 32 : BT;
+  constexpr uint32_t W_TILE = WN * BK * 2, W_BYTES = WT * W_TILE, A_BYTES = BT * BK * 2, STAGE_BYTES = W_BYTES + A_BYTES;
+  constexpr uint32_t TMEM_COLS = WT * BT < 32 ? 32 : WT * BT;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   __shared__ __align__(8) uint64_t bars[2 * STAGES + 1];
@@ -152,7 +154,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     row_hi = args.rows;
     if (row_lo >= row_hi) return;
   }
-  const int n0 = blockIdx.x * WN;
+  const int n0 = blockIdx.x * (WN * WT);
   const int k_begin = blockIdx.z * args.k_per_split;
   const int k_end = min(args.K, k_begin + args.k_per_split);
   const int k_iters = (k_end - k_begin + BK - 1) / BK;
@@ -184,7 +186,9 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         if (!ok || *(volatile int*)&failed) { ok = false; break; }
         const uint32_t dst = smem_base + s * STAGE_BYTES;
         mbar_expect_tx(bar_full + 8 * s, STAGE_BYTES);
-        tma_load_2d(dst, &map_w, k_begin + it * BK, group * args.N + n0, bar_full + 8 * s);
+#pragma unroll
+        for (int w = 0; w < WT; ++w)  // rows beyond this group's N belong to the next group or to nobody: never stored
+          tma_load_2d(dst + w * W_TILE, &map_w, k_begin + it * BK, group * args.N + n0 + w * WN, bar_full + 8 * s);
         tma_load_2d(dst + W_BYTES, &map_a, k_begin + it * BK, row_lo, bar_full + 8 * s);
         issued = it + 1;
       }
@@ -206,11 +210,15 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         if (!ok || *(volatile int*)&failed) { ok = false; break; }
         tc_fence_after();
         const uint32_t w_addr = smem_base + s * STAGE_BYTES, a_addr = w_addr + W_BYTES;
-        const uint64_t wdesc = smem_desc_sw128(w_addr), adesc = smem_desc_sw128(a_addr);
+        const uint64_t adesc = smem_desc_sw128(a_addr);
 #pragma unroll
-        for (int k = 0; k < BK / UMMA_K; ++k) {
-          // 16 elements = 32 bytes further along K inside the swizzled row: +2 in the address field
-          umma_bf16(tmem_acc, wdesc + 2 * k, adesc + 2 * k, idesc, (it | k) != 0);
+        for (int w = 0; w < WT; ++w) {
+          const uint64_t wdesc = smem_desc_sw128(w_addr + w * W_TILE);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            // 16 elements = 32 bytes further along K inside the swizzled row: +2 in the address field
+            umma_bf16(tmem_acc + w * BT, wdesc + 2 * k, adesc + 2 * k, idesc, (it | k) != 0);
+          }
         }
         umma_commit(bar_empty + 8 * s);  // frees the stage when these MMAs have read it
       }
@@ -229,33 +237,38 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     ok = __all_sync(0xffffffffu, ok);  // the tensor-memory loads below need the whole warp
     if (ok) {
       tc_fence_after();
-      const int n = n0 + quarter * 32 + lane;
-      const bool n_ok = n < args.N;
       const size_t split_off = args.splits > 1 ? (size_t)blockIdx.z * args.rows * args.N : 0;
 #pragma unroll 1
-      for (int c0 = 0; c0 < BT; c0 += 16) {
-        if (row_lo + c0 >= row_hi) break;  // uniform across the warp
-        uint32_t r[16];
-        tmem_ld16(tmem_acc + ((uint32_t)(quarter * 32) << 16) + c0, r);
-        tmem_ld_wait();
+      for (int w = 0; w < WT; ++w) {
+        const int nb = n0 + w * WN + quarter * 32;  // first weight row of this warp in tile w
+        const int n = nb + lane;
+        const bool n_ok = n < args.N;
+        if (nb >= args.N) break;  // uniform across the warp
+#pragma unroll 1
+        for (int c0 = 0; c0 < BT; c0 += 16) {
+          if (row_lo + c0 >= row_hi) break;  // uniform across the warp
+          uint32_t r[16];
+          tmem_ld16(tmem_acc + ((uint32_t)(quarter * 32) << 16) + w * BT + c0, r);
+          tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const int m = row_lo + c0 + j;
-          const float v = __uint_as_float(r[j]);
-          if (args.silu) {
-            // lanes 0..15 hold gate rows, lanes 16..31 the matching up rows of the same 32-row block
-            const float up = __shfl_down_sync(0xffffffffu, v, 16);
-            if (lane < 16 && m < row_hi && n_ok) {
-              const float act = v / (1.f + __expf(-v)) * up;
-              const size_t col = (size_t)((n0 + quarter * 32) >> 1) + lane;
-              if (args.out_is_f32) ((float*)args.out)[(size_t)m * (args.N >> 1) + col] = act;
-              else ((bf16*)args.out)[(size_t)m * (args.N >> 1) + col] = __float2bfloat16_rn(act);
+          for (int j = 0; j < 16; ++j) {
+            const int m = row_lo + c0 + j;
+            const float v = __uint_as_float(r[j]);
+            if (args.silu) {
+              // lanes 0..15 hold gate rows, lanes 16..31 the matching up rows of the same 32-row block
+              const float up = __shfl_down_sync(0xffffffffu, v, 16);
+              if (lane < 16 && m < row_hi && n_ok) {
+                const float act = v / (1.f + __expf(-v)) * up;
+                const size_t col = (size_t)(nb >> 1) + lane;
+                if (args.out_is_f32) ((float*)args.out)[(size_t)m * (args.N >> 1) + col] = act;
+                else ((bf16*)args.out)[(size_t)m * (args.N >> 1) + col] = __float2bfloat16_rn(act);
+              }
+            } else if (m < row_hi && n_ok) {
+              if (args.out_is_f32 || args.splits > 1)
+                ((float*)args.out)[split_off + (size_t)m * args.N + n] = v;
+              else
+                ((bf16*)args.out)[(size_t)m * args.N + n] = __float2bfloat16_rn(v);
             }
-          } else if (m < row_hi && n_ok) {
-            if (args.out_is_f32 || args.splits > 1)
-              ((float*)args.out)[split_off + (size_t)m * args.N + n] = v;
-            else
-              ((bf16*)args.out)[(size_t)m * args.N + n] = __float2bfloat16_rn(v);
           }
         }
       }
@@ -314,16 +327,16 @@ static int make_map(CUtensorMap* map, const void* base, long long rows, long lon
   return 0;
 }
 
-template <int BT, int STAGES>
+template <int BT, int STAGES, int WT>
 static int launch(const CUtensorMap& mw, const CUtensorMap& ma, const StreamArgs& a, int row_tiles, cudaStream_t stream) {
-  constexpr size_t smem = (size_t)STAGES * (WN * BK * 2 + BT * BK * 2) + 1024;
+  constexpr size_t smem = (size_t)STAGES * (WT * WN * BK * 2 + BT * BK * 2) + 1024;
   static bool configured = false;
   if (!configured) {
-    JLX_CUDA(cudaFuncSetAttribute(gemm_stream_kernel<BT, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    JLX_CUDA(cudaFuncSetAttribute(gemm_stream_kernel<BT, STAGES, WT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured = true;
   }
-  dim3 grid((a.N + WN - 1) / WN, row_tiles, a.splits);
-  gemm_stream_kernel<BT, STAGES><<<grid, NTHREADS, smem, stream>>>(mw, ma, a);
+  dim3 grid((a.N + WN * WT - 1) / (WN * WT), row_tiles, a.splits);
+  gemm_stream_kernel<BT, STAGES, WT><<<grid, NTHREADS, smem, stream>>>(mw, ma, a);
   JLX_LAUNCH_CHECK("gemm_stream");
   return 0;
 }
@@ -381,11 +394,12 @@ JLX_API int jlx_gemm_stream(const void* A, const void* W, void* out, int out_is_
   int rc;
   switch (bt) {
     // stages sized so that two blocks share an SM (about 100 KB each), except for the widest tile
-    case 16: rc = launch<16, 5>(mw, ma, a, row_tiles, stream); break;
-    case 32: rc = launch<32, 5>(mw, ma, a, row_tiles, stream); break;
-    case 64: rc = launch<64, 4>(mw, ma, a, row_tiles, stream); break;
-    case 128: rc = launch<128, 3>(mw, ma, a, row_tiles, stream); break;
-    default: rc = launch<256, 4>(mw, ma, a, row_tiles, stream); break;
+    case 16: rc = launch<16, 5, 1>(mw, ma, a, row_tiles, stream); break;
+    case 32: rc = launch<32, 5, 1>(mw, ma, a, row_tiles, stream); break;
+    case 64: rc = launch<64, 4, 1>(mw, ma, a, row_tiles, stream); break;
+    // wide token tiles: two weight tiles per block (192 KB of stages, one block per SM)
+    case 128: rc = launch<128, 4, 2>(mw, ma, a, row_tiles, stream); break;
+    default: rc = launch<256, 3, 2>(mw, ma, a, row_tiles, stream); break;
   }
   if (rc) return rc;
   if (splits > 1 && mode == 0) {

@@ -162,6 +162,8 @@ class Engine:
         if int(n_tok.max()) > 1:
             firsts = np.concatenate([[0], np.cumsum(n_tok)[:-1]])
             tiles = np.array([(f + t, min(16, n - t)) for f, n in zip(firsts, n_tok) for t in range(0, n, 16)], dtype=np.int32)
+            # late tiles of a causal prompt read the most keys: launch them first so that the tail is short
+            tiles = np.ascontiguousarray(tiles[::-1])
         size = packed + (tiles.size if tiles is not None else 0)
         host, ring_i = self._ring.next(size)
         host_np = host.numpy()

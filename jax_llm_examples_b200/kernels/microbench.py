@@ -109,7 +109,7 @@ def gemm(a) -> dict:
     mode = K.GEMM_SWIGLU if a.swiglu else K.GEMM_PLAIN
     out = torch.empty(a.rows, a.n // 2 if a.swiglu else a.n, device=dev, dtype=torch.bfloat16 if a.swiglu else torch.float32)
     scratch = torch.empty(a.splits * a.rows * a.n, device=dev) if a.splits > 1 else None
-    hint = min(a.rows, 2 * -(-a.rows // E)) if E else 0
+    hint = a.hint or (min(a.rows, 2 * -(-a.rows // E)) if E else 0)
 
     def run():
         K.gemm_stream(x, w, out, status, offsets=offsets, rows_hint=hint, splits=a.splits, scratch=scratch, mode=mode)
@@ -151,6 +151,7 @@ def main(argv=None) -> int:
             p.add_argument("--k", type=int, default=5120)
             p.add_argument("--experts", type=int, default=0, help="0: one dense weight; else rows are spread over this many groups")
             p.add_argument("--splits", type=int, default=1)
+            p.add_argument("--hint", type=int, default=0, help="rows per group that the token tile is sized for (0: twice the mean)")
             p.add_argument("--swiglu", action="store_true", help="fused SiLU(gate) * up epilogue")
     a = ap.parse_args(argv)
     print(json.dumps({"attention_decode": attention_decode, "attention_prefill": attention_prefill, "gemm": gemm}[a.what](a)))
