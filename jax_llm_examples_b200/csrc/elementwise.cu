@@ -81,16 +81,18 @@ add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, int d
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
   for (int e = warp; e < E; e += nwarp) {
     const float* wr = w_router + (size_t)e * D;
-    float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+    // eight independent loads of the router row in flight per lane: this loop waits on memory, not on math
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     int d = lane;
-    for (; d + 96 < D; d += 128) {
-      s0 = fmaf(rowbuf[d], wr[d], s0);
-      s1 = fmaf(rowbuf[d + 32], wr[d + 32], s1);
-      s2 = fmaf(rowbuf[d + 64], wr[d + 64], s2);
-      s3 = fmaf(rowbuf[d + 96], wr[d + 96], s3);
+    for (; d + 7 * 32 < D; d += 8 * 32) {
+      float wv[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) wv[u] = wr[d + 32 * u];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) acc[u] = fmaf(rowbuf[d + 32 * u], wv[u], acc[u]);
     }
-    for (; d < D; d += 32) s0 = fmaf(rowbuf[d], wr[d], s0);
-    const float s = warp_sum((s0 + s1) + (s2 + s3));
+    for (; d < D; d += 32) acc[0] = fmaf(rowbuf[d], wr[d], acc[0]);
+    const float s = warp_sum(((acc[0] + acc[1]) + (acc[2] + acc[3])) + ((acc[4] + acc[5]) + (acc[6] + acc[7])));
     if (lane == 0) scores[e] = s;
   }
   __syncthreads();

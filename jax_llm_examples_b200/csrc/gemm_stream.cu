@@ -369,7 +369,6 @@ JLX_API int jlx_gemm_stream(const void* A, const void* W, void* out, int out_is_
   JLX_REQUIRE(!offsets || E > 0, "gemm_stream: a grouped product needs a group count");
   JLX_REQUIRE(mode >= 0 && mode <= 2, "gemm_stream: unknown mode %d", mode);
   JLX_REQUIRE(splits >= 1 && (splits == 1 || mode == 1 || scratch), "gemm_stream: split-K needs scratch memory");
-  JLX_REQUIRE(splits == 1 || !offsets, "gemm_stream: split-K is for ungrouped products");
   JLX_REQUIRE(mode != 2 || (splits == 1 && N % 32 == 0), "gemm_stream: the SwiGLU epilogue needs N %% 32 == 0 and no split-K");
   JLX_REQUIRE(mode != 1 || out_is_f32, "gemm_stream: partials are float32");
   if (splits_used) *splits_used = 1;

@@ -62,8 +62,11 @@ JLX_API int jlx_router(const float* h, const float* w_router, int* topk_idx, flo
 // Counting sort of the P = N * k (token, choice) pairs by expert, stable in pair order.  One block;
 // warp w owns experts w, w + nwarp, ...  Writes offsets[E + 1], sorted_pair[P] (pair id at each sorted
 // row) and sorted_pos[P] (sorted row of each pair).
+// With extra_rows > 0 one more group is appended after the experts (offsets has E + 2 entries): rows
+// [P, P + extra_rows), used for a shared expert that takes every token.
 __global__ void expert_sort_kernel(const int* __restrict__ topk_idx, int* __restrict__ offsets,
-                                   int* __restrict__ sorted_pair, int* __restrict__ sorted_pos, int P, int E, int* status) {
+                                   int* __restrict__ sorted_pair, int* __restrict__ sorted_pos, int P, int E, int extra_rows,
+                                   int* status) {
   __shared__ int counts[ROUTER_MAX_E + 1];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
   for (int e = warp; e < E; e += nwarp) {
@@ -86,6 +89,7 @@ __global__ void expert_sort_kernel(const int* __restrict__ topk_idx, int* __rest
     }
     counts[E] = run;
     offsets[E] = run;
+    if (extra_rows > 0) offsets[E + 1] = run + extra_rows;
     if (run != P) atomicOr(status, JLX_STATUS_BAD_EXPERT);
   }
   __syncthreads();
@@ -106,58 +110,68 @@ __global__ void expert_sort_kernel(const int* __restrict__ topk_idx, int* __rest
 }
 
 JLX_API int jlx_expert_sort(const int* topk_idx, int* offsets, int* sorted_pair, int* sorted_pos, int P, int E,
-                            int* status, cudaStream_t stream) {
-  JLX_REQUIRE(P >= 0 && E >= 1 && E <= ROUTER_MAX_E, "expert_sort: bad sizes P=%d E=%d", P, E);
+                            int extra_rows, int* status, cudaStream_t stream) {
+  JLX_REQUIRE(P >= 0 && E >= 1 && E <= ROUTER_MAX_E && extra_rows >= 0, "expert_sort: bad sizes P=%d E=%d", P, E);
   const int warps = E < 32 ? E : 32;
-  expert_sort_kernel<<<1, warps * 32, 0, stream>>>(topk_idx, offsets, sorted_pair, sorted_pos, P, E, status);
+  expert_sort_kernel<<<1, warps * 32, 0, stream>>>(topk_idx, offsets, sorted_pair, sorted_pos, P, E, extra_rows, status);
   JLX_LAUNCH_CHECK("expert_sort");
   return 0;
 }
 
-// a_sorted[i, :] = weight(pair) * h[token(pair), :]  with pair = sorted_pair[i], token = pair / k
+// a_sorted[i, :] = weight(pair) * h[token(pair), :]  with pair = sorted_pair[i], token = pair / k;
+// rows i >= P (the appended group of a shared expert) are the unscaled rows h[i - P].
 template <typename T>
 __global__ void permute_scale_kernel(const float* __restrict__ h, const int* __restrict__ sorted_pair,
-                                     const float* __restrict__ topk_w, T* __restrict__ a_sorted, int D, int k) {
+                                     const float* __restrict__ topk_w, T* __restrict__ a_sorted, int D, int k, int P) {
   const int i = blockIdx.x;
-  const int pair = sorted_pair[i];
-  const float w = topk_w[pair];
-  const float* src = h + (size_t)(pair / k) * D;
+  const int pair = i < P ? sorted_pair[i] : 0;
+  const float w = i < P ? topk_w[pair] : 1.f;
+  const float* src = h + (size_t)(i < P ? pair / k : i - P) * D;
   T* dst = a_sorted + (size_t)i * D;
   for (int d = blockIdx.y * blockDim.x + threadIdx.x; d < D; d += gridDim.y * blockDim.x) dst[d] = from_f32<T>(w * src[d]);
 }
 
 JLX_API int jlx_permute_scale(const float* h, const int* sorted_pair, const float* topk_w, void* a_sorted, int dtype,
-                              int P, int D, int k, cudaStream_t stream) {
-  JLX_REQUIRE(P >= 0 && D > 0 && k >= 1, "permute_scale: bad sizes");
-  if (P == 0) return 0;
+                              int P, int extra_rows, int D, int k, cudaStream_t stream) {
+  JLX_REQUIRE(P >= 0 && D > 0 && k >= 1 && extra_rows >= 0, "permute_scale: bad sizes");
+  const int rows = P + extra_rows;
+  if (rows == 0) return 0;
   // few rows: spread each row over several blocks
-  const int ysplit = P >= 512 ? 1 : (D + 1023) / 1024;
-  JLX_DISPATCH_DTYPE(dtype, T, (permute_scale_kernel<T><<<dim3(P, ysplit), 256, 0, stream>>>(h, sorted_pair, topk_w, (T*)a_sorted, D, k)));
+  const int ysplit = rows >= 512 ? 1 : (D + 1023) / 1024;
+  JLX_DISPATCH_DTYPE(dtype, T, (permute_scale_kernel<T><<<dim3(rows, ysplit), 256, 0, stream>>>(h, sorted_pair, topk_w, (T*)a_sorted, D, k, P)));
   JLX_LAUNCH_CHECK("permute_scale");
   return 0;
 }
 
-// delta[n, :] = sum over splits of shared[z][n, :] + sum_j y_sorted[sorted_pos[n * k + j], :]
-// (splits and j ascending: a fixed order)
-__global__ void moe_combine_kernel(const float* __restrict__ y_sorted, const float* __restrict__ shared, int splits,
-                                   long long split_stride, const int* __restrict__ sorted_pos, float* __restrict__ delta,
-                                   int D, int k) {
+// delta[n, :] = sum_j y[sorted_pos[n * k + j], :]  (+ y[extra_base + n, :] if extra_base >= 0: the appended
+// shared-expert group)  (+ shared[n, :]), where y and shared may be split-K partials [z][rows][D] that are
+// added first, z ascending; j ascending: a fixed order.
+__global__ void moe_combine_kernel(const float* __restrict__ y, int y_splits, long long y_stride, int extra_base,
+                                   const float* __restrict__ shared, int splits, long long split_stride,
+                                   const int* __restrict__ sorted_pos, float* __restrict__ delta, int D, int k) {
   const int n = blockIdx.x;
   for (int d = blockIdx.y * blockDim.x + threadIdx.x; d < D; d += gridDim.y * blockDim.x) {
     float s = 0.f;
     if (shared)
       for (int z = 0; z < splits; ++z) s += shared[(size_t)z * split_stride + (size_t)n * D + d];
-    for (int j = 0; j < k; ++j) s += y_sorted[(size_t)sorted_pos[(size_t)n * k + j] * D + d];
+    if (extra_base >= 0)
+      for (int z = 0; z < y_splits; ++z) s += y[(size_t)z * y_stride + (size_t)(extra_base + n) * D + d];
+    for (int j = 0; j < k; ++j) {
+      const size_t row = (size_t)sorted_pos[(size_t)n * k + j] * D + d;
+      for (int z = 0; z < y_splits; ++z) s += y[(size_t)z * y_stride + row];
+    }
     delta[(size_t)n * D + d] = s;
   }
 }
 
-JLX_API int jlx_moe_combine(const float* y_sorted, const float* shared, int splits, long long split_stride,
-                            const int* sorted_pos, float* delta, int N, int D, int k, cudaStream_t stream) {
-  JLX_REQUIRE(N >= 0 && D > 0 && k >= 1 && splits >= 1, "moe_combine: bad sizes");
+JLX_API int jlx_moe_combine(const float* y, int y_splits, long long y_stride, int extra_base, const float* shared,
+                            int splits, long long split_stride, const int* sorted_pos, float* delta, int N, int D, int k,
+                            cudaStream_t stream) {
+  JLX_REQUIRE(N >= 0 && D > 0 && k >= 1 && splits >= 1 && y_splits >= 1, "moe_combine: bad sizes");
   if (N == 0) return 0;
   const int ysplit = N >= 512 ? 1 : (D + 1023) / 1024;
-  moe_combine_kernel<<<dim3(N, ysplit), 256, 0, stream>>>(y_sorted, shared, splits, split_stride, sorted_pos, delta, D, k);
+  moe_combine_kernel<<<dim3(N, ysplit), 256, 0, stream>>>(y, y_splits, y_stride, extra_base, shared, splits, split_stride,
+                                                          sorted_pos, delta, D, k);
   JLX_LAUNCH_CHECK("moe_combine");
   return 0;
 }

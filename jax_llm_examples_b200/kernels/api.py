@@ -299,26 +299,35 @@ def router(h32: torch.Tensor, w_router: torch.Tensor, topk_idx: torch.Tensor, to
 
 
 def expert_sort(topk_idx: torch.Tensor, offsets: torch.Tensor, sorted_pair: torch.Tensor, sorted_pos: torch.Tensor,
-                E: int, status: torch.Tensor) -> None:
+                E: int, status: torch.Tensor, extra_rows: int = 0) -> None:
+    """Counting sort of the (token, choice) pairs by expert.  offsets: [E + 1], or [E + 2] with extra_rows > 0:
+    one more group of that many rows appended after the experts."""
     _contig(topk_idx, offsets, sorted_pair, sorted_pos)
+    if offsets.numel() < E + 1 + (extra_rows > 0):
+        raise KernelError("expert_sort: offsets too short")
     _run("moe", "jlx_expert_sort", _ptr(topk_idx), _ptr(offsets), _ptr(sorted_pair), _ptr(sorted_pos),
-         c_int(topk_idx.numel()), c_int(E), _ptr(status), _stream())
+         c_int(topk_idx.numel()), c_int(E), c_int(extra_rows), _ptr(status), _stream())
 
 
-def permute_scale(h32: torch.Tensor, sorted_pair: torch.Tensor, topk_w: torch.Tensor, a_sorted: torch.Tensor, k: int) -> None:
+def permute_scale(h32: torch.Tensor, sorted_pair: torch.Tensor, topk_w: torch.Tensor, a_sorted: torch.Tensor, k: int,
+                  extra_rows: int = 0) -> None:
+    """a_sorted[i] = weight * h32[token] in expert order; then extra_rows unscaled copies of h32's rows."""
     _contig(h32, sorted_pair, topk_w, a_sorted)
+    P = a_sorted.shape[0] - extra_rows
     _run("moe", "jlx_permute_scale", _ptr(h32), _ptr(sorted_pair), _ptr(topk_w), _ptr(a_sorted),
-         c_int(code(a_sorted.dtype)), c_int(a_sorted.shape[0]), c_int(h32.shape[1]), c_int(k), _stream())
+         c_int(code(a_sorted.dtype)), c_int(P), c_int(extra_rows), c_int(h32.shape[1]), c_int(k), _stream())
 
 
 def moe_combine(y_sorted: torch.Tensor, shared: torch.Tensor | None, sorted_pos: torch.Tensor, delta: torch.Tensor, k: int,
-                shared_splits: int = 1) -> None:
-    """delta = shared (or the sum of its split-K partials) + the sum of each token's expert rows."""
+                shared_splits: int = 1, y_splits: int = 1, extra_base: int = -1) -> None:
+    """delta = the sum of each token's expert rows (+ row extra_base + n of y: an appended shared group)
+    (+ shared); y_sorted and shared may be split-K partials."""
     _contig(y_sorted, shared, sorted_pos, delta)
     N, D = delta.shape
     sp, stride = _splits(shared, shared_splits)
-    _run("moe", "jlx_moe_combine", _ptr(y_sorted), _ptr(shared), c_int(sp), c_longlong(stride), _ptr(sorted_pos),
-         _ptr(delta), c_int(N), c_int(D), c_int(k), _stream())
+    ysp, ystride = _splits(y_sorted, y_splits)
+    _run("moe", "jlx_moe_combine", _ptr(y_sorted), c_int(ysp), c_longlong(ystride), c_int(extra_base), _ptr(shared),
+         c_int(sp), c_longlong(stride), _ptr(sorted_pos), _ptr(delta), c_int(N), c_int(D), c_int(k), _stream())
 
 
 # ---------------------------------------------------------------------------------- sampling

@@ -6,7 +6,7 @@ import torch
 
 from ..kernels import api as K
 from .base import FeedForward, Rows, StepContext, as_rows, register_part
-from .linear import grouped_linear, grouped_swiglu_linear, interleave_gate_up, linear, swiglu_linear
+from .linear import STREAM_MAX_ROWS, grouped_linear, grouped_swiglu_linear, interleave_gate_up, linear, swiglu_linear
 
 
 def _can_interleave(w_gate_up: torch.Tensor) -> bool:
@@ -58,6 +58,16 @@ class RoutedExperts(FeedForward):
         self.we_gate_up = interleave_gate_up(we_gate_up) if self.interleaved else we_gate_up
         self.we_down, self.top_k, self.shared = we_down, top_k, shared
         self.num_experts = E
+        # A shared expert of the experts' own shape rides along as group E of the grouped products when a step
+        # has few rows (decoding): two launches fewer, and its weights stream at the grouped kernel's rate.
+        # Its weights then live at the end of the experts' tensors; the shared part keeps views of them.
+        self.merged = (shared is not None and shared.interleaved == self.interleaved
+                       and shared.w_gate_up.shape == self.we_gate_up.shape[1:] and shared.w_down.shape == we_down.shape[1:]
+                       and shared.w_gate_up.dtype == self.we_gate_up.dtype == torch.bfloat16 and shared.w_down.dtype == we_down.dtype)
+        if self.merged:
+            self.we_gate_up = torch.cat([self.we_gate_up, shared.w_gate_up[None]])
+            self.we_down = torch.cat([self.we_down, shared.w_down[None]])
+            shared.w_gate_up, shared.w_down = self.we_gate_up[E], self.we_down[E]
 
     def router_request(self):
         return (self.w_router, self.top_k)
@@ -70,30 +80,35 @@ class RoutedExperts(FeedForward):
         K.router(h32, self.w_router, topk_idx, topk_w)
         return topk_idx, topk_w
 
-    def sort(self, ctx: StepContext, topk_idx: torch.Tensor):
+    def sort(self, ctx: StepContext, topk_idx: torch.Tensor, extra_rows: int = 0):
         n, k, dev = topk_idx.shape[0], self.top_k, topk_idx.device
-        offsets = torch.empty(self.num_experts + 1, dtype=torch.int32, device=dev)
+        offsets = torch.empty(self.num_experts + 2, dtype=torch.int32, device=dev)
         sorted_pair = torch.empty(n * k, dtype=torch.int32, device=dev)
         sorted_pos = torch.empty(n * k, dtype=torch.int32, device=dev)
-        K.expert_sort(topk_idx, offsets, sorted_pair, sorted_pos, self.num_experts, ctx.status)
+        K.expert_sort(topk_idx, offsets, sorted_pair, sorted_pos, self.num_experts, ctx.status, extra_rows)
         return offsets, sorted_pair, sorted_pos
 
     def forward(self, ctx: StepContext, h, h32, routing=None):
         rt = ctx.runtime
         n, D = h32.shape
-        k = self.top_k
+        k, E = self.top_k, self.num_experts
         topk_idx, topk_w = routing if routing is not None else self.route(ctx, h32)
         if "record_routing" in ctx.scratch:  # tests compare the choices with a plain router's
             ctx.scratch["record_routing"].append(topk_idx)
-        offsets, sorted_pair, sorted_pos = self.sort(ctx, topk_idx)
-        a_sorted = torch.empty((n * k, D), dtype=rt.dtype, device=h.device)
-        K.permute_scale(h32, sorted_pair, topk_w, a_sorted, k)
-        act = grouped_swiglu_linear(ctx, a_sorted, self.we_gate_up, offsets, self.interleaved, rt.dtype)
-        y = grouped_linear(ctx, act, self.we_down, offsets, torch.float32)
-        shared = as_rows(self.shared.forward(ctx, h, None)) if self.shared is not None else None
+        merged = self.merged and n <= STREAM_MAX_ROWS
+        extra = n if merged else 0
+        offsets, sorted_pair, sorted_pos = self.sort(ctx, topk_idx, extra)
+        a_sorted = torch.empty((n * k + extra, D), dtype=rt.dtype, device=h.device)
+        K.permute_scale(h32, sorted_pair, topk_w, a_sorted, k, extra)
+        groups = E + 1 if merged else E
+        act = grouped_swiglu_linear(ctx, a_sorted, self.we_gate_up[:groups], offsets, self.interleaved, rt.dtype, extra)
+        y = grouped_linear(ctx, act, self.we_down[:groups], offsets, torch.float32, partials=True, largest_group=extra)
+        shared = None
+        if self.shared is not None and not merged:
+            shared = as_rows(self.shared.forward(ctx, h, None))
         delta = torch.empty((n, D), dtype=torch.float32, device=h.device)
-        K.moe_combine(y, None if shared is None else shared.data, sorted_pos, delta, k,
-                      1 if shared is None else shared.splits)
+        K.moe_combine(y.data, None if shared is None else shared.data, sorted_pos, delta, k,
+                      1 if shared is None else shared.splits, y.splits, n * k if merged else -1)
         return delta
 
 

@@ -86,24 +86,33 @@ def swiglu_linear(ctx: StepContext, a: torch.Tensor, w_gate_up: torch.Tensor, in
 
 
 def grouped_linear(ctx: StepContext, a_sorted: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor,
-                   out_dtype: torch.dtype) -> torch.Tensor:
-    """Rows [offsets[e], offsets[e+1]) of a_sorted times w[e]^T.  w: [E, N, K]."""
-    rows, E = a_sorted.shape[0], w.shape[0]
-    out = torch.empty((rows, w.shape[1]), dtype=out_dtype, device=a_sorted.device)
+                   out_dtype: torch.dtype, partials: bool = False, largest_group: int = 0):
+    """Rows [offsets[e], offsets[e+1]) of a_sorted times w[e]^T.  w: [E, N, K].  With ``partials`` the result
+    is float32 :class:`Rows`; few rows (few groups in use) then get K cut across blocks to fill the GPU."""
+    rows, E, N = a_sorted.shape[0], w.shape[0], w.shape[1]
     if _streams(a_sorted, w, False):
-        hint = min(rows, 2 * -(-rows // E))  # groups are uneven: tile for twice the mean
+        hint = max(min(rows, 2 * -(-rows // E)), largest_group)  # groups are uneven: tile for twice the mean
+        if partials:
+            tiles = -(-N // 128) * min(E, rows)  # at most this many blocks have work
+            splits = max(1, min(-(-2 * _SM_COUNT // tiles), a_sorted.shape[1] // 512, 8)) if rows <= STREAM_MAX_ROWS else 1
+            out = torch.empty((splits, rows, N), dtype=torch.float32, device=a_sorted.device)
+            used = K.gemm_stream(a_sorted, w, out, ctx.status, offsets=offsets, rows_hint=hint, splits=splits, mode=K.GEMM_PARTIALS)
+            return Rows(out[:used], used)
+        out = torch.empty((rows, N), dtype=out_dtype, device=a_sorted.device)
         K.gemm_stream(a_sorted, w, out, ctx.status, offsets=offsets, rows_hint=hint)
-    else:
-        K.gemm_simt(a_sorted, w, out, offsets)
-    return out
+        return out
+    out = torch.empty((rows, N), dtype=torch.float32 if partials else out_dtype, device=a_sorted.device)
+    K.gemm_simt(a_sorted, w, out, offsets)
+    return Rows(out, 1) if partials else out
 
 
 def grouped_swiglu_linear(ctx: StepContext, a_sorted: torch.Tensor, w_gate_up: torch.Tensor, offsets: torch.Tensor,
-                          interleaved: bool, out_dtype: torch.dtype) -> torch.Tensor:
+                          interleaved: bool, out_dtype: torch.dtype, largest_group: int = 0) -> torch.Tensor:
+    """``largest_group``: rows of a group known to be large (a shared expert's), so that one tile holds it."""
     rows, E, F = a_sorted.shape[0], w_gate_up.shape[0], w_gate_up.shape[1] // 2
     act = torch.empty((rows, F), dtype=out_dtype, device=a_sorted.device)
     if interleaved and _streams(a_sorted, w_gate_up, False):
-        hint = min(rows, 2 * -(-rows // E))
+        hint = max(min(rows, 2 * -(-rows // E)), largest_group)
         K.gemm_stream(a_sorted, w_gate_up, act, ctx.status, offsets=offsets, rows_hint=hint, mode=K.GEMM_SWIGLU)
         return act
     gu = grouped_linear(ctx, a_sorted, w_gate_up, offsets, out_dtype)

@@ -307,6 +307,18 @@ def test_permute_scale_and_combine(dtype):
     y, shared, delta = torch.randn(N * k, D, device=DEV), torch.randn(N, D, device=DEV), torch.empty(N, D, device=DEV)
     K().moe_combine(y, shared, pos, delta, k)
     close(delta, shared + y[pos.long()].reshape(N, k, D).sum(1), 1e-6)
+    # an appended shared group: offsets get one more entry, rows N*k.. are unscaled copies, the combine adds them
+    off2 = torch.empty(E + 2, device=DEV, dtype=torch.int32)
+    K().expert_sort(idx, off2, pair, pos, E, st, N)
+    assert off2.tolist() == off.tolist() + [N * k + N]
+    a2 = torch.empty(N * k + N, D, device=DEV, dtype=dtype)
+    K().permute_scale(h, pair, wt, a2, k, N)
+    close(a2[: N * k], ref, 1e-6 if dtype == torch.float32 else 5e-3)
+    close(a2[N * k:], h, 1e-6 if dtype == torch.float32 else 5e-3)
+    y2 = torch.randn(2, N * k + N, D, device=DEV)
+    K().moe_combine(y2, None, pos, delta, k, 1, 2, N * k)
+    ys = y2.sum(0)
+    close(delta, ys[N * k:] + ys[pos.long()].reshape(N, k, D).sum(1), 1e-6)
 
 
 def test_sampling_argmax_and_draws():
@@ -501,3 +513,18 @@ def test_two_stage_argmax():
     want = logits.argmax(-1).tolist()
     want[3] = 5000
     assert out.tolist() == want
+
+
+def test_gemm_stream_grouped_split_k_partials():
+    api = K()
+    E, rows, N, Kd = 4, 5, 256, 2048
+    a, w = torch.randn(rows, Kd, device=DEV).bfloat16(), torch.randn(E, N, Kd, device=DEV).bfloat16()
+    off = torch.tensor([0, 2, 2, 4, 5], device=DEV, dtype=torch.int32)
+    parts, st = torch.full((4, rows, N), float("nan"), device=DEV), status()
+    used = api.gemm_stream(a, w, parts, st, offsets=off, rows_hint=2, splits=4, mode=api.GEMM_PARTIALS)
+    assert used == 4 and int(st) == 0
+    got = parts.sum(0)
+    for e in range(E):
+        lo, hi = int(off[e]), int(off[e + 1])
+        if hi > lo:
+            close(got[lo:hi], a[lo:hi].double() @ w[e].double().T, 1e-5)
