@@ -182,9 +182,10 @@ def run_trace(engine, steps):
     return out, routing
 
 
-# A router score difference below this is a tie that either precision may break either way:
-# float32 sums of D products differ by ~1e-6; bfloat16 rounds the layer inputs to 3 digits.
-TIE = {"float32": 1e-5, "bfloat16": 5e-3}
+# A router score difference below this fraction of the token's largest score is a tie that either precision
+# may break either way: float32 sums of D products differ by ~1e-6 relative; bfloat16 rounds what feeds the
+# layer to 3 digits (eps 4e-3), a few times per layer.
+TIE = {"float32": 1e-5, "bfloat16": 2e-2}
 
 
 def compare_with_plain(model_dir, requests, got, routing, dtype: str):
@@ -198,7 +199,7 @@ def compare_with_plain(model_dir, requests, got, routing, dtype: str):
         if layers:
             forced = {L: np.stack([routing[(rid, p)][j] for p in range(len(toks))]) for j, L in enumerate(layers)}
         ref, shortfall = plain_logits(model_dir, toks, forced)
-        assert shortfall < TIE[dtype], f"{dtype}: request {rid}: an expert was chosen whose score is {shortfall:.2e} too low"
+        assert shortfall < TIE[dtype], f"{dtype}: request {rid}: an expert was chosen whose score is too low by {shortfall:.2e} of the largest score"
         for pos in range(len(toks)):
             if (rid, pos) not in got:
                 continue

@@ -128,7 +128,7 @@ def test_feed_forward_parts(dtype, tol):
     forced = ctx.scratch["record_routing"][0].cpu()
     # the plain MoE takes the unrounded rows (as the engine's router and scaled gather do)
     ref, shortfall = plain.moe(h32, wr.T, egu.float(), edn.float(), wg.float().T, wu.float().T, wd.float().T, k, forced)
-    assert float(shortfall.max()) < 1e-5
+    assert float(shortfall.max()) < H.TIE['float32' if dtype == torch.float32 else 'bfloat16']
     assert H.rel_err(got.numpy(), ref.numpy()) < tol
     assert int(ctx.status) == 0
 
