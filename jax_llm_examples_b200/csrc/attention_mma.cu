@@ -322,6 +322,8 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map, const AttnP
   constexpr uint32_t STAGE_BYTES = 2 * HALVES * HALF_BYTES;  // K and V
   __shared__ __align__(8) uint64_t full_bar[DEC_STAGES];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  pdl_launch_dependents();
+  pdl_wait();
   const int n = blockIdx.z, hk = blockIdx.y, split = blockIdx.x;
   const int G = P.Hq / P.Hkv;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -503,6 +505,8 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map, const AttnP
 template <int DH>
 __global__ void attention_combine_kernel(const AttnParams P) {
   __shared__ float wgt[512];
+  pdl_launch_dependents();
+  pdl_wait();
   const int n = blockIdx.x, h = blockIdx.y;
   const int p = P.positions[n];
   const int lo = first_key(p, P.chunk, P.window);
@@ -960,11 +964,11 @@ JLX_API int jlx_attention_decode(const void* q, const void* pages, const int* bl
     if (dh == 128) {
       static bool cfg = false;
       if (!cfg) { JLX_CUDA(cudaFuncSetAttribute(attention_decode_tma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem + 1024)); cfg = true; }
-      attention_decode_tma_kernel<128><<<grid, 128, smem + 1024, stream>>>(map, P, box_rows);
+      JLX_CUDA(jlx_launch_pdl(attention_decode_tma_kernel<128>, grid, dim3(128), smem + 1024, stream, map, P, box_rows));
     } else {
       static bool cfg = false;
       if (!cfg) { JLX_CUDA(cudaFuncSetAttribute(attention_decode_tma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem + 1024)); cfg = true; }
-      attention_decode_tma_kernel<64><<<grid, 128, smem + 1024, stream>>>(map, P, box_rows);
+      JLX_CUDA(jlx_launch_pdl(attention_decode_tma_kernel<64>, grid, dim3(128), smem + 1024, stream, map, P, box_rows));
     }
     JLX_LAUNCH_CHECK("attention_decode_tma");
   } else if (dh == 128) {
@@ -978,8 +982,8 @@ JLX_API int jlx_attention_decode(const void* q, const void* pages, const int* bl
     attention_decode_kernel<64><<<grid, 128, smem, stream>>>(P);
     JLX_LAUNCH_CHECK("attention_decode");
   }
-  if (dh == 128) attention_combine_kernel<128><<<dim3(N, Hq), 128, 0, stream>>>(P);
-  else attention_combine_kernel<64><<<dim3(N, Hq), 64, 0, stream>>>(P);
+  if (dh == 128) JLX_CUDA(jlx_launch_pdl(attention_combine_kernel<128>, dim3(N, Hq), dim3(128), 0, stream, P));
+  else JLX_CUDA(jlx_launch_pdl(attention_combine_kernel<64>, dim3(N, Hq), dim3(64), 0, stream, P));
   JLX_LAUNCH_CHECK("attention_combine");
   return 0;
 }

@@ -96,3 +96,25 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
     else if ((dtype) == JLX_BF16) { typedef bf16 T; __VA_ARGS__; } \
     else JLX_REQUIRE(false, "unknown element type code %d", (int)(dtype)); \
   } while (0)
+
+// ---- programmatic dependent launch: a kernel launched with JLX_LAUNCH_PDL may start while its predecessor in
+// the stream still runs.  It must call pdl_wait() before it reads or writes anything that a predecessor
+// touches; what comes before (barrier set-up, tensor-memory allocation, loads of weights) overlaps the
+// predecessor's tail.  pdl_launch_dependents() lets the successor start the same way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+static cudaError_t jlx_launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}

@@ -9,6 +9,8 @@
 template <typename TW>
 __global__ void embed_kernel(const int* __restrict__ ids, const TW* __restrict__ table, float* __restrict__ x,
                              int D, int V, int* status) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int n = blockIdx.x;
   int id = ids[n];
   if (id < 0 || id >= V) {
@@ -24,8 +26,7 @@ JLX_API int jlx_embed(const int* ids, const void* table, int table_dtype, float*
                       int* status, cudaStream_t stream) {
   JLX_REQUIRE(N >= 0 && D > 0 && V > 0, "embed: bad sizes N=%d D=%d V=%d", N, D, V);
   if (N == 0) return 0;
-  JLX_DISPATCH_DTYPE(table_dtype, TW, (embed_kernel<TW><<<N, 256, 0, stream>>>(ids, (const TW*)table, x, D, V, status)));
-  JLX_LAUNCH_CHECK("embed");
+  JLX_DISPATCH_DTYPE(table_dtype, TW, { JLX_CUDA(jlx_launch_pdl(embed_kernel<TW>, dim3(N), dim3(256), 0, stream, ids, (const TW*)table, x, D, V, status)); });
   return 0;
 }
 
@@ -46,6 +47,8 @@ add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, int d
   extern __shared__ float rowbuf[];  // [D] when row_in_smem
   __shared__ float scratch[33];
   __shared__ float scores[ROUTER_MAX_E];
+  pdl_launch_dependents();
+  pdl_wait();
   const int n = blockIdx.x;
   const size_t r = row_index ? (size_t)row_index[n] : (size_t)n;
   float* xr = x + r * D;
@@ -138,8 +141,8 @@ JLX_API int jlx_add_rmsnorm(float* x, const float* delta, int delta_splits, long
     }
     // wide rows with few tokens are latency-bound: more threads per row keep more loads in flight
     const int threads = D >= 2048 ? 1024 : 256;
-    add_rmsnorm_kernel<TO><<<N, threads, smem, stream>>>(x, delta, delta_splits, delta_stride, gamma, eps, (TO*)out, out32,
-                                                     row_index, D, row_in_smem, w_router, E, k, topk_idx, topk_w);
+    JLX_CUDA(jlx_launch_pdl(add_rmsnorm_kernel<TO>, dim3(N), dim3(threads), smem, stream, x, delta, delta_splits, delta_stride,
+                            gamma, eps, (TO*)out, out32, row_index, D, row_in_smem, w_router, E, k, topk_idx, topk_w));
   });
   JLX_LAUNCH_CHECK("add_rmsnorm");
   return 0;

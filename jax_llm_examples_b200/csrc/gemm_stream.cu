@@ -129,7 +129,8 @@ template <int BT, int STAGES, int WT>
 __global__ void __launch_bounds__(NTHREADS)
 gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a, const StreamArgs args) {
   constexpr uint32_t W_TILE = WN * BK * 2, W_BYTES = WT * W_TILE, A_BYTES = BT * BK * 2, STAGE_BYTES = W_BYTES + A_BYTES;
-  constexpr uint32_t TMEM_COLS = WT * BT < 32 ? 32 : WT * BT;
+  constexpr uint32_t TMEM_NEED = WT * BT;  // allocations are powers of two from 32 columns
+  constexpr uint32_t TMEM_COLS = TMEM_NEED <= 32 ? 32 : TMEM_NEED <= 64 ? 64 : TMEM_NEED <= 128 ? 128 : TMEM_NEED <= 256 ? 256 : 512;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   __shared__ __align__(8) uint64_t bars[2 * STAGES + 1];
@@ -137,10 +138,12 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   __shared__ int failed;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  pdl_launch_dependents();
 
-  // ---- which tile
+  // ---- which tile.  The group offsets are written by an earlier kernel of the stream: wait for it first.
   int row_lo, row_hi, group = 0;
   if (args.offsets) {
+    pdl_wait();
     int t = blockIdx.y, found = 0;
     for (int e = 0; e < args.E; ++e) {
       const int lo = args.offsets[e], hi = args.offsets[e + 1];
@@ -178,16 +181,29 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      int issued = 0;
+      // The weights depend on no earlier kernel: the first stages' weight tiles are requested before the
+      // wait for the predecessor, whose tail they overlap; the token tiles follow after it.
+      const int early = k_iters < STAGES ? k_iters : STAGES;
+      for (int it = 0; it < early; ++it) {
+        mbar_expect_tx(bar_full + 8 * it, STAGE_BYTES);
+#pragma unroll
+        for (int w = 0; w < WT; ++w)  // rows beyond this group's N belong to the next group or to nobody: never stored
+          tma_load_2d(smem_base + it * STAGE_BYTES + w * W_TILE, &map_w, k_begin + it * BK, group * args.N + n0 + w * WN,
+                      bar_full + 8 * it);
+      }
+      pdl_wait();
+      for (int it = 0; it < early; ++it)
+        tma_load_2d(smem_base + it * STAGE_BYTES + W_BYTES, &map_a, k_begin + it * BK, row_lo, bar_full + 8 * it);
+      int issued = early;
       bool ok = true;
-      for (int it = 0; it < k_iters && ok; ++it) {
+      for (int it = early; it < k_iters && ok; ++it) {
         const int s = it % STAGES;
         ok = mbar_wait(bar_empty + 8 * s, ((it / STAGES) & 1) ^ 1);
         if (!ok || *(volatile int*)&failed) { ok = false; break; }
         const uint32_t dst = smem_base + s * STAGE_BYTES;
         mbar_expect_tx(bar_full + 8 * s, STAGE_BYTES);
 #pragma unroll
-        for (int w = 0; w < WT; ++w)  // rows beyond this group's N belong to the next group or to nobody: never stored
+        for (int w = 0; w < WT; ++w)
           tma_load_2d(dst + w * W_TILE, &map_w, k_begin + it * BK, group * args.N + n0 + w * WN, bar_full + 8 * s);
         tma_load_2d(dst + W_BYTES, &map_a, k_begin + it * BK, row_lo, bar_full + 8 * s);
         issued = it + 1;
@@ -232,6 +248,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..5)
     const int quarter = warp & 3;  // tensor-memory lanes [32 * quarter, 32 * quarter + 32)
+    pdl_wait();  // the output buffer may still be read by a predecessor
     bool ok = mbar_wait(bar_acc, 0);
     if (*(volatile int*)&failed) ok = false;
     ok = __all_sync(0xffffffffu, ok);  // the tensor-memory loads below need the whole warp
@@ -336,17 +353,15 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& ma, const StreamArgs
     configured = true;
   }
   dim3 grid((a.N + WN * WT - 1) / (WN * WT), row_tiles, a.splits);
-  gemm_stream_kernel<BT, STAGES, WT><<<grid, NTHREADS, smem, stream>>>(mw, ma, a);
-  JLX_LAUNCH_CHECK("gemm_stream");
+  JLX_CUDA(jlx_launch_pdl(gemm_stream_kernel<BT, STAGES, WT>, grid, dim3(NTHREADS), smem, stream, mw, ma, a));
   return 0;
 }
 
-// Token-tile width for a product whose largest group has about `rows_hint` rows.
+// Token-tile width (the MMA's N, a multiple of 16) for a product whose groups have up to about `rows_hint` rows.
 static int pick_bt(int rows_hint) {
-  if (rows_hint <= 16) return 16;
-  if (rows_hint <= 32) return 32;
-  if (rows_hint <= 64) return 64;
-  if (rows_hint <= 128) return 128;
+  static const int widths[] = {16, 32, 64, 96, 128, 160, 192, 224, 256};
+  for (int w : widths)
+    if (rows_hint <= w) return w;
   return 256;
 }
 
@@ -392,13 +407,18 @@ JLX_API int jlx_gemm_stream(const void* A, const void* W, void* out, int out_is_
   JLX_REQUIRE(row_tiles <= 65535, "gemm_stream: too many row tiles");
   int rc;
   switch (bt) {
-    // stages sized so that two blocks share an SM (about 100 KB each), except for the widest tile
+    // up to 192 token rows: one weight tile and stages sized so that two blocks share an SM (about 100 KB
+    // each): one block's epilogue (tensor memory -> registers -> global) overlaps the other's main loop.
+    // wider: two weight tiles per block (the token tile is fetched once for both), one block per SM.
     case 16: rc = launch<16, 5, 1>(mw, ma, a, row_tiles, stream); break;
     case 32: rc = launch<32, 5, 1>(mw, ma, a, row_tiles, stream); break;
     case 64: rc = launch<64, 4, 1>(mw, ma, a, row_tiles, stream); break;
-    // wide token tiles: two weight tiles per block (192 KB of stages, one block per SM)
-    case 128: rc = launch<128, 4, 2>(mw, ma, a, row_tiles, stream); break;
-    default: rc = launch<256, 3, 2>(mw, ma, a, row_tiles, stream); break;
+    case 96: rc = launch<96, 3, 1>(mw, ma, a, row_tiles, stream); break;
+    case 128: rc = launch<128, 3, 1>(mw, ma, a, row_tiles, stream); break;
+    case 160: rc = launch<160, 3, 1>(mw, ma, a, row_tiles, stream); break;
+    case 192: rc = launch<192, 2, 1>(mw, ma, a, row_tiles, stream); break;
+    case 224: rc = launch<224, 3, 2>(mw, ma, a, row_tiles, stream); break;  // 60 KB
+    default: rc = launch<256, 3, 2>(mw, ma, a, row_tiles, stream); break;   // 64 KB
   }
   if (rc) return rc;
   if (splits > 1 && mode == 0) {

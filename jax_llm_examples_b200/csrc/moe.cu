@@ -68,6 +68,8 @@ __global__ void expert_sort_kernel(const int* __restrict__ topk_idx, int* __rest
                                    int* __restrict__ sorted_pair, int* __restrict__ sorted_pos, int P, int E, int extra_rows,
                                    int* status) {
   __shared__ int counts[ROUTER_MAX_E + 1];
+  pdl_launch_dependents();
+  pdl_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
   for (int e = warp; e < E; e += nwarp) {
     int c = 0;
@@ -113,8 +115,8 @@ JLX_API int jlx_expert_sort(const int* topk_idx, int* offsets, int* sorted_pair,
                             int extra_rows, int* status, cudaStream_t stream) {
   JLX_REQUIRE(P >= 0 && E >= 1 && E <= ROUTER_MAX_E && extra_rows >= 0, "expert_sort: bad sizes P=%d E=%d", P, E);
   const int warps = E < 32 ? E : 32;
-  expert_sort_kernel<<<1, warps * 32, 0, stream>>>(topk_idx, offsets, sorted_pair, sorted_pos, P, E, extra_rows, status);
-  JLX_LAUNCH_CHECK("expert_sort");
+  JLX_CUDA(jlx_launch_pdl(expert_sort_kernel, dim3(1), dim3(warps * 32), 0, stream, topk_idx, offsets, sorted_pair, sorted_pos, P, E,
+                          extra_rows, status));
   return 0;
 }
 
@@ -123,6 +125,8 @@ JLX_API int jlx_expert_sort(const int* topk_idx, int* offsets, int* sorted_pair,
 template <typename T>
 __global__ void permute_scale_kernel(const float* __restrict__ h, const int* __restrict__ sorted_pair,
                                      const float* __restrict__ topk_w, T* __restrict__ a_sorted, int D, int k, int P) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int i = blockIdx.x;
   const int pair = i < P ? sorted_pair[i] : 0;
   const float w = i < P ? topk_w[pair] : 1.f;
@@ -138,8 +142,7 @@ JLX_API int jlx_permute_scale(const float* h, const int* sorted_pair, const floa
   if (rows == 0) return 0;
   // few rows: spread each row over several blocks
   const int ysplit = rows >= 512 ? 1 : (D + 1023) / 1024;
-  JLX_DISPATCH_DTYPE(dtype, T, (permute_scale_kernel<T><<<dim3(rows, ysplit), 256, 0, stream>>>(h, sorted_pair, topk_w, (T*)a_sorted, D, k, P)));
-  JLX_LAUNCH_CHECK("permute_scale");
+  JLX_DISPATCH_DTYPE(dtype, T, { JLX_CUDA(jlx_launch_pdl(permute_scale_kernel<T>, dim3(rows, ysplit), dim3(256), 0, stream, h, sorted_pair, topk_w, (T*)a_sorted, D, k, P)); });
   return 0;
 }
 
@@ -149,6 +152,8 @@ JLX_API int jlx_permute_scale(const float* h, const int* sorted_pair, const floa
 __global__ void moe_combine_kernel(const float* __restrict__ y, int y_splits, long long y_stride, int extra_base,
                                    const float* __restrict__ shared, int splits, long long split_stride,
                                    const int* __restrict__ sorted_pos, float* __restrict__ delta, int D, int k) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int n = blockIdx.x;
   for (int d = blockIdx.y * blockDim.x + threadIdx.x; d < D; d += gridDim.y * blockDim.x) {
     float s = 0.f;
@@ -170,8 +175,7 @@ JLX_API int jlx_moe_combine(const float* y, int y_splits, long long y_stride, in
   JLX_REQUIRE(N >= 0 && D > 0 && k >= 1 && splits >= 1 && y_splits >= 1, "moe_combine: bad sizes");
   if (N == 0) return 0;
   const int ysplit = N >= 512 ? 1 : (D + 1023) / 1024;
-  moe_combine_kernel<<<dim3(N, ysplit), 256, 0, stream>>>(y, y_splits, y_stride, extra_base, shared, splits, split_stride,
-                                                          sorted_pos, delta, D, k);
-  JLX_LAUNCH_CHECK("moe_combine");
+  JLX_CUDA(jlx_launch_pdl(moe_combine_kernel, dim3(N, ysplit), dim3(256), 0, stream, y, y_splits, y_stride, extra_base, shared,
+                          splits, split_stride, sorted_pos, delta, D, k));
   return 0;
 }

@@ -20,6 +20,8 @@ rope_kv_store_kernel(const TI* __restrict__ qkv, int splits, long long split_str
                      int num_pages, int store_kv, int* status) {
   extern __shared__ float sc[];  // [dh / 2][2]: sine and cosine of this token's angles
   // grid (tokens, head groups): each block takes up to 8 heads of one token, one per warp
+  pdl_launch_dependents();
+  pdl_wait();
   const int n = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int pos = positions[n];
@@ -112,11 +114,11 @@ JLX_API int jlx_rope_kv_store(const void* qkv, int in_dtype, int splits, long lo
   JLX_REQUIRE((Hq + 2 * Hkv + 7) / 8 <= 65535, "rope_kv_store: too many heads");
   if (N == 0) return 0;
   const size_t smem = (size_t)dh * sizeof(float);
-  JLX_DISPATCH_DTYPE(in_dtype, TI, JLX_DISPATCH_DTYPE(dtype, T,
-                     (rope_kv_store_kernel<TI, T><<<dim3(N, (Hq + 2 * Hkv + 7) / 8), 256, smem, stream>>>(
-                         (const TI*)qkv, splits, split_stride, (T*)q_out, (T*)pages, block_table, bt_stride, req_of_token,
-                         positions, inv_freq, l2norm, eps, Hq, Hkv, dh, page_size, num_pages, store_kv, status))));
-  JLX_LAUNCH_CHECK("rope_kv_store");
+  JLX_DISPATCH_DTYPE(in_dtype, TI, JLX_DISPATCH_DTYPE(dtype, T, {
+    JLX_CUDA(jlx_launch_pdl(rope_kv_store_kernel<TI, T>, dim3(N, (Hq + 2 * Hkv + 7) / 8), dim3(256), smem, stream,
+                            (const TI*)qkv, splits, split_stride, (T*)q_out, (T*)pages, block_table, bt_stride, req_of_token,
+                            positions, inv_freq, l2norm, eps, Hq, Hkv, dh, page_size, num_pages, store_kv, status));
+  }));
   return 0;
 }
 

@@ -33,6 +33,14 @@ def _splits_for(n_out: int, k: int) -> int:
     return max(1, min(want, k // 512, 8))
 
 
+def _group_rows_hint(rows: int, groups: int, largest_group: int = 0) -> int:
+    """Rows that a token tile should hold so that almost every group fits one tile: rows spread over the
+    groups like a binomial, so mean + 2.5 sigma (the rare larger group takes a second tile); at least the
+    size of a group known to be large."""
+    mean = rows / max(groups, 1)
+    return max(min(rows, int(mean + 2.5 * mean ** 0.5 + 1)), largest_group, 1)
+
+
 def _streams(a: torch.Tensor, w: torch.Tensor, rows_limit: bool) -> bool:
     return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and K.gemm_stream_supported(a, w)
             and (not rows_limit or a.shape[0] <= STREAM_MAX_ROWS))
@@ -91,7 +99,7 @@ def grouped_linear(ctx: StepContext, a_sorted: torch.Tensor, w: torch.Tensor, of
     is float32 :class:`Rows`; few rows (few groups in use) then get K cut across blocks to fill the GPU."""
     rows, E, N = a_sorted.shape[0], w.shape[0], w.shape[1]
     if _streams(a_sorted, w, False):
-        hint = max(min(rows, 2 * -(-rows // E)), largest_group)  # groups are uneven: tile for twice the mean
+        hint = _group_rows_hint(rows, E, largest_group)
         if partials:
             tiles = -(-N // 128) * min(E, rows)  # at most this many blocks have work
             splits = max(1, min(-(-2 * _SM_COUNT // tiles), a_sorted.shape[1] // 512, 8)) if rows <= STREAM_MAX_ROWS else 1
@@ -112,7 +120,7 @@ def grouped_swiglu_linear(ctx: StepContext, a_sorted: torch.Tensor, w_gate_up: t
     rows, E, F = a_sorted.shape[0], w_gate_up.shape[0], w_gate_up.shape[1] // 2
     act = torch.empty((rows, F), dtype=out_dtype, device=a_sorted.device)
     if interleaved and _streams(a_sorted, w_gate_up, False):
-        hint = max(min(rows, 2 * -(-rows // E)), largest_group)
+        hint = _group_rows_hint(rows, E, largest_group)
         K.gemm_stream(a_sorted, w_gate_up, act, ctx.status, offsets=offsets, rows_hint=hint, mode=K.GEMM_SWIGLU)
         return act
     gu = grouped_linear(ctx, a_sorted, w_gate_up, offsets, out_dtype)
