@@ -169,12 +169,39 @@ __global__ void silu_mul_kernel(const TI* __restrict__ gu, int splits, long long
   }
 }
 
+// The common case in prompts: bfloat16 in and out, no partials; eight outputs per thread with 16-byte accesses.
+__global__ void silu_mul_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int F, int interleaved) {
+  const size_t i = blockIdx.x;
+  const bf16* g = gu + i * 2 * F;
+  for (int f0 = threadIdx.x * 8; f0 < F; f0 += blockDim.x * 8) {
+    const int gi = interleaved ? ((f0 >> 4) << 5) + (f0 & 15) : f0;
+    const int ui = interleaved ? gi + 16 : F + f0;
+    const uint4 a = *reinterpret_cast<const uint4*>(g + gi), b = *reinterpret_cast<const uint4*>(g + ui);
+    const __nv_bfloat162* ap = reinterpret_cast<const __nv_bfloat162*>(&a);
+    const __nv_bfloat162* bp = reinterpret_cast<const __nv_bfloat162*>(&b);
+    uint4 o;
+    __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 x = __bfloat1622float2(ap[j]), y = __bfloat1622float2(bp[j]);
+      op[j] = __floats2bfloat162_rn(x.x / (1.f + expf(-x.x)) * y.x, x.y / (1.f + expf(-x.y)) * y.y);
+    }
+    *reinterpret_cast<uint4*>(out + i * F + f0) = o;
+  }
+}
+
 JLX_API int jlx_silu_mul(const void* gu, int in_dtype, int splits, long long split_stride, void* out, int out_dtype,
                          int rows, int F, int interleaved, cudaStream_t stream) {
   JLX_REQUIRE(rows >= 0 && F > 0 && splits >= 1, "silu_mul: bad sizes rows=%d F=%d splits=%d", rows, F, splits);
   JLX_REQUIRE(!interleaved || F % 16 == 0, "silu_mul: the interleaved layout needs a width that is a multiple of 16");
   JLX_REQUIRE(splits == 1 || in_dtype == JLX_F32, "silu_mul: split-K partials are float32");
   if (rows == 0) return 0;
+  if (in_dtype == JLX_BF16 && out_dtype == JLX_BF16 && splits == 1 && F % 16 == 0 && ((uintptr_t)gu & 15) == 0 &&
+      ((uintptr_t)out & 15) == 0) {
+    silu_mul_bf16x8_kernel<<<rows, 256, 0, stream>>>((const bf16*)gu, (bf16*)out, F, interleaved);
+    JLX_LAUNCH_CHECK("silu_mul");
+    return 0;
+  }
   JLX_DISPATCH_DTYPE(in_dtype, TI, JLX_DISPATCH_DTYPE(out_dtype, TO,
       (silu_mul_kernel<TI, TO><<<rows, 256, 0, stream>>>((const TI*)gu, splits, split_stride, (TO*)out, F, interleaved))));
   JLX_LAUNCH_CHECK("silu_mul");

@@ -115,6 +115,8 @@ struct StreamArgs {
   int rows;              // token rows in A (upper bound of offsets[E])
   const int* offsets;    // null: one group over all rows
   int E;
+  const int* tile_list;  // optional, with offsets: (group, first row) of every row tile that has rows
+  const int* n_tiles;    // ... and how many there are
   void* out;             // [rows, N] (bf16 or f32), or partials [splits][rows][N] f32 when splits > 1
   int out_is_f32;
   int silu;              // 1: rows come in blocks of [16 gate, 16 up]; out[m, j] = silu(gate_j) * up_j, [rows, N / 2]
@@ -145,7 +147,14 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   if (args.offsets) {
     pdl_wait();
     int t = blockIdx.y, found = 0;
-    for (int e = 0; e < args.E; ++e) {
+    if (args.tile_list) {
+      if (t >= args.n_tiles[0]) return;
+      group = args.tile_list[2 * t];
+      row_lo = args.tile_list[2 * t + 1];
+      row_hi = args.offsets[group + 1];
+      found = 1;
+    }
+    for (int e = 0; !found && e < args.E; ++e) {
       const int lo = args.offsets[e], hi = args.offsets[e + 1];
       const int tiles = (hi - lo + BT - 1) / BT;
       if (t < tiles) { row_lo = lo + t * BT; row_hi = hi; group = e; found = 1; break; }
@@ -367,6 +376,9 @@ static int pick_bt(int rows_hint) {
 
 JLX_API int jlx_gemm_stream_supported(int K) { return K % 8 == 0 && K >= 8; }
 
+// The token-tile width that jlx_gemm_stream uses for this hint (a tile list must be made for the same width).
+JLX_API int jlx_gemm_stream_token_tile(int rows_hint) { return pick_bt(rows_hint); }
+
 // rows: token rows of A (grouped: an upper bound of offsets[E]); rows_hint: typical rows per group
 // (chooses the token-tile width).
 // mode 0: out[rows, N] (bfloat16 or float32); with splits > 1 the partials go to `scratch` (float32
@@ -374,14 +386,18 @@ JLX_API int jlx_gemm_stream_supported(int K) { return K % 8 == 0 && K >= 8; }
 // mode 1: out receives the float32 partials themselves, [splits][rows][N], for a consumer that adds them.
 // mode 2: fused SwiGLU epilogue: weight rows are interleaved in blocks of [16 gate, 16 up], out is
 //         [rows, N / 2] = silu(gate) * up; no split-K.
+// tile_list / n_tiles (optional, grouped only): the row tiles that have rows, made by jlx_expert_sort for the
+// tile width jlx_gemm_stream_token_tile(rows_hint); without them every block walks the offsets.
 // Returns the split count used through *splits_used (it may be lower than asked).
 JLX_API int jlx_gemm_stream(const void* A, const void* W, void* out, int out_is_f32, int rows, int N, int K,
                             const int* offsets, int E, int rows_hint, int splits, float* scratch, int mode,
-                            int* splits_used, int* status, cudaStream_t stream) {
+                            const int* tile_list, const int* n_tiles, int* splits_used, int* status,
+                            cudaStream_t stream) {
   JLX_REQUIRE(rows >= 0 && N > 0 && K > 0, "gemm_stream: bad sizes rows=%d N=%d K=%d", rows, N, K);
   JLX_REQUIRE(K % 8 == 0, "gemm_stream: K = %d is no multiple of 8 (TMA needs 16-byte row strides); use the SIMT product", K);
   JLX_REQUIRE(((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0, "gemm_stream: operands must be 16-byte aligned");
   JLX_REQUIRE(!offsets || E > 0, "gemm_stream: a grouped product needs a group count");
+  JLX_REQUIRE(!tile_list || n_tiles, "gemm_stream: a tile list needs its count");
   JLX_REQUIRE(mode >= 0 && mode <= 2, "gemm_stream: unknown mode %d", mode);
   JLX_REQUIRE(splits >= 1 && (splits == 1 || mode == 1 || scratch), "gemm_stream: split-K needs scratch memory");
   JLX_REQUIRE(mode != 2 || (splits == 1 && N % 32 == 0), "gemm_stream: the SwiGLU epilogue needs N %% 32 == 0 and no split-K");
@@ -401,6 +417,7 @@ JLX_API int jlx_gemm_stream(const void* A, const void* W, void* out, int out_is_
   if (splits_used) *splits_used = splits;
   StreamArgs a;
   a.N = N; a.K = K; a.rows = rows; a.offsets = offsets; a.E = E;
+  a.tile_list = offsets ? tile_list : nullptr; a.n_tiles = n_tiles;
   a.out = (splits > 1 && mode == 0) ? (void*)scratch : out;
   a.out_is_f32 = out_is_f32; a.silu = mode == 2; a.splits = splits; a.k_per_split = kps; a.status = status;
   const int row_tiles = (rows + bt - 1) / bt + (offsets ? E : 0);

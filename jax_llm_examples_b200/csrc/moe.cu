@@ -64,9 +64,12 @@ JLX_API int jlx_router(const float* h, const float* w_router, int* topk_idx, flo
 // row) and sorted_pos[P] (sorted row of each pair).
 // With extra_rows > 0 one more group is appended after the experts (offsets has E + 2 entries): rows
 // [P, P + extra_rows), used for a shared expert that takes every token.
+// With tile_rows > 0 it also lists the row tiles of the grouped products that follow: tile_list[t] =
+// (group, first row) for every tile of tile_rows rows that holds at least one row, and n_tiles[0] = how many,
+// so that a product's blocks find their work with one load instead of a walk over the offsets.
 __global__ void expert_sort_kernel(const int* __restrict__ topk_idx, int* __restrict__ offsets,
                                    int* __restrict__ sorted_pair, int* __restrict__ sorted_pos, int P, int E, int extra_rows,
-                                   int* status) {
+                                   int tile_rows, int* __restrict__ tile_list, int* __restrict__ n_tiles, int* status) {
   __shared__ int counts[ROUTER_MAX_E + 1];
   pdl_launch_dependents();
   pdl_wait();
@@ -93,6 +96,19 @@ __global__ void expert_sort_kernel(const int* __restrict__ topk_idx, int* __rest
     offsets[E] = run;
     if (extra_rows > 0) offsets[E + 1] = run + extra_rows;
     if (run != P) atomicOr(status, JLX_STATUS_BAD_EXPERT);
+    if (tile_rows > 0) {
+      int t = 0;
+      const int groups = extra_rows > 0 ? E + 1 : E;
+      for (int e = 0; e < groups; ++e) {
+        const int lo = offsets[e], hi = offsets[e + 1];
+        for (int r = lo; r < hi; r += tile_rows) {
+          tile_list[2 * t] = e;
+          tile_list[2 * t + 1] = r;
+          ++t;
+        }
+      }
+      n_tiles[0] = t;
+    }
   }
   __syncthreads();
   for (int e = warp; e < E; e += nwarp) {
@@ -111,12 +127,14 @@ __global__ void expert_sort_kernel(const int* __restrict__ topk_idx, int* __rest
   }
 }
 
+// tile_list: int [(ceil((P + extra_rows) / tile_rows) + groups) * 2]; n_tiles: int [1]; both unused if tile_rows == 0.
 JLX_API int jlx_expert_sort(const int* topk_idx, int* offsets, int* sorted_pair, int* sorted_pos, int P, int E,
-                            int extra_rows, int* status, cudaStream_t stream) {
+                            int extra_rows, int tile_rows, int* tile_list, int* n_tiles, int* status, cudaStream_t stream) {
+  JLX_REQUIRE(tile_rows == 0 || (tile_list && n_tiles), "expert_sort: tile list outputs missing");
   JLX_REQUIRE(P >= 0 && E >= 1 && E <= ROUTER_MAX_E && extra_rows >= 0, "expert_sort: bad sizes P=%d E=%d", P, E);
   const int warps = E < 32 ? E : 32;
   JLX_CUDA(jlx_launch_pdl(expert_sort_kernel, dim3(1), dim3(warps * 32), 0, stream, topk_idx, offsets, sorted_pair, sorted_pos, P, E,
-                          extra_rows, status));
+                          extra_rows, tile_rows, tile_list, n_tiles, status));
   return 0;
 }
 
@@ -132,6 +150,16 @@ __global__ void permute_scale_kernel(const float* __restrict__ h, const int* __r
   const float w = i < P ? topk_w[pair] : 1.f;
   const float* src = h + (size_t)(i < P ? pair / k : i - P) * D;
   T* dst = a_sorted + (size_t)i * D;
+  if ((D & 3) == 0) {  // rows are 16-byte aligned: four elements per thread and access
+    for (int d = (blockIdx.y * blockDim.x + threadIdx.x) * 4; d < D; d += gridDim.y * blockDim.x * 4) {
+      const float4 v = *reinterpret_cast<const float4*>(src + d);
+      dst[d] = from_f32<T>(w * v.x);
+      dst[d + 1] = from_f32<T>(w * v.y);
+      dst[d + 2] = from_f32<T>(w * v.z);
+      dst[d + 3] = from_f32<T>(w * v.w);
+    }
+    return;
+  }
   for (int d = blockIdx.y * blockDim.x + threadIdx.x; d < D; d += gridDim.y * blockDim.x) dst[d] = from_f32<T>(w * src[d]);
 }
 
@@ -141,7 +169,7 @@ JLX_API int jlx_permute_scale(const float* h, const int* sorted_pair, const floa
   const int rows = P + extra_rows;
   if (rows == 0) return 0;
   // few rows: spread each row over several blocks
-  const int ysplit = rows >= 512 ? 1 : (D + 1023) / 1024;
+  const int ysplit = rows >= 512 ? 1 : (D + 1023) / 1024;  // four columns per thread: 1024 columns per block
   JLX_DISPATCH_DTYPE(dtype, T, { JLX_CUDA(jlx_launch_pdl(permute_scale_kernel<T>, dim3(rows, ysplit), dim3(256), 0, stream, h, sorted_pair, topk_w, (T*)a_sorted, D, k, P)); });
   return 0;
 }
@@ -155,6 +183,25 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, int y_splits, lo
   pdl_launch_dependents();
   pdl_wait();
   const int n = blockIdx.x;
+  if ((D & 3) == 0 && (y_stride & 3) == 0 && (split_stride & 3) == 0) {  // the same sums, four columns at a time
+    for (int d = (blockIdx.y * blockDim.x + threadIdx.x) * 4; d < D; d += gridDim.y * blockDim.x * 4) {
+      float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+      auto add = [&s](const float* p) {
+        const float4 v = *reinterpret_cast<const float4*>(p);
+        s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+      };
+      if (shared)
+        for (int z = 0; z < splits; ++z) add(shared + (size_t)z * split_stride + (size_t)n * D + d);
+      if (extra_base >= 0)
+        for (int z = 0; z < y_splits; ++z) add(y + (size_t)z * y_stride + (size_t)(extra_base + n) * D + d);
+      for (int j = 0; j < k; ++j) {
+        const size_t row = (size_t)sorted_pos[(size_t)n * k + j] * D + d;
+        for (int z = 0; z < y_splits; ++z) add(y + (size_t)z * y_stride + row);
+      }
+      *reinterpret_cast<float4*>(delta + (size_t)n * D + d) = s;
+    }
+    return;
+  }
   for (int d = blockIdx.y * blockDim.x + threadIdx.x; d < D; d += gridDim.y * blockDim.x) {
     float s = 0.f;
     if (shared)
@@ -174,7 +221,7 @@ JLX_API int jlx_moe_combine(const float* y, int y_splits, long long y_stride, in
                             cudaStream_t stream) {
   JLX_REQUIRE(N >= 0 && D > 0 && k >= 1 && splits >= 1 && y_splits >= 1, "moe_combine: bad sizes");
   if (N == 0) return 0;
-  const int ysplit = N >= 512 ? 1 : (D + 1023) / 1024;
+  const int ysplit = N >= 512 ? 1 : (D + 1023) / 1024;  // four columns per thread: 1024 columns per block
   JLX_CUDA(jlx_launch_pdl(moe_combine_kernel, dim3(N, ysplit), dim3(256), 0, stream, y, y_splits, y_stride, extra_base, shared,
                           splits, split_stride, sorted_pos, delta, D, k));
   return 0;

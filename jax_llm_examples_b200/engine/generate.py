@@ -8,6 +8,7 @@ only the chosen ids come back to the host each step.
 
 from __future__ import annotations
 
+import time
 from typing import Sequence
 
 import torch
@@ -23,7 +24,7 @@ class Generator:
 
     def __init__(self, model: DecoderModel, *, max_tokens: int, page_size: int = 64, max_slots: int = 64,
                  max_tokens_per_step: int = 2048, max_live: int | None = None, max_seq_len: int | None = None,
-                 seed: int = 0):
+                 seed: int = 0, profile: bool = False):
         self.engine = Engine(model, max_tokens=max_tokens, page_size=page_size, max_slots=max_slots,
                              max_seq_len=max_seq_len)
         self.sampler = Sampler(seed)
@@ -32,6 +33,9 @@ class Generator:
         self.h2d_bytes = 0
         self.d2h_bytes = 0
         self._next_id = 0
+        # profile=True: every step is timed on the host (the read of the sampled tokens ends it)
+        self.profile = profile
+        self.step_times: list[tuple[int, int, float]] = []  # (prompt tokens, decode tokens, seconds)
 
     def _admit(self, r: Request) -> None:
         for s in self.engine.states:
@@ -39,6 +43,18 @@ class Generator:
 
     def _run(self, entries: Sequence[PlannedEntry]) -> list[int]:
         batch = [StepEntry(e.request.slot, e.tokens, [len(e.tokens) - 1] if e.wants_logits else []) for e in entries]
+        if self.profile:
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+        try:
+            return self._run_batch(entries, batch)
+        finally:
+            if self.profile:
+                torch.cuda.synchronize()
+                decode = sum(1 for e in entries if len(e.tokens) == 1 and e.request.output)
+                self.step_times.append((sum(len(e.tokens) for e in entries) - decode, decode, time.perf_counter() - t0))
+
+    def _run_batch(self, entries: Sequence[PlannedEntry], batch: list[StepEntry]) -> list[int]:
         logits = self.engine.step(batch)
         self.h2d_bytes += 4 * sum(len(e.tokens) for e in entries)
         want = [e.request for e in entries if e.wants_logits]

@@ -257,15 +257,22 @@ def gemm_stream_supported(a: torch.Tensor, w: torch.Tensor) -> bool:
 GEMM_PLAIN, GEMM_PARTIALS, GEMM_SWIGLU = 0, 1, 2
 
 
+def gemm_stream_token_tile(rows_hint: int) -> int:
+    """The token-tile width gemm_stream uses for this rows_hint."""
+    return int(library("gemm_stream").jlx_gemm_stream_token_tile(c_int(rows_hint)))
+
+
 def gemm_stream(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: torch.Tensor,
                 offsets: torch.Tensor | None = None, rows_hint: int = 0, splits: int = 1,
-                scratch: torch.Tensor | None = None, mode: int = GEMM_PLAIN) -> int:
+                scratch: torch.Tensor | None = None, mode: int = GEMM_PLAIN,
+                tiles: tuple[torch.Tensor, torch.Tensor] | None = None) -> int:
     """a @ w^T on the tcgen05 tensor cores (bfloat16 in, float32 accumulate).  a: [M, K]; w: [N, K] or,
     with row-group offsets [E + 1], [E, N, K].
     GEMM_PLAIN: out [M, N] bfloat16 or float32; splits > 1 cuts K across blocks (scratch: float32
     [splits * M * N]) and adds the partials.  GEMM_PARTIALS: out is float32 [splits, M, N], left for the
     consumer to add.  GEMM_SWIGLU: w's rows are interleaved [16 gate, 16 up]; out [M, N / 2] =
-    silu(gate) * up.  Returns the split count used."""
+    silu(gate) * up.  ``tiles`` = (tile_list, n_tiles) from expert_sort for the same rows_hint.
+    Returns the split count used."""
     _contig(a, w, out, offsets, scratch)
     M, K = a.shape
     E = w.shape[0] if offsets is not None else 0
@@ -282,7 +289,7 @@ def gemm_stream(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: tor
     used = c_int(1)
     _run("gemm_stream", "jlx_gemm_stream", _ptr(a), _ptr(w), _ptr(out), c_int(int(out.dtype == torch.float32)), c_int(M),
          c_int(N), c_int(K), _ptr(offsets), c_int(E), c_int(rows_hint), c_int(splits), _ptr(scratch), c_int(mode),
-         ctypes.byref(used), _ptr(status), _stream())
+         _ptr(tiles[0]) if tiles else None, _ptr(tiles[1]) if tiles else None, ctypes.byref(used), _ptr(status), _stream())
     return used.value
 
 
@@ -299,14 +306,21 @@ def router(h32: torch.Tensor, w_router: torch.Tensor, topk_idx: torch.Tensor, to
 
 
 def expert_sort(topk_idx: torch.Tensor, offsets: torch.Tensor, sorted_pair: torch.Tensor, sorted_pos: torch.Tensor,
-                E: int, status: torch.Tensor, extra_rows: int = 0) -> None:
+                E: int, status: torch.Tensor, extra_rows: int = 0, tile_rows: int = 0,
+                tile_list: torch.Tensor | None = None, n_tiles: torch.Tensor | None = None) -> None:
     """Counting sort of the (token, choice) pairs by expert.  offsets: [E + 1], or [E + 2] with extra_rows > 0:
-    one more group of that many rows appended after the experts."""
-    _contig(topk_idx, offsets, sorted_pair, sorted_pos)
+    one more group of that many rows appended after the experts.  With tile_rows > 0 also the list of row
+    tiles of that height that hold rows: tile_list int32 [(ceil(rows / tile_rows) + groups) * 2], n_tiles [1]."""
+    _contig(topk_idx, offsets, sorted_pair, sorted_pos, tile_list, n_tiles)
     if offsets.numel() < E + 1 + (extra_rows > 0):
         raise KernelError("expert_sort: offsets too short")
+    if tile_rows > 0:
+        rows, groups = topk_idx.numel() + extra_rows, E + (extra_rows > 0)
+        if tile_list is None or n_tiles is None or tile_list.numel() < 2 * (-(-rows // tile_rows) + groups):
+            raise KernelError("expert_sort: tile list too short")
     _run("moe", "jlx_expert_sort", _ptr(topk_idx), _ptr(offsets), _ptr(sorted_pair), _ptr(sorted_pos),
-         c_int(topk_idx.numel()), c_int(E), c_int(extra_rows), _ptr(status), _stream())
+         c_int(topk_idx.numel()), c_int(E), c_int(extra_rows), c_int(tile_rows), _ptr(tile_list), _ptr(n_tiles),
+         _ptr(status), _stream())
 
 
 def permute_scale(h32: torch.Tensor, sorted_pair: torch.Tensor, topk_w: torch.Tensor, a_sorted: torch.Tensor, k: int,

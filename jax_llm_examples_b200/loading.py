@@ -23,6 +23,14 @@ _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.
            torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
 
 
+def _built(model: DecoderModel) -> DecoderModel:
+    """Building re-lays weights through temporaries as large as the largest tensor; they go back to the
+    driver here, so that the cache pool and the steps' buffers do not compete with a full allocator cache."""
+    if model.runtime.device.type == "cuda":
+        torch.cuda.empty_cache()
+    return model
+
+
 def parse_dtype(dtype: str | torch.dtype) -> torch.dtype:
     try:
         return _DTYPES[dtype]
@@ -38,7 +46,7 @@ def load_model(model_dir: str | Path, dtype: str | torch.dtype = "bfloat16", dev
     arch = resolve(cfg_json)
     cfg = arch.parse_config(cfg_json)
     tensors = load_tensors(model_dir, arch.tensor_specs(cfg), arch.canonical_name, dt, device)
-    return arch.build(cfg, tensors, Runtime(dt, torch.device(device)))
+    return _built(arch.build(cfg, tensors, Runtime(dt, torch.device(device))))
 
 
 def random_model(config_json: Mapping[str, Any], seed: int, dtype: str | torch.dtype = "bfloat16",
@@ -60,7 +68,7 @@ def random_model(config_json: Mapping[str, Any], seed: int, dtype: str | torch.d
         def __contains__(self, name):
             return name in specs and not specs[name].optional
 
-    return arch.build(cfg, _Lazy(), Runtime(dt, torch.device(device)))
+    return _built(arch.build(cfg, _Lazy(), Runtime(dt, torch.device(device))))
 
 
 def model_from_tensors(config_json: Mapping[str, Any], tensors: Mapping[str, torch.Tensor],
@@ -71,4 +79,4 @@ def model_from_tensors(config_json: Mapping[str, Any], tensors: Mapping[str, tor
     check_tensors(tensors, arch.tensor_specs(cfg))
     conv = {n: (t.to(torch.float32) if dt == torch.float32 or t.dtype == torch.float32 else t.to(torch.bfloat16)).to(device)
             for n, t in tensors.items()}
-    return arch.build(cfg, conv, Runtime(dt, torch.device(device)))
+    return _built(arch.build(cfg, conv, Runtime(dt, torch.device(device))))

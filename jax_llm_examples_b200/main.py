@@ -97,7 +97,8 @@ def main(argv: list[str] | None = None) -> int:
     ps = args.page_size
     max_tokens = args.max_tokens or sum(-(-(len(p) + args.max_new_tokens) // ps) * ps for p in prompts)
     gen = J.Generator(model, max_tokens=max_tokens, page_size=ps, max_slots=max(len(prompts), 1),
-                      max_tokens_per_step=args.max_tokens_per_step, max_live=args.max_live, seed=args.seed)
+                      max_tokens_per_step=args.max_tokens_per_step, max_live=args.max_live, seed=args.seed,
+                      profile=args.verbose)
     t0 = time.time()
     outputs = gen.generate(prompts, params)
     dt = time.time() - t0
@@ -109,6 +110,15 @@ def main(argv: list[str] | None = None) -> int:
         n = sum(map(len, outputs))
         print(f"{n} tokens in {dt:.3f} s ({n / dt:.1f} tok/s), {gen.scheduler.step_count} steps, "
               f"{sum(r.preemptions for r in gen.scheduler.finished)} preemptions", file=sys.stderr)
+        pre = [(p_, t) for p_, d, t in gen.step_times if p_ > 0]
+        dec = [(d, t) for p_, d, t in gen.step_times if p_ == 0 and d > 0]
+        if pre:
+            print(f"steps with prompt tokens: {sum(p_ for p_, _ in pre)} tokens in {sum(t for _, t in pre):.3f} s "
+                  f"({sum(p_ for p_, _ in pre) / sum(t for _, t in pre):.0f} tok/s)", file=sys.stderr)
+        if dec:
+            print(f"decode-only steps: {len(dec)} steps, {sum(d for d, _ in dec)} tokens in {sum(t for _, t in dec):.3f} s "
+                  f"({sum(d for d, _ in dec) / sum(t for _, t in dec):.1f} tok/s, {1e3 * sum(t for _, t in dec) / len(dec):.2f} ms/step)",
+                  file=sys.stderr)
     return 0
 
 

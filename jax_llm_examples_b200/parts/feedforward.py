@@ -6,7 +6,8 @@ import torch
 
 from ..kernels import api as K
 from .base import FeedForward, Rows, StepContext, as_rows, register_part
-from .linear import STREAM_MAX_ROWS, grouped_linear, grouped_swiglu_linear, interleave_gate_up, linear, swiglu_linear
+from .linear import (STREAM_MAX_ROWS, group_rows_hint, grouped_linear, grouped_swiglu_linear, interleave_gate_up, linear,
+                     swiglu_linear)
 
 
 def _can_interleave(w_gate_up: torch.Tensor) -> bool:
@@ -85,8 +86,17 @@ class RoutedExperts(FeedForward):
         offsets = torch.empty(self.num_experts + 2, dtype=torch.int32, device=dev)
         sorted_pair = torch.empty(n * k, dtype=torch.int32, device=dev)
         sorted_pos = torch.empty(n * k, dtype=torch.int32, device=dev)
-        K.expert_sort(topk_idx, offsets, sorted_pair, sorted_pos, self.num_experts, ctx.status, extra_rows)
-        return offsets, sorted_pair, sorted_pos
+        tiles = None
+        if self.we_gate_up.dtype == torch.bfloat16 and ctx.runtime.dtype == torch.bfloat16:
+            # the grouped products will run on the streaming kernel: list their row tiles once, here
+            rows, groups = n * k + extra_rows, self.num_experts + (extra_rows > 0)
+            tile_rows = K.gemm_stream_token_tile(group_rows_hint(rows, groups, extra_rows))
+            tiles = (torch.empty(2 * (-(-rows // tile_rows) + groups), dtype=torch.int32, device=dev),
+                     torch.empty(1, dtype=torch.int32, device=dev))
+            K.expert_sort(topk_idx, offsets, sorted_pair, sorted_pos, self.num_experts, ctx.status, extra_rows, tile_rows, *tiles)
+        else:
+            K.expert_sort(topk_idx, offsets, sorted_pair, sorted_pos, self.num_experts, ctx.status, extra_rows)
+        return offsets, sorted_pair, sorted_pos, tiles
 
     def forward(self, ctx: StepContext, h, h32, routing=None):
         rt = ctx.runtime
@@ -97,12 +107,13 @@ class RoutedExperts(FeedForward):
             ctx.scratch["record_routing"].append(topk_idx)
         merged = self.merged and n <= STREAM_MAX_ROWS
         extra = n if merged else 0
-        offsets, sorted_pair, sorted_pos = self.sort(ctx, topk_idx, extra)
+        offsets, sorted_pair, sorted_pos, tiles = self.sort(ctx, topk_idx, extra)
         a_sorted = torch.empty((n * k + extra, D), dtype=rt.dtype, device=h.device)
         K.permute_scale(h32, sorted_pair, topk_w, a_sorted, k, extra)
         groups = E + 1 if merged else E
-        act = grouped_swiglu_linear(ctx, a_sorted, self.we_gate_up[:groups], offsets, self.interleaved, rt.dtype, extra)
-        y = grouped_linear(ctx, act, self.we_down[:groups], offsets, torch.float32, partials=True, largest_group=extra)
+        act = grouped_swiglu_linear(ctx, a_sorted, self.we_gate_up[:groups], offsets, self.interleaved, rt.dtype, extra, tiles)
+        y = grouped_linear(ctx, act, self.we_down[:groups], offsets, torch.float32, partials=True, largest_group=extra,
+                           tiles=tiles)
         shared = None
         if self.shared is not None and not merged:
             shared = as_rows(self.shared.forward(ctx, h, None))

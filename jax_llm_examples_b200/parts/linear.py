@@ -57,7 +57,8 @@ def interleave_gate_up(w_gate_up: torch.Tensor) -> torch.Tensor:
 
 def linear(ctx: StepContext, a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, partials: bool = False):
     """a: [M, K]; w: [N, K]; returns [M, N] in out_dtype (float32 accumulation).  With ``partials`` the
-    result is :class:`Rows` in float32 whose split-K slices the consumer adds."""
+    result is :class:`Rows`: float32 split-K slices that the consumer adds when the streaming kernel ran,
+    else one slice in out_dtype."""
     M, N = a.shape[0], w.shape[0]
     if _streams(a, w, True):
         splits = _splits_for(N, a.shape[1])
@@ -69,8 +70,7 @@ def linear(ctx: StepContext, a: torch.Tensor, w: torch.Tensor, out_dtype: torch.
         scratch = ctx.workspace.get("splitk", splits * M * N, torch.float32) if splits > 1 else None
         K.gemm_stream(a, w, out, ctx.status, splits=splits, scratch=scratch)
         return out
-    if partials:
-        out_dtype = torch.float32
+    # not the streaming kernel: one complete result in the type asked for (a consumer of Rows takes any type)
     if a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
         out = torch.mm(a, w.t()) if out_dtype == torch.bfloat16 else torch.mm(a, w.t(), out_dtype=torch.float32)
     else:
@@ -93,21 +93,26 @@ def swiglu_linear(ctx: StepContext, a: torch.Tensor, w_gate_up: torch.Tensor, in
     return act
 
 
+def group_rows_hint(rows: int, groups: int, largest_group: int = 0) -> int:
+    return _group_rows_hint(rows, groups, largest_group)
+
+
 def grouped_linear(ctx: StepContext, a_sorted: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor,
-                   out_dtype: torch.dtype, partials: bool = False, largest_group: int = 0):
+                   out_dtype: torch.dtype, partials: bool = False, largest_group: int = 0, tiles=None):
     """Rows [offsets[e], offsets[e+1]) of a_sorted times w[e]^T.  w: [E, N, K].  With ``partials`` the result
     is float32 :class:`Rows`; few rows (few groups in use) then get K cut across blocks to fill the GPU."""
     rows, E, N = a_sorted.shape[0], w.shape[0], w.shape[1]
     if _streams(a_sorted, w, False):
         hint = _group_rows_hint(rows, E, largest_group)
         if partials:
-            tiles = -(-N // 128) * min(E, rows)  # at most this many blocks have work
-            splits = max(1, min(-(-2 * _SM_COUNT // tiles), a_sorted.shape[1] // 512, 8)) if rows <= STREAM_MAX_ROWS else 1
+            busy = -(-N // 128) * min(E, rows)  # at most this many blocks have work
+            splits = max(1, min(-(-2 * _SM_COUNT // busy), a_sorted.shape[1] // 512, 8)) if rows <= STREAM_MAX_ROWS else 1
             out = torch.empty((splits, rows, N), dtype=torch.float32, device=a_sorted.device)
-            used = K.gemm_stream(a_sorted, w, out, ctx.status, offsets=offsets, rows_hint=hint, splits=splits, mode=K.GEMM_PARTIALS)
+            used = K.gemm_stream(a_sorted, w, out, ctx.status, offsets=offsets, rows_hint=hint, splits=splits, mode=K.GEMM_PARTIALS,
+                                 tiles=tiles)
             return Rows(out[:used], used)
         out = torch.empty((rows, N), dtype=out_dtype, device=a_sorted.device)
-        K.gemm_stream(a_sorted, w, out, ctx.status, offsets=offsets, rows_hint=hint)
+        K.gemm_stream(a_sorted, w, out, ctx.status, offsets=offsets, rows_hint=hint, tiles=tiles)
         return out
     out = torch.empty((rows, N), dtype=torch.float32 if partials else out_dtype, device=a_sorted.device)
     K.gemm_simt(a_sorted, w, out, offsets)
@@ -115,13 +120,13 @@ def grouped_linear(ctx: StepContext, a_sorted: torch.Tensor, w: torch.Tensor, of
 
 
 def grouped_swiglu_linear(ctx: StepContext, a_sorted: torch.Tensor, w_gate_up: torch.Tensor, offsets: torch.Tensor,
-                          interleaved: bool, out_dtype: torch.dtype, largest_group: int = 0) -> torch.Tensor:
+                          interleaved: bool, out_dtype: torch.dtype, largest_group: int = 0, tiles=None) -> torch.Tensor:
     """``largest_group``: rows of a group known to be large (a shared expert's), so that one tile holds it."""
     rows, E, F = a_sorted.shape[0], w_gate_up.shape[0], w_gate_up.shape[1] // 2
     act = torch.empty((rows, F), dtype=out_dtype, device=a_sorted.device)
     if interleaved and _streams(a_sorted, w_gate_up, False):
         hint = _group_rows_hint(rows, E, largest_group)
-        K.gemm_stream(a_sorted, w_gate_up, act, ctx.status, offsets=offsets, rows_hint=hint, mode=K.GEMM_SWIGLU)
+        K.gemm_stream(a_sorted, w_gate_up, act, ctx.status, offsets=offsets, rows_hint=hint, mode=K.GEMM_SWIGLU, tiles=tiles)
         return act
     gu = grouped_linear(ctx, a_sorted, w_gate_up, offsets, out_dtype)
     K.silu_mul(gu, act, interleaved=interleaved)

@@ -528,3 +528,72 @@ def test_gemm_stream_grouped_split_k_partials():
         lo, hi = int(off[e]), int(off[e + 1])
         if hi > lo:
             close(got[lo:hi], a[lo:hi].double() @ w[e].double().T, 1e-5)
+
+
+@pytest.mark.parametrize("E, N, k, extra", [(128, 300, 1, 0), (16, 40, 2, 40), (5, 7, 1, 7)])
+def test_grouped_product_with_the_sort_kernels_tile_list(E, N, k, extra):
+    """expert_sort lists the row tiles that hold rows; the grouped product then finds its work from that list."""
+    api = K()
+    D, Nout = 128, 256
+    idx = torch.randint(0, E, (N, k), device=DEV, dtype=torch.int32)
+    groups, rows = E + (extra > 0), N * k + extra
+    hint = max(3, extra)
+    tile_rows = api.gemm_stream_token_tile(hint)
+    off = torch.empty(E + 2, device=DEV, dtype=torch.int32)
+    pair, pos, st = torch.empty(N * k, device=DEV, dtype=torch.int32), torch.empty(N * k, device=DEV, dtype=torch.int32), status()
+    tl = torch.full((2 * (-(-rows // tile_rows) + groups),), -1, device=DEV, dtype=torch.int32)
+    nt = torch.zeros(1, device=DEV, dtype=torch.int32)
+    api.expert_sort(idx, off, pair, pos, E, st, extra, tile_rows, tl, nt)
+    offs = off[: groups + 1].tolist()
+    want = [(e, r) for e in range(groups) for r in range(offs[e], offs[e + 1], tile_rows)]
+    assert int(nt) == len(want) and tl[: 2 * len(want)].view(-1, 2).tolist() == [list(t) for t in want]
+    a = torch.randn(rows, D, device=DEV).bfloat16()
+    w = torch.randn(groups, Nout, D, device=DEV).bfloat16()
+    out = torch.full((rows, Nout), float("nan"), device=DEV)
+    api.gemm_stream(a, w, out, st, offsets=off[: groups + 1].contiguous(), rows_hint=hint, tiles=(tl, nt))
+    assert int(st) == 0
+    for e in range(groups):
+        lo, hi = offs[e], offs[e + 1]
+        if hi > lo:
+            close(out[lo:hi], a[lo:hi].double() @ w[e].double().T, 1e-5)
+
+
+@pytest.mark.parametrize("kind, size", [("window", 100), ("chunk", 192), ("chunk", 80)])
+def test_attention_edges_of_windows_and_chunks(kind, size):
+    """A key whose score would swamp all others sits exactly on the first position a query may see, and then
+    one position before it: seen, the output is that key's value; one before, the output must not contain
+    it at all.  Random keys would hide an edge that is off by one.  All three kernels, 32-bit and bfloat16."""
+    Hq, Hkv, dh, page = 6, 2, 64, 16
+    api = K()
+    L = 500
+    p = L - 1
+    first = p - size + 1 if kind == "window" else (p // size) * size
+    chunk, window = (size, 0) if kind == "chunk" else (0, size)
+    for dtype in (torch.float32, torch.bfloat16):
+        for hot, seen in ((first, True), (first - 1, False)):
+            q, pages, bt, req, pos, ks, vs = _paged_case(dtype, Hq, Hkv, dh, page, [L], [1], seed=hot)
+            pg, slot = int(bt[0, hot // page]), hot % page
+            pages[pg, 0, :, slot] = 0
+            pages[pg, 0, :, slot, 0] = 40.0
+            pages[pg, 1, :, slot] = 1000.0  # its value is unmistakable
+            q[:] = 0
+            q[..., 0] = 40.0
+            outs = []
+            out, st = torch.empty_like(q), status()
+            api.attention_generic(q, pages, bt, req, pos, out, dh ** -0.5, chunk, window, 0.0, 1.0, st)
+            outs.append(out)
+            if dtype == torch.bfloat16:
+                keys, splits = api.attention_decode_plan(L, chunk, window, Hkv)
+                part_o, part_ml = torch.empty(Hq * splits * dh, device=DEV), torch.empty(Hq * splits * 2, device=DEV)
+                o2 = torch.empty_like(q)
+                api.attention_decode(q, pages, bt, req, pos, o2, dh ** -0.5, chunk, window, 0.0, 1.0, part_o, part_ml, splits, keys, st)
+                o3 = torch.empty_like(q)
+                api.attention_prefill(q, pages, bt, req, pos, o3, torch.tensor([[0, 1]], device=DEV, dtype=torch.int32), 1,
+                                      dh ** -0.5, chunk, window, 0.0, 1.0, st)
+                outs += [o2, o3]
+            assert int(st) == 0
+            for o in outs:
+                if seen:
+                    assert float((o.float() - 1000.0).abs().max()) < 10.0
+                else:
+                    assert float(o.float().abs().max()) < 10.0  # ordinary values are ~N(0, 1)
