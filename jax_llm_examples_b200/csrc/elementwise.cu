@@ -38,15 +38,17 @@ JLX_API int jlx_embed(const int* ids, const void* table, int table_dtype, float*
 // With w_router the same block also routes the token (llama4/llama4_jax/model.py:958-972): scores =
 // normed row . w_router[e] in 32-bit, top-k of the raw scores (lower index wins ties), weight = sigmoid.
 #define ROUTER_MAX_E 256
+#define ROUTER_MAX_PARTS 4
 template <typename TO>
 __global__ void __launch_bounds__(1024)
 add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, int delta_splits, long long delta_stride,
                    const float* __restrict__ gamma, float eps, TO* __restrict__ out, float* __restrict__ out32,
                    const int* __restrict__ row_index, int D, int row_in_smem, const float* __restrict__ w_router, int E,
                    int k, int* __restrict__ topk_idx, float* __restrict__ topk_w) {
-  extern __shared__ float rowbuf[];  // [D] when row_in_smem
+  extern __shared__ __align__(16) float rowbuf[];  // [D] when row_in_smem
   __shared__ float scratch[33];
   __shared__ float scores[ROUTER_MAX_E];
+  __shared__ float partial[ROUTER_MAX_E * ROUTER_MAX_PARTS];
   pdl_launch_dependents();
   pdl_wait();
   const int n = blockIdx.x;
@@ -81,22 +83,45 @@ add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, int d
   }
   if (!w_router) return;
   __syncthreads();
+  // Router scores.  The walk over a router row waits on memory, so it is spread wide: `parts` warps share one
+  // expert (each a contiguous piece of the row, added in a fixed order afterwards), every lane keeps eight
+  // independent 16-byte loads in flight.
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
-  for (int e = warp; e < E; e += nwarp) {
+  int parts = nwarp / E;
+  parts = parts < 1 ? 1 : (parts > ROUTER_MAX_PARTS ? ROUTER_MAX_PARTS : parts);
+  const int piece = (((D + parts - 1) / parts) + 127) / 128 * 128;  // a multiple of a warp's 128 floats
+  for (int item = warp; item < E * parts; item += nwarp) {
+    const int e = item / parts, part = item - e * parts;
     const float* wr = w_router + (size_t)e * D;
-    // eight independent loads of the router row in flight per lane: this loop waits on memory, not on math
+    const int lo = part * piece, hi = min(D, lo + piece);
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    int d = lane;
-    for (; d + 7 * 32 < D; d += 8 * 32) {
-      float wv[8];
+    int d = lo + lane * 4;
+    if ((D & 3) == 0 && (((uintptr_t)w_router) & 15) == 0) {
+      for (; d + 7 * 128 < hi; d += 8 * 128) {
+        float4 wv[8];
 #pragma unroll
-      for (int u = 0; u < 8; ++u) wv[u] = wr[d + 32 * u];
+        for (int u = 0; u < 8; ++u) wv[u] = *reinterpret_cast<const float4*>(wr + d + 128 * u);
 #pragma unroll
-      for (int u = 0; u < 8; ++u) acc[u] = fmaf(rowbuf[d + 32 * u], wv[u], acc[u]);
+        for (int u = 0; u < 8; ++u) {
+          const float4 xv = *reinterpret_cast<const float4*>(rowbuf + d + 128 * u);
+          acc[u] = fmaf(xv.x, wv[u].x, fmaf(xv.y, wv[u].y, fmaf(xv.z, wv[u].z, fmaf(xv.w, wv[u].w, acc[u]))));
+        }
+      }
+      for (; d < hi; d += 128) {
+        const float4 wv = *reinterpret_cast<const float4*>(wr + d), xv = *reinterpret_cast<const float4*>(rowbuf + d);
+        acc[0] = fmaf(xv.x, wv.x, fmaf(xv.y, wv.y, fmaf(xv.z, wv.z, fmaf(xv.w, wv.w, acc[0]))));
+      }
+    } else {
+      for (int i = lo + lane; i < hi; i += 32) acc[0] = fmaf(rowbuf[i], wr[i], acc[0]);
     }
-    for (; d < D; d += 32) acc[0] = fmaf(rowbuf[d], wr[d], acc[0]);
     const float s = warp_sum(((acc[0] + acc[1]) + (acc[2] + acc[3])) + ((acc[4] + acc[5]) + (acc[6] + acc[7])));
-    if (lane == 0) scores[e] = s;
+    if (lane == 0) partial[e * ROUTER_MAX_PARTS + part] = s;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    float s = 0.f;
+    for (int part = 0; part < parts; ++part) s += partial[e * ROUTER_MAX_PARTS + part];
+    scores[e] = s;
   }
   __syncthreads();
   if (threadIdx.x == 0) {
