@@ -27,6 +27,7 @@
 #define KT 64            // keys per tile
 #define SPLIT_UNIT 64    // decode splits are multiples of this many keys (one tile), aligned to absolute positions
 #define SPLIT_MIN 256    // ... and at least this long: shorter blocks spend their time on set-up
+#define DEC_MAX_BOXES 1024  // block-table entries of a decode split kept in shared memory
 #define DEC_STAGES 3     // key/value tiles in flight per decode block (96 KB at head size 128: two blocks per SM)
 #define NEG_BIG (-1.0e30f)
 
@@ -341,6 +342,19 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map, const AttnP
   }
   __syncthreads();
 
+  // The block-table entries of the whole split come into shared memory first (all threads, one round of
+  // loads), so that the producer's copies never wait on a global load.
+  __shared__ int page_of_box[DEC_MAX_BOXES];
+  const int boxes_per_tile = KT / box_rows;
+  const int n_boxes = n_tiles * boxes_per_tile;
+  const bool cached = n_boxes <= DEC_MAX_BOXES;
+  if (cached) {
+    for (int b = threadIdx.x; b < n_boxes; b += blockDim.x) {
+      const int pi = (key_begin + b * box_rows) / P.page_size;
+      page_of_box[b] = pi < P.bt_stride ? table[pi] : -1;
+    }
+    __syncthreads();
+  }
   // producer: thread 0 issues all boxes of a tile
   auto issue = [&](int t) {
     const int st = t % DEC_STAGES;
@@ -348,10 +362,10 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map, const AttnP
     const uint32_t dst = base + st * STAGE_BYTES;
     mbar_expect_tx(bar, STAGE_BYTES);
     const int key0 = key_begin + t * KT;
-    for (int b = 0; b < KT / box_rows; ++b) {
+    for (int b = 0; b < boxes_per_tile; ++b) {
       const int pos = key0 + b * box_rows;
       const int pi = pos / P.page_size;
-      int page = pi < P.bt_stride ? table[pi] : -1;
+      int page = cached ? page_of_box[t * boxes_per_tile + b] : (pi < P.bt_stride ? table[pi] : -1);
       if (page >= P.num_pages) { atomicOr(P.status, JLX_STATUS_BAD_PAGE); page = 0; }
       if (page < 0) page = 0;  // no page there: every key of the box is masked
       const int row_k = ((page * 2 + 0) * P.Hkv + hk) * P.page_size + (pos - pi * P.page_size);

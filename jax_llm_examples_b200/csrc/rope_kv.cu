@@ -9,6 +9,8 @@
 // Cache layout of one layer: pages[page][0 = K, 1 = V][kv head][slot in page][dh].
 #include "common.cuh"
 
+#define ROPE_REG_PAIRS 4  // head sizes up to 256 keep a lane's pairs in registers
+
 // TI: element type of the projected rows (the activation type, or float32 split-K partials that are
 // added first); T: element type of q_out and of the cache.
 template <typename TI, typename T>
@@ -61,7 +63,47 @@ rope_kv_store_kernel(const TI* __restrict__ qkv, int splits, long long split_str
       continue;
     }
     T* dst = h < Hq ? q_out + ((size_t)n * Hq + h) * dh : (kdst ? kdst + (size_t)(h - Hq) * page_size * dh : nullptr);
-    // pass 1: rotate, accumulate the sum of squares
+    if (half <= 32 * ROPE_REG_PAIRS) {
+      // one pass: a lane keeps its pairs in registers between the sum of squares and the write
+      float va[ROPE_REG_PAIRS], vb[ROPE_REG_PAIRS];
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < ROPE_REG_PAIRS; ++i) {
+        const int j = lane + 32 * i;
+        float a = 0.f, b = 0.f;
+        if (j < half) {
+          for (int z = 0; z < splits; ++z) {
+            a += to_f32<TI>(src[(size_t)z * split_stride + 2 * j]);
+            b += to_f32<TI>(src[(size_t)z * split_stride + 2 * j + 1]);
+          }
+          if (inv_freq) {
+            const float s = sc[2 * j], c = sc[2 * j + 1];
+            const float ra = a * c - b * s, rb = b * c + a * s;
+            a = ra;
+            b = rb;
+          }
+          ss += a * a + b * b;
+        }
+        va[i] = a;
+        vb[i] = b;
+      }
+      float inv = 1.f;
+      if (l2norm) {
+        ss = warp_sum(ss);
+        inv = 1.f / sqrtf(ss / (float)dh + eps);
+      }
+      if (!dst) continue;
+#pragma unroll
+      for (int i = 0; i < ROPE_REG_PAIRS; ++i) {
+        const int j = lane + 32 * i;
+        if (j < half) {
+          dst[2 * j] = from_f32<T>(va[i] * inv);
+          dst[2 * j + 1] = from_f32<T>(vb[i] * inv);
+        }
+      }
+      continue;
+    }
+    // larger heads: pass 1 rotates and accumulates the sum of squares
     float ss = 0.f;
     for (int j = lane; j < half; j += 32) {
       float a = 0.f, b = 0.f;
@@ -83,7 +125,7 @@ rope_kv_store_kernel(const TI* __restrict__ qkv, int splits, long long split_str
       inv = 1.f / sqrtf(ss / (float)dh + eps);
     }
     if (!dst) continue;
-    // pass 2: the same values again (cheaper than keeping dh of them live for any dh), scaled and written
+    // pass 2: the same values again, scaled and written
     for (int j = lane; j < half; j += 32) {
       float a = 0.f, b = 0.f;
       for (int z = 0; z < splits; ++z) {
