@@ -232,19 +232,3 @@ JLX_API int jlx_silu_mul(const void* gu, int in_dtype, int splits, long long spl
   JLX_LAUNCH_CHECK("silu_mul");
   return 0;
 }
-
-// dst[i] = src[i] converted between element types (activations entering a 32-bit weight's product).
-template <typename TS, typename TD>
-__global__ void convert_kernel(const TS* __restrict__ src, TD* __restrict__ dst, size_t n) {
-  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
-    dst[i] = from_f32<TD>(to_f32<TS>(src[i]));
-}
-
-JLX_API int jlx_convert(const void* src, int src_dtype, void* dst, int dst_dtype, long long n, cudaStream_t stream) {
-  if (n <= 0) return 0;
-  int blocks = (int)((n + 255) / 256 < 65535 ? (n + 255) / 256 : 65535);
-  JLX_DISPATCH_DTYPE(src_dtype, TS, JLX_DISPATCH_DTYPE(dst_dtype, TD,
-      (convert_kernel<TS, TD><<<blocks, 256, 0, stream>>>((const TS*)src, (TD*)dst, (size_t)n))));
-  JLX_LAUNCH_CHECK("convert");
-  return 0;
-}

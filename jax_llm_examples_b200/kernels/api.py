@@ -140,12 +140,6 @@ def silu_mul(gu: torch.Tensor, out: torch.Tensor, splits: int = 1, interleaved: 
          c_int(code(out.dtype)), c_int(rows), c_int(F), c_int(int(interleaved)), _stream())
 
 
-def convert(src: torch.Tensor, dst: torch.Tensor) -> None:
-    _contig(src, dst)
-    _run("elementwise", "jlx_convert", _ptr(src), c_int(code(src.dtype)), _ptr(dst), c_int(code(dst.dtype)),
-         c_longlong(src.numel()), _stream())
-
-
 # ------------------------------------------------------------------- position encoding + cache
 def rope_kv_store(qkv: torch.Tensor, q_out: torch.Tensor, pages: torch.Tensor | None, block_table: torch.Tensor | None,
                   req_of_token: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor | None, l2norm: bool,

@@ -23,8 +23,7 @@ import torch
 
 from ..config.llama4 import Llama4Config
 from ..config.registry import Architecture, register_architecture
-from ..parts import (DecoderModel, DenseSwiGLU, InterleavedRope, NoPositionWithTemperature, PagedAttention,
-                     PreNormBlock, RMSNorm, RoutedExperts, Runtime, llama3_scaled_frequencies)
+from ..parts import DecoderModel, Runtime, llama3_scaled_frequencies, make_part
 from ..weights.loader import TensorSpec
 
 _SKIP = re.compile(r"^(vision_model\.|multi_modal_projector\.)")
@@ -82,8 +81,10 @@ def build(cfg: Llama4Config, tensors: Mapping[str, torch.Tensor], runtime: Runti
         rs = cfg.rope_scaling
         scaling = {"factor": rs.factor, "low_freq_factor": rs.low_freq_factor, "high_freq_factor": rs.high_freq_factor,
                    "original_max_position_embeddings": rs.original_max_position_embeddings}
-    rope = InterleavedRope(llama3_scaled_frequencies(dh, cfg.rope_theta, scaling), dev)
-    nope = NoPositionWithTemperature(cfg.attn_scale if cfg.attn_temperature_tuning else 0.0, cfg.floor_scale)
+    # Which part serves which layer is decided here, layer by layer, by name from the parts registry.
+    rope = make_part("position", "interleaved_rope", inv_freq=llama3_scaled_frequencies(dh, cfg.rope_theta, scaling), device=dev)
+    nope = make_part("position", "none_with_temperature",
+                     attn_scale=cfg.attn_scale if cfg.attn_temperature_tuning else 0.0, floor_scale=cfg.floor_scale)
 
     def take(name: str) -> torch.Tensor:
         return t.pop(name).to(dev)
@@ -94,31 +95,37 @@ def build(cfg: Llama4Config, tensors: Mapping[str, torch.Tensor], runtime: Runti
         w_qkv = torch.cat([take(p + "self_attn.q_proj.weight"), take(p + "self_attn.k_proj.weight"),
                            take(p + "self_attn.v_proj.weight")], dim=0).contiguous()
         uses_rope = cfg.layer_uses_rope(i)
-        mixer = PagedAttention(
-            w_qkv, take(p + "self_attn.o_proj.weight").contiguous(), Hq, Hkv, dh,
-            position=rope if uses_rope else nope,
+        mixer = make_part(
+            "mixer", "paged_attention", w_qkv=w_qkv, w_o=take(p + "self_attn.o_proj.weight").contiguous(),
+            n_heads=Hq, n_kv_heads=Hkv, head_dim=dh, position=rope if uses_rope else nope,
             qk_norm_eps=cfg.rms_norm_eps if (cfg.use_qk_norm and uses_rope) else None,
             chunk=cfg.attention_chunk_size if uses_rope else None,
         )
         if cfg.layer_is_moe(i):
-            shared = DenseSwiGLU(
-                torch.cat([take(p + "feed_forward.shared_expert.gate_proj.weight"),
-                           take(p + "feed_forward.shared_expert.up_proj.weight")], dim=0).contiguous(),
-                take(p + "feed_forward.shared_expert.down_proj.weight").contiguous())
+            shared = make_part(
+                "feed_forward", "dense_swiglu",
+                w_gate_up=torch.cat([take(p + "feed_forward.shared_expert.gate_proj.weight"),
+                                     take(p + "feed_forward.shared_expert.up_proj.weight")], dim=0).contiguous(),
+                w_down=take(p + "feed_forward.shared_expert.down_proj.weight").contiguous())
             # HF keeps expert matrices as [in, out] (chkpt_utils.py:110-115); the kernels read [out, in]
             gate_up = take(p + "feed_forward.experts.gate_up_proj").transpose(1, 2).contiguous()
             down = take(p + "feed_forward.experts.down_proj").transpose(1, 2).contiguous()
-            ffn = RoutedExperts(take(p + "feed_forward.router.weight"), gate_up, down, cfg.num_experts_per_tok, shared)
+            ffn = make_part("feed_forward", "routed_experts", w_router=take(p + "feed_forward.router.weight"),
+                            we_gate_up=gate_up, we_down=down, top_k=cfg.num_experts_per_tok, shared=shared)
         else:
-            ffn = DenseSwiGLU(
-                torch.cat([take(p + "feed_forward.gate_proj.weight"), take(p + "feed_forward.up_proj.weight")],
-                          dim=0).contiguous(),
-                take(p + "feed_forward.down_proj.weight").contiguous())
-        blocks.append(PreNormBlock(RMSNorm(take(p + "input_layernorm.weight"), cfg.rms_norm_eps), mixer,
-                                   RMSNorm(take(p + "post_attention_layernorm.weight"), cfg.rms_norm_eps), ffn))
+            ffn = make_part(
+                "feed_forward", "dense_swiglu",
+                w_gate_up=torch.cat([take(p + "feed_forward.gate_proj.weight"), take(p + "feed_forward.up_proj.weight")],
+                                    dim=0).contiguous(),
+                w_down=take(p + "feed_forward.down_proj.weight").contiguous())
+        blocks.append(make_part(
+            "block", "pre_norm",
+            norm1=make_part("norm", "rms", weight=take(p + "input_layernorm.weight"), eps=cfg.rms_norm_eps), mixer=mixer,
+            norm2=make_part("norm", "rms", weight=take(p + "post_attention_layernorm.weight"), eps=cfg.rms_norm_eps),
+            feed_forward=ffn))
     embedding = take("model.embed_tokens.weight").contiguous()
     lm_head = take("lm_head.weight").contiguous() if "lm_head.weight" in t else embedding
-    final_norm = RMSNorm(take("model.norm.weight"), cfg.rms_norm_eps)
+    final_norm = make_part("norm", "rms", weight=take("model.norm.weight"), eps=cfg.rms_norm_eps)
     return DecoderModel(runtime, embedding, blocks, final_norm, lm_head, config=cfg)
 
 

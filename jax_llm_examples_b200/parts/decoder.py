@@ -108,9 +108,10 @@ class DecoderModel:
         def walk(o):
             nonlocal total
             if isinstance(o, torch.Tensor):
-                if o.data_ptr() not in seen:
-                    seen.add(o.data_ptr())
-                    total += o.numel() * o.element_size()
+                store = o.untyped_storage()
+                if store.data_ptr() not in seen:  # views (a shared expert inside the experts' tensor) count once
+                    seen.add(store.data_ptr())
+                    total += store.nbytes()
             elif hasattr(o, "__dict__"):
                 for v in vars(o).values():
                     walk(v)

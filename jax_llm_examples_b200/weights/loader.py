@@ -18,7 +18,7 @@ from __future__ import annotations
 import dataclasses
 import json
 from pathlib import Path
-from typing import Callable, Iterable, Mapping
+from typing import Callable, Mapping
 
 import torch
 
@@ -123,7 +123,3 @@ def check_tensors(tensors: Mapping[str, torch.Tensor], specs: Mapping[str, Tenso
     ]
     if missing or unexpected or wrong:
         raise WeightError(where, missing, unexpected, wrong)
-
-
-def names_with_prefix(names: Iterable[str], prefix: str) -> list[str]:
-    return [n for n in names if n.startswith(prefix)]

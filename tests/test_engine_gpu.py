@@ -87,3 +87,32 @@ def test_cutting_does_not_change_float32_logits(model_dirs, name):
     worst = max(H.rel_err(cut[k], whole[k]) for k in whole)
     print(f"{name}: whole vs portions, float32: {worst:.2e}")
     assert worst < 2e-6
+
+
+def test_a_checkpoint_stored_in_float32_served_in_bfloat16(tmp_path):
+    """Tensors stored in 32-bit stay 32-bit in bfloat16 mode: activations and cache are bfloat16, the products
+    run on the mixed-precision FMA kernel.  Same tolerance as any bfloat16 run."""
+    import jax_llm_examples_b200 as J
+
+    folder = H.make_model_dir(tmp_path / "m", "tiny_b", seed=3, dtype=torch.float32)
+    model = J.load_model(folder, "bfloat16", "cuda")
+    assert model.lm_head.dtype == torch.float32 and model.blocks[0].mixer.w_qkv.dtype == torch.float32
+    eng = J.Engine(model, max_tokens=160, page_size=16, max_slots=4)
+    assert eng.kv[0].dtype == torch.bfloat16
+    rng = random.Random(5)
+    reqs = H.random_requests(rng, 384, [90, 31])
+    got, routing = H.run_trace(eng, H.trace_mixed(reqs, rng, max_live=2))
+    H.compare_with_plain(folder, reqs, got, routing, "bfloat16")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_tied_embeddings(tmp_path, dtype):
+    import jax_llm_examples_b200 as J
+
+    folder = H.make_model_dir(tmp_path / "m", "tiny_a", seed=6, tie_word_embeddings=True)
+    model = J.load_model(folder, dtype, "cuda")
+    assert model.lm_head.data_ptr() == model.embedding.data_ptr()
+    eng = J.Engine(model, max_tokens=128, page_size=16, max_slots=2)
+    reqs = H.random_requests(random.Random(8), 256, [40, 9])
+    got, routing = H.run_trace(eng, H.trace_tail_decode(reqs, 8))
+    H.compare_with_plain(folder, reqs, got, routing, dtype)
