@@ -56,30 +56,66 @@ add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, int d
   float* xr = x + r * D;
   const float* dr = delta ? delta + r * D : nullptr;
   float ss = 0.f;
-  for (int d = threadIdx.x; d < D; d += blockDim.x) {
-    float s = xr[d];
-    if (dr) {
-      for (int z = 0; z < delta_splits; ++z) s += dr[(size_t)z * delta_stride + d];
-      if (!row_index) xr[d] = s;
+  // 16-byte accesses when the row allows it (width a multiple of 4, row kept in shared memory)
+  const bool vec = row_in_smem && (D & 3) == 0 && (delta_stride & 3) == 0;
+  if (vec) {
+    const int D4 = D >> 2;
+    float4* x4 = reinterpret_cast<float4*>(xr);
+    const float4* d4 = reinterpret_cast<const float4*>(dr);
+    float4* row4 = reinterpret_cast<float4*>(rowbuf);
+    const long long stride4 = delta_stride >> 2;
+    for (int i = threadIdx.x; i < D4; i += blockDim.x) {
+      float4 s = x4[i];
+      if (dr) {
+        for (int z = 0; z < delta_splits; ++z) {
+          const float4 v = d4[(size_t)z * stride4 + i];
+          s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+        }
+        if (!row_index) x4[i] = s;
+      }
+      row4[i] = s;
+      ss += (s.x * s.x + s.y * s.y) + (s.z * s.z + s.w * s.w);
     }
-    if (row_in_smem) rowbuf[d] = s;
-    ss += s * s;
-  }
-  ss = block_sum(ss, scratch);
-  const float rms = sqrtf(ss / (float)D + eps);
-  for (int d = threadIdx.x; d < D; d += blockDim.x) {
-    float s;
-    if (row_in_smem) {
-      s = rowbuf[d];
-    } else {
-      s = xr[d];
-      if (dr && row_index)
+    ss = block_sum(ss, scratch);
+    const float rms = sqrtf(ss / (float)D + eps);
+    const float4* g4 = reinterpret_cast<const float4*>(gamma);
+    for (int i = threadIdx.x; i < D4; i += blockDim.x) {
+      const float4 s = row4[i];
+      const float4 g = gamma ? g4[i] : make_float4(1.f, 1.f, 1.f, 1.f);
+      const float4 v = make_float4(g.x * s.x / rms, g.y * s.y / rms, g.z * s.z / rms, g.w * s.w / rms);
+      if (out) {
+        TO* o = out + (size_t)n * D + 4 * i;
+        o[0] = from_f32<TO>(v.x); o[1] = from_f32<TO>(v.y); o[2] = from_f32<TO>(v.z); o[3] = from_f32<TO>(v.w);
+      }
+      if (out32) reinterpret_cast<float4*>(out32 + (size_t)n * D)[i] = v;
+      row4[i] = v;
+    }
+  } else {
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+      float s = xr[d];
+      if (dr) {
         for (int z = 0; z < delta_splits; ++z) s += dr[(size_t)z * delta_stride + d];
+        if (!row_index) xr[d] = s;
+      }
+      if (row_in_smem) rowbuf[d] = s;
+      ss += s * s;
     }
-    const float v = (gamma ? gamma[d] * s : s) / rms;
-    if (out) out[(size_t)n * D + d] = from_f32<TO>(v);
-    if (out32) out32[(size_t)n * D + d] = v;
-    if (row_in_smem) rowbuf[d] = v;
+    ss = block_sum(ss, scratch);
+    const float rms = sqrtf(ss / (float)D + eps);
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+      float s;
+      if (row_in_smem) {
+        s = rowbuf[d];
+      } else {
+        s = xr[d];
+        if (dr && row_index)
+          for (int z = 0; z < delta_splits; ++z) s += dr[(size_t)z * delta_stride + d];
+      }
+      const float v = (gamma ? gamma[d] * s : s) / rms;
+      if (out) out[(size_t)n * D + d] = from_f32<TO>(v);
+      if (out32) out32[(size_t)n * D + d] = v;
+      if (row_in_smem) rowbuf[d] = v;
+    }
   }
   if (!w_router) return;
   __syncthreads();
@@ -164,8 +200,9 @@ JLX_API int jlx_add_rmsnorm(float* x, const float* delta, int delta_splits, long
       static bool cfg = false;
       if (!cfg) { JLX_CUDA(cudaFuncSetAttribute(add_rmsnorm_kernel<TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024)); cfg = true; }
     }
-    // wide rows with few tokens are latency-bound: more threads per row keep more loads in flight
-    const int threads = D >= 2048 ? 1024 : 256;
+    // wide rows with few tokens are latency-bound: more threads per row keep more loads in flight; with many
+    // rows smaller blocks give more blocks per SM and cheaper barriers
+    const int threads = (D >= 2048 && N <= 256) ? 1024 : 256;
     JLX_CUDA(jlx_launch_pdl(add_rmsnorm_kernel<TO>, dim3(N), dim3(threads), smem, stream, x, delta, delta_splits, delta_stride,
                             gamma, eps, (TO*)out, out32, row_index, D, row_in_smem, w_router, E, k, topk_idx, topk_w));
   });

@@ -11,6 +11,18 @@
 
 #define ROPE_REG_PAIRS 4  // head sizes up to 256 keep a lane's pairs in registers
 
+// A rotary pair (2j, 2j+1) as one access.
+template <typename T> __device__ __forceinline__ float2 load_pair(const T* p);
+template <> __device__ __forceinline__ float2 load_pair<float>(const float* p) { return *reinterpret_cast<const float2*>(p); }
+template <> __device__ __forceinline__ float2 load_pair<bf16>(const bf16* p) {
+  return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+}
+template <typename T> __device__ __forceinline__ void store_pair(T* p, float a, float b);
+template <> __device__ __forceinline__ void store_pair<float>(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
+template <> __device__ __forceinline__ void store_pair<bf16>(bf16* p, float a, float b) {
+  *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
+}
+
 // TI: element type of the projected rows (the activation type, or float32 split-K partials that are
 // added first); T: element type of q_out and of the cache.
 template <typename TI, typename T>
@@ -54,10 +66,14 @@ rope_kv_store_kernel(const TI* __restrict__ qkv, int splits, long long split_str
     if (h >= Hq + Hkv) {  // value head: copy (sum of the partials)
       if (vdst) {
         T* dst = vdst + (size_t)(h - Hq - Hkv) * page_size * dh;
-        for (int d = lane; d < dh; d += 32) {
-          float v = 0.f;
-          for (int z = 0; z < splits; ++z) v += to_f32<TI>(src[(size_t)z * split_stride + d]);
-          dst[d] = from_f32<T>(v);
+        for (int j = lane; j < half; j += 32) {
+          float a = 0.f, b = 0.f;
+          for (int z = 0; z < splits; ++z) {
+            const float2 v = load_pair<TI>(src + (size_t)z * split_stride + 2 * j);
+            a += v.x;
+            b += v.y;
+          }
+          store_pair<T>(dst + 2 * j, a, b);
         }
       }
       continue;
@@ -73,8 +89,9 @@ rope_kv_store_kernel(const TI* __restrict__ qkv, int splits, long long split_str
         float a = 0.f, b = 0.f;
         if (j < half) {
           for (int z = 0; z < splits; ++z) {
-            a += to_f32<TI>(src[(size_t)z * split_stride + 2 * j]);
-            b += to_f32<TI>(src[(size_t)z * split_stride + 2 * j + 1]);
+            const float2 v = load_pair<TI>(src + (size_t)z * split_stride + 2 * j);
+            a += v.x;
+            b += v.y;
           }
           if (inv_freq) {
             const float s = sc[2 * j], c = sc[2 * j + 1];
@@ -96,10 +113,7 @@ rope_kv_store_kernel(const TI* __restrict__ qkv, int splits, long long split_str
 #pragma unroll
       for (int i = 0; i < ROPE_REG_PAIRS; ++i) {
         const int j = lane + 32 * i;
-        if (j < half) {
-          dst[2 * j] = from_f32<T>(va[i] * inv);
-          dst[2 * j + 1] = from_f32<T>(vb[i] * inv);
-        }
+        if (j < half) store_pair<T>(dst + 2 * j, va[i] * inv, vb[i] * inv);
       }
       continue;
     }
