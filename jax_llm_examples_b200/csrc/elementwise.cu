@@ -200,9 +200,12 @@ JLX_API int jlx_add_rmsnorm(float* x, const float* delta, int delta_splits, long
       static bool cfg = false;
       if (!cfg) { JLX_CUDA(cudaFuncSetAttribute(add_rmsnorm_kernel<TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024)); cfg = true; }
     }
-    // wide rows with few tokens are latency-bound: more threads per row keep more loads in flight; with many
-    // rows smaller blocks give more blocks per SM and cheaper barriers
-    const int threads = (D >= 2048 && N <= 256) ? 1024 : 256;
+    // Wide rows with few tokens are latency-bound: more threads per row keep more loads in flight; with many
+    // rows smaller blocks give more blocks per SM and cheaper barriers.  The block size fixes the order of the
+    // sum of squares, so in 32-bit output (the exact path) it depends on the width alone: a row's result must
+    // not change with the number of rows that happen to share its step.
+    const bool exact = out_dtype == JLX_F32;
+    const int threads = (D >= 2048 && (exact || N <= 256)) ? 1024 : 256;
     JLX_CUDA(jlx_launch_pdl(add_rmsnorm_kernel<TO>, dim3(N), dim3(threads), smem, stream, x, delta, delta_splits, delta_stride,
                             gamma, eps, (TO*)out, out32, row_index, D, row_in_smem, w_router, E, k, topk_idx, topk_w));
   });
