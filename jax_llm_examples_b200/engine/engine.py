@@ -158,18 +158,27 @@ class Engine:
         width = self.max_pages_per_request if static else -(-max_kv // self.page_size)
         packed = CacheManager.packed_size(G, N, R, M, width)
         # query tiles for the flash kernel: up to 16 consecutive tokens of one request
-        tiles = None
+        tiles = tiles_big = tiles_rest = None
         if int(n_tok.max()) > 1:
             firsts = np.concatenate([[0], np.cumsum(n_tok)[:-1]])
-            tiles = np.array([(f + t, min(16, n - t)) for f, n in zip(firsts, n_tok) for t in range(0, n, 16)], dtype=np.int32)
-            # late tiles of a causal prompt read the most keys: launch them first so that the tail is short
-            tiles = np.ascontiguousarray(tiles[::-1])
-        size = packed + (tiles.size if tiles is not None else 0)
+
+            def cut_tiles(rows: int, which) -> np.ndarray:
+                t = [(f + o, min(rows, n - o)) for f, n in zip(firsts, n_tok) if which(n) for o in range(0, n, rows)]
+                # late tiles of a causal prompt read the most keys: launch them first so that the tail is short
+                return np.ascontiguousarray(np.array(t, dtype=np.int32).reshape(-1, 2)[::-1])
+
+            tiles = cut_tiles(16, lambda n: True)
+            tiles_big = cut_tiles(128, lambda n: n >= 64)
+            tiles_rest = cut_tiles(16, lambda n: n < 64)
+        extra = [t for t in (tiles, tiles_big, tiles_rest) if t is not None]
+        size = packed + sum(t.size for t in extra)
         host, ring_i = self._ring.next(size)
         host_np = host.numpy()
         self.manager.pack_step(slots, n_tok, tokens, want_off, want, width, N, R, M, host_np)
-        if tiles is not None:
-            host_np[packed:size] = tiles.reshape(-1)
+        at = packed
+        for t in extra:
+            host_np[at:at + t.size] = t.reshape(-1)
+            at += t.size
         if static:
             if "desc" not in graph:
                 graph["desc"] = torch.empty(size, dtype=torch.int32, device=self.runtime.device)
@@ -205,6 +214,8 @@ class Engine:
             block_tables = [cut(R * width).view(R, width) for _ in range(G)]
             if tiles is not None:
                 ctx.attn_tiles, ctx.n_attn_tiles = cut(tiles.size).view(-1, 2), tiles.shape[0]
+                ctx.attn_tiles_big, ctx.n_attn_tiles_big = cut(tiles_big.size).view(-1, 2), tiles_big.shape[0]
+                ctx.attn_tiles_rest, ctx.n_attn_tiles_rest = cut(tiles_rest.size).view(-1, 2), tiles_rest.shape[0]
             if self.record_routing:
                 ctx.scratch["record_routing"] = []
             if static:

@@ -226,6 +226,27 @@ def attention_prefill(q: torch.Tensor, pages: torch.Tensor, block_table: torch.T
          c_float(floor_scale), _ptr(status), _stream())
 
 
+def attention_prefill_tc_supported(q_dtype: torch.dtype, Hq: int, Hkv: int, dh: int, page_size: int) -> bool:
+    if q_dtype != torch.bfloat16:
+        return False
+    return bool(library("attention_tc").jlx_attention_prefill_tc_supported(c_int(Hq), c_int(Hkv), c_int(dh), c_int(page_size)))
+
+
+def attention_prefill_tc(q: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor, req_of_token: torch.Tensor,
+                         positions: torch.Tensor, out: torch.Tensor, tiles: torch.Tensor, n_tiles: int, scale: float,
+                         chunk: int, window: int, attn_scale: float, floor_scale: float, status: torch.Tensor) -> None:
+    """Flash attention for prompt portions on tcgen05 (bfloat16, head size 128, pages of a multiple of 64).
+    tiles: int32 [n_tiles, 2] = (first token row, count <= 128), each within one request; only the rows
+    of these tiles are written."""
+    _contig(q, pages, block_table, out, tiles)
+    N, Hq, dh = q.shape
+    P, _, Hkv, page_size, _ = pages.shape
+    _run("attention_tc", "jlx_attention_prefill_tc", _ptr(q), _ptr(pages), _ptr(block_table), c_int(block_table.shape[1]),
+         _ptr(req_of_token), _ptr(positions), _ptr(out), _ptr(tiles), c_int(n_tiles), c_int(N), c_int(Hq), c_int(Hkv),
+         c_int(dh), c_int(page_size), c_int(P), c_float(scale), c_int(chunk), c_int(window), c_float(attn_scale),
+         c_float(floor_scale), _ptr(status), _stream())
+
+
 # ------------------------------------------------------------------------------------- GEMMs
 def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, offsets: torch.Tensor | None = None) -> None:
     """out = a @ w^T.  a: [M, K]; w: [N, K], or [E, N, K] with row-group offsets [E + 1] on the device."""

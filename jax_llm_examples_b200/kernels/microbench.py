@@ -76,17 +76,18 @@ def attention_prefill(a) -> dict:
     out = torch.empty_like(q)
     pos = torch.arange(T, device=dev, dtype=torch.int32)
     req = torch.zeros(T, device=dev, dtype=torch.int32)
-    tiles = torch.tensor([(t, min(16, T - t)) for t in range(0, T, 16)], device=dev, dtype=torch.int32)
+    rows = 128 if a.tc else 16
+    tiles = torch.tensor([(t, min(rows, T - t)) for t in range(0, T, rows)][::-1], device=dev, dtype=torch.int32)
     status = torch.zeros(1, device=dev, dtype=torch.int32)
+    fn = K.attention_prefill_tc if a.tc else K.attention_prefill
 
     def run():
-        K.attention_prefill(q, pages, table, req, pos, out, tiles, tiles.shape[0], a.head_dim ** -0.5, a.chunk, 0, 0.0, 1.0,
-                            status)
+        fn(q, pages, table, req, pos, out, tiles, tiles.shape[0], a.head_dim ** -0.5, a.chunk, 0, 0.0, 1.0, status)
 
     t = _time(run, a.reps, _flush(a))
     flops = 4 * a.heads * a.head_dim * T * (T + 1) / 2
     assert int(status) == 0
-    return {"kernel": "attention_prefill", "tokens": T, "us": round(t * 1e6, 1), "TFLOP": round(flops / 1e12, 4),
+    return {"kernel": "attention_prefill_tc" if a.tc else "attention_prefill", "tokens": T, "us": round(t * 1e6, 1), "TFLOP": round(flops / 1e12, 4),
             "TFLOP/s": round(flops / t / 1e12, 1)}
 
 
@@ -145,6 +146,7 @@ def main(argv=None) -> int:
             p.add_argument("--context", type=int, default=8192)
         if name == "attention_prefill":
             p.add_argument("--tokens", type=int, default=2048)
+            p.add_argument("--tc", action="store_true", help="the tcgen05 kernel (128-token tiles) instead of the mma.sync one")
         if name == "gemm":
             p.add_argument("--rows", type=int, default=8)
             p.add_argument("--n", type=int, default=16384)

@@ -21,7 +21,7 @@ class PagedAttention(Mixer):
     A layer with ``shares_cache`` projects only q and reads pages that another layer wrote.
     """
 
-    kernel_libraries = ("attention_generic", "attention_mma", "rope_kv", "gemm_simt", "gemm_stream")
+    kernel_libraries = ("attention_generic", "attention_mma", "attention_tc", "rope_kv", "gemm_simt", "gemm_stream")
 
     def __init__(self, w_qkv: torch.Tensor, w_o: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
                  position: PositionEncoding, qk_norm_eps: float | None = None, chunk: int | None = None,
@@ -75,9 +75,17 @@ class PagedAttention(Mixer):
                                    chunk, window, attn_scale, floor_scale, part_o, part_ml, splits, split_keys, ctx.status)
                 return
             if ctx.attn_tiles is not None:
-                K.attention_prefill(q, cache.pages, cache.block_table, ctx.req_of_token, ctx.positions, out,
-                                    ctx.attn_tiles, ctx.n_attn_tiles, self.scale, chunk, window, attn_scale,
-                                    floor_scale, ctx.status)
+                tiles, n_tiles = ctx.attn_tiles, ctx.n_attn_tiles
+                if ctx.n_attn_tiles_big and K.attention_prefill_tc_supported(q.dtype, self.n_heads, self.n_kv_heads,
+                                                                             self.head_dim, cache.pages.shape[3]):
+                    # long portions on the tcgen05 kernel (128-token tiles), the short ones below
+                    K.attention_prefill_tc(q, cache.pages, cache.block_table, ctx.req_of_token, ctx.positions, out,
+                                           ctx.attn_tiles_big, ctx.n_attn_tiles_big, self.scale, chunk, window,
+                                           attn_scale, floor_scale, ctx.status)
+                    tiles, n_tiles = ctx.attn_tiles_rest, ctx.n_attn_tiles_rest
+                if n_tiles:
+                    K.attention_prefill(q, cache.pages, cache.block_table, ctx.req_of_token, ctx.positions, out, tiles,
+                                        n_tiles, self.scale, chunk, window, attn_scale, floor_scale, ctx.status)
                 return
         K.attention_generic(q, cache.pages, cache.block_table, ctx.req_of_token, ctx.positions, out, self.scale,
                             self.chunk or 0, self.window or 0, attn_scale, floor_scale, ctx.status)

@@ -128,9 +128,15 @@ class StepContext:
     workspace: Workspace | None = None  # buffers that outlive the step
     attn_tiles: torch.Tensor | None = None  # int32 [n, 2]: (first token row, count <= 16) tiles of one request each
     n_attn_tiles: int = 0
+    # the same tokens cut for kernels with 128-row tiles: requests that bring at least 64 tokens in tiles of up
+    # to 128, and the 16-token tiles of the remaining requests
+    attn_tiles_big: torch.Tensor | None = None
+    n_attn_tiles_big: int = 0
+    attn_tiles_rest: torch.Tensor | None = None
+    n_attn_tiles_rest: int = 0
 
 
-BF16_ONLY_LIBRARIES = ("gemm_stream", "attention_mma")
+BF16_ONLY_LIBRARIES = ("gemm_stream", "attention_mma", "attention_tc")
 
 
 class Part:

@@ -160,7 +160,8 @@ def moe(h, w_router, we_gate_up, we_down, ws_gate, ws_up, ws_down, k: int, force
     sigmoid of this implementation's scores).  It exists for comparing with an implementation in
     lower precision, whose choice may rightly differ where two scores are nearly equal.  Returns
     (output, by how much each forced expert's score lies below the k-th best score, as a fraction of the
-    token's largest score magnitude [T])."""
+    router's typical score size, the RMS of all scores of the sequence [T]).  Rounding noise in a score is
+    proportional to that size, not to the size of the token's own scores."""
     T, D = h.shape
     F = we_down.shape[1]
     w, idx, _ = route(h, w_router, k)
@@ -169,7 +170,7 @@ def moe(h, w_router, we_gate_up, we_down, ws_gate, ws_up, ws_down, k: int, force
     if forced_idx is not None:
         idx = torch.as_tensor(forced_idx, dtype=torch.long)
         w = torch.sigmoid(torch.gather(scores, 1, idx))
-    shortfall = (kth[:, None] - torch.gather(scores, 1, idx)).max(dim=-1).values / scores.abs().max(dim=-1).values
+    shortfall = (kth[:, None] - torch.gather(scores, 1, idx)).max(dim=-1).values / scores.pow(2).mean().sqrt()
     routed = torch.zeros_like(h)
     for t in range(T):
         for j in range(k):

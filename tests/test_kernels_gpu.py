@@ -597,3 +597,29 @@ def test_attention_edges_of_windows_and_chunks(kind, size):
                     assert float((o.float() - 1000.0).abs().max()) < 10.0
                 else:
                     assert float(o.float().abs().max()) < 10.0  # ordinary values are ~N(0, 1)
+
+
+@pytest.mark.parametrize("Hq, Hkv, page, chunk, window, temp", [
+    (4, 2, 64, 0, 0, False), (10, 2, 128, 0, 0, True), (3, 1, 64, 200, 0, False), (4, 4, 64, 0, 150, False)])
+def test_attention_prefill_tc(Hq, Hkv, page, chunk, window, temp):
+    """The tcgen05 flash kernel: tiles of up to 128 tokens, several requests, cached history before the portion."""
+    dh = 128
+    lens, q_lens = [700, 128, 130, 300], [700, 128, 1, 45]
+    q, pages, bt, req, pos, ks, vs = _paged_case(torch.bfloat16, Hq, Hkv, dh, page, lens, q_lens)
+    out, st = torch.full_like(q, float("nan")), status()
+    attn_scale, floor_scale = (0.1, 64.0) if temp else (0.0, 1.0)
+    api = K()
+    assert api.attention_prefill_tc_supported(q.dtype, Hq, Hkv, dh, page)
+    tiles, at = [], 0
+    for n in q_lens:
+        tiles += [(at + t, min(128, n - t)) for t in range(0, n, 128)]
+        at += n
+    tl = torch.tensor(tiles, device=DEV, dtype=torch.int32)
+    api.attention_prefill_tc(q, pages, bt, req, pos, out, tl, len(tiles), dh ** -0.5, chunk, window, attn_scale, floor_scale, st)
+    torch.cuda.synchronize()
+    assert int(st) == 0
+    at = 0
+    for r, n in enumerate(q_lens):
+        ref = _attention_ref(q[at:at + n], ks[r], vs[r], pos[at:at + n].long(), chunk, window, dh ** -0.5, attn_scale, floor_scale)
+        close(out[at:at + n], ref, 1.5e-2)
+        at += n
