@@ -26,7 +26,7 @@
 
 #define KT 64            // keys per tile
 #define SPLIT_UNIT 64    // decode splits are multiples of this many keys (one tile), aligned to absolute positions
-#define SPLIT_MIN 256    // ... and at least this long: shorter blocks spend their time on set-up
+#define SPLIT_MIN 512    // ... and at least this long: shorter blocks spend their time on set-up
 #define DEC_MAX_BOXES 1024  // block-table entries of a decode split kept in shared memory
 #define DEC_STAGES 3     // key/value tiles in flight per decode block (96 KB at head size 128: two blocks per SM)
 #define NEG_BIG (-1.0e30f)
@@ -932,12 +932,14 @@ JLX_API int jlx_attention_mma_supported(int Hq, int Hkv, int dh, int decode) {
 }
 
 // Keys per decode split for `pairs` (request, KV head) pairs that read up to max_kv_len keys: a multiple
-// of SPLIT_UNIT chosen so that about four blocks per SM exist (two resident, two waiting).
+// of SPLIT_UNIT chosen so that all blocks are resident at once (two per SM): a second, partly filled round of
+// blocks costs more than longer splits do.
 JLX_API int jlx_attention_decode_split_keys(int max_kv_len, int chunk, int window, int pairs) {
   int span = max_kv_len;
   if (chunk > 0 && chunk < span) span = chunk;
   if (window > 0 && window < span) span = window;
-  const int want_splits = (4 * 148 + pairs - 1) / (pairs > 0 ? pairs : 1);
+  int want_splits = 2 * 148 / (pairs > 0 ? pairs : 1);
+  if (want_splits < 1) want_splits = 1;
   int keys = (span + want_splits - 1) / (want_splits > 0 ? want_splits : 1);
   keys = (keys + SPLIT_UNIT - 1) / SPLIT_UNIT * SPLIT_UNIT;
   return keys < SPLIT_MIN ? SPLIT_MIN : keys;

@@ -3,6 +3,8 @@
 // The residual stream is 32-bit in every precision mode: the sum x + delta and the norm's mean of
 // squares are computed in 32-bit (reference: llama4/llama4_jax/model.py:885-888 computes the mean in
 // float32; model.py:1173,1181 are the residual sums).
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 
 // x[n, :] = table[ids[n], :]                                     (model.py:1191)
@@ -38,7 +40,78 @@ JLX_API int jlx_embed(const int* ids, const void* table, int table_dtype, float*
 // With w_router the same block also routes the token (llama4/llama4_jax/model.py:958-972): scores =
 // normed row . w_router[e] in 32-bit, top-k of the raw scores (lower index wins ties), weight = sigmoid.
 #define ROUTER_MAX_E 256
+// Four consecutive outputs as one access (the address is a multiple of 4 elements).
+template <typename T> __device__ __forceinline__ void store4(T* p, float4 v);
+template <> __device__ __forceinline__ void store4<float>(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+template <> __device__ __forceinline__ void store4<bf16>(bf16* p, float4 v) {
+  uint2 o;
+  *reinterpret_cast<__nv_bfloat162*>(&o.x) = __floats2bfloat162_rn(v.x, v.y);
+  *reinterpret_cast<__nv_bfloat162*>(&o.y) = __floats2bfloat162_rn(v.z, v.w);
+  *reinterpret_cast<uint2*>(p) = o;
+}
 #define ROUTER_MAX_PARTS 4
+// Router scores of one row over the columns [lo, hi) (lo a multiple of 4 when the row is 16-byte aligned):
+// partial[e * ROUTER_MAX_PARTS + part] for every expert.  `row` points at column lo of the normed row in
+// shared memory.  The walk over a router row waits on memory, so it is spread wide: `parts` warps share one
+// expert (each a contiguous piece of the range, added in a fixed order afterwards), every lane keeps eight
+// independent 16-byte loads in flight.  Returns `parts`.
+__device__ __forceinline__ int router_partials(const float* __restrict__ row, const float* __restrict__ w_router, int D, int lo,
+                                               int hi, int E, float* partial) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  int parts = nwarp / E;
+  parts = parts < 1 ? 1 : (parts > ROUTER_MAX_PARTS ? ROUTER_MAX_PARTS : parts);
+  const int piece = (((hi - lo + parts - 1) / parts) + 127) / 128 * 128;  // a multiple of a warp's 128 floats
+  for (int item = warp; item < E * parts; item += nwarp) {
+    const int e = item / parts, part = item - e * parts;
+    const float* wr = w_router + (size_t)e * D;
+    const int p_lo = lo + part * piece, p_hi = min(hi, p_lo + piece);
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    int d = p_lo + lane * 4;
+    if ((D & 3) == 0 && (lo & 3) == 0 && (((uintptr_t)w_router) & 15) == 0) {
+      for (; d + 7 * 128 + 3 < p_hi; d += 8 * 128) {
+        float4 wv[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) wv[u] = *reinterpret_cast<const float4*>(wr + d + 128 * u);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const float4 xv = *reinterpret_cast<const float4*>(row + (d - lo) + 128 * u);
+          acc[u] = fmaf(xv.x, wv[u].x, fmaf(xv.y, wv[u].y, fmaf(xv.z, wv[u].z, fmaf(xv.w, wv[u].w, acc[u]))));
+        }
+      }
+      for (; d + 3 < p_hi; d += 128) {
+        const float4 wv = *reinterpret_cast<const float4*>(wr + d), xv = *reinterpret_cast<const float4*>(row + (d - lo));
+        acc[0] = fmaf(xv.x, wv.x, fmaf(xv.y, wv.y, fmaf(xv.z, wv.z, fmaf(xv.w, wv.w, acc[0]))));
+      }
+    } else {
+      for (int i = p_lo + lane; i < p_hi; i += 32) acc[0] = fmaf(row[i - lo], wr[i], acc[0]);
+    }
+    const float s = warp_sum(((acc[0] + acc[1]) + (acc[2] + acc[3])) + ((acc[4] + acc[5]) + (acc[6] + acc[7])));
+    if (lane == 0) partial[e * ROUTER_MAX_PARTS + part] = s;
+  }
+  return parts;
+}
+
+// Top-k of the raw scores by one thread (lower index wins ties; NaN never wins), weight = sigmoid of the score.
+// Destroys `scores`.
+__device__ __forceinline__ void router_topk(float* scores, int E, int k, size_t n, int* topk_idx, float* topk_w) {
+  for (int j = 0; j < k; ++j) {
+    int best = -1;
+    float bv = 0.f;
+    for (int e = 0; e < E; ++e) {
+      const float v = scores[e];
+      if (isnan(v)) continue;
+      if (best < 0 || v > bv) {
+        best = e;
+        bv = v;
+      }
+    }
+    if (best < 0) best = j;
+    topk_idx[n * k + j] = best;
+    topk_w[n * k + j] = 1.f / (1.f + expf(-bv));
+    scores[best] = NAN;
+  }
+}
+
 template <typename TO>
 __global__ void __launch_bounds__(1024)
 add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, int delta_splits, long long delta_stride,
@@ -64,17 +137,35 @@ add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, int d
     const float4* d4 = reinterpret_cast<const float4*>(dr);
     float4* row4 = reinterpret_cast<float4*>(rowbuf);
     const long long stride4 = delta_stride >> 2;
-    for (int i = threadIdx.x; i < D4; i += blockDim.x) {
-      float4 s = x4[i];
+    // four 16-byte loads of the residual (and of each partial) in flight per thread
+    for (int i0 = threadIdx.x; i0 < D4; i0 += 4 * blockDim.x) {
+      float4 s[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + u * blockDim.x;
+        s[u] = i < D4 ? x4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
       if (dr) {
         for (int z = 0; z < delta_splits; ++z) {
-          const float4 v = d4[(size_t)z * stride4 + i];
-          s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int i = i0 + u * blockDim.x;
+            if (i < D4) {
+              const float4 v = d4[(size_t)z * stride4 + i];
+              s[u].x += v.x; s[u].y += v.y; s[u].z += v.z; s[u].w += v.w;
+            }
+          }
         }
-        if (!row_index) x4[i] = s;
       }
-      row4[i] = s;
-      ss += (s.x * s.x + s.y * s.y) + (s.z * s.z + s.w * s.w);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + u * blockDim.x;
+        if (i < D4) {
+          if (dr && !row_index) x4[i] = s[u];
+          row4[i] = s[u];
+          ss += (s[u].x * s[u].x + s[u].y * s[u].y) + (s[u].z * s[u].z + s[u].w * s[u].w);
+        }
+      }
     }
     ss = block_sum(ss, scratch);
     const float rms = sqrtf(ss / (float)D + eps);
@@ -83,10 +174,7 @@ add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, int d
       const float4 s = row4[i];
       const float4 g = gamma ? g4[i] : make_float4(1.f, 1.f, 1.f, 1.f);
       const float4 v = make_float4(g.x * s.x / rms, g.y * s.y / rms, g.z * s.z / rms, g.w * s.w / rms);
-      if (out) {
-        TO* o = out + (size_t)n * D + 4 * i;
-        o[0] = from_f32<TO>(v.x); o[1] = from_f32<TO>(v.y); o[2] = from_f32<TO>(v.z); o[3] = from_f32<TO>(v.w);
-      }
+      if (out) store4<TO>(out + (size_t)n * D + 4 * i, v);
       if (out32) reinterpret_cast<float4*>(out32 + (size_t)n * D)[i] = v;
       row4[i] = v;
     }
@@ -119,40 +207,7 @@ add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, int d
   }
   if (!w_router) return;
   __syncthreads();
-  // Router scores.  The walk over a router row waits on memory, so it is spread wide: `parts` warps share one
-  // expert (each a contiguous piece of the row, added in a fixed order afterwards), every lane keeps eight
-  // independent 16-byte loads in flight.
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
-  int parts = nwarp / E;
-  parts = parts < 1 ? 1 : (parts > ROUTER_MAX_PARTS ? ROUTER_MAX_PARTS : parts);
-  const int piece = (((D + parts - 1) / parts) + 127) / 128 * 128;  // a multiple of a warp's 128 floats
-  for (int item = warp; item < E * parts; item += nwarp) {
-    const int e = item / parts, part = item - e * parts;
-    const float* wr = w_router + (size_t)e * D;
-    const int lo = part * piece, hi = min(D, lo + piece);
-    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    int d = lo + lane * 4;
-    if ((D & 3) == 0 && (((uintptr_t)w_router) & 15) == 0) {
-      for (; d + 7 * 128 < hi; d += 8 * 128) {
-        float4 wv[8];
-#pragma unroll
-        for (int u = 0; u < 8; ++u) wv[u] = *reinterpret_cast<const float4*>(wr + d + 128 * u);
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-          const float4 xv = *reinterpret_cast<const float4*>(rowbuf + d + 128 * u);
-          acc[u] = fmaf(xv.x, wv[u].x, fmaf(xv.y, wv[u].y, fmaf(xv.z, wv[u].z, fmaf(xv.w, wv[u].w, acc[u]))));
-        }
-      }
-      for (; d < hi; d += 128) {
-        const float4 wv = *reinterpret_cast<const float4*>(wr + d), xv = *reinterpret_cast<const float4*>(rowbuf + d);
-        acc[0] = fmaf(xv.x, wv.x, fmaf(xv.y, wv.y, fmaf(xv.z, wv.z, fmaf(xv.w, wv.w, acc[0]))));
-      }
-    } else {
-      for (int i = lo + lane; i < hi; i += 32) acc[0] = fmaf(rowbuf[i], wr[i], acc[0]);
-    }
-    const float s = warp_sum(((acc[0] + acc[1]) + (acc[2] + acc[3])) + ((acc[4] + acc[5]) + (acc[6] + acc[7])));
-    if (lane == 0) partial[e * ROUTER_MAX_PARTS + part] = s;
-  }
+  const int parts = router_partials(rowbuf, w_router, D, 0, D, E, partial);
   __syncthreads();
   for (int e = threadIdx.x; e < E; e += blockDim.x) {
     float s = 0.f;
@@ -160,24 +215,83 @@ add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, int d
     scores[e] = s;
   }
   __syncthreads();
-  if (threadIdx.x == 0) {
-    for (int j = 0; j < k; ++j) {
-      int best = -1;
-      float bv = 0.f;
-      for (int e = 0; e < E; ++e) {
-        const float v = scores[e];
-        if (isnan(v)) continue;
-        if (best < 0 || v > bv) {
-          best = e;
-          bv = v;
-        }
+  if (threadIdx.x == 0) router_topk(scores, E, k, (size_t)n, topk_idx, topk_w);
+}
+
+// The same for a handful of rows (a decode step), where one block per row would leave the row's router
+// weights (E * D * 4 bytes) to a single SM: a cluster of blocks shares the row.  Each block takes a slice of
+// the columns: its part of the sum of squares and of every expert's score goes through distributed shared
+// memory, block 0 of the cluster adds the parts in rank order and chooses the experts.  bfloat16 output only:
+// the order of the sums differs from the one-block kernel's, which the 32-bit path must not depend on.
+template <typename TO>
+__global__ void __launch_bounds__(512)
+add_rmsnorm_router_cluster_kernel(float* __restrict__ x, const float* __restrict__ delta, int delta_splits, long long delta_stride,
+                                  const float* __restrict__ gamma, float eps, TO* __restrict__ out, int D, int slice,
+                                  const float* __restrict__ w_router, int E, int k, int* __restrict__ topk_idx,
+                                  float* __restrict__ topk_w) {
+  namespace cg = cooperative_groups;
+  cg::cluster_group cluster = cg::this_cluster();
+  const int rank = (int)cluster.block_rank(), C = (int)cluster.num_blocks();
+  extern __shared__ __align__(16) float rowbuf[];  // [slice]
+  __shared__ float scratch[33];
+  __shared__ float cl_ss;                      // this block's part of the sum of squares
+  __shared__ float cl_scores[ROUTER_MAX_E];    // this block's part of every expert's score
+  __shared__ float scores[ROUTER_MAX_E];
+  __shared__ float partial[ROUTER_MAX_E * ROUTER_MAX_PARTS];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int n = blockIdx.x / C;
+  const int lo = min(D, rank * slice), hi = min(D, lo + slice);  // multiples of 4
+  float4* x4 = reinterpret_cast<float4*>(x + (size_t)n * D);
+  const float4* d4 = delta ? reinterpret_cast<const float4*>(delta + (size_t)n * D) : nullptr;
+  float4* row4 = reinterpret_cast<float4*>(rowbuf);
+  const long long stride4 = delta_stride >> 2;
+  float ss = 0.f;
+  for (int i = (lo >> 2) + threadIdx.x; i < (hi >> 2); i += blockDim.x) {
+    float4 s = x4[i];
+    if (d4) {
+      for (int z = 0; z < delta_splits; ++z) {
+        const float4 v = d4[(size_t)z * stride4 + i];
+        s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
       }
-      if (best < 0) best = j;
-      topk_idx[(size_t)n * k + j] = best;
-      topk_w[(size_t)n * k + j] = 1.f / (1.f + expf(-bv));
-      scores[best] = NAN;
+      x4[i] = s;
     }
+    row4[i - (lo >> 2)] = s;
+    ss += (s.x * s.x + s.y * s.y) + (s.z * s.z + s.w * s.w);
   }
+  ss = block_sum(ss, scratch);
+  if (threadIdx.x == 0) cl_ss = ss;
+  cluster.sync();
+  float total = 0.f;
+  for (int r = 0; r < C; ++r) total += *cluster.map_shared_rank(&cl_ss, r);
+  const float rms = sqrtf(total / (float)D + eps);
+  const float4* g4 = reinterpret_cast<const float4*>(gamma);
+  for (int i = (lo >> 2) + threadIdx.x; i < (hi >> 2); i += blockDim.x) {
+    const float4 s = row4[i - (lo >> 2)];
+    const float4 g = gamma ? g4[i] : make_float4(1.f, 1.f, 1.f, 1.f);
+    const float4 v = make_float4(g.x * s.x / rms, g.y * s.y / rms, g.z * s.z / rms, g.w * s.w / rms);
+    store4<TO>(out + (size_t)n * D + 4 * i, v);
+    row4[i - (lo >> 2)] = v;
+  }
+  __syncthreads();
+  const int parts = router_partials(rowbuf, w_router, D, lo, hi, E, partial);
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    float s = 0.f;
+    for (int part = 0; part < parts; ++part) s += partial[e * ROUTER_MAX_PARTS + part];
+    cl_scores[e] = s;
+  }
+  cluster.sync();
+  if (rank == 0) {
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+      float s = 0.f;
+      for (int r = 0; r < C; ++r) s += cluster.map_shared_rank(cl_scores, r)[e];
+      scores[e] = s;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) router_topk(scores, E, k, (size_t)n, topk_idx, topk_w);
+  }
+  cluster.sync();  // every block's shared memory stays alive until block 0 has read it
 }
 
 JLX_API int jlx_add_rmsnorm(float* x, const float* delta, int delta_splits, long long delta_stride, const float* gamma,
@@ -195,6 +309,30 @@ JLX_API int jlx_add_rmsnorm(float* x, const float* delta, int delta_splits, long
     JLX_REQUIRE(topk_idx && topk_w, "router: outputs missing");
   }
   const size_t smem = row_in_smem ? (size_t)D * 4 : 0;
+  // A few rows with a router: a cluster of 8 blocks per row (all rows resident at once), bfloat16 output only.
+  if (w_router && out_dtype == JLX_BF16 && !row_index && !out32 && out && N <= 32 && (D & 3) == 0 && D >= 1024 &&
+      (delta_stride & 3) == 0 && (((uintptr_t)x | (uintptr_t)delta | (uintptr_t)gamma | (uintptr_t)out) & 15) == 0) {
+    const int C = 8;
+    const int slice = ((D / 4 + C - 1) / C) * 4;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(N * C);
+    cfg.blockDim = dim3(512);
+    cfg.dynamicSmemBytes = (size_t)slice * 4;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = C;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    JLX_CUDA(cudaLaunchKernelEx(&cfg, add_rmsnorm_router_cluster_kernel<bf16>, x, delta, delta_splits, delta_stride, gamma, eps,
+                                (bf16*)out, D, slice, w_router, E, k, topk_idx, topk_w));
+    JLX_LAUNCH_CHECK("add_rmsnorm (cluster)");
+    return 0;
+  }
   JLX_DISPATCH_DTYPE(out_dtype, TO, {
     if (smem > 48 * 1024) {
       static bool cfg = false;

@@ -15,7 +15,7 @@
 //   adds the partials in a fixed order.
 //
 // One block = one (weight tile, token tile, K range).  Warp 0 issues TMA loads, warp 1 allocates tensor
-// memory and issues the MMAs, warps 2..5 read the accumulator back (each its own 32-lane quarter) and
+// memory and issues the MMAs, warps 2..9 read the accumulator back (two per 32-lane quarter) and
 // store it transposed (for a fixed token, 32 consecutive outputs per warp: coalesced).
 // Every wait on a barrier is bounded; on a timeout the block raises JLX_STATUS_WAIT_TIMEOUT, drains its
 // own copies, frees its tensor memory and returns.
@@ -26,7 +26,7 @@
 #define WN 128          // weight rows per tile (MMA M)
 #define BK 64           // K elements per stage (128 bytes of bfloat16)
 #define UMMA_K 16
-#define NTHREADS 192
+#define NTHREADS 320     // warp 0: TMA, warp 1: MMA, warps 2..9: epilogue (two per quarter of the tensor-memory lanes)
 #define WAIT_LIMIT (1u << 22)
 
 // ------------------------------------------------------------------------------------ PTX wrappers
@@ -127,15 +127,17 @@ struct StreamArgs {
 
 // WT: weight tiles of 128 rows per block.  With many token rows per group the token tile is the larger part of
 // a stage; two weight tiles (two accumulators in tensor memory) per token tile halve its traffic.
-template <int BT, int STAGES, int WT>
+// SW, SA: stages of the weight ring and of the token ring.  Weights come from HBM and need many bytes in
+// flight; token tiles are read again by every weight tile of the group, come from L2 and need fewer.
+template <int BT, int SW, int SA, int WT>
 __global__ void __launch_bounds__(NTHREADS)
 gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a, const StreamArgs args) {
-  constexpr uint32_t W_TILE = WN * BK * 2, W_BYTES = WT * W_TILE, A_BYTES = BT * BK * 2, STAGE_BYTES = W_BYTES + A_BYTES;
+  constexpr uint32_t W_TILE = WN * BK * 2, W_BYTES = WT * W_TILE, A_BYTES = BT * BK * 2;
   constexpr uint32_t TMEM_NEED = WT * BT;  // allocations are powers of two from 32 columns
   constexpr uint32_t TMEM_COLS = TMEM_NEED <= 32 ? 32 : TMEM_NEED <= 64 ? 64 : TMEM_NEED <= 128 ? 128 : TMEM_NEED <= 256 ? 256 : 512;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  __shared__ __align__(8) uint64_t bars[2 * STAGES + 1];
+  const uint32_t smem_w = (smem_u32(smem_raw) + 1023u) & ~1023u, smem_a = smem_w + SW * W_BYTES;
+  __shared__ __align__(8) uint64_t bars[2 * SW + 2 * SA + 1];
   __shared__ uint32_t tmem_slot;
   __shared__ int failed;
 
@@ -171,13 +173,10 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   const int k_end = min(args.K, k_begin + args.k_per_split);
   const int k_iters = (k_end - k_begin + BK - 1) / BK;
 
-  const uint32_t bar_full = smem_u32(&bars[0]), bar_empty = smem_u32(&bars[STAGES]), bar_acc = smem_u32(&bars[2 * STAGES]);
+  const uint32_t w_full = smem_u32(&bars[0]), w_empty = w_full + 8 * SW, a_full = w_empty + 8 * SW, a_empty = a_full + 8 * SA,
+                 bar_acc = a_empty + 8 * SA;
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) {
-      mbar_init(bar_full + 8 * s, 1);
-      mbar_init(bar_empty + 8 * s, 1);
-    }
-    mbar_init(bar_acc, 1);
+    for (int s = 0; s < 2 * SW + 2 * SA + 1; ++s) mbar_init(w_full + 8 * s, 1);
     failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -192,36 +191,38 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     if (lane == 0) {
       // The weights depend on no earlier kernel: the first stages' weight tiles are requested before the
       // wait for the predecessor, whose tail they overlap; the token tiles follow after it.
-      const int early = k_iters < STAGES ? k_iters : STAGES;
-      for (int it = 0; it < early; ++it) {
-        mbar_expect_tx(bar_full + 8 * it, STAGE_BYTES);
+      auto load_w = [&](int it) {
+        const int s = it % SW;
+        mbar_expect_tx(w_full + 8 * s, W_BYTES);
 #pragma unroll
         for (int w = 0; w < WT; ++w)  // rows beyond this group's N belong to the next group or to nobody: never stored
-          tma_load_2d(smem_base + it * STAGE_BYTES + w * W_TILE, &map_w, k_begin + it * BK, group * args.N + n0 + w * WN,
-                      bar_full + 8 * it);
-      }
+          tma_load_2d(smem_w + s * W_BYTES + w * W_TILE, &map_w, k_begin + it * BK, group * args.N + n0 + w * WN, w_full + 8 * s);
+      };
+      auto load_a = [&](int it) {
+        const int s = it % SA;
+        mbar_expect_tx(a_full + 8 * s, A_BYTES);
+        tma_load_2d(smem_a + s * A_BYTES, &map_a, k_begin + it * BK, row_lo, a_full + 8 * s);
+      };
+      int iw = 0, ia = 0;
+      for (; iw < k_iters && iw < SW; ++iw) load_w(iw);
       pdl_wait();
-      for (int it = 0; it < early; ++it)
-        tma_load_2d(smem_base + it * STAGE_BYTES + W_BYTES, &map_a, k_begin + it * BK, row_lo, bar_full + 8 * it);
-      int issued = early;
+      for (; ia < k_iters && ia < SA; ++ia) load_a(ia);
+      // both rings advance as their stages come free; neither waits for the other
+      uint32_t idle = 0;
       bool ok = true;
-      for (int it = early; it < k_iters && ok; ++it) {
-        const int s = it % STAGES;
-        ok = mbar_wait(bar_empty + 8 * s, ((it / STAGES) & 1) ^ 1);
-        if (!ok || *(volatile int*)&failed) { ok = false; break; }
-        const uint32_t dst = smem_base + s * STAGE_BYTES;
-        mbar_expect_tx(bar_full + 8 * s, STAGE_BYTES);
-#pragma unroll
-        for (int w = 0; w < WT; ++w)
-          tma_load_2d(dst + w * W_TILE, &map_w, k_begin + it * BK, group * args.N + n0 + w * WN, bar_full + 8 * s);
-        tma_load_2d(dst + W_BYTES, &map_a, k_begin + it * BK, row_lo, bar_full + 8 * s);
-        issued = it + 1;
+      while ((iw < k_iters || ia < k_iters) && ok) {
+        bool moved = false;
+        if (iw < k_iters && mbar_try_wait(w_empty + 8 * (iw % SW), ((iw / SW) & 1) ^ 1)) { load_w(iw); ++iw; moved = true; }
+        if (ia < k_iters && mbar_try_wait(a_empty + 8 * (ia % SA), ((ia / SA) & 1) ^ 1)) { load_a(ia); ++ia; moved = true; }
+        if (moved) idle = 0;
+        else if (++idle >= WAIT_LIMIT || *(volatile int*)&failed) ok = false;
       }
       if (!ok) {
         atomicOr(args.status, JLX_STATUS_WAIT_TIMEOUT);
         failed = 1;
         // let this block's copies in flight land before its shared memory is given up
-        for (int it = max(0, issued - STAGES); it < issued; ++it) mbar_wait(bar_full + 8 * (it % STAGES), (it / STAGES) & 1);
+        for (int it = max(0, iw - SW); it < iw; ++it) mbar_wait(w_full + 8 * (it % SW), (it / SW) & 1);
+        for (int it = max(0, ia - SA); it < ia; ++it) mbar_wait(a_full + 8 * (it % SA), (it / SA) & 1);
       }
     }
   } else if (warp == 1) {
@@ -230,12 +231,12 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       constexpr uint32_t idesc = make_idesc(BT);
       bool ok = true;
       for (int it = 0; it < k_iters; ++it) {
-        const int s = it % STAGES;
-        ok = mbar_wait(bar_full + 8 * s, (it / STAGES) & 1);
+        const int sw = it % SW, sa = it % SA;
+        ok = mbar_wait(w_full + 8 * sw, (it / SW) & 1) && mbar_wait(a_full + 8 * sa, (it / SA) & 1);
         if (!ok || *(volatile int*)&failed) { ok = false; break; }
         tc_fence_after();
-        const uint32_t w_addr = smem_base + s * STAGE_BYTES, a_addr = w_addr + W_BYTES;
-        const uint64_t adesc = smem_desc_sw128(a_addr);
+        const uint32_t w_addr = smem_w + sw * W_BYTES;
+        const uint64_t adesc = smem_desc_sw128(smem_a + sa * A_BYTES);
 #pragma unroll
         for (int w = 0; w < WT; ++w) {
           const uint64_t wdesc = smem_desc_sw128(w_addr + w * W_TILE);
@@ -245,7 +246,8 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             umma_bf16(tmem_acc + w * BT, wdesc + 2 * k, adesc + 2 * k, idesc, (it | k) != 0);
           }
         }
-        umma_commit(bar_empty + 8 * s);  // frees the stage when these MMAs have read it
+        umma_commit(w_empty + 8 * sw);  // frees the stages when these MMAs have read them
+        umma_commit(a_empty + 8 * sa);
       }
       if (ok) {
         umma_commit(bar_acc);  // accumulator complete
@@ -255,8 +257,9 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue (warps 2..5)
-    const int quarter = warp & 3;  // tensor-memory lanes [32 * quarter, 32 * quarter + 32)
+    // ------------------------------------------------------------------ epilogue (warps 2..9)
+    const int quarter = warp & 3;         // tensor-memory lanes [32 * quarter, 32 * quarter + 32): fixed by the warp's number
+    const int half = (warp - 2) >> 2;     // the two warps of a quarter take alternate blocks of 16 token columns
     pdl_wait();  // the output buffer may still be read by a predecessor
     bool ok = mbar_wait(bar_acc, 0);
     if (*(volatile int*)&failed) ok = false;
@@ -271,29 +274,41 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         const bool n_ok = n < args.N;
         if (nb >= args.N) break;  // uniform across the warp
 #pragma unroll 1
-        for (int c0 = 0; c0 < BT; c0 += 16) {
+        for (int c0 = half * 16; c0 < BT; c0 += 32) {
           if (row_lo + c0 >= row_hi) break;  // uniform across the warp
           uint32_t r[16];
           tmem_ld16(tmem_acc + ((uint32_t)(quarter * 32) << 16) + w * BT + c0, r);
           tmem_ld_wait();
+          if (args.silu) {
+            // lanes 0..15 hold gate rows, lanes 16..31 the matching up rows of the same 32-row block.  Of two
+            // token columns the lower lanes finish the even one and the upper lanes the odd one: one exchange
+            // gives the lower lanes the even column's up values and the upper lanes the odd column's gates.
+            const size_t half_n = (size_t)(args.N >> 1);
+            const bool upper = lane >= 16;
+            const size_t col = (size_t)(nb >> 1) + (lane & 15);
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int m = row_lo + c0 + j;
-            const float v = __uint_as_float(r[j]);
-            if (args.silu) {
-              // lanes 0..15 hold gate rows, lanes 16..31 the matching up rows of the same 32-row block
-              const float up = __shfl_down_sync(0xffffffffu, v, 16);
-              if (lane < 16 && m < row_hi && n_ok) {
-                const float act = v / (1.f + __expf(-v)) * up;
-                const size_t col = (size_t)(nb >> 1) + lane;
-                if (args.out_is_f32) ((float*)args.out)[(size_t)m * (args.N >> 1) + col] = act;
-                else ((bf16*)args.out)[(size_t)m * (args.N >> 1) + col] = __float2bfloat16_rn(act);
+            for (int j = 0; j < 16; j += 2) {
+              const float mine = __uint_as_float(upper ? r[j + 1] : r[j]);   // gate (lower) or up (upper) of my column
+              const float send = __uint_as_float(upper ? r[j] : r[j + 1]);
+              const float got = __shfl_xor_sync(0xffffffffu, send, 16);
+              const float gate = upper ? got : mine, up = upper ? mine : got;
+              const int m = row_lo + c0 + j + (upper ? 1 : 0);
+              if (m < row_hi) {  // N % 32 == 0: a block of 32 weight rows that starts below N lies wholly below it
+                const float act = __fdividef(gate, 1.f + __expf(-gate)) * up;
+                if (args.out_is_f32) ((float*)args.out)[(size_t)m * half_n + col] = act;
+                else ((bf16*)args.out)[(size_t)m * half_n + col] = __float2bfloat16_rn(act);
               }
-            } else if (m < row_hi && n_ok) {
-              if (args.out_is_f32 || args.splits > 1)
-                ((float*)args.out)[split_off + (size_t)m * args.N + n] = v;
-              else
-                ((bf16*)args.out)[(size_t)m * args.N + n] = __float2bfloat16_rn(v);
+            }
+          } else if (n_ok) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int m = row_lo + c0 + j;
+              if (m < row_hi) {
+                if (args.out_is_f32 || args.splits > 1)
+                  ((float*)args.out)[split_off + (size_t)m * args.N + n] = __uint_as_float(r[j]);
+                else
+                  ((bf16*)args.out)[(size_t)m * args.N + n] = __float2bfloat16_rn(__uint_as_float(r[j]));
+              }
             }
           }
         }
@@ -353,16 +368,16 @@ static int make_map(CUtensorMap* map, const void* base, long long rows, long lon
   return 0;
 }
 
-template <int BT, int STAGES, int WT>
+template <int BT, int SW, int SA, int WT>
 static int launch(const CUtensorMap& mw, const CUtensorMap& ma, const StreamArgs& a, int row_tiles, cudaStream_t stream) {
-  constexpr size_t smem = (size_t)STAGES * (WT * WN * BK * 2 + BT * BK * 2) + 1024;
+  constexpr size_t smem = (size_t)SW * (WT * WN * BK * 2) + (size_t)SA * (BT * BK * 2) + 1024;
   static bool configured = false;
   if (!configured) {
-    JLX_CUDA(cudaFuncSetAttribute(gemm_stream_kernel<BT, STAGES, WT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    JLX_CUDA(cudaFuncSetAttribute(gemm_stream_kernel<BT, SW, SA, WT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured = true;
   }
   dim3 grid((a.N + WN * WT - 1) / (WN * WT), row_tiles, a.splits);
-  JLX_CUDA(jlx_launch_pdl(gemm_stream_kernel<BT, STAGES, WT>, grid, dim3(NTHREADS), smem, stream, mw, ma, a));
+  JLX_CUDA(jlx_launch_pdl(gemm_stream_kernel<BT, SW, SA, WT>, grid, dim3(NTHREADS), smem, stream, mw, ma, a));
   return 0;
 }
 
@@ -427,15 +442,15 @@ JLX_API int jlx_gemm_stream(const void* A, const void* W, void* out, int out_is_
     // up to 192 token rows: one weight tile and stages sized so that two blocks share an SM (about 100 KB
     // each): one block's epilogue (tensor memory -> registers -> global) overlaps the other's main loop.
     // wider: two weight tiles per block (the token tile is fetched once for both), one block per SM.
-    case 16: rc = launch<16, 5, 1>(mw, ma, a, row_tiles, stream); break;
-    case 32: rc = launch<32, 5, 1>(mw, ma, a, row_tiles, stream); break;
-    case 64: rc = launch<64, 4, 1>(mw, ma, a, row_tiles, stream); break;
-    case 96: rc = launch<96, 3, 1>(mw, ma, a, row_tiles, stream); break;
-    case 128: rc = launch<128, 3, 1>(mw, ma, a, row_tiles, stream); break;
-    case 160: rc = launch<160, 3, 1>(mw, ma, a, row_tiles, stream); break;
-    case 192: rc = launch<192, 2, 1>(mw, ma, a, row_tiles, stream); break;
-    case 224: rc = launch<224, 3, 2>(mw, ma, a, row_tiles, stream); break;  // 60 KB
-    default: rc = launch<256, 3, 2>(mw, ma, a, row_tiles, stream); break;   // 64 KB
+    case 16: rc = launch<16, 5, 5, 1>(mw, ma, a, row_tiles, stream); break;
+    case 32: rc = launch<32, 5, 5, 1>(mw, ma, a, row_tiles, stream); break;
+    case 64: rc = launch<64, 4, 4, 1>(mw, ma, a, row_tiles, stream); break;
+    case 96: rc = launch<96, 3, 3, 1>(mw, ma, a, row_tiles, stream); break;
+    case 128: rc = launch<128, 3, 3, 1>(mw, ma, a, row_tiles, stream); break;
+    case 160: rc = launch<160, 3, 3, 1>(mw, ma, a, row_tiles, stream); break;
+    case 192: rc = launch<192, 2, 2, 1>(mw, ma, a, row_tiles, stream); break;
+    case 224: rc = launch<224, 3, 3, 2>(mw, ma, a, row_tiles, stream); break;  // 60 KB
+    default: rc = launch<256, 3, 3, 2>(mw, ma, a, row_tiles, stream); break;   // 64 KB
   }
   if (rc) return rc;
   if (splits > 1 && mode == 0) {

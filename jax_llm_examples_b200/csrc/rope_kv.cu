@@ -42,11 +42,6 @@ rope_kv_store_kernel(const TI* __restrict__ qkv, int splits, long long split_str
   const int heads = Hq + 2 * Hkv;
   const int half = dh >> 1;
   const TI* row = qkv + (size_t)n * heads * dh;
-  if (inv_freq) {
-    for (int j = threadIdx.x; j < half; j += blockDim.x) sincosf((float)pos * inv_freq[j], &sc[2 * j], &sc[2 * j + 1]);
-    __syncthreads();
-  }
-
   T* kdst = nullptr;
   T* vdst = nullptr;
   if (store_kv) {
@@ -59,6 +54,33 @@ rope_kv_store_kernel(const TI* __restrict__ qkv, int splits, long long split_str
       kdst = base + (size_t)(pos % page_size) * dh;
       vdst = base + (size_t)Hkv * page_size * dh + (size_t)(pos % page_size) * dh;
     }
+  }
+
+  // Each warp has at most one head.  With the pairs kept in registers its loads are issued first, so that
+  // they are in flight while the block computes the angles' sines and cosines.
+  const int my_head = blockIdx.y * 8 + warp;
+  const bool in_regs = half <= 32 * ROPE_REG_PAIRS;
+  float va[ROPE_REG_PAIRS], vb[ROPE_REG_PAIRS];
+  if (in_regs && my_head < heads && my_head < Hq + Hkv) {
+    const TI* src = row + (size_t)my_head * dh;
+#pragma unroll
+    for (int i = 0; i < ROPE_REG_PAIRS; ++i) {
+      const int j = lane + 32 * i;
+      float a = 0.f, b = 0.f;
+      if (j < half) {
+        for (int z = 0; z < splits; ++z) {
+          const float2 v = load_pair<TI>(src + (size_t)z * split_stride + 2 * j);
+          a += v.x;
+          b += v.y;
+        }
+      }
+      va[i] = a;
+      vb[i] = b;
+    }
+  }
+  if (inv_freq) {
+    for (int j = threadIdx.x; j < half; j += blockDim.x) sincosf((float)pos * inv_freq[j], &sc[2 * j], &sc[2 * j + 1]);
+    __syncthreads();
   }
 
   for (int h = blockIdx.y * 8 + warp; h < min(heads, (int)blockIdx.y * 8 + 8); h += 8) {
@@ -79,20 +101,14 @@ rope_kv_store_kernel(const TI* __restrict__ qkv, int splits, long long split_str
       continue;
     }
     T* dst = h < Hq ? q_out + ((size_t)n * Hq + h) * dh : (kdst ? kdst + (size_t)(h - Hq) * page_size * dh : nullptr);
-    if (half <= 32 * ROPE_REG_PAIRS) {
+    if (in_regs) {
       // one pass: a lane keeps its pairs in registers between the sum of squares and the write
-      float va[ROPE_REG_PAIRS], vb[ROPE_REG_PAIRS];
       float ss = 0.f;
 #pragma unroll
       for (int i = 0; i < ROPE_REG_PAIRS; ++i) {
         const int j = lane + 32 * i;
-        float a = 0.f, b = 0.f;
         if (j < half) {
-          for (int z = 0; z < splits; ++z) {
-            const float2 v = load_pair<TI>(src + (size_t)z * split_stride + 2 * j);
-            a += v.x;
-            b += v.y;
-          }
+          float a = va[i], b = vb[i];
           if (inv_freq) {
             const float s = sc[2 * j], c = sc[2 * j + 1];
             const float ra = a * c - b * s, rb = b * c + a * s;
@@ -100,9 +116,9 @@ rope_kv_store_kernel(const TI* __restrict__ qkv, int splits, long long split_str
             b = rb;
           }
           ss += a * a + b * b;
+          va[i] = a;
+          vb[i] = b;
         }
-        va[i] = a;
-        vb[i] = b;
       }
       float inv = 1.f;
       if (l2norm) {

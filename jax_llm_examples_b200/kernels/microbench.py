@@ -54,6 +54,8 @@ def attention_decode(a) -> dict:
     req = torch.arange(a.batch, device=dev, dtype=torch.int32)
     status = torch.zeros(1, device=dev, dtype=torch.int32)
     keys, splits = K.attention_decode_plan(a.context, a.chunk, 0, a.batch * a.kv_heads)
+    if a.split_keys:
+        keys, splits = a.split_keys, -(-a.context // a.split_keys) + 1
     part_o = torch.empty(a.batch * a.heads * splits * a.head_dim, device=dev)
     part_ml = torch.empty(a.batch * a.heads * splits * 2, device=dev)
 
@@ -144,6 +146,7 @@ def main(argv=None) -> int:
         if name == "attention_decode":
             p.add_argument("--batch", type=int, default=8)
             p.add_argument("--context", type=int, default=8192)
+            p.add_argument("--split-keys", type=int, default=0, help="keys per split (a multiple of 64) instead of the planned size")
         if name == "attention_prefill":
             p.add_argument("--tokens", type=int, default=2048)
             p.add_argument("--tc", action="store_true", help="the tcgen05 kernel (128-token tiles) instead of the mma.sync one")
