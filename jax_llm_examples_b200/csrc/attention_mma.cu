@@ -516,9 +516,12 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map, const AttnP
 }
 
 // out[n, h, :] = sum_s o_s 2^(m_s - m) / sum_s l_s 2^(m_s - m), splits in ascending order.
+// The splits' (m, l) pairs are fetched by as many threads at once and kept in shared memory; with more than
+// COMBINE_CACHE splits they are read from global memory again.
+#define COMBINE_CACHE 512
 template <int DH>
 __global__ void attention_combine_kernel(const AttnParams P) {
-  __shared__ float wgt[512];
+  __shared__ float ms[COMBINE_CACHE], wgt[COMBINE_CACHE];
   pdl_launch_dependents();
   pdl_wait();
   const int n = blockIdx.x, h = blockIdx.y;
@@ -526,19 +529,34 @@ __global__ void attention_combine_kernel(const AttnParams P) {
   const int lo = first_key(p, P.chunk, P.window);
   const int splits = p / P.split_keys - lo / P.split_keys + 1;
   const size_t row = ((size_t)n * P.Hq + h) * P.max_splits;
-  float mm = NEG_BIG;
-  for (int s = 0; s < splits; ++s) mm = fmaxf(mm, P.part_ml[(row + s) * 2]);
-  float ll = 0.f;
-  for (int s = 0; s < splits; ++s) ll += P.part_ml[(row + s) * 2 + 1] * exp2f(P.part_ml[(row + s) * 2] - mm);
-  const bool cached = splits <= 512;
+  const float2* ml = reinterpret_cast<const float2*>(P.part_ml) + row;
+  const bool cached = splits <= COMBINE_CACHE;
+  float mm = NEG_BIG, ll = 0.f;
   if (cached) {
-    for (int s = threadIdx.x; s < splits; s += blockDim.x) wgt[s] = exp2f(P.part_ml[(row + s) * 2] - mm) / ll;
+    for (int s = threadIdx.x; s < splits; s += blockDim.x) {
+      const float2 v = ml[s];
+      ms[s] = v.x;
+      wgt[s] = v.y;
+    }
     __syncthreads();
+    for (int s = 0; s < splits; ++s) mm = fmaxf(mm, ms[s]);
+    for (int s = 0; s < splits; ++s) ll += wgt[s] * exp2f(ms[s] - mm);
+    __syncthreads();
+    for (int s = threadIdx.x; s < splits; s += blockDim.x) wgt[s] = exp2f(ms[s] - mm) / ll;
+    __syncthreads();
+  } else {
+    for (int s = 0; s < splits; ++s) mm = fmaxf(mm, ml[s].x);
+    for (int s = 0; s < splits; ++s) ll += ml[s].y * exp2f(ml[s].x - mm);
   }
+  const float* po = P.part_o + row * DH;
   for (int d = threadIdx.x; d < DH; d += blockDim.x) {
     float acc = 0.f;
-    for (int s = 0; s < splits; ++s)
-      acc += P.part_o[(row + s) * DH + d] * (cached ? wgt[s] : exp2f(P.part_ml[(row + s) * 2] - mm) / ll);
+    if (cached) {
+#pragma unroll 8
+      for (int s = 0; s < splits; ++s) acc += po[(size_t)s * DH + d] * wgt[s];
+    } else {
+      for (int s = 0; s < splits; ++s) acc += po[(size_t)s * DH + d] * (exp2f(ml[s].x - mm) / ll);
+    }
     P.out[((size_t)n * P.Hq + h) * DH + d] = __float2bfloat16_rn(acc);
   }
 }

@@ -38,16 +38,18 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {  // bounded: false = gave up
-  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.b32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    if (ok) return true;
-  }
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
   return false;
 }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
@@ -96,6 +98,11 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
         "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
         "r"(r[30]), "r"(r[31])
       : "memory");
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
@@ -146,8 +153,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t q_s = base, k_s = base + TILE_BYTES, v_s = k_s + 2 * TILE_BYTES, p_s = v_s + 2 * TILE_BYTES;
-  // barriers: 0 q_full | 1,2 k_full | 3,4 v_full | 5,6 kv_empty | 7,8 s_full | 9,10 s_free | 11 p_ready | 12 o_done
-  __shared__ __align__(8) uint64_t bars[13];
+  // barriers: 0 q_full | 1,2 k_full | 3,4 v_full | 5,6 v_empty | 7,8 s_full | 9,10 s_free | 11 p_ready | 12 o_done | 13,14 k_empty
+  __shared__ __align__(8) uint64_t bars[15];
   __shared__ uint32_t tmem_slot;
   __shared__ int failed;
   const uint32_t bar0 = smem_u32(&bars[0]);
@@ -170,6 +177,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     mbar_init(BAR(10), 128);
     mbar_init(BAR(11), 128);
     mbar_init(BAR(12), 1);
+    mbar_init(BAR(13), 1);
+    mbar_init(BAR(14), 1);
     failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -186,36 +195,39 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       mbar_expect_tx(BAR(0), TILE_BYTES);
       tma_load_3d(q_s, &map_q, 0, head, n0, BAR(0));
       tma_load_3d(q_s + HALF_BYTES, &map_q, 64, head, n0, BAR(0));
-      bool ok = true;
-      int issued = 0;
-      for (int j = 0; j < n_kv && ok; ++j) {
+      // One tile of keys (which = 0) or values (which = 1) into stage j & 1: four boxes of 64 rows x 64 elements.
+      auto load_tile = [&](int j, int which) {
         const int st = j & 1;
-        ok = mbar_wait(BAR(5 + st), ((j >> 1) & 1) ^ 1);
-        if (!ok || *(volatile int*)&failed) { ok = false; break; }
-        mbar_expect_tx(BAR(1 + st), TILE_BYTES);
-        mbar_expect_tx(BAR(3 + st), TILE_BYTES);
+        const uint32_t bar = BAR((which ? 3 : 1) + st);
+        const uint32_t dst = (which ? v_s : k_s) + st * TILE_BYTES;
+        mbar_expect_tx(bar, TILE_BYTES);
         for (int b = 0; b < BKV / 64; ++b) {  // pages hold whole 64-key blocks
           const int pos = key_begin + j * BKV + b * 64;
           const int pi = pos / P.page_size;
           int page = pi < P.bt_stride ? table[pi] : -1;
           if (page >= P.num_pages) { atomicOr(P.status, JLX_STATUS_BAD_PAGE); page = 0; }
           if (page < 0) page = 0;  // no page there: every key of the block is masked
-          const int row_k = ((page * 2 + 0) * P.Hkv + hk) * P.page_size + (pos - pi * P.page_size);
-          const int row_v = ((page * 2 + 1) * P.Hkv + hk) * P.page_size + (pos - pi * P.page_size);
-          for (int h = 0; h < 2; ++h) {
-            tma_load_2d(k_s + st * TILE_BYTES + h * HALF_BYTES + b * 64 * 128, &map_kv, h * 64, row_k, BAR(1 + st));
-            tma_load_2d(v_s + st * TILE_BYTES + h * HALF_BYTES + b * 64 * 128, &map_kv, h * 64, row_v, BAR(3 + st));
-          }
+          const int row = ((page * 2 + which) * P.Hkv + hk) * P.page_size + (pos - pi * P.page_size);
+          for (int h = 0; h < 2; ++h) tma_load_2d(dst + h * HALF_BYTES + b * 64 * 128, &map_kv, h * 64, row, bar);
         }
-        issued = j + 1;
+      };
+      // Keys are free again after their score product, values after the product with P, which comes a tile
+      // later: each ring advances as soon as its own stage is free.
+      int ik = 0, iv = 0;
+      uint32_t idle = 0;
+      bool ok = true;
+      while ((ik < n_kv || iv < n_kv) && ok) {
+        bool moved = false;
+        if (ik < n_kv && (ik < 2 || mbar_try_wait(BAR(13 + (ik & 1)), ((ik >> 1) - 1) & 1))) { load_tile(ik, 0); ++ik; moved = true; }
+        if (iv < n_kv && (iv < 2 || mbar_try_wait(BAR(5 + (iv & 1)), ((iv >> 1) - 1) & 1))) { load_tile(iv, 1); ++iv; moved = true; }
+        if (moved) idle = 0;
+        else if (++idle >= WAIT_LIMIT || *(volatile int*)&failed) ok = false;
       }
       if (!ok) {
         atomicOr(P.status, JLX_STATUS_WAIT_TIMEOUT);
         failed = 1;
-        for (int j = max(0, issued - 2); j < issued; ++j) {
-          mbar_wait(BAR(1 + (j & 1)), (j >> 1) & 1);
-          mbar_wait(BAR(3 + (j & 1)), (j >> 1) & 1);
-        }
+        for (int j = max(0, ik - 2); j < ik; ++j) mbar_wait(BAR(1 + (j & 1)), (j >> 1) & 1);
+        for (int j = max(0, iv - 2); j < iv; ++j) mbar_wait(BAR(3 + (j & 1)), (j >> 1) & 1);
       }
     }
   } else if (warp == 1) {
@@ -231,7 +243,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
           const uint32_t off = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;  // 16 elements = 32 bytes along the row
           umma_bf16(tm_s0 + st * 128, desc_k_major(q_s + off), desc_k_major(kb + off), idesc_qk, kk != 0);
         }
-        umma_commit(BAR(7 + st));
+        umma_commit(BAR(7 + st));   // S is complete
+        umma_commit(BAR(13 + st));  // K_j may be overwritten
       };
       if (ok) ok = mbar_wait(BAR(1), 0);
       if (ok) {
@@ -259,7 +272,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
           const uint32_t p_off = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
           umma_bf16(tm_o, desc_k_major(p_s + p_off), desc_mn_major(vb + kk * 16 * 128, HALF_BYTES), idesc_pv, (j | kk) != 0);
         }
-        umma_commit(BAR(5 + st));  // K_j and V_j may be overwritten
+        umma_commit(BAR(5 + st));  // V_j may be overwritten
         umma_commit(BAR(12));      // O holds tiles 0..j; P may be overwritten
       }
       if (!ok) {
@@ -313,17 +326,28 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       }
       tc_fence_before();
       mbar_arrive(BAR(9 + st));  // S[st] has been read
-      const float corr = exp2f(m - mx);
-      // probabilities and their sum; masked scores are NEG_BIG and give exactly 0
+      const float corr = fast_exp2(m - mx);
+      // probabilities and their sum; a masked score is NEG_BIG and gives exactly 0, also in a row whose scores
+      // are all masked so far (mx = NEG_BIG)
       float rs = 0.f;
       uint32_t packed[BKV / 2];
+      if (need_mask) {
 #pragma unroll
-      for (int i = 0; i < BKV; i += 2) {
-        const float s0 = __uint_as_float(v[i]), s1 = __uint_as_float(v[i + 1]);
-        const float p0 = s0 > 0.5f * NEG_BIG ? exp2f(s0 - mx) : 0.f, p1 = s1 > 0.5f * NEG_BIG ? exp2f(s1 - mx) : 0.f;
-        rs += p0 + p1;
-        __nv_bfloat162 b2 = __floats2bfloat162_rn(p0, p1);
-        packed[i >> 1] = *reinterpret_cast<uint32_t*>(&b2);
+        for (int i = 0; i < BKV; i += 2) {
+          const float s0 = __uint_as_float(v[i]), s1 = __uint_as_float(v[i + 1]);
+          const float p0 = s0 > 0.5f * NEG_BIG ? fast_exp2(s0 - mx) : 0.f, p1 = s1 > 0.5f * NEG_BIG ? fast_exp2(s1 - mx) : 0.f;
+          rs += p0 + p1;
+          __nv_bfloat162 b2 = __floats2bfloat162_rn(p0, p1);
+          packed[i >> 1] = *reinterpret_cast<uint32_t*>(&b2);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < BKV; i += 2) {
+          const float p0 = fast_exp2(__uint_as_float(v[i]) - mx), p1 = fast_exp2(__uint_as_float(v[i + 1]) - mx);
+          rs += p0 + p1;
+          __nv_bfloat162 b2 = __floats2bfloat162_rn(p0, p1);
+          packed[i >> 1] = *reinterpret_cast<uint32_t*>(&b2);
+        }
       }
       // P may be overwritten, and O rescaled, only when the product of the previous tile is done
       if (j > 0) {
