@@ -91,6 +91,50 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+
+// ---- wrappers for a pair of blocks (a cluster of two) that share one MMA: cta_group::2
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t smem_addr, uint32_t rank) {  // the same location in another block of the cluster
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// The copy lands in this block's shared memory; its bytes are counted on a barrier that may lie in the pair's other block.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar_cluster) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar_cluster)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t dst_smem, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrives, once the MMAs issued so far are complete, on the barrier at this offset in both blocks of the pair.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(bar), "h"((uint16_t)3) : "memory");
+}
+
 // Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, stored with the
 // 128-byte swizzle (as TMA writes it): 8-row groups are 1024 bytes apart.
 __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
@@ -104,8 +148,8 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
 }
 
 // Instruction descriptor: bfloat16 x bfloat16 -> float32, both operands K-major, M = 128, N = bt.
-__host__ __device__ constexpr uint32_t make_idesc(int bt) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bt >> 3) << 17) | ((uint32_t)(WN >> 4) << 24);
+__host__ __device__ constexpr uint32_t make_idesc(int bt, int m = WN) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bt >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
 // ------------------------------------------------------------------------------------------ kernel
@@ -124,6 +168,71 @@ struct StreamArgs {
   int k_per_split;       // multiple of BK
   int* status;
 };
+
+// Epilogue of warps 2..9: the accumulator (tensor-memory lanes = weight rows n0.., columns = token rows row_lo..)
+// goes to global memory transposed, optionally through SiLU(gate) * up.
+template <int BT, int WT>
+__device__ __forceinline__ void stream_epilogue(const StreamArgs& args, int warp, int lane, uint32_t bar_acc, volatile int* failed,
+                                                uint32_t tmem_acc, int n0, int row_lo, int row_hi) {
+  const int quarter = warp & 3;         // tensor-memory lanes [32 * quarter, 32 * quarter + 32): fixed by the warp's number
+  const int half = (warp - 2) >> 2;     // the two warps of a quarter take alternate blocks of 16 token columns
+  pdl_wait();  // the output buffer may still be read by a predecessor
+  bool ok = mbar_wait(bar_acc, 0);
+  if (*(volatile int*)failed) ok = false;
+  ok = __all_sync(0xffffffffu, ok);  // the tensor-memory loads below need the whole warp
+  if (ok) {
+    tc_fence_after();
+    const size_t split_off = args.splits > 1 ? (size_t)blockIdx.z * args.rows * args.N : 0;
+#pragma unroll 1
+    for (int w = 0; w < WT; ++w) {
+      const int nb = n0 + w * WN + quarter * 32;  // first weight row of this warp in tile w
+      const int n = nb + lane;
+      const bool n_ok = n < args.N;
+      if (nb >= args.N) break;  // uniform across the warp
+#pragma unroll 1
+      for (int c0 = half * 16; c0 < BT; c0 += 32) {
+        if (row_lo + c0 >= row_hi) break;  // uniform across the warp
+        uint32_t r[16];
+        tmem_ld16(tmem_acc + ((uint32_t)(quarter * 32) << 16) + w * BT + c0, r);
+        tmem_ld_wait();
+        if (args.silu) {
+          // lanes 0..15 hold gate rows, lanes 16..31 the matching up rows of the same 32-row block.  Of two
+          // token columns the lower lanes finish the even one and the upper lanes the odd one: one exchange
+          // gives the lower lanes the even column's up values and the upper lanes the odd column's gates.
+          const size_t half_n = (size_t)(args.N >> 1);
+          const bool upper = lane >= 16;
+          const size_t col = (size_t)(nb >> 1) + (lane & 15);
+#pragma unroll
+          for (int j = 0; j < 16; j += 2) {
+            const float mine = __uint_as_float(upper ? r[j + 1] : r[j]);   // gate (lower) or up (upper) of my column
+            const float send = __uint_as_float(upper ? r[j] : r[j + 1]);
+            const float got = __shfl_xor_sync(0xffffffffu, send, 16);
+            const float gate = upper ? got : mine, up = upper ? mine : got;
+            const int m = row_lo + c0 + j + (upper ? 1 : 0);
+            if (m < row_hi) {  // N % 32 == 0: a block of 32 weight rows that starts below N lies wholly below it
+              const float act = __fdividef(gate, 1.f + __expf(-gate)) * up;
+              if (args.out_is_f32) ((float*)args.out)[(size_t)m * half_n + col] = act;
+              else ((bf16*)args.out)[(size_t)m * half_n + col] = __float2bfloat16_rn(act);
+            }
+          }
+        } else if (n_ok) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int m = row_lo + c0 + j;
+            if (m < row_hi) {
+              if (args.out_is_f32 || args.splits > 1)
+                ((float*)args.out)[split_off + (size_t)m * args.N + n] = __uint_as_float(r[j]);
+              else
+                ((bf16*)args.out)[(size_t)m * args.N + n] = __float2bfloat16_rn(__uint_as_float(r[j]));
+            }
+          }
+        }
+      }
+    }
+  } else if (lane == 0) {
+    atomicOr(args.status, JLX_STATUS_WAIT_TIMEOUT);
+  }
+}
 
 // WT: weight tiles of 128 rows per block.  With many token rows per group the token tile is the larger part of
 // a stage; two weight tiles (two accumulators in tensor memory) per token tile halve its traffic.
@@ -257,65 +366,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue (warps 2..9)
-    const int quarter = warp & 3;         // tensor-memory lanes [32 * quarter, 32 * quarter + 32): fixed by the warp's number
-    const int half = (warp - 2) >> 2;     // the two warps of a quarter take alternate blocks of 16 token columns
-    pdl_wait();  // the output buffer may still be read by a predecessor
-    bool ok = mbar_wait(bar_acc, 0);
-    if (*(volatile int*)&failed) ok = false;
-    ok = __all_sync(0xffffffffu, ok);  // the tensor-memory loads below need the whole warp
-    if (ok) {
-      tc_fence_after();
-      const size_t split_off = args.splits > 1 ? (size_t)blockIdx.z * args.rows * args.N : 0;
-#pragma unroll 1
-      for (int w = 0; w < WT; ++w) {
-        const int nb = n0 + w * WN + quarter * 32;  // first weight row of this warp in tile w
-        const int n = nb + lane;
-        const bool n_ok = n < args.N;
-        if (nb >= args.N) break;  // uniform across the warp
-#pragma unroll 1
-        for (int c0 = half * 16; c0 < BT; c0 += 32) {
-          if (row_lo + c0 >= row_hi) break;  // uniform across the warp
-          uint32_t r[16];
-          tmem_ld16(tmem_acc + ((uint32_t)(quarter * 32) << 16) + w * BT + c0, r);
-          tmem_ld_wait();
-          if (args.silu) {
-            // lanes 0..15 hold gate rows, lanes 16..31 the matching up rows of the same 32-row block.  Of two
-            // token columns the lower lanes finish the even one and the upper lanes the odd one: one exchange
-            // gives the lower lanes the even column's up values and the upper lanes the odd column's gates.
-            const size_t half_n = (size_t)(args.N >> 1);
-            const bool upper = lane >= 16;
-            const size_t col = (size_t)(nb >> 1) + (lane & 15);
-#pragma unroll
-            for (int j = 0; j < 16; j += 2) {
-              const float mine = __uint_as_float(upper ? r[j + 1] : r[j]);   // gate (lower) or up (upper) of my column
-              const float send = __uint_as_float(upper ? r[j] : r[j + 1]);
-              const float got = __shfl_xor_sync(0xffffffffu, send, 16);
-              const float gate = upper ? got : mine, up = upper ? mine : got;
-              const int m = row_lo + c0 + j + (upper ? 1 : 0);
-              if (m < row_hi) {  // N % 32 == 0: a block of 32 weight rows that starts below N lies wholly below it
-                const float act = __fdividef(gate, 1.f + __expf(-gate)) * up;
-                if (args.out_is_f32) ((float*)args.out)[(size_t)m * half_n + col] = act;
-                else ((bf16*)args.out)[(size_t)m * half_n + col] = __float2bfloat16_rn(act);
-              }
-            }
-          } else if (n_ok) {
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const int m = row_lo + c0 + j;
-              if (m < row_hi) {
-                if (args.out_is_f32 || args.splits > 1)
-                  ((float*)args.out)[split_off + (size_t)m * args.N + n] = __uint_as_float(r[j]);
-                else
-                  ((bf16*)args.out)[(size_t)m * args.N + n] = __float2bfloat16_rn(__uint_as_float(r[j]));
-              }
-            }
-          }
-        }
-      }
-    } else if (lane == 0) {
-      atomicOr(args.status, JLX_STATUS_WAIT_TIMEOUT);
-    }
+    stream_epilogue<BT, WT>(args, warp, lane, bar_acc, &failed, tmem_acc, n0, row_lo, row_hi);
   }
   tc_fence_before();
   __syncthreads();
@@ -323,6 +374,140 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     __syncwarp();
     tc_fence_after();
     tmem_dealloc(tmem_acc, TMEM_COLS);
+  }
+}
+
+// The same product by a pair of blocks on neighbouring SMs (a cluster of two) that share each MMA
+// (cta_group::2, M = 256): block r of the pair stages its own 128 weight rows and half of the token tile, the
+// MMA reads both halves, and each block's tensor memory receives the accumulator of its own weight rows.  A
+// token tile is so fetched once per 256 weight rows and a stage is a quarter smaller, which buys a fourth stage
+// where the one-block kernel has three.  Block 0 issues the MMAs; the copies of both blocks count on block 0's
+// `full` barriers, and its commits arrive on the `empty` barriers of both.
+template <int BT, int ST>
+__global__ void __launch_bounds__(NTHREADS)
+gemm_stream_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a, const StreamArgs args) {
+  constexpr uint32_t W_BYTES = WN * BK * 2, A_HALF = (BT / 2) * BK * 2;
+  constexpr uint32_t TMEM_COLS = BT <= 32 ? 32 : BT <= 64 ? 64 : BT <= 128 ? 128 : 256;
+  static_assert(BT % 16 == 0 && A_HALF % 1024 == 0, "half a token tile must be whole 8-row swizzle groups");
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t smem_w = (smem_u32(smem_raw) + 1023u) & ~1023u, smem_a = smem_w + ST * W_BYTES;
+  __shared__ __align__(8) uint64_t bars[2 * ST + 1];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int failed;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_rank();  // 0 or 1: blockIdx.x is even or odd
+  pdl_launch_dependents();
+
+  // ---- which tile (both blocks of a pair have the same blockIdx.y and decide alike)
+  int row_lo, row_hi, group = 0;
+  if (args.offsets) {
+    pdl_wait();
+    int t = blockIdx.y, found = 0;
+    if (args.tile_list) {
+      if (t >= args.n_tiles[0]) return;
+      group = args.tile_list[2 * t];
+      row_lo = args.tile_list[2 * t + 1];
+      row_hi = args.offsets[group + 1];
+      found = 1;
+    }
+    for (int e = 0; !found && e < args.E; ++e) {
+      const int lo = args.offsets[e], hi = args.offsets[e + 1];
+      const int tiles = (hi - lo + BT - 1) / BT;
+      if (t < tiles) { row_lo = lo + t * BT; row_hi = hi; group = e; found = 1; break; }
+      t -= tiles;
+    }
+    if (!found) return;
+  } else {
+    row_lo = blockIdx.y * BT;
+    row_hi = args.rows;
+    if (row_lo >= row_hi) return;
+  }
+  const int n0 = blockIdx.x * WN;  // this block's weight rows
+  const int k_begin = blockIdx.z * args.k_per_split;
+  const int k_end = min(args.K, k_begin + args.k_per_split);
+  const int k_iters = (k_end - k_begin + BK - 1) / BK;
+
+  const uint32_t bar_full = smem_u32(&bars[0]), bar_empty = bar_full + 8 * ST, bar_acc = bar_empty + 8 * ST;
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 2 * ST + 1; ++i) mbar_init(bar_full + 8 * i, 1);
+    failed = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc_pair(smem_u32(&tmem_slot), TMEM_COLS);
+  tc_fence_before();
+  cluster_sync_all();  // both blocks' barriers exist before either block's copies or commits reach them
+  tc_fence_after();
+  const uint32_t tmem_acc = tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (one per block)
+    if (lane == 0) {
+      const uint32_t full0 = map_to_rank(bar_full, 0);  // block 0's `full` barriers
+      const int a_row = row_lo + (int)rank * (BT / 2);
+      auto load_w = [&](int it) {
+        const int s = it % ST;
+        if (rank == 0) mbar_expect_tx(bar_full + 8 * s, 2 * (W_BYTES + A_HALF));  // the bytes of both blocks
+        tma_load_2d_pair(smem_w + s * W_BYTES, &map_w, k_begin + it * BK, group * args.N + n0, full0 + 8 * s);
+      };
+      auto load_a = [&](int it) {
+        const int s = it % ST;
+        tma_load_2d_pair(smem_a + s * A_HALF, &map_a, k_begin + it * BK, a_row, full0 + 8 * s);
+      };
+      // the weights depend on no earlier kernel: their first stages are requested before the wait for it
+      const int early = k_iters < ST ? k_iters : ST;
+      for (int it = 0; it < early; ++it) load_w(it);
+      pdl_wait();
+      for (int it = 0; it < early; ++it) load_a(it);
+      int issued = early;
+      bool ok = true;
+      for (int it = early; it < k_iters && ok; ++it) {
+        const int s = it % ST;
+        ok = mbar_wait(bar_empty + 8 * s, ((it / ST) & 1) ^ 1);
+        if (!ok || *(volatile int*)&failed) { ok = false; break; }
+        load_w(it);
+        load_a(it);
+        issued = it + 1;
+      }
+      if (!ok) {
+        atomicOr(args.status, JLX_STATUS_WAIT_TIMEOUT);
+        failed = 1;
+        // block 0 can see its copies land; block 1's are counted there too, so it waits for the accumulator
+        // barrier or for its own time limit in the epilogue warps before it leaves
+        if (rank == 0)
+          for (int it = max(0, issued - ST); it < issued; ++it) mbar_wait(bar_full + 8 * (it % ST), (it / ST) & 1);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (block 0 only)
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = make_idesc(BT, 2 * WN);
+      bool ok = true;
+      for (int it = 0; it < k_iters; ++it) {
+        const int s = it % ST;
+        ok = mbar_wait(bar_full + 8 * s, (it / ST) & 1);
+        if (!ok || *(volatile int*)&failed) { ok = false; break; }
+        tc_fence_after();
+        const uint64_t wdesc = smem_desc_sw128(smem_w + s * W_BYTES), adesc = smem_desc_sw128(smem_a + s * A_HALF);
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k) umma_bf16_pair(tmem_acc, wdesc + 2 * k, adesc + 2 * k, idesc, (it | k) != 0);
+        umma_commit_pair(bar_empty + 8 * s);  // frees the stage in both blocks
+      }
+      if (ok) {
+        umma_commit_pair(bar_acc);  // accumulators complete in both blocks
+      } else {
+        atomicOr(args.status, JLX_STATUS_WAIT_TIMEOUT);
+        failed = 1;
+      }
+    }
+  } else {
+    stream_epilogue<BT, 1>(args, warp, lane, bar_acc, &failed, tmem_acc, n0, row_lo, row_hi);
+  }
+  tc_fence_before();
+  cluster_sync_all();  // neither block gives up shared or tensor memory that the pair's MMAs may still use
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_acc, TMEM_COLS);
   }
 }
 
@@ -378,6 +563,32 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& ma, const StreamArgs
   }
   dim3 grid((a.N + WN * WT - 1) / (WN * WT), row_tiles, a.splits);
   JLX_CUDA(jlx_launch_pdl(gemm_stream_kernel<BT, SW, SA, WT>, grid, dim3(NTHREADS), smem, stream, mw, ma, a));
+  return 0;
+}
+
+template <int BT, int ST>
+static int launch_pair(const CUtensorMap& mw, const CUtensorMap& ma, const StreamArgs& a, int row_tiles, cudaStream_t stream) {
+  constexpr size_t smem = (size_t)ST * (WN * BK * 2 + (BT / 2) * BK * 2) + 1024;
+  static bool configured = false;
+  if (!configured) {
+    JLX_CUDA(cudaFuncSetAttribute(gemm_stream_pair_kernel<BT, ST>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(a.N / WN, row_tiles, a.splits);
+  cfg.blockDim = dim3(NTHREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  attr[1].id = cudaLaunchAttributeClusterDimension;
+  attr[1].val.clusterDim.x = 2;
+  attr[1].val.clusterDim.y = 1;
+  attr[1].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  JLX_CUDA(cudaLaunchKernelEx(&cfg, gemm_stream_pair_kernel<BT, ST>, mw, ma, a));
   return 0;
 }
 
@@ -438,6 +649,20 @@ JLX_API int jlx_gemm_stream(const void* A, const void* W, void* out, int out_is_
   const int row_tiles = (rows + bt - 1) / bt + (offsets ? E : 0);
   JLX_REQUIRE(row_tiles <= 65535, "gemm_stream: too many row tiles");
   int rc;
+  // Wide token tiles (prompt portions): a pair of blocks per 256 weight rows, when the rows divide so.
+  const bool pair = bt >= 96 && N % (2 * WN) == 0;
+  if (pair) {
+    CUtensorMap ma_half;
+    if (make_map(&ma_half, A, rows, K, bt / 2)) return 1;
+    switch (bt) {
+      case 96: rc = launch_pair<96, 4>(mw, ma_half, a, row_tiles, stream); break;
+      case 128: rc = launch_pair<128, 4>(mw, ma_half, a, row_tiles, stream); break;
+      case 160: rc = launch_pair<160, 4>(mw, ma_half, a, row_tiles, stream); break;
+      case 192: rc = launch_pair<192, 4>(mw, ma_half, a, row_tiles, stream); break;
+      case 224: rc = launch_pair<224, 3>(mw, ma_half, a, row_tiles, stream); break;
+      default: rc = launch_pair<256, 3>(mw, ma_half, a, row_tiles, stream); break;
+    }
+  } else
   switch (bt) {
     // up to 192 token rows: one weight tile and stages sized so that two blocks share an SM (about 100 KB
     // each): one block's epilogue (tensor memory -> registers -> global) overlaps the other's main loop.

@@ -223,7 +223,10 @@ def test_gemm_simt_grouped(E, rows, N, Kd):
 @pytest.mark.parametrize("M, N, Kd, out_dtype, splits", [
     (1, 128, 64, torch.float32, 1), (8, 384, 512, torch.bfloat16, 1), (5, 200, 136, torch.float32, 1),
     (64, 1000, 1024, torch.float32, 1), (130, 256, 320, torch.bfloat16, 1), (300, 130, 72, torch.float32, 1),
-    (8, 640, 2048, torch.float32, 4), (33, 130, 1000, torch.bfloat16, 3)])
+    (8, 640, 2048, torch.float32, 4), (33, 130, 1000, torch.bfloat16, 3),
+    # 96 rows and more with outputs in multiples of 256: pairs of blocks sharing each MMA (cta_group::2)
+    (100, 256, 320, torch.float32, 1), (150, 512, 1096, torch.bfloat16, 1), (256, 768, 2048, torch.float32, 2),
+    (203, 256, 64, torch.float32, 1)])
 def test_gemm_stream_dense(M, N, Kd, out_dtype, splits):
     """The tcgen05 product against float64 of the same bfloat16 operands."""
     a = torch.randn(M, Kd, device=DEV).bfloat16()
@@ -238,7 +241,8 @@ def test_gemm_stream_dense(M, N, Kd, out_dtype, splits):
 
 
 @pytest.mark.parametrize("E, rows, N, Kd, hint", [(4, 37, 256, 128, 0), (16, 64, 384, 512, 4), (8, 700, 130, 200, 88),
-                                                  (5, 9, 128, 64, 16)])
+                                                  (5, 9, 128, 64, 16), (6, 900, 512, 328, 150), (3, 500, 256, 1024, 250),
+                                                  (7, 640, 768, 192, 100)])
 def test_gemm_stream_grouped(E, rows, N, Kd, hint):
     a = torch.randn(rows, Kd, device=DEV).bfloat16()
     w = torch.randn(E, N, Kd, device=DEV).bfloat16()
@@ -458,6 +462,19 @@ def test_gemm_stream_partials_and_swiglu_epilogue():
         if hi > lo:
             g, u = a2[lo:hi].double() @ we[e, :F].double().T, a2[lo:hi].double() @ we[e, F:].double().T
             close(act2[lo:hi], torch.nn.functional.silu(g) * u, 1e-4)
+    # wide token tiles and outputs in multiples of 256: the paired kernel's epilogue
+    E, rows, F2 = 3, 400, 256
+    a3 = torch.randn(rows, Kd, device=DEV).bfloat16()
+    we3 = (torch.randn(E, 2 * F2, Kd, device=DEV) * 0.05).bfloat16()
+    off = _groups(E, 5, rows)
+    act3 = torch.full((rows, F2), float("nan"), device=DEV, dtype=torch.bfloat16)
+    api.gemm_stream(a3, interleave_gate_up(we3), act3, st, offsets=off.to(DEV), rows_hint=160, mode=api.GEMM_SWIGLU)
+    assert int(st) == 0
+    for e in range(E):
+        lo, hi = int(off[e]), int(off[e + 1])
+        if hi > lo:
+            g, u = a3[lo:hi].double() @ we3[e, :F2].double().T, a3[lo:hi].double() @ we3[e, F2:].double().T
+            close(act3[lo:hi], torch.nn.functional.silu(g) * u, 1e-2)
     # the activation kernel reads the same interleaved layout and split partials
     gu = torch.randn(3, 7, 2 * F, device=DEV)
     out = torch.empty(7, F, device=DEV)
