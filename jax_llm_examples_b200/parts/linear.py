@@ -26,10 +26,18 @@ STREAM_MAX_ROWS = 256  # above this a dense product is compute-bound and goes to
 _SM_COUNT = 148
 
 
-def _splits_for(n_out: int, k: int) -> int:
-    """K cuts so that about two blocks per SM stream weights; each cut keeps at least 512 of K."""
-    tiles = -(-n_out // 128)
-    want = -(-2 * _SM_COUNT // tiles)
+_RESIDENT = 2 * _SM_COUNT  # blocks of the streaming kernel that the GPU holds at once (two per SM)
+
+
+def _splits_for(n_out: int, k: int, groups: int = 1, partials: bool = True) -> int:
+    """K cuts for a product that streams `groups` weight matrices of n_out rows.  Fewer blocks than the GPU
+    holds at once: cut K so that one round of blocks fills it, and no more (a second, nearly empty round
+    costs as much as the first).  More blocks than that: rounds cannot be avoided, so cut K to about 2048
+    per block (half a megabyte of weights), which keeps the last, partly filled round short; but only where
+    the consumer adds the partials itself (`partials`): a separate pass over them costs more than the tail.
+    Each cut keeps at least 512 of K."""
+    busy = -(-n_out // 128) * max(groups, 1)
+    want = _RESIDENT // busy if busy <= _RESIDENT else (k // 2048 if partials else 1)
     return max(1, min(want, k // 512, 8))
 
 
@@ -61,7 +69,7 @@ def linear(ctx: StepContext, a: torch.Tensor, w: torch.Tensor, out_dtype: torch.
     else one slice in out_dtype."""
     M, N = a.shape[0], w.shape[0]
     if _streams(a, w, True):
-        splits = _splits_for(N, a.shape[1])
+        splits = _splits_for(N, a.shape[1], partials=partials)
         if partials:
             out = torch.empty((splits, M, N), dtype=torch.float32, device=a.device)
             used = K.gemm_stream(a, w, out, ctx.status, splits=splits, mode=K.GEMM_PARTIALS)
@@ -105,8 +113,8 @@ def grouped_linear(ctx: StepContext, a_sorted: torch.Tensor, w: torch.Tensor, of
     if _streams(a_sorted, w, False):
         hint = _group_rows_hint(rows, E, largest_group)
         if partials:
-            busy = -(-N // 128) * min(E, rows)  # at most this many blocks have work
-            splits = max(1, min(-(-2 * _SM_COUNT // busy), a_sorted.shape[1] // 512, 8)) if rows <= STREAM_MAX_ROWS else 1
+            # at most min(E, rows) groups have rows, and so many weight matrices are streamed
+            splits = _splits_for(N, a_sorted.shape[1], min(E, rows)) if rows <= STREAM_MAX_ROWS else 1
             out = torch.empty((splits, rows, N), dtype=torch.float32, device=a_sorted.device)
             used = K.gemm_stream(a_sorted, w, out, ctx.status, offsets=offsets, rows_hint=hint, splits=splits, mode=K.GEMM_PARTIALS,
                                  tiles=tiles)
