@@ -3,13 +3,18 @@
 // One block = 128 consecutive query tokens of one request and one query head.  Keys and values come from
 // the paged cache in tiles of 128 keys.  Per tile:
 //   S = Q K^T        tcgen05.mma, Q and K from shared memory (TMA, 128-byte swizzle), S in tensor memory
-//   P = softmax part one thread per query row reads its row of S from tensor memory, keeps the running
-//                    max and sum in 32-bit, writes P (bfloat16) to shared memory and rescales O
-//   O += P V         tcgen05.mma, P from shared memory, V from shared memory as an MN-major operand
-//                    (the cache keeps values as [key][dh], so dh is the contiguous direction), O in tensor memory
-// S is double-buffered in tensor memory, so the product of the next tile runs while this tile's softmax does;
+//   P = softmax part two threads per query row read the halves of its row of S from tensor memory, keep the running
+//                    max and sum in 32-bit, and write P (bfloat16, two keys per 32-bit column) back over the
+//                    first half of the same S buffer; when a row's maximum moved they rescale O
+//   O += P V         tcgen05.mma with P as the operand in tensor memory and V from shared memory as an MN-major
+//                    operand (the cache keeps values as [key][dh], so dh is the contiguous direction), O in
+//                    tensor memory
+// S is double-buffered in tensor memory, so the product of the next tile runs while this tile's softmax does.
+// MMAs run in the order of their issue: the score product of tile j+2, which overwrites the buffer of S_j and
+// P_j, is issued after O += P_j V_j and so needs no barrier of its own;
 // K and V tiles are double-buffered in shared memory.  Warp 0 issues TMA copies, warp 1 issues the MMAs,
-// warps 2..5 (one thread per query row = per tensor-memory lane) do softmax, rescaling and the final store.
+// warps 2..9 (two threads per query row = per tensor-memory lane, each half of the tile's keys) do softmax,
+// rescaling and the final store.
 //
 // Mask, scale and softmax are those of llama4/llama4_jax/model.py:731-794 (causal, same chunk, optional
 // window; scale dh^-0.5; 32-bit softmax), with the attention temperature on layers that have it.  The
@@ -24,7 +29,7 @@
 #define DH 128
 #define BQ 128           // query rows per block
 #define BKV 128          // keys per tile
-#define NTHREADS 192
+#define NTHREADS 320     // warp 0: TMA, warp 1: MMA, warps 2..9: softmax (two per quarter of the query rows)
 #define WAIT_LIMIT (1u << 22)
 #define NEG_BIG (-1.0e30f)
 
@@ -75,6 +80,13 @@ __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint6
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_bf16_a_tmem(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -144,19 +156,22 @@ __device__ __forceinline__ int first_key(int p, int chunk, int window) {
 }
 
 // Shared-memory plan (bytes from a 1024-aligned base): Q [2 halves][128][128B] = 32 KB, then K and V
-// stages [2][2 halves][128][128B] = 64 KB each, then P [2 halves][128][128B] = 32 KB.
+// stages [2][2 halves][128][128B] = 64 KB each.
 #define TILE_BYTES (2 * 128 * 128)  // one [128 rows][128 elements] operand: two halves of 16 KB
 #define HALF_BYTES (128 * 128)
 
-__global__ void __launch_bounds__(NTHREADS)
+__global__ void __launch_bounds__(NTHREADS, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv, const TcParams P) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t q_s = base, k_s = base + TILE_BYTES, v_s = k_s + 2 * TILE_BYTES, p_s = v_s + 2 * TILE_BYTES;
-  // barriers: 0 q_full | 1,2 k_full | 3,4 v_full | 5,6 v_empty | 7,8 s_full | 9,10 s_free | 11 p_ready | 12 o_done | 13,14 k_empty
-  __shared__ __align__(8) uint64_t bars[15];
+  const uint32_t q_s = base, k_s = base + TILE_BYTES, v_s = k_s + 2 * TILE_BYTES;
+  // barriers: 0 q_full | 1,2 k_full | 3,4 v_full | 5,6 v_empty | 7,8 s_full | 9,10 unused | 11 p_ready | 12 o_done | 13,14 k_empty |
+  // 15..18 the meeting of the two softmax warps of each quarter of the rows
+  __shared__ __align__(8) uint64_t bars[19];
   __shared__ uint32_t tmem_slot;
   __shared__ int failed;
+  __shared__ float xmax[2][2][BQ];  // [tile parity][half of the keys][row]: what the two warps of a row exchange
+  __shared__ float xsum[2][BQ];
   const uint32_t bar0 = smem_u32(&bars[0]);
   auto BAR = [bar0](int i) { return bar0 + 8u * i; };
 
@@ -173,12 +188,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < 9; ++i) mbar_init(BAR(i), 1);
-    mbar_init(BAR(9), 128);
-    mbar_init(BAR(10), 128);
-    mbar_init(BAR(11), 128);
+    mbar_init(BAR(9), 256);
+    mbar_init(BAR(10), 256);
+    mbar_init(BAR(11), 256);
     mbar_init(BAR(12), 1);
     mbar_init(BAR(13), 1);
     mbar_init(BAR(14), 1);
+    for (int i = 15; i < 19; ++i) mbar_init(BAR(i), 64);
     failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -255,25 +271,23 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const int st = j & 1;
         if (j + 1 < n_kv) {
           const int s1 = (j + 1) & 1;
-          ok = mbar_wait(BAR(1 + s1), ((j + 1) >> 1) & 1);                      // K_{j+1} has landed
-          if (ok && j + 1 >= 2) ok = mbar_wait(BAR(9 + s1), (((j + 1) >> 1) - 1) & 1);  // softmax has read S of tile j-1
+          ok = mbar_wait(BAR(1 + s1), ((j + 1) >> 1) & 1);  // K_{j+1} has landed
           if (!ok || *(volatile int*)&failed) { ok = false; break; }
           tc_fence_after();
           issue_qk(j + 1);
         }
-        ok = mbar_wait(BAR(11), j & 1);                   // P_j is in shared memory, O is rescaled
+        ok = mbar_wait(BAR(11), j & 1);                   // P_j is in tensor memory, O is rescaled
         if (ok) ok = mbar_wait(BAR(3 + st), (j >> 1) & 1);  // V_j has landed
         if (!ok || *(volatile int*)&failed) { ok = false; break; }
         tc_fence_after();
         const uint32_t vb = v_s + st * TILE_BYTES;
 #pragma unroll
         for (int kk = 0; kk < BKV / 16; ++kk) {
-          // P: K-major, 16 keys = 32 bytes along the row; V: MN-major, 16 keys = 16 rows of 128 bytes
-          const uint32_t p_off = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
-          umma_bf16(tm_o, desc_k_major(p_s + p_off), desc_mn_major(vb + kk * 16 * 128, HALF_BYTES), idesc_pv, (j | kk) != 0);
+          // P: 16 keys = 8 columns of tensor memory; V: MN-major, 16 keys = 16 rows of 128 bytes
+          umma_bf16_a_tmem(tm_o, tm_s0 + st * 128 + kk * 8, desc_mn_major(vb + kk * 16 * 128, HALF_BYTES), idesc_pv, (j | kk) != 0);
         }
         umma_commit(BAR(5 + st));  // V_j may be overwritten
-        umma_commit(BAR(12));      // O holds tiles 0..j; P may be overwritten
+        umma_commit(BAR(12));      // O holds tiles 0..j
       }
       if (!ok) {
         atomicOr(P.status, JLX_STATUS_WAIT_TIMEOUT);
@@ -282,9 +296,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     }
   } else {
     // ------------------------------------------------------------------------------ softmax, rescale, store
-    const int quarter = warp & 3;
+    // Warps 2..9: a warp reaches the tensor-memory lanes [32 * (warp & 3), +32), so two warps share each
+    // quarter of the query rows and split the tile's 128 key columns (and the output's 128 columns) in halves
+    // of 64.  The two meet once per tile to agree on the row's maximum; each keeps the sum of its own half.
+    const int quarter = warp & 3, half = (warp - 2) >> 2;
     const int row = quarter * 32 + lane;             // query row = tensor-memory lane
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    const int col0 = half * (BKV / 2);
     const bool live = row < cnt;
     const int p_row = p_first + min(row, cnt - 1);
     const int lo_row = first_key(p_row, P.chunk, P.window);
@@ -299,88 +317,89 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const int tile_key = key_begin + j * BKV;
-      const bool need_mask = tile_key + BKV - 1 > p_first || tile_key < first_key(p_last, P.chunk, P.window);
-      const uint32_t s_addr = tm_s0 + st * 128 + lane_addr;
-      // the row's 128 scores come into registers once
-      uint32_t v[BKV];
-#pragma unroll
-      for (int c0 = 0; c0 < BKV; c0 += 32) tmem_ld32(s_addr + c0, v + c0);
+      const int tile_key = key_begin + j * BKV + col0;
+      const bool need_mask = key_begin + j * BKV + BKV - 1 > p_first || key_begin + j * BKV < first_key(p_last, P.chunk, P.window);
+      const uint32_t s_addr = tm_s0 + st * 128 + lane_addr + col0;
+      // this warp's 64 scores of the row come into registers once
+      uint32_t v[BKV / 2];
+      tmem_ld32(s_addr, v);
+      tmem_ld32(s_addr + 32, v + 32);
       tmem_ld_wait();
-      float mx = m;
+      float mx4[4] = {NEG_BIG, NEG_BIG, NEG_BIG, NEG_BIG};  // four chains instead of one of 64 dependent steps
       if (need_mask) {
 #pragma unroll
-        for (int i = 0; i < BKV; ++i) {
+        for (int i = 0; i < BKV / 2; ++i) {
           const int key = tile_key + i;
           const float sv = (key >= lo_row && key <= p_row) ? __uint_as_float(v[i]) * sc : NEG_BIG;
           v[i] = __float_as_uint(sv);
-          mx = fmaxf(mx, sv);
+          mx4[i & 3] = fmaxf(mx4[i & 3], sv);
         }
       } else {
 #pragma unroll
-        for (int i = 0; i < BKV; ++i) {
+        for (int i = 0; i < BKV / 2; ++i) {
           const float sv = __uint_as_float(v[i]) * sc;
           v[i] = __float_as_uint(sv);
-          mx = fmaxf(mx, sv);
+          mx4[i & 3] = fmaxf(mx4[i & 3], sv);
         }
       }
-      tc_fence_before();
-      mbar_arrive(BAR(9 + st));  // S[st] has been read
+      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      // the row's maximum over both halves (double-buffered by tile parity: the partner may be a tile ahead)
+      xmax[st][half][row] = mx;
+      mbar_arrive(BAR(15 + quarter));
+      ok = mbar_wait(BAR(15 + quarter), j & 1);
+      if (*(volatile int*)&failed) ok = false;
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      mx = fmaxf(m, fmaxf(mx, xmax[st][half ^ 1][row]));
       const float corr = fast_exp2(m - mx);
       // probabilities and their sum; a masked score is NEG_BIG and gives exactly 0, also in a row whose scores
       // are all masked so far (mx = NEG_BIG)
-      float rs = 0.f;
-      uint32_t packed[BKV / 2];
+      float rs4[4] = {0.f, 0.f, 0.f, 0.f};
+      uint32_t packed[BKV / 4];
       if (need_mask) {
 #pragma unroll
-        for (int i = 0; i < BKV; i += 2) {
+        for (int i = 0; i < BKV / 2; i += 2) {
           const float s0 = __uint_as_float(v[i]), s1 = __uint_as_float(v[i + 1]);
           const float p0 = s0 > 0.5f * NEG_BIG ? fast_exp2(s0 - mx) : 0.f, p1 = s1 > 0.5f * NEG_BIG ? fast_exp2(s1 - mx) : 0.f;
-          rs += p0 + p1;
+          rs4[(i >> 1) & 3] += p0 + p1;
           __nv_bfloat162 b2 = __floats2bfloat162_rn(p0, p1);
           packed[i >> 1] = *reinterpret_cast<uint32_t*>(&b2);
         }
       } else {
 #pragma unroll
-        for (int i = 0; i < BKV; i += 2) {
+        for (int i = 0; i < BKV / 2; i += 2) {
           const float p0 = fast_exp2(__uint_as_float(v[i]) - mx), p1 = fast_exp2(__uint_as_float(v[i + 1]) - mx);
-          rs += p0 + p1;
+          rs4[(i >> 1) & 3] += p0 + p1;
           __nv_bfloat162 b2 = __floats2bfloat162_rn(p0, p1);
           packed[i >> 1] = *reinterpret_cast<uint32_t*>(&b2);
         }
       }
-      // P may be overwritten, and O rescaled, only when the product of the previous tile is done
-      if (j > 0) {
+      const float rs = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
+      // P over the first half of this S buffer: keys 2c and 2c+1 in column c (the partner has read its scores:
+      // the two met after their loads)
+      tmem_st32(tm_s0 + st * 128 + lane_addr + half * (BKV / 4), packed);
+      l = l * corr + rs;
+      m = mx;
+      // Rescale this warp's half of O's columns when a row of the warp moved its maximum; the product of the
+      // previous tile must be complete first (nothing to rescale before the first product).
+      if (j > 0 && !__all_sync(0xffffffffu, corr == 1.f)) {
         ok = mbar_wait(BAR(12), (j - 1) & 1);
         if (*(volatile int*)&failed) ok = false;
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
-      }
-      // P to shared memory: K-major rows of 64 keys (128 bytes), 128-byte swizzle
-#pragma unroll
-      for (int c16 = 0; c16 < BKV / 8; ++c16) {  // 16-byte chunks of 8 keys
-        const uint32_t dst = p_s + (c16 >> 3) * HALF_BYTES + row * 128 + (((c16 & 7) ^ (row & 7)) << 4);
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(packed[4 * c16]), "r"(packed[4 * c16 + 1]),
-                     "r"(packed[4 * c16 + 2]), "r"(packed[4 * c16 + 3]) : "memory");
-      }
-      l = l * corr + rs;
-      m = mx;
-      // rescale O, unless no row of this warp moved its maximum (nothing to rescale before the first product)
-      if (j > 0 && !__all_sync(0xffffffffu, corr == 1.f)) {
         uint32_t o[32];
 #pragma unroll 1
-        for (int c0 = 0; c0 < DH; c0 += 32) {
+        for (int c0 = half * (DH / 2); c0 < (half + 1) * (DH / 2); c0 += 32) {
           tmem_ld32(tm_o + lane_addr + c0, o);
           tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
           tmem_st32(tm_o + lane_addr + c0, o);
         }
-        tmem_st_wait();
       }
+      tmem_st_wait();
       tc_fence_before();
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // P's stores before the MMA's reads
       mbar_arrive(BAR(11));
     }
     if (ok) {
@@ -390,11 +409,17 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     }
     if (ok) {
       tc_fence_after();
-      const float inv = 1.f / l;
+      // the row's sum is the sum of the halves' sums
+      xsum[half][row] = l;
+      mbar_arrive(BAR(15 + quarter));
+      ok = __all_sync(0xffffffffu, mbar_wait(BAR(15 + quarter), n_kv & 1));
+    }
+    if (ok) {
+      const float inv = 1.f / (xsum[0][row] + xsum[1][row]);
       bf16* dst = P.out + ((size_t)(n0 + row) * P.Hq + head) * DH;
       uint32_t v[32];
 #pragma unroll 1
-      for (int c0 = 0; c0 < DH; c0 += 32) {
+      for (int c0 = half * (DH / 2); c0 < (half + 1) * (DH / 2); c0 += 32) {
         tmem_ld32(tm_o + lane_addr + c0, v);
         tmem_ld_wait();
         if (live) {
@@ -487,7 +512,7 @@ JLX_API int jlx_attention_prefill_tc(const void* q, const void* pages, const int
   P.out = (bf16*)out; P.tiles = tiles; P.Hq = Hq; P.Hkv = Hkv; P.page_size = page_size; P.num_pages = num_pages;
   P.scale_log2 = scale * 1.4426950408889634f; P.chunk = chunk; P.window = window; P.attn_scale = attn_scale;
   P.floor_scale = floor_scale; P.status = status;
-  const size_t smem = 6 * (size_t)TILE_BYTES + 1024;
+  const size_t smem = 5 * (size_t)TILE_BYTES + 1024;
   static bool cfg = false;
   if (!cfg) {
     JLX_CUDA(cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));

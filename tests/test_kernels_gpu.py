@@ -500,6 +500,29 @@ def test_add_rmsnorm_with_partials_and_fused_router():
     close(wt, torch.sigmoid(order.values[:, :k]), 1e-5)
 
 
+@pytest.mark.parametrize("N, D, E, k, splits", [(5, 5120, 16, 1, 3), (1, 1288, 5, 2, 1), (32, 2048, 128, 4, 2)])
+def test_add_rmsnorm_router_on_few_rows_by_a_cluster(N, D, E, k, splits):
+    """A few rows, bfloat16 output, a router and no 32-bit copy: eight blocks share a row (a cluster with
+    distributed shared memory).  The same sums in another order: compare with float64."""
+    eps = 1e-5
+    x, parts, g = torch.randn(N, D, device=DEV), torch.randn(splits, N, D, device=DEV), 1 + 0.1 * torch.randn(D, device=DEV)
+    w = torch.randn(E, D, device=DEV)
+    s = x.double() + parts.double().sum(0)
+    ref = g.double() * s / torch.sqrt((s * s).mean(-1, keepdim=True) + eps)
+    xc, out = x.clone(), torch.full((N, D), float("nan"), device=DEV, dtype=torch.bfloat16)
+    idx, wt = torch.full((N, k), -1, device=DEV, dtype=torch.int32), torch.empty(N, k, device=DEV)
+    K().add_rmsnorm(xc, parts, g, eps, out, None, None, splits, w, idx, wt)
+    torch.cuda.synchronize()
+    close(out, ref, 5e-3)
+    assert torch.allclose(xc.double(), s, atol=1e-5)
+    scores = ref @ w.double().T
+    order = torch.sort(scores, dim=-1, descending=True, stable=True)
+    # a choice may differ from float64's only where two scores tie to within 32-bit rounding
+    chosen = torch.gather(scores, 1, idx.long())
+    assert float((order.values[:, :k] - chosen).abs().max()) < 1e-3 * float(scores.abs().max())
+    close(wt, torch.sigmoid(chosen), 1e-4)
+
+
 def test_rope_kv_store_from_float32_partials():
     N, Hq, Hkv, dh, page, P, eps = 5, 4, 2, 64, 16, 4, 1e-5
     parts = torch.randn(2, N, (Hq + 2 * Hkv) * dh, device=DEV)
