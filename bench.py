@@ -139,8 +139,8 @@ def run_ours(args) -> dict:
 
     peaks, peak_src = _peaks()
     torch.cuda.set_device(0)
-    cfg_json = J.preset("scout16", num_hidden_layers=args.layers) if args.layers else J.preset("scout16")
-    full_layers = J.preset("scout16")["num_hidden_layers"]
+    cfg_json = J.preset(args.preset, num_hidden_layers=args.layers) if args.layers else J.preset(args.preset)
+    full_layers = J.preset(args.preset)["num_hidden_layers"]
     ctx_len, batch, page = args.context, args.batch, 64
     t0 = time.time()
     model = J.random_model(cfg_json, seed=0, dtype="bfloat16")
@@ -269,13 +269,13 @@ def run_ours(args) -> dict:
     tok_s = batch / (main["ms"] / 1e3)
     achieved = main["bytes"] / (main["ms"] / 1e3) / 1e9
     return {
-        "metric": "decode tok/s at batch 8, context 8192 (Llama 4 Scout layer sizes)",
+        "metric": f"decode tok/s at batch {batch}, context {ctx_len} (Llama 4 {'Scout' if args.preset == 'scout16' else args.preset} layer sizes)",
         "value": round(tok_s, 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(main["ms"], 3), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: random N(0,0.02) weights, seeded uniform token ids, random cache contents",
         "config": {
-            "model": "llama4-scout-layer-sizes", "layers": cfg.num_hidden_layers, "layers_full_config": full_layers,
+            "model": "llama4-scout-layer-sizes" if args.preset == "scout16" else f"llama4-{args.preset}", "layers": cfg.num_hidden_layers, "layers_full_config": full_layers,
             "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
             "head_dim": cfg.head_dim, "experts": cfg.num_local_experts, "top_k": cfg.num_experts_per_tok,
             "expert_inter": cfg.intermediate_size, "vocab": cfg.vocab_size, "chunk": cfg.attention_chunk_size,
@@ -301,6 +301,7 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--preset", default="scout16", help="named configuration (the default is the benchmark's: 16 Scout-sized layers)")
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (same layer sizes)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=8192)

@@ -68,19 +68,18 @@ __device__ __forceinline__ int router_partials(const float* __restrict__ row, co
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     int d = p_lo + lane * 4;
     if ((D & 3) == 0 && (lo & 3) == 0 && (((uintptr_t)w_router) & 15) == 0) {
-      for (; d + 7 * 128 + 3 < p_hi; d += 8 * 128) {
+      for (; d < p_hi; d += 8 * 128) {  // the last round's loads are guarded, not looped: all are in flight at once
         float4 wv[8];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) wv[u] = *reinterpret_cast<const float4*>(wr + d + 128 * u);
+        for (int u = 0; u < 8; ++u)
+          wv[u] = d + 128 * u < p_hi ? *reinterpret_cast<const float4*>(wr + d + 128 * u) : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
-          const float4 xv = *reinterpret_cast<const float4*>(row + (d - lo) + 128 * u);
-          acc[u] = fmaf(xv.x, wv[u].x, fmaf(xv.y, wv[u].y, fmaf(xv.z, wv[u].z, fmaf(xv.w, wv[u].w, acc[u]))));
+          if (d + 128 * u < p_hi) {
+            const float4 xv = *reinterpret_cast<const float4*>(row + (d - lo) + 128 * u);
+            acc[u] = fmaf(xv.x, wv[u].x, fmaf(xv.y, wv[u].y, fmaf(xv.z, wv[u].z, fmaf(xv.w, wv[u].w, acc[u]))));
+          }
         }
-      }
-      for (; d + 3 < p_hi; d += 128) {
-        const float4 wv = *reinterpret_cast<const float4*>(wr + d), xv = *reinterpret_cast<const float4*>(row + (d - lo));
-        acc[0] = fmaf(xv.x, wv.x, fmaf(xv.y, wv.y, fmaf(xv.z, wv.z, fmaf(xv.w, wv.w, acc[0]))));
       }
     } else {
       for (int i = p_lo + lane; i < p_hi; i += 32) acc[0] = fmaf(row[i - lo], wr[i], acc[0]);
@@ -226,7 +225,8 @@ add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, int d
 template <typename TO>
 __global__ void __launch_bounds__(512)
 add_rmsnorm_router_cluster_kernel(float* __restrict__ x, const float* __restrict__ delta, int delta_splits, long long delta_stride,
-                                  const float* __restrict__ gamma, float eps, TO* __restrict__ out, int D, int slice,
+                                  const float* __restrict__ gamma, float eps, TO* __restrict__ out, float* __restrict__ out32, int D,
+                                  int slice,
                                   const float* __restrict__ w_router, int E, int k, int* __restrict__ topk_idx,
                                   float* __restrict__ topk_w) {
   namespace cg = cooperative_groups;
@@ -271,6 +271,7 @@ add_rmsnorm_router_cluster_kernel(float* __restrict__ x, const float* __restrict
     const float4 g = gamma ? g4[i] : make_float4(1.f, 1.f, 1.f, 1.f);
     const float4 v = make_float4(g.x * s.x / rms, g.y * s.y / rms, g.z * s.z / rms, g.w * s.w / rms);
     store4<TO>(out + (size_t)n * D + 4 * i, v);
+    if (out32) reinterpret_cast<float4*>(out32 + (size_t)n * D)[i] = v;
     row4[i - (lo >> 2)] = v;
   }
   __syncthreads();
@@ -310,8 +311,8 @@ JLX_API int jlx_add_rmsnorm(float* x, const float* delta, int delta_splits, long
   }
   const size_t smem = row_in_smem ? (size_t)D * 4 : 0;
   // A few rows with a router: a cluster of 8 blocks per row (all rows resident at once), bfloat16 output only.
-  if (w_router && out_dtype == JLX_BF16 && !row_index && !out32 && out && N <= 32 && (D & 3) == 0 && D >= 1024 &&
-      (delta_stride & 3) == 0 && (((uintptr_t)x | (uintptr_t)delta | (uintptr_t)gamma | (uintptr_t)out) & 15) == 0) {
+  if (w_router && out_dtype == JLX_BF16 && !row_index && out && N <= 32 && (D & 3) == 0 && D >= 1024 && (delta_stride & 3) == 0 &&
+      (((uintptr_t)x | (uintptr_t)delta | (uintptr_t)gamma | (uintptr_t)out | (uintptr_t)out32) & 15) == 0) {
     const int C = 8;
     const int slice = ((D / 4 + C - 1) / C) * 4;
     cudaLaunchConfig_t cfg = {};
@@ -329,7 +330,7 @@ JLX_API int jlx_add_rmsnorm(float* x, const float* delta, int delta_splits, long
     cfg.attrs = attr;
     cfg.numAttrs = 2;
     JLX_CUDA(cudaLaunchKernelEx(&cfg, add_rmsnorm_router_cluster_kernel<bf16>, x, delta, delta_splits, delta_stride, gamma, eps,
-                                (bf16*)out, D, slice, w_router, E, k, topk_idx, topk_w));
+                                (bf16*)out, out32, D, slice, w_router, E, k, topk_idx, topk_w));
     JLX_LAUNCH_CHECK("add_rmsnorm (cluster)");
     return 0;
   }

@@ -500,8 +500,9 @@ def test_add_rmsnorm_with_partials_and_fused_router():
     close(wt, torch.sigmoid(order.values[:, :k]), 1e-5)
 
 
+@pytest.mark.parametrize("want32", [False, True])
 @pytest.mark.parametrize("N, D, E, k, splits", [(5, 5120, 16, 1, 3), (1, 1288, 5, 2, 1), (32, 2048, 128, 4, 2)])
-def test_add_rmsnorm_router_on_few_rows_by_a_cluster(N, D, E, k, splits):
+def test_add_rmsnorm_router_on_few_rows_by_a_cluster(N, D, E, k, splits, want32):
     """A few rows, bfloat16 output, a router and no 32-bit copy: eight blocks share a row (a cluster with
     distributed shared memory).  The same sums in another order: compare with float64."""
     eps = 1e-5
@@ -511,9 +512,12 @@ def test_add_rmsnorm_router_on_few_rows_by_a_cluster(N, D, E, k, splits):
     ref = g.double() * s / torch.sqrt((s * s).mean(-1, keepdim=True) + eps)
     xc, out = x.clone(), torch.full((N, D), float("nan"), device=DEV, dtype=torch.bfloat16)
     idx, wt = torch.full((N, k), -1, device=DEV, dtype=torch.int32), torch.empty(N, k, device=DEV)
-    K().add_rmsnorm(xc, parts, g, eps, out, None, None, splits, w, idx, wt)
+    out32 = torch.full((N, D), float("nan"), device=DEV) if want32 else None
+    K().add_rmsnorm(xc, parts, g, eps, out, out32, None, splits, w, idx, wt)
     torch.cuda.synchronize()
     close(out, ref, 5e-3)
+    if want32:
+        close(out32, ref, 2e-6)
     assert torch.allclose(xc.double(), s, atol=1e-5)
     scores = ref @ w.double().T
     order = torch.sort(scores, dim=-1, descending=True, stable=True)
@@ -640,7 +644,8 @@ def test_attention_edges_of_windows_and_chunks(kind, size):
 
 
 @pytest.mark.parametrize("Hq, Hkv, page, chunk, window, temp", [
-    (4, 2, 64, 0, 0, False), (10, 2, 128, 0, 0, True), (3, 1, 64, 200, 0, False), (4, 4, 64, 0, 150, False)])
+    (4, 2, 64, 0, 0, False), (10, 2, 128, 0, 0, True), (3, 1, 64, 200, 0, False), (4, 4, 64, 0, 150, False),
+    (2, 1, 64, 128, 0, False)])
 def test_attention_prefill_tc(Hq, Hkv, page, chunk, window, temp):
     """The tcgen05 flash kernel: tiles of up to 128 tokens, several requests, cached history before the portion."""
     dh = 128
