@@ -39,8 +39,16 @@ class PagedAttention(Mixer):
         self.chunk, self.window = chunk, window
         self.scale = float(head_dim) ** -0.5 if scale is None else float(scale)  # model.py:774
 
+    # Head sizes that the tensor-core attention kernels are built for: a model with another head size never
+    # asks for them (and so never compiles them).
+    MMA_HEAD_SIZES = (64, 128)
+    TC_HEAD_SIZES = (128,)
+
     def required_libraries(self, runtime: Runtime):
-        return tuple(dict.fromkeys(super().required_libraries(runtime) + self.position.required_libraries(runtime)))
+        mine = [n for n in super().required_libraries(runtime)
+                if not (n == "attention_mma" and self.head_dim not in self.MMA_HEAD_SIZES)
+                and not (n == "attention_tc" and self.head_dim not in self.TC_HEAD_SIZES)]
+        return tuple(dict.fromkeys(tuple(mine) + self.position.required_libraries(runtime)))
 
     def kv_need(self) -> KVNeed:
         if self.chunk is not None and self.window is None:
@@ -65,7 +73,8 @@ class PagedAttention(Mixer):
         when every request brings one token, flash tiles otherwise; the generic kernel for the rest."""
         chunk, window = self.chunk or 0, self.window or 0
         decode = ctx.max_q_len == 1
-        if K.attention_mma_supported(q.dtype, self.n_heads, self.n_kv_heads, self.head_dim, decode):
+        if self.head_dim in self.MMA_HEAD_SIZES and K.attention_mma_supported(q.dtype, self.n_heads, self.n_kv_heads,
+                                                                              self.head_dim, decode):
             if decode:
                 split_keys, splits = K.attention_decode_plan(ctx.max_kv_len, chunk, window, q.shape[0] * self.n_kv_heads)
                 n = q.shape[0] * self.n_heads * splits
@@ -76,8 +85,8 @@ class PagedAttention(Mixer):
                 return
             if ctx.attn_tiles is not None:
                 tiles, n_tiles = ctx.attn_tiles, ctx.n_attn_tiles
-                if ctx.n_attn_tiles_big and K.attention_prefill_tc_supported(q.dtype, self.n_heads, self.n_kv_heads,
-                                                                             self.head_dim, cache.pages.shape[3]):
+                if ctx.n_attn_tiles_big and self.head_dim in self.TC_HEAD_SIZES and K.attention_prefill_tc_supported(
+                        q.dtype, self.n_heads, self.n_kv_heads, self.head_dim, cache.pages.shape[3]):
                     # long portions on the tcgen05 kernel (128-token tiles), the short ones below
                     K.attention_prefill_tc(q, cache.pages, cache.block_table, ctx.req_of_token, ctx.positions, out,
                                            ctx.attn_tiles_big, ctx.n_attn_tiles_big, self.scale, chunk, window,
