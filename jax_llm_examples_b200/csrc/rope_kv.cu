@@ -25,7 +25,10 @@ template <> __device__ __forceinline__ void store_pair<bf16>(bf16* p, float a, f
 
 // TI: element type of the projected rows (the activation type, or float32 split-K partials that are
 // added first); T: element type of q_out and of the cache.
-template <typename TI, typename T>
+// HPW: heads per warp.  A block takes 8 * HPW heads of one token (head h0 + 8 i for warp h0's i-th turn).  With many
+// tokens a block's fixed chain of dependent loads (position, request, block table) is paid once for more heads,
+// and a warp's loads of all its heads are in flight together; with few tokens one head per warp gives the most blocks.
+template <typename TI, typename T, int HPW>
 __global__ void __launch_bounds__(256)
 rope_kv_store_kernel(const TI* __restrict__ qkv, int splits, long long split_stride, T* __restrict__ q_out,
                      T* __restrict__ pages, const int* __restrict__ block_table, int bt_stride,
@@ -33,7 +36,6 @@ rope_kv_store_kernel(const TI* __restrict__ qkv, int splits, long long split_str
                      const float* __restrict__ inv_freq, int l2norm, float eps, int Hq, int Hkv, int dh, int page_size,
                      int num_pages, int store_kv, int* status) {
   extern __shared__ float sc[];  // [dh / 2][2]: sine and cosine of this token's angles
-  // grid (tokens, head groups): each block takes up to 8 heads of one token, one per warp
   pdl_launch_dependents();
   pdl_wait();
   const int n = blockIdx.x;
@@ -56,26 +58,30 @@ rope_kv_store_kernel(const TI* __restrict__ qkv, int splits, long long split_str
     }
   }
 
-  // Each warp has at most one head.  With the pairs kept in registers its loads are issued first, so that
-  // they are in flight while the block computes the angles' sines and cosines.
-  const int my_head = blockIdx.y * 8 + warp;
+  // With the pairs kept in registers a warp's loads are issued first, so that they are in flight while the
+  // block computes the angles' sines and cosines.
+  const int h0 = blockIdx.y * 8 * HPW + warp;
   const bool in_regs = half <= 32 * ROPE_REG_PAIRS;
-  float va[ROPE_REG_PAIRS], vb[ROPE_REG_PAIRS];
-  if (in_regs && my_head < heads && my_head < Hq + Hkv) {
-    const TI* src = row + (size_t)my_head * dh;
+  float va[HPW][ROPE_REG_PAIRS], vb[HPW][ROPE_REG_PAIRS];
+  if (in_regs) {
 #pragma unroll
-    for (int i = 0; i < ROPE_REG_PAIRS; ++i) {
-      const int j = lane + 32 * i;
-      float a = 0.f, b = 0.f;
-      if (j < half) {
-        for (int z = 0; z < splits; ++z) {
-          const float2 v = load_pair<TI>(src + (size_t)z * split_stride + 2 * j);
-          a += v.x;
-          b += v.y;
+    for (int t = 0; t < HPW; ++t) {
+      const int h = h0 + 8 * t;
+      const TI* src = row + (size_t)h * dh;
+#pragma unroll
+      for (int i = 0; i < ROPE_REG_PAIRS; ++i) {
+        const int j = lane + 32 * i;
+        float a = 0.f, b = 0.f;
+        if (h < heads && j < half) {
+          for (int z = 0; z < splits; ++z) {
+            const float2 v = load_pair<TI>(src + (size_t)z * split_stride + 2 * j);
+            a += v.x;
+            b += v.y;
+          }
         }
+        va[t][i] = a;
+        vb[t][i] = b;
       }
-      va[i] = a;
-      vb[i] = b;
     }
   }
   if (inv_freq) {
@@ -83,11 +89,49 @@ rope_kv_store_kernel(const TI* __restrict__ qkv, int splits, long long split_str
     __syncthreads();
   }
 
-  for (int h = blockIdx.y * 8 + warp; h < min(heads, (int)blockIdx.y * 8 + 8); h += 8) {
+#pragma unroll
+  for (int t = 0; t < HPW; ++t) {
+    const int h = h0 + 8 * t;
+    if (h >= heads) break;
     const TI* src = row + (size_t)h * dh;
-    if (h >= Hq + Hkv) {  // value head: copy (sum of the partials)
-      if (vdst) {
-        T* dst = vdst + (size_t)(h - Hq - Hkv) * page_size * dh;
+    const bool is_v = h >= Hq + Hkv;  // value heads are copied (the sum of the partials): no rotation, no norm
+    T* dst = h < Hq ? q_out + ((size_t)n * Hq + h) * dh
+                    : (is_v ? (vdst ? vdst + (size_t)(h - Hq - Hkv) * page_size * dh : nullptr)
+                            : (kdst ? kdst + (size_t)(h - Hq) * page_size * dh : nullptr));
+    if (in_regs) {
+      // one pass: a lane keeps its pairs in registers between the sum of squares and the write
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < ROPE_REG_PAIRS; ++i) {
+        const int j = lane + 32 * i;
+        if (j < half) {
+          float a = va[t][i], b = vb[t][i];
+          if (inv_freq && !is_v) {
+            const float s = sc[2 * j], c = sc[2 * j + 1];
+            const float ra = a * c - b * s, rb = b * c + a * s;
+            a = ra;
+            b = rb;
+          }
+          ss += a * a + b * b;
+          va[t][i] = a;
+          vb[t][i] = b;
+        }
+      }
+      float inv = 1.f;
+      if (l2norm && !is_v) {
+        ss = warp_sum(ss);
+        inv = 1.f / sqrtf(ss / (float)dh + eps);
+      }
+      if (!dst) continue;
+#pragma unroll
+      for (int i = 0; i < ROPE_REG_PAIRS; ++i) {
+        const int j = lane + 32 * i;
+        if (j < half) store_pair<T>(dst + 2 * j, va[t][i] * inv, vb[t][i] * inv);
+      }
+      continue;
+    }
+    if (is_v) {
+      if (dst) {
         for (int j = lane; j < half; j += 32) {
           float a = 0.f, b = 0.f;
           for (int z = 0; z < splits; ++z) {
@@ -97,39 +141,6 @@ rope_kv_store_kernel(const TI* __restrict__ qkv, int splits, long long split_str
           }
           store_pair<T>(dst + 2 * j, a, b);
         }
-      }
-      continue;
-    }
-    T* dst = h < Hq ? q_out + ((size_t)n * Hq + h) * dh : (kdst ? kdst + (size_t)(h - Hq) * page_size * dh : nullptr);
-    if (in_regs) {
-      // one pass: a lane keeps its pairs in registers between the sum of squares and the write
-      float ss = 0.f;
-#pragma unroll
-      for (int i = 0; i < ROPE_REG_PAIRS; ++i) {
-        const int j = lane + 32 * i;
-        if (j < half) {
-          float a = va[i], b = vb[i];
-          if (inv_freq) {
-            const float s = sc[2 * j], c = sc[2 * j + 1];
-            const float ra = a * c - b * s, rb = b * c + a * s;
-            a = ra;
-            b = rb;
-          }
-          ss += a * a + b * b;
-          va[i] = a;
-          vb[i] = b;
-        }
-      }
-      float inv = 1.f;
-      if (l2norm) {
-        ss = warp_sum(ss);
-        inv = 1.f / sqrtf(ss / (float)dh + eps);
-      }
-      if (!dst) continue;
-#pragma unroll
-      for (int i = 0; i < ROPE_REG_PAIRS; ++i) {
-        const int j = lane + 32 * i;
-        if (j < half) store_pair<T>(dst + 2 * j, va[i] * inv, vb[i] * inv);
       }
       continue;
     }
@@ -186,10 +197,19 @@ JLX_API int jlx_rope_kv_store(const void* qkv, int in_dtype, int splits, long lo
   JLX_REQUIRE((Hq + 2 * Hkv + 7) / 8 <= 65535, "rope_kv_store: too many heads");
   if (N == 0) return 0;
   const size_t smem = (size_t)dh * sizeof(float);
+  const int heads = Hq + 2 * Hkv;
+  // many tokens (prompt portions): four heads per warp; few (decoding): one, for the most blocks
+  const bool wide = N >= 256 && heads > 8;
   JLX_DISPATCH_DTYPE(in_dtype, TI, JLX_DISPATCH_DTYPE(dtype, T, {
-    JLX_CUDA(jlx_launch_pdl(rope_kv_store_kernel<TI, T>, dim3(N, (Hq + 2 * Hkv + 7) / 8), dim3(256), smem, stream,
-                            (const TI*)qkv, splits, split_stride, (T*)q_out, (T*)pages, block_table, bt_stride, req_of_token,
-                            positions, inv_freq, l2norm, eps, Hq, Hkv, dh, page_size, num_pages, store_kv, status));
+    if (wide) {
+      JLX_CUDA(jlx_launch_pdl(rope_kv_store_kernel<TI, T, 4>, dim3(N, (heads + 31) / 32), dim3(256), smem, stream,
+                              (const TI*)qkv, splits, split_stride, (T*)q_out, (T*)pages, block_table, bt_stride, req_of_token,
+                              positions, inv_freq, l2norm, eps, Hq, Hkv, dh, page_size, num_pages, store_kv, status));
+    } else {
+      JLX_CUDA(jlx_launch_pdl(rope_kv_store_kernel<TI, T, 1>, dim3(N, (heads + 7) / 8), dim3(256), smem, stream,
+                              (const TI*)qkv, splits, split_stride, (T*)q_out, (T*)pages, block_table, bt_stride, req_of_token,
+                              positions, inv_freq, l2norm, eps, Hq, Hkv, dh, page_size, num_pages, store_kv, status));
+    }
   }));
   return 0;
 }

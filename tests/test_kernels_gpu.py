@@ -117,6 +117,32 @@ def test_rope_kv_store(dtype, tol, Hq, Hkv, dh, page, rope, l2):
     assert int(st) == 1
 
 
+@pytest.mark.parametrize("dtype, tol", [(torch.float32, 3e-6), (torch.bfloat16, 8e-3)])
+@pytest.mark.parametrize("Hq, Hkv, dh, page, l2", [(40, 8, 128, 64, True), (9, 3, 48, 16, False), (3, 1, 320, 32, True)])
+def test_rope_kv_store_many_tokens(dtype, tol, Hq, Hkv, dh, page, l2):
+    """A prompt portion: 300 tokens of one request from position 70 on (several heads per warp)."""
+    N, eps, first = 300, 1e-5, 70
+    qkv = torch.randn(N, (Hq + 2 * Hkv) * dh, device=DEV).to(dtype)
+    pos = torch.arange(first, first + N, device=DEV, dtype=torch.int32)
+    req = torch.zeros(N, device=DEV, dtype=torch.int32)
+    width = (first + N - 1) // page + 1
+    bt = torch.randperm(width + 3)[:width].to(torch.int32).reshape(1, width).to(DEV)
+    pages = torch.zeros(width + 3, 2, Hkv, page, dh, device=DEV, dtype=dtype)
+    inv_freq = 1.0 / (500000.0 ** (torch.arange(0, dh, 2, device=DEV).float() / dh))
+    q_out, st = torch.full((N, Hq, dh), float("nan"), device=DEV, dtype=dtype), status()
+    K().rope_kv_store(qkv, q_out, pages, bt, req, pos, inv_freq, l2, eps, Hq, Hkv, dh, st)
+    assert int(st) == 0
+    x = qkv.float().reshape(N, Hq + 2 * Hkv, dh)
+    q, k, v = _rope_ref(x[:, :Hq], pos, inv_freq), _rope_ref(x[:, Hq:Hq + Hkv], pos, inv_freq), x[:, Hq + Hkv:]
+    if l2:
+        q = q / torch.sqrt((q * q).mean(-1, keepdim=True) + eps)
+        k = k / torch.sqrt((k * k).mean(-1, keepdim=True) + eps)
+    close(q_out, q, tol)
+    pg, slot = bt[0, (pos // page).long()].long(), (pos % page).long()
+    close(pages[pg, 0, :, slot], k, tol)
+    assert torch.equal(pages[pg, 1, :, slot].float(), v)
+
+
 def _attention_ref(q, k_all, v_all, q_pos, chunk, window, scale, attn_scale, floor_scale):
     """q: [n, Hq, dh] at positions q_pos of one request; k_all, v_all: [S, Hkv, dh] for positions 0..S-1."""
     n, Hq, dh = q.shape
