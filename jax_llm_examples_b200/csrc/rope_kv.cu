@@ -40,25 +40,11 @@ rope_kv_store_kernel(const TI* __restrict__ qkv, int splits, long long split_str
   pdl_wait();
   const int n = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int pos = positions[n];
   const int heads = Hq + 2 * Hkv;
   const int half = dh >> 1;
   const TI* row = qkv + (size_t)n * heads * dh;
-  T* kdst = nullptr;
-  T* vdst = nullptr;
-  if (store_kv) {
-    const int r = req_of_token[n];
-    const int page = block_table[(size_t)r * bt_stride + pos / page_size];
-    if (page < 0 || page >= num_pages) {
-      if (threadIdx.x == 0) atomicOr(status, JLX_STATUS_BAD_PAGE);
-    } else {
-      T* base = pages + (size_t)page * 2 * Hkv * page_size * dh;
-      kdst = base + (size_t)(pos % page_size) * dh;
-      vdst = base + (size_t)Hkv * page_size * dh + (size_t)(pos % page_size) * dh;
-    }
-  }
-
-  // With the pairs kept in registers a warp's loads are issued first, so that they are in flight while the
+  // With the pairs kept in registers a warp's loads are issued first of all: they depend on nothing, and so
+  // are in flight during the chain of dependent loads below (position, request, block table) and while the
   // block computes the angles' sines and cosines.
   const int h0 = blockIdx.y * 8 * HPW + warp;
   const bool in_regs = half <= 32 * ROPE_REG_PAIRS;
@@ -73,7 +59,10 @@ rope_kv_store_kernel(const TI* __restrict__ qkv, int splits, long long split_str
         const int j = lane + 32 * i;
         float a = 0.f, b = 0.f;
         if (h < heads && j < half) {
-          for (int z = 0; z < splits; ++z) {
+          const float2 v0 = load_pair<TI>(src + 2 * j);  // no use of the value yet: the next load follows at once
+          a = v0.x;
+          b = v0.y;
+          for (int z = 1; z < splits; ++z) {
             const float2 v = load_pair<TI>(src + (size_t)z * split_stride + 2 * j);
             a += v.x;
             b += v.y;
@@ -84,6 +73,21 @@ rope_kv_store_kernel(const TI* __restrict__ qkv, int splits, long long split_str
       }
     }
   }
+  const int pos = positions[n];
+  T* kdst = nullptr;
+  T* vdst = nullptr;
+  if (store_kv) {
+    const int r = req_of_token[n];
+    const int page = block_table[(size_t)r * bt_stride + pos / page_size];
+    if (page < 0 || page >= num_pages) {
+      if (threadIdx.x == 0) atomicOr(status, JLX_STATUS_BAD_PAGE);
+    } else {
+      T* base = pages + (size_t)page * 2 * Hkv * page_size * dh;
+      kdst = base + (size_t)(pos % page_size) * dh;
+      vdst = base + (size_t)Hkv * page_size * dh + (size_t)(pos % page_size) * dh;
+    }
+  }
+
   if (inv_freq) {
     for (int j = threadIdx.x; j < half; j += blockDim.x) sincosf((float)pos * inv_freq[j], &sc[2 * j], &sc[2 * j + 1]);
     __syncthreads();
