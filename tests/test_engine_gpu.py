@@ -116,3 +116,37 @@ def test_tied_embeddings(tmp_path, dtype):
     reqs = H.random_requests(random.Random(8), 256, [40, 9])
     got, routing = H.run_trace(eng, H.trace_tail_decode(reqs, 8))
     H.compare_with_plain(folder, reqs, got, routing, dtype)
+
+
+@pytest.mark.parametrize("dtype, tol", [("float32", 1e-5), ("bfloat16", 4e-2)])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
+def test_renumbering_the_experts_changes_nothing(model_dirs, name, dtype, tol):
+    """The same experts under other numbers (router rows and expert matrices permuted alike) are the same
+    model: the sort by expert, the grouped products' tile lists and the combine must not care which number an
+    expert has.  (Only the order in which a token's experts are added may change.)"""
+    import jax_llm_examples_b200 as J
+    from safetensors.torch import load_file
+
+    folder = model_dirs[name]
+    from jax_llm_examples_b200.config import load_config_json
+
+    cfg_json = load_config_json(folder)
+    tensors = load_file(str(folder / "model.safetensors"))
+    E = cfg_json["num_local_experts"]
+    perm = torch.tensor(random.Random(11).sample(range(E), E))
+    assert not torch.equal(perm, torch.arange(E))
+    renumbered = {}
+    for key, t in tensors.items():
+        if key.endswith("feed_forward.router.weight") or ".feed_forward.experts." in key:
+            t = t[perm]
+        renumbered[key] = t
+    reqs = H.random_requests(random.Random(12), VOCAB[name], [70, 33])
+    rows = []
+    for ts in (tensors, renumbered):
+        model = J.model_from_tensors(cfg_json, ts, dtype)
+        eng = J.Engine(model, max_tokens=128, page_size=16, max_slots=2)
+        got, _ = H.run_trace(eng, H.trace_portions(reqs, random.Random(13)))
+        rows.append(got)
+    assert rows[0].keys() == rows[1].keys() and len(rows[0]) > 0
+    worst = max(H.rel_err(rows[1][k], rows[0][k]) for k in rows[0])
+    assert worst < tol, f"{name} {dtype}: relative difference {worst:.2e} after renumbering the experts"
