@@ -165,7 +165,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t q_s = base, k_s = base + TILE_BYTES, v_s = k_s + 2 * TILE_BYTES;
-  // barriers: 0 q_full | 1,2 k_full | 3,4 v_full | 5,6 v_empty | 7,8 s_full | 9,10 unused | 11 p_ready | 12 o_done | 13,14 k_empty |
+  // barriers: 0 q_full | 1,2 k_full | 3,4 v_full | 5,6 v_empty | 7,8 s_full | 9,10 free | 11 p_ready | 12 o_done | 13,14 k_empty |
   // 15..18 the meeting of the two softmax warps of each quarter of the rows
   __shared__ __align__(8) uint64_t bars[19];
   __shared__ uint32_t tmem_slot;
@@ -188,8 +188,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < 9; ++i) mbar_init(BAR(i), 1);
-    mbar_init(BAR(9), 256);
-    mbar_init(BAR(10), 256);
+    mbar_init(BAR(9), 1);
+    mbar_init(BAR(10), 1);
     mbar_init(BAR(11), 256);
     mbar_init(BAR(12), 1);
     mbar_init(BAR(13), 1);

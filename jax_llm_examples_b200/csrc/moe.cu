@@ -48,12 +48,90 @@ __global__ void router_kernel(const float* __restrict__ h, const float* __restri
   }
 }
 
+// Many tokens (prompt portions): a block takes ROWS tokens, so that a router row that a warp fetches serves all
+// of them (one block per token would fetch all E * D weights once per token).  Warp w computes the scores of
+// EPW experts at a time for all the block's rows: per step of 128 columns it loads each row's four values once
+// and each expert's four weights once.  The order of the D products of a (token, expert) pair is fixed by the
+// column alone, so a token's routing does not depend on which tokens share its block.  D % 4 == 0.
+#define ROUTER_ROWS 8
+template <int EPW>
+__global__ void __launch_bounds__(256, 2)
+router_rows_kernel(const float* __restrict__ h, const float* __restrict__ w_router, int* __restrict__ topk_idx,
+                   float* __restrict__ topk_w, int N, int D, int E, int k) {
+  __shared__ float scores[ROUTER_ROWS][ROUTER_MAX_E];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int n0 = blockIdx.x * ROUTER_ROWS;
+  const int rows = min(ROUTER_ROWS, N - n0);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  for (int e0 = warp * EPW; e0 < E; e0 += nwarp * EPW) {
+    float acc[EPW][ROUTER_ROWS];
+#pragma unroll
+    for (int i = 0; i < EPW; ++i)
+#pragma unroll
+      for (int r = 0; r < ROUTER_ROWS; ++r) acc[i][r] = 0.f;
+    // two steps' loads are in flight together: the walk waits on memory, not on arithmetic
+#pragma unroll 2
+    for (int d = lane * 4; d < D; d += 128) {
+      float4 xv[ROUTER_ROWS], wv[EPW];
+#pragma unroll
+      for (int r = 0; r < ROUTER_ROWS; ++r)
+        xv[r] = r < rows ? *reinterpret_cast<const float4*>(h + (size_t)(n0 + r) * D + d) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int i = 0; i < EPW; ++i)
+        wv[i] = e0 + i < E ? *reinterpret_cast<const float4*>(w_router + (size_t)(e0 + i) * D + d) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int i = 0; i < EPW; ++i)
+#pragma unroll
+        for (int r = 0; r < ROUTER_ROWS; ++r)
+          acc[i][r] = fmaf(xv[r].x, wv[i].x, fmaf(xv[r].y, wv[i].y, fmaf(xv[r].z, wv[i].z, fmaf(xv[r].w, wv[i].w, acc[i][r]))));
+    }
+#pragma unroll
+    for (int i = 0; i < EPW; ++i)
+#pragma unroll
+      for (int r = 0; r < ROUTER_ROWS; ++r) {
+        const float s = warp_sum(acc[i][r]);
+        if (lane == 0 && e0 + i < E) scores[r][e0 + i] = s;
+      }
+  }
+  __syncthreads();
+  if (threadIdx.x < rows) {
+    float* sc = scores[threadIdx.x];
+    const size_t n = (size_t)n0 + threadIdx.x;
+    for (int j = 0; j < k; ++j) {
+      int best = -1;
+      float bv = 0.f;
+      for (int e = 0; e < E; ++e) {
+        const float v = sc[e];
+        if (isnan(v)) continue;
+        if (best < 0 || v > bv) {  // strict: the lower index wins a tie
+          best = e;
+          bv = v;
+        }
+      }
+      if (best < 0) best = j;  // all NaN: still a valid expert index
+      topk_idx[n * k + j] = best;
+      topk_w[n * k + j] = 1.f / (1.f + expf(-bv));
+      sc[best] = NAN;  // taken
+    }
+  }
+}
+
+// many_rows: the kernel that shares router rows among eight tokens (another order of the sums than the
+// one-token kernel's: a caller whose results must not depend on the batch uses one of the two throughout).
 JLX_API int jlx_router(const float* h, const float* w_router, int* topk_idx, float* topk_w, float* scores_out, int N,
-                       int D, int E, int k, cudaStream_t stream) {
+                       int D, int E, int k, int many_rows, cudaStream_t stream) {
   JLX_REQUIRE(N >= 0 && D > 0, "router: bad sizes N=%d D=%d", N, D);
   JLX_REQUIRE(E >= 1 && E <= ROUTER_MAX_E, "router: %d experts; supported 1..%d", E, ROUTER_MAX_E);
   JLX_REQUIRE(k >= 1 && k <= E && k <= ROUTER_MAX_K, "router: top-%d of %d experts; supported k in 1..min(E, %d)", k, E, ROUTER_MAX_K);
   if (N == 0) return 0;
+  if (many_rows && !scores_out && D % 4 == 0 && (((uintptr_t)h | (uintptr_t)w_router) & 15) == 0) {
+    const dim3 grid((N + ROUTER_ROWS - 1) / ROUTER_ROWS);
+    if (E <= 16) JLX_CUDA(jlx_launch_pdl(router_rows_kernel<2>, grid, dim3(256), 0, stream, h, w_router, topk_idx, topk_w, N, D, E, k));
+    else JLX_CUDA(jlx_launch_pdl(router_rows_kernel<4>, grid, dim3(256), 0, stream, h, w_router, topk_idx, topk_w, N, D, E, k));
+    JLX_LAUNCH_CHECK("router_rows");
+    return 0;
+  }
   router_kernel<<<N, 256, 0, stream>>>(h, w_router, topk_idx, topk_w, scores_out, D, E, k);
   JLX_LAUNCH_CHECK("router");
   return 0;

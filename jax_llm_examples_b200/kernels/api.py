@@ -310,14 +310,17 @@ def gemm_stream(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: tor
 
 # --------------------------------------------------------------------------------------- MoE
 def router(h32: torch.Tensor, w_router: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tensor,
-           scores_out: torch.Tensor | None = None) -> None:
+           scores_out: torch.Tensor | None = None, many_rows: bool = False) -> None:
+    """Scores h32 @ w_router^T in 32-bit, top-k of the raw scores (lower index wins ties), weight = sigmoid.
+    ``many_rows``: the kernel that shares each router row among eight tokens (for prompt portions; its sums
+    run in another order than the one-token kernel's)."""
     _contig(h32, w_router, topk_idx, topk_w, scores_out)
     N, D = h32.shape
     E, k = w_router.shape[0], topk_idx.shape[1]
     if h32.dtype != torch.float32 or w_router.dtype != torch.float32:
         raise KernelError("router: scores are computed from float32 input and weight")
     _run("moe", "jlx_router", _ptr(h32), _ptr(w_router), _ptr(topk_idx), _ptr(topk_w), _ptr(scores_out), c_int(N),
-         c_int(D), c_int(E), c_int(k), _stream())
+         c_int(D), c_int(E), c_int(k), c_int(int(many_rows)), _stream())
 
 
 def expert_sort(topk_idx: torch.Tensor, offsets: torch.Tensor, sorted_pair: torch.Tensor, sorted_pos: torch.Tensor,

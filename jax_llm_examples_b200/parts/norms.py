@@ -15,6 +15,7 @@ class RMSNorm(Norm):
 
     kernel_libraries = ("elementwise",)
     fuses_router = True
+    FUSED_ROUTER_MAX_ROWS = 64  # above this many rows (bfloat16) the router runs as its own many-rows kernel
 
     def __init__(self, weight: torch.Tensor | None, eps: float):
         self.weight = None if weight is None else weight.to(torch.float32).contiguous()
@@ -28,13 +29,22 @@ class RMSNorm(Norm):
         d = as_rows(delta)
         routing = None
         w_router = idx = wt = None
+        unfused = False
         if router is not None and x.shape[1] <= 16384:
             w_router, k = router
             idx = torch.empty((n, k), dtype=torch.int32, device=dev)
             wt = torch.empty((n, k), dtype=torch.float32, device=dev)
             routing = (idx, wt)
+            # Prompt portions in bfloat16: the router as a kernel of its own that shares each router row among
+            # eight tokens (the fused kernel would fetch all router weights once per token).  The 32-bit path
+            # keeps the fused kernel at every size: its sums must not depend on the batch.
+            unfused = out_dtype == torch.bfloat16 and n > self.FUSED_ROUTER_MAX_ROWS and x.shape[1] % 4 == 0
+            if unfused and out32 is None:
+                out32 = torch.empty((n, x.shape[1]), dtype=torch.float32, device=dev)
         K.add_rmsnorm(x, None if d is None else d.data, self.weight, self.eps, out, out32, row_index,
-                      1 if d is None else d.splits, w_router, idx, wt)
+                      1 if d is None else d.splits, None if unfused else w_router, idx, wt)
+        if unfused:
+            K.router(out32, w_router, idx, wt, many_rows=True)
         return out, out32, routing
 
 

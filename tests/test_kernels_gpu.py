@@ -311,6 +311,24 @@ def test_router_and_sort(N, D, E, k):
     assert torch.equal(pos.long()[pair.long()], torch.arange(N * k, device=DEV)) and int(st) == 0
 
 
+@pytest.mark.parametrize("N, D, E, k", [(301, 5120, 16, 1), (70, 96, 8, 2), (1000, 200, 128, 4), (9, 64, 3, 3)])
+def test_router_for_many_rows(N, D, E, k):
+    """The kernel that shares each router row among eight tokens: the same choices as float64 makes, except
+    where two scores tie to within 32-bit rounding; ties still go to the lower expert."""
+    h, w = torch.randn(N, D, device=DEV), torch.randn(E, D, device=DEV)
+    h[3] = 0.0  # every score of this token ties
+    idx, wt = torch.full((N, k), -1, device=DEV, dtype=torch.int32), torch.empty(N, k, device=DEV)
+    K().router(h, w, idx, wt, many_rows=True)
+    torch.cuda.synchronize()
+    scores = h.double() @ w.double().T
+    order = torch.sort(scores, dim=-1, descending=True, stable=True)
+    chosen = torch.gather(scores, 1, idx.long())
+    assert float((order.values[:, :k] - chosen).abs().max()) < 1e-4 * float(scores.abs().max())
+    close(wt, torch.sigmoid(chosen), 1e-5)
+    assert idx[3].tolist() == list(range(k))
+    assert all(len(set(row)) == k for row in idx.tolist())
+
+
 def test_router_tie_goes_to_the_lower_expert():
     h = torch.zeros(2, 32, device=DEV)
     h[:, 0] = 1
