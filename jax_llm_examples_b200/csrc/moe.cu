@@ -147,16 +147,23 @@ JLX_API int jlx_router(const float* h, const float* w_router, int* topk_idx, flo
 // so that a product's blocks find their work with one load instead of a walk over the offsets.
 __global__ void expert_sort_kernel(const int* __restrict__ topk_idx, int* __restrict__ offsets,
                                    int* __restrict__ sorted_pair, int* __restrict__ sorted_pos, int P, int E, int extra_rows,
-                                   int tile_rows, int* __restrict__ tile_list, int* __restrict__ n_tiles, int* status) {
+                                   int tile_rows, int* __restrict__ tile_list, int* __restrict__ n_tiles, int* status,
+                                   int in_smem) {
   __shared__ int counts[ROUTER_MAX_E + 1];
+  extern __shared__ int staged[];  // the choices, when `in_smem`: both passes below walk them once per expert
   pdl_launch_dependents();
   pdl_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  if (in_smem) {
+    for (int i = threadIdx.x; i < P; i += blockDim.x) staged[i] = topk_idx[i];
+    __syncthreads();
+  }
+  const int* choice = in_smem ? staged : topk_idx;
   for (int e = warp; e < E; e += nwarp) {
     int c = 0;
     for (int base = 0; base < P; base += 32) {
       const int i = base + lane;
-      const int v = i < P ? topk_idx[i] : -1;
+      const int v = i < P ? choice[i] : -1;
       c += __popc(__ballot_sync(0xffffffffu, v == e));
     }
     if (lane == 0) counts[e] = c;
@@ -178,7 +185,7 @@ __global__ void expert_sort_kernel(const int* __restrict__ topk_idx, int* __rest
       int t = 0;
       const int groups = extra_rows > 0 ? E + 1 : E;
       for (int e = 0; e < groups; ++e) {
-        const int lo = offsets[e], hi = offsets[e + 1];
+        const int lo = counts[e], hi = e < E ? counts[e + 1] : run + extra_rows;
         for (int r = lo; r < hi; r += tile_rows) {
           tile_list[2 * t] = e;
           tile_list[2 * t + 1] = r;
@@ -193,7 +200,7 @@ __global__ void expert_sort_kernel(const int* __restrict__ topk_idx, int* __rest
     int at = counts[e];
     for (int base = 0; base < P; base += 32) {
       const int i = base + lane;
-      const int v = i < P ? topk_idx[i] : -1;
+      const int v = i < P ? choice[i] : -1;
       const unsigned mask = __ballot_sync(0xffffffffu, v == e);
       if (v == e) {
         const int dst = at + __popc(mask & ((1u << lane) - 1u));
@@ -211,8 +218,9 @@ JLX_API int jlx_expert_sort(const int* topk_idx, int* offsets, int* sorted_pair,
   JLX_REQUIRE(tile_rows == 0 || (tile_list && n_tiles), "expert_sort: tile list outputs missing");
   JLX_REQUIRE(P >= 0 && E >= 1 && E <= ROUTER_MAX_E && extra_rows >= 0, "expert_sort: bad sizes P=%d E=%d", P, E);
   const int warps = E < 32 ? E : 32;
-  JLX_CUDA(jlx_launch_pdl(expert_sort_kernel, dim3(1), dim3(warps * 32), 0, stream, topk_idx, offsets, sorted_pair, sorted_pos, P, E,
-                          extra_rows, tile_rows, tile_list, n_tiles, status));
+  const int in_smem = (size_t)P * sizeof(int) <= 40 * 1024;
+  JLX_CUDA(jlx_launch_pdl(expert_sort_kernel, dim3(1), dim3(warps * 32), in_smem ? (size_t)P * sizeof(int) : 0, stream, topk_idx,
+                          offsets, sorted_pair, sorted_pos, P, E, extra_rows, tile_rows, tile_list, n_tiles, status, in_smem));
   return 0;
 }
 
