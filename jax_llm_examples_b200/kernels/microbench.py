@@ -99,23 +99,27 @@ def gemm(a) -> dict:
     x = torch.randn(a.rows, a.k, device=dev).bfloat16()
     E = a.experts
     w = (torch.randn(max(E, 1), a.n, a.k, device=dev) * 0.05).bfloat16()
-    offsets, used = None, 1
+    offsets, used, tiles = None, 1, None
+    hint = a.hint or (min(a.rows, 2 * -(-a.rows // E)) if E else 0)
     if E:
+        # rows spread over the groups at random; the sort kernel gives the offsets and, as in the engine, the
+        # list of row tiles that hold rows
         rng = random.Random(0)
-        counts = [0] * E
-        for _ in range(a.rows):
-            counts[rng.randrange(E)] += 1
-        offsets = torch.tensor([0] + list(torch.tensor(counts).cumsum(0)), device=dev, dtype=torch.int32)
-        used = sum(1 for c in counts if c)
+        choice = torch.tensor([rng.randrange(E) for _ in range(a.rows)], device=dev, dtype=torch.int32).view(-1, 1)
+        offsets = torch.empty(E + 1, device=dev, dtype=torch.int32)
+        pair, pos = torch.empty(a.rows, device=dev, dtype=torch.int32), torch.empty(a.rows, device=dev, dtype=torch.int32)
+        tile_rows = K.gemm_stream_token_tile(hint)
+        tiles = (torch.empty(2 * (-(-a.rows // tile_rows) + E), device=dev, dtype=torch.int32), torch.empty(1, device=dev, dtype=torch.int32))
+        K.expert_sort(choice, offsets, pair, pos, E, status, 0, tile_rows, *tiles)
+        used = int((offsets[1:] > offsets[:-1]).sum())
     else:
         w = w[0]
     mode = K.GEMM_SWIGLU if a.swiglu else K.GEMM_PLAIN
     out = torch.empty(a.rows, a.n // 2 if a.swiglu else a.n, device=dev, dtype=torch.bfloat16 if a.swiglu else torch.float32)
     scratch = torch.empty(a.splits * a.rows * a.n, device=dev) if a.splits > 1 else None
-    hint = a.hint or (min(a.rows, 2 * -(-a.rows // E)) if E else 0)
 
     def run():
-        K.gemm_stream(x, w, out, status, offsets=offsets, rows_hint=hint, splits=a.splits, scratch=scratch, mode=mode)
+        K.gemm_stream(x, w, out, status, offsets=offsets, rows_hint=hint, splits=a.splits, scratch=scratch, mode=mode, tiles=tiles)
 
     t = _time(run, a.reps, _flush(a))
     nbytes = used * a.n * a.k * 2 + a.rows * a.k * 2 + out.numel() * out.element_size()
