@@ -55,6 +55,10 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     if (mbar_try_wait(bar, parity)) return true;
   return false;
 }
+// Fetches a tensor map's descriptor ahead of its first use by a copy.
+__device__ __forceinline__ void prefetch_map(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
@@ -252,6 +256,10 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   pdl_launch_dependents();
+  if (threadIdx.x == 0) {
+    prefetch_map(&map_w);
+    prefetch_map(&map_a);
+  }
 
   // ---- which tile.  The group offsets are written by an earlier kernel of the stream: wait for it first.
   int row_lo, row_hi, group = 0;
@@ -398,6 +406,10 @@ gemm_stream_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_rank();  // 0 or 1: blockIdx.x is even or odd
   pdl_launch_dependents();
+  if (threadIdx.x == 0) {
+    prefetch_map(&map_w);
+    prefetch_map(&map_a);
+  }
 
   // ---- which tile (both blocks of a pair have the same blockIdx.y and decide alike)
   int row_lo, row_hi, group = 0;
