@@ -265,6 +265,31 @@ def run_ours(args) -> dict:
         eng.finish(s)
     pre = sorted(pre_ms)[len(pre_ms) // 2] if pre_ms else float("nan")
     flops = _prefill_flops(cfg, T)
+    del g, eng
+    torch.cuda.empty_cache()
+
+    # a mixed step: the batch's decoded tokens beside one T-token prompt portion, in one step
+    if not args.skip_points and not args.skip_prefill:
+        g = J.Generator(model, max_tokens=batch * ctx_len + T + page, page_size=page, max_slots=batch + 1,
+                        max_tokens_per_step=T + batch, max_seq_len=ctx_len)
+        eng = g.engine
+        slots = [eng.new_request() for _ in range(batch)]
+        _fill_cache(eng, slots, ctx_len - 16, gen)
+        mixed_ms = []
+        for it in range(3 + 3):
+            s = eng.new_request()
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ev0.record()
+            eng.step([J.StepEntry(x, [rng.randrange(cfg.vocab_size)], [0]) for x in slots] + [J.StepEntry(s, prompt, [T - 1])])
+            ev1.record()
+            torch.cuda.synchronize()
+            if it >= 3:
+                mixed_ms.append(ev0.elapsed_time(ev1))
+            eng.finish(s)
+        eng.check_status()
+        points[f"mixed_b{batch}_plus_{T}_ms"] = round(sorted(mixed_ms)[len(mixed_ms) // 2], 3)
+        del g, eng
+        torch.cuda.empty_cache()
 
     tok_s = batch / (main["ms"] / 1e3)
     achieved = main["bytes"] / (main["ms"] / 1e3) / 1e9

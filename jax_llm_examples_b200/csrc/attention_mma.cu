@@ -102,6 +102,7 @@ struct AttnParams {
   float* part_o;        // [N, Hq, max_splits, DH]
   float* part_ml;       // [N, Hq, max_splits, 2]
   int max_splits;
+  const int* rows;      // optional, decode: the token rows to work on (null: rows 0..N-1); partials are indexed by the list's order
   int split_keys;       // keys per decode split (a multiple of SPLIT_UNIT)
 };
 
@@ -158,7 +159,7 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttnParams 
   constexpr int CH = DH / 8;
   bf16* ks = reinterpret_cast<bf16*>(smem);                  // [DEC_STAGES][KT][DH]
   bf16* vs = ks + DEC_STAGES * KT * DH;                      // [DEC_STAGES][KT][DH]
-  const int n = blockIdx.z, hk = blockIdx.y, split = blockIdx.x;
+  const int slot = blockIdx.z, n = P.rows ? P.rows[slot] : slot, hk = blockIdx.y, split = blockIdx.x;
   const int G = P.Hq / P.Hkv;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int p = P.positions[n], r = P.req_of_token[n];
@@ -298,7 +299,7 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttnParams 
       acc += red[(w * 16 + g) * LD + d] * f;
       ll += red[(w * 16 + g) * LD + DH + 1] * f;
     }
-    const size_t row = ((size_t)n * P.Hq + hk * G + g) * P.max_splits + split;
+    const size_t row = ((size_t)slot * P.Hq + hk * G + g) * P.max_splits + split;
     P.part_o[row * DH + d] = acc;
     if (d == 0) {
       P.part_ml[row * 2] = mm;
@@ -325,7 +326,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map, const AttnP
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   pdl_launch_dependents();
   pdl_wait();
-  const int n = blockIdx.z, hk = blockIdx.y, split = blockIdx.x;
+  const int slot = blockIdx.z, n = P.rows ? P.rows[slot] : slot, hk = blockIdx.y, split = blockIdx.x;
   const int G = P.Hq / P.Hkv;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int p = P.positions[n], r = P.req_of_token[n];
@@ -506,7 +507,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map, const AttnP
       acc += red[(w * 16 + g) * LD + d] * f;
       ll += red[(w * 16 + g) * LD + DH + 1] * f;
     }
-    const size_t row = ((size_t)n * P.Hq + hk * G + g) * P.max_splits + split;
+    const size_t row = ((size_t)slot * P.Hq + hk * G + g) * P.max_splits + split;
     P.part_o[row * DH + d] = acc;
     if (d == 0) {
       P.part_ml[row * 2] = mm;
@@ -524,11 +525,11 @@ __global__ void attention_combine_kernel(const AttnParams P) {
   __shared__ float ms[COMBINE_CACHE], wgt[COMBINE_CACHE];
   pdl_launch_dependents();
   pdl_wait();
-  const int n = blockIdx.x, h = blockIdx.y;
+  const int slot = blockIdx.x, n = P.rows ? P.rows[slot] : slot, h = blockIdx.y;
   const int p = P.positions[n];
   const int lo = first_key(p, P.chunk, P.window);
   const int splits = p / P.split_keys - lo / P.split_keys + 1;
-  const size_t row = ((size_t)n * P.Hq + h) * P.max_splits;
+  const size_t row = ((size_t)slot * P.Hq + h) * P.max_splits;
   const float2* ml = reinterpret_cast<const float2*>(P.part_ml) + row;
   const bool cached = splits <= COMBINE_CACHE;
   float mm = NEG_BIG, ll = 0.f;
@@ -908,7 +909,7 @@ static int fill_params(AttnParams& P, const void* q, const void* pages, const in
   P.req_of_token = req_of_token; P.positions = positions; P.out = (bf16*)out; P.Hq = Hq; P.Hkv = Hkv;
   P.page_size = page_size; P.num_pages = num_pages; P.scale_log2 = scale * 1.4426950408889634f;
   P.chunk = chunk; P.window = window; P.attn_scale = attn_scale; P.floor_scale = floor_scale; P.status = status;
-  P.tiles = nullptr; P.part_o = nullptr; P.part_ml = nullptr; P.max_splits = 0; P.split_keys = SPLIT_UNIT;
+  P.tiles = nullptr; P.part_o = nullptr; P.part_ml = nullptr; P.max_splits = 0; P.split_keys = SPLIT_UNIT; P.rows = nullptr;
   return 0;
 }
 
@@ -972,11 +973,13 @@ JLX_API int jlx_attention_decode_splits(int max_kv_len, int chunk, int window, i
 }
 
 // One query token per request.  part_o: float [N * Hq * max_splits * dh]; part_ml: float [N * Hq * max_splits * 2].
+// rows (optional): int [N], the token rows of q / positions / req_of_token / out to work on (a step that mixes
+// prompt portions with decoded tokens sends only the latter here); null: rows 0..N-1.
 JLX_API int jlx_attention_decode(const void* q, const void* pages, const int* block_table, int bt_stride,
                                  const int* req_of_token, const int* positions, void* out, int N, int Hq, int Hkv, int dh,
                                  int page_size, int num_pages, float scale, int chunk, int window, float attn_scale,
                                  float floor_scale, float* part_o, float* part_ml, int max_splits, int split_keys,
-                                 int* status, cudaStream_t stream) {
+                                 const int* rows, int* status, cudaStream_t stream) {
   AttnParams P;
   if (fill_params(P, q, pages, block_table, bt_stride, req_of_token, positions, out, Hq, Hkv, dh, page_size, num_pages,
                   scale, chunk, window, attn_scale, floor_scale, status)) return 1;
@@ -985,7 +988,7 @@ JLX_API int jlx_attention_decode(const void* q, const void* pages, const int* bl
   JLX_REQUIRE(split_keys > 0 && split_keys % SPLIT_UNIT == 0, "attention_decode: split size %d is no multiple of %d", split_keys, SPLIT_UNIT);
   JLX_REQUIRE(N <= 65535 && Hkv <= 65535, "attention_decode: too many rows");
   if (N == 0) return 0;
-  P.part_o = part_o; P.part_ml = part_ml; P.max_splits = max_splits; P.split_keys = split_keys;
+  P.part_o = part_o; P.part_ml = part_ml; P.max_splits = max_splits; P.split_keys = split_keys; P.rows = rows;
   const size_t smem = (size_t)2 * DEC_STAGES * KT * dh * 2;
   dim3 grid(max_splits, Hkv, N);
   // pages that hold whole 64-key tiles, or divide them, go through TMA; other page sizes through cp.async

@@ -157,8 +157,8 @@ class Engine:
         # a graph's descriptor is laid out for the longest request the engine allows, so that it fits every replay
         width = self.max_pages_per_request if static else -(-max_kv // self.page_size)
         packed = CacheManager.packed_size(G, N, R, M, width)
-        # query tiles for the flash kernel: up to 16 consecutive tokens of one request
-        tiles = tiles_big = tiles_rest = None
+        # query tiles for the flash kernels: up to 16 consecutive tokens of one request that brings several
+        tiles = tiles_big = tiles_rest = single_rows = None
         if int(n_tok.max()) > 1:
             firsts = np.concatenate([[0], np.cumsum(n_tok)[:-1]])
 
@@ -167,10 +167,12 @@ class Engine:
                 # late tiles of a causal prompt read the most keys: launch them first so that the tail is short
                 return np.ascontiguousarray(np.array(t, dtype=np.int32).reshape(-1, 2)[::-1])
 
-            tiles = cut_tiles(16, lambda n: True)
+            tiles = cut_tiles(16, lambda n: n > 1)
             tiles_big = cut_tiles(128, lambda n: n >= 64)
-            tiles_rest = cut_tiles(16, lambda n: n < 64)
-        extra = [t for t in (tiles, tiles_big, tiles_rest) if t is not None]
+            tiles_rest = cut_tiles(16, lambda n: 1 < n < 64)
+            # requests that bring a single (decoded) token beside the portions: their rows, for the split-KV kernel
+            single_rows = np.ascontiguousarray(firsts[n_tok == 1].astype(np.int32))
+        extra = [t for t in (tiles, tiles_big, tiles_rest, single_rows) if t is not None]
         size = packed + sum(t.size for t in extra)
         host, ring_i = self._ring.next(size)
         host_np = host.numpy()
@@ -216,6 +218,7 @@ class Engine:
                 ctx.attn_tiles, ctx.n_attn_tiles = cut(tiles.size).view(-1, 2), tiles.shape[0]
                 ctx.attn_tiles_big, ctx.n_attn_tiles_big = cut(tiles_big.size).view(-1, 2), tiles_big.shape[0]
                 ctx.attn_tiles_rest, ctx.n_attn_tiles_rest = cut(tiles_rest.size).view(-1, 2), tiles_rest.shape[0]
+                ctx.attn_single_rows, ctx.n_attn_single_rows = cut(single_rows.size), single_rows.shape[0]
             if self.record_routing:
                 ctx.scratch["record_routing"] = []
             if static:

@@ -198,18 +198,22 @@ def attention_decode_plan(max_kv_len: int, chunk: int, window: int, pairs: int) 
 def attention_decode(q: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor, req_of_token: torch.Tensor,
                      positions: torch.Tensor, out: torch.Tensor, scale: float, chunk: int, window: int, attn_scale: float,
                      floor_scale: float, part_o: torch.Tensor, part_ml: torch.Tensor, max_splits: int, split_keys: int,
-                     status: torch.Tensor) -> None:
+                     status: torch.Tensor, rows: torch.Tensor | None = None, n_rows: int = 0) -> None:
     """Split-KV attention for one query token per request (tensor cores, bfloat16).
-    part_o: float32 [N * Hq * max_splits * dh]; part_ml: float32 [N * Hq * max_splits * 2]."""
-    _contig(q, pages, block_table, out, part_o, part_ml)
+    part_o: float32 [N * Hq * max_splits * dh]; part_ml: float32 [N * Hq * max_splits * 2].
+    rows / n_rows: work on these token rows only (int32, the first n_rows entries): the single decoded tokens of
+    a step that also holds prompt portions; N is then n_rows."""
+    _contig(q, pages, block_table, out, part_o, part_ml, rows)
     N, Hq, dh = q.shape
+    if rows is not None:
+        N = n_rows
     P, _, Hkv, page_size, _ = pages.shape
     if part_o.numel() < N * Hq * max_splits * dh or part_ml.numel() < N * Hq * max_splits * 2:
         raise KernelError("attention_decode: scratch for the partial results is too small")
     _run("attention_mma", "jlx_attention_decode", _ptr(q), _ptr(pages), _ptr(block_table), c_int(block_table.shape[1]),
          _ptr(req_of_token), _ptr(positions), _ptr(out), c_int(N), c_int(Hq), c_int(Hkv), c_int(dh), c_int(page_size),
          c_int(P), c_float(scale), c_int(chunk), c_int(window), c_float(attn_scale), c_float(floor_scale), _ptr(part_o),
-         _ptr(part_ml), c_int(max_splits), c_int(split_keys), _ptr(status), _stream())
+         _ptr(part_ml), c_int(max_splits), c_int(split_keys), _ptr(rows), _ptr(status), _stream())
 
 
 def attention_prefill(q: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor, req_of_token: torch.Tensor,

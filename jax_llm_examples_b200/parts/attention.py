@@ -68,23 +68,33 @@ class PagedAttention(Mixer):
         self.attend(ctx, q, cache, out, attn_scale, floor_scale)
         return linear(ctx, out.view(q.shape[0], -1), self.w_o, torch.float32, partials=True)
 
+    def _split_kv(self, ctx: StepContext, q, cache: LayerCache, out, attn_scale, floor_scale, rows, n_rows: int) -> None:
+        """Split-KV attention for requests that bring one token: all rows of q, or the listed ones."""
+        chunk, window = self.chunk or 0, self.window or 0
+        split_keys, splits = K.attention_decode_plan(ctx.max_kv_len, chunk, window, n_rows * self.n_kv_heads)
+        n = n_rows * self.n_heads * splits
+        part_o = ctx.workspace.get("attn_part_o", n * self.head_dim, torch.float32)
+        part_ml = ctx.workspace.get("attn_part_ml", n * 2, torch.float32)
+        K.attention_decode(q, cache.pages, cache.block_table, ctx.req_of_token, ctx.positions, out, self.scale,
+                           chunk, window, attn_scale, floor_scale, part_o, part_ml, splits, split_keys, ctx.status,
+                           rows, n_rows)
+
     def attend(self, ctx: StepContext, q, cache: LayerCache, out, attn_scale: float, floor_scale: float) -> None:
-        """Tensor-core kernels where they are built (bfloat16, head size 64 or 128, small groups): split-KV
-        when every request brings one token, flash tiles otherwise; the generic kernel for the rest."""
+        """Tensor-core kernels where they are built (bfloat16, head size 64 or 128, small groups): split-KV for
+        requests that bring one token, flash tiles for the others (tcgen05 for long portions of head size 128);
+        the generic kernel where those are not built."""
         chunk, window = self.chunk or 0, self.window or 0
         decode = ctx.max_q_len == 1
         if self.head_dim in self.MMA_HEAD_SIZES and K.attention_mma_supported(q.dtype, self.n_heads, self.n_kv_heads,
                                                                               self.head_dim, decode):
             if decode:
-                split_keys, splits = K.attention_decode_plan(ctx.max_kv_len, chunk, window, q.shape[0] * self.n_kv_heads)
-                n = q.shape[0] * self.n_heads * splits
-                part_o = ctx.workspace.get("attn_part_o", n * self.head_dim, torch.float32)
-                part_ml = ctx.workspace.get("attn_part_ml", n * 2, torch.float32)
-                K.attention_decode(q, cache.pages, cache.block_table, ctx.req_of_token, ctx.positions, out, self.scale,
-                                   chunk, window, attn_scale, floor_scale, part_o, part_ml, splits, split_keys, ctx.status)
+                self._split_kv(ctx, q, cache, out, attn_scale, floor_scale, None, q.shape[0])
                 return
             if ctx.attn_tiles is not None:
-                tiles, n_tiles = ctx.attn_tiles, ctx.n_attn_tiles
+                if ctx.n_attn_single_rows:
+                    # the single decoded tokens of a mixed step go to the split-KV kernel, by their row list
+                    self._split_kv(ctx, q, cache, out, attn_scale, floor_scale, ctx.attn_single_rows, ctx.n_attn_single_rows)
+                tiles, n_tiles = ctx.attn_tiles, ctx.n_attn_tiles  # every request that brings more than one token
                 if ctx.n_attn_tiles_big and self.head_dim in self.TC_HEAD_SIZES and K.attention_prefill_tc_supported(
                         q.dtype, self.n_heads, self.n_kv_heads, self.head_dim, cache.pages.shape[3]):
                     # long portions on the tcgen05 kernel (128-token tiles), the short ones below

@@ -126,14 +126,17 @@ class StepContext:
     max_kv_len: int = 0
     scratch: dict[str, Any] = dataclasses.field(default_factory=dict)  # per-step memo shared by parts
     workspace: Workspace | None = None  # buffers that outlive the step
-    attn_tiles: torch.Tensor | None = None  # int32 [n, 2]: (first token row, count <= 16) tiles of one request each
+    attn_tiles: torch.Tensor | None = None  # int32 [n, 2]: (first token row, count <= 16) tiles of the requests that bring several tokens
     n_attn_tiles: int = 0
-    # the same tokens cut for kernels with 128-row tiles: requests that bring at least 64 tokens in tiles of up
-    # to 128, and the 16-token tiles of the remaining requests
+    # the same tokens cut three ways for a mixer with several kernels: requests that bring at least 64 tokens in
+    # tiles of up to 128; requests that bring 2..63 tokens in tiles of up to 16; and the token rows of the
+    # requests that bring a single token (int32 [n]), which a split-KV kernel serves best
     attn_tiles_big: torch.Tensor | None = None
     n_attn_tiles_big: int = 0
     attn_tiles_rest: torch.Tensor | None = None
     n_attn_tiles_rest: int = 0
+    attn_single_rows: torch.Tensor | None = None
+    n_attn_single_rows: int = 0
 
 
 BF16_ONLY_LIBRARIES = ("gemm_stream", "attention_mma", "attention_tc")

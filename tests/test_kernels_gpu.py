@@ -429,6 +429,15 @@ def test_attention_decode_mma(Hq, Hkv, dh, page, chunk, window, temp):
         for r in range(len(lens)):
             ref = _attention_ref(q[r:r + 1], ks[r], vs[r], pos[r:r + 1].long(), chunk, window, dh ** -0.5, attn_scale, floor_scale)
             close(out[r:r + 1], ref, 1.5e-2)
+        # some of the rows only, by a list (the decoded tokens of a step that also holds prompt portions): the
+        # same results in those rows, the others untouched
+        rows = torch.tensor([4, 0, 3], device=DEV, dtype=torch.int32)
+        out2 = torch.full_like(out, 7.0)
+        api.attention_decode(q, pages, bt, req, pos, out2, dh ** -0.5, chunk, window, attn_scale, floor_scale, part_o, part_ml,
+                             splits, keys, st, rows, 3)
+        assert int(st) == 0
+        assert torch.equal(out2[rows.long()], out[rows.long()])
+        assert bool((out2[[1, 2, 5]] == 7.0).all())
 
 
 @pytest.mark.parametrize("Hq, Hkv, dh, page, chunk, window, temp", [
