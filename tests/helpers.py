@@ -191,10 +191,12 @@ def run_trace(engine, steps):
 # A router score is a logit of the layer's hidden state, so it carries the error a logit carries, and a choice
 # compares two of them.  A difference below this fraction of the layer's typical score (RMS over the sequence)
 # is therefore a tie that either precision may break either way: in bfloat16 the bound of a logit (TOL); in
-# float32, where sums of D products differ by ~1e-6 relative, half of it.  Ties are rare: at most TIE_SHARE of
-# all choices of a comparison may differ from the plain implementation's own.
+# float32, where sums of D products differ by ~1e-6 relative, half of it.  How many choices fall into that band
+# depends on the number of experts (with 40 experts and top-1, 1.1 % were seen; with 4 to 16, under 0.5 %); a
+# fault in the routing itself (a wrong expert table, a wrong tie rule) changes tens of percent: the share of
+# differing choices is capped well between the two.
 TIE = {"float32": 1e-5, "bfloat16": TOL["bfloat16"]}
-TIE_SHARE = 0.01
+TIE_SHARE = 0.05
 
 
 def compare_with_plain(model_dir, requests, got, routing, dtype: str):
