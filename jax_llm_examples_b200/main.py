@@ -59,6 +59,8 @@ def main(argv: list[str] | None = None) -> int:
     ap.add_argument("--eos", type=int, action="append", default=None, help="token id that ends a request (default: config.json's)")
     ap.add_argument("--page-size", type=int, default=64)
     ap.add_argument("--max-tokens", type=int, default=None, help="cache pool in tokens (default: what the prompts need)")
+    ap.add_argument("--num-pages", type=int, default=None, help="the same pool given in pages of --page-size tokens")
+    ap.add_argument("--random-weights", action="store_true", help="with --preset (which always has random weights): accepted for clarity")
     ap.add_argument("--max-tokens-per-step", type=int, default=2048, help="token budget of one step")
     ap.add_argument("--max-live", type=int, default=None, help="most requests in the cache at a time")
     ap.add_argument("--verbose", action="store_true")
@@ -95,6 +97,8 @@ def main(argv: list[str] | None = None) -> int:
     params = J.SamplingParams(temperature=args.temperature, top_k=args.top_k, seed=args.seed,
                               max_new_tokens=args.max_new_tokens, eos_token_ids=eos)
     ps = args.page_size
+    if args.num_pages is not None and args.max_tokens is None:
+        args.max_tokens = args.num_pages * ps
     max_tokens = args.max_tokens or sum(-(-(len(p) + args.max_new_tokens) // ps) * ps for p in prompts)
     gen = J.Generator(model, max_tokens=max_tokens, page_size=ps, max_slots=max(len(prompts), 1),
                       max_tokens_per_step=args.max_tokens_per_step, max_live=args.max_live, seed=args.seed,
