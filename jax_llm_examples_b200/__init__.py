@@ -3,14 +3,14 @@ one step function -> scheduler and sampling -> generated tokens.  CUDA kernels f
 
 from .cache import CacheManager, OutOfPages, Retention
 from .config import ConfigError, Llama4Config, known_architectures, preset, register_architecture, resolve
-from .engine import Engine, EngineError, Generator, Request, Scheduler, StepEntry, generate
+from .engine import Batch, Engine, EngineError, Generator, Request, Scheduler, StepEntry, decode_step, generate, prefill
 from .loading import load_model, model_from_tensors, random_model
 from .sampling import Sampler, SamplingParams
 from .weights import WeightError, write_random_model
 
 __all__ = [
-    "CacheManager", "ConfigError", "Engine", "EngineError", "Generator", "Llama4Config", "OutOfPages", "Request",
-    "Retention", "Sampler", "SamplingParams", "Scheduler", "StepEntry", "WeightError", "generate",
-    "known_architectures", "load_model", "model_from_tensors", "preset", "random_model", "register_architecture",
+    "Batch", "CacheManager", "ConfigError", "Engine", "EngineError", "Generator", "Llama4Config", "OutOfPages", "Request",
+    "Retention", "Sampler", "SamplingParams", "Scheduler", "StepEntry", "WeightError", "decode_step", "generate",
+    "known_architectures", "load_model", "model_from_tensors", "prefill", "preset", "random_model", "register_architecture",
     "resolve", "write_random_model",
 ]

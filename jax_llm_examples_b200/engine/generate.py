@@ -96,3 +96,58 @@ def generate(model: DecoderModel, prompts: Sequence[Sequence[int]], params: Samp
     gen = Generator(model, max_tokens=max_tokens, page_size=page_size, max_slots=max(len(prompts), 1),
                     max_tokens_per_step=max_tokens_per_step, seed=seed)
     return gen.generate(prompts, params)
+
+
+# ------------------------------------------------------------------ the reference's two calls, on this engine
+class Batch:
+    """What ``prefill`` hands to ``decode_step``: an engine and one live request (cache slot) per prompt.  It
+    stands where the reference passes its KVCache from call to call (llama4/llama4_jax/model.py:595-640)."""
+
+    def __init__(self, engine: Engine, slots: list[int]):
+        self.engine, self.slots = engine, slots
+        self._scratch = (torch.empty(32 * len(slots), device=engine.runtime.device),
+                         torch.empty(32 * len(slots), device=engine.runtime.device, dtype=torch.int32))
+
+    def release(self) -> None:
+        """Gives the requests' pages and slots back."""
+        for s in self.slots:
+            self.engine.finish(s)
+        self.slots = []
+
+    def _argmax(self, logits: torch.Tensor) -> torch.Tensor:
+        from ..kernels import api as K
+
+        out = torch.empty(logits.shape[0], device=logits.device, dtype=torch.int32)
+        K.argmax(logits, out, *self._scratch)
+        return out
+
+
+def prefill(model_or_engine, prompts: Sequence[Sequence[int]], *, page_size: int = 64, max_new_tokens: int = 32):
+    """The reference's ``prefill`` (llama4/llama4_jax/model.py:1243-1267): runs the prompts and returns
+    (next token of each [B] on the host, logits at each prompt's last position [B, V] float32 on the device,
+    the batch to decode on).  The reference pads the prompts to a common power of two and returns logits for
+    every position; here each prompt runs at its own length and only the last position's logits are made.
+    ``model_or_engine``: an Engine with room for the prompts, or a model, for which an engine is made that
+    holds the prompts and ``max_new_tokens`` more tokens each."""
+    if isinstance(model_or_engine, Engine):
+        engine = model_or_engine
+    else:
+        need = sum(-(-(len(p) + max_new_tokens) // page_size) * page_size for p in prompts)
+        engine = Engine(model_or_engine, max_tokens=need, page_size=page_size, max_slots=max(len(prompts), 1))
+    slots = [engine.new_request() for _ in prompts]
+    batch = Batch(engine, slots)
+    logits = engine.step([StepEntry(s, list(p), [len(p) - 1]) for s, p in zip(slots, prompts)])
+    next_tokens = batch._argmax(logits).cpu().tolist()
+    engine.check_status()
+    return next_tokens, logits, batch
+
+
+def decode_step(batch: Batch, last_tokens: Sequence[int]):
+    """The reference's ``decode_step`` (model.py:1270-1277): feeds each request its last token and returns
+    (the next token of each by argmax, on the host; the batch)."""
+    if len(last_tokens) != len(batch.slots):
+        raise ValueError(f"{len(last_tokens)} tokens for {len(batch.slots)} requests")
+    logits = batch.engine.step([StepEntry(s, [int(t)], [0]) for s, t in zip(batch.slots, last_tokens)])
+    next_tokens = batch._argmax(logits).cpu().tolist()
+    batch.engine.check_status()
+    return next_tokens, batch

@@ -137,3 +137,26 @@ def test_command_line(model_dirs):
     model = J.load_model(model_dirs["tiny_a"], "float32")
     want = J.generate(model, [[5, 6, 7, 8], [9]], J.SamplingParams(max_new_tokens=6), page_size=16)
     assert [list(map(int, ln.split())) for ln in lines] == want
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_prefill_then_decode_steps_as_the_reference_calls_them(model_dirs, dtype):
+    """The reference's offline loop (llama4/main.py:68-75): prefill, then decode_step over the same batch.
+    The tokens are those of the scheduler's path."""
+    import jax_llm_examples_b200 as J
+
+    model = J.load_model(model_dirs["tiny_b"], dtype, "cuda")
+    rng = random.Random(21)
+    prompts = [[rng.randrange(384) for _ in range(n)] for n in (37, 5, 64)]
+    want = J.generate(model, prompts, J.SamplingParams(max_new_tokens=9), page_size=16)
+    tokens, logits, batch = J.prefill(model, prompts, page_size=16, max_new_tokens=9)
+    assert logits.shape == (3, 384) and logits.dtype == torch.float32
+    got = [[t] for t in tokens]
+    for _ in range(8):
+        tokens, batch = J.decode_step(batch, tokens)
+        for g, t in zip(got, tokens):
+            g.append(t)
+    batch.release()
+    assert got == want
+    eng = batch.engine
+    assert all(eng.manager.free_pages(g) == eng.num_pages for g in range(len(eng.manager.groups)))
