@@ -38,6 +38,14 @@ def parse_dtype(dtype: str | torch.dtype) -> torch.dtype:
         raise ValueError(f"dtype must be bfloat16 or float32, not {dtype!r}") from None
 
 
+def load_config(config_path: str | Path):
+    """config.json (the file, or the folder that holds it) -> the typed configuration of its architecture
+    (the reference's ``load_config``, llama4/llama4_jax/model.py:229-231)."""
+    path = Path(config_path)
+    cfg_json = load_config_json(path.parent if path.is_file() else path)
+    return resolve(cfg_json).parse_config(cfg_json)
+
+
 def load_model(model_dir: str | Path, dtype: str | torch.dtype = "bfloat16", device: str | torch.device = "cuda") -> DecoderModel:
     """config.json + model.safetensors -> model.  ``dtype``: bfloat16 (serving precision; stored
     32-bit tensors stay 32-bit) or float32 (everything in true 32-bit)."""

@@ -12,32 +12,11 @@ mains' flags are argparse too (serving/main_serving_gemma4.py:163-171).
 from __future__ import annotations
 
 import argparse
-import json
 import random
 import sys
 import tempfile
 import time
 from pathlib import Path
-
-
-def _encode(tokenizer, texts: list[str]) -> list[list[int]]:
-    """llama4/main.py:29-39: chat template plus the assistant header (no left padding is needed here)."""
-    out = []
-    for text in texts:
-        ids = tokenizer.apply_chat_template([{"role": "user", "content": text}])
-        ids = getattr(ids, "input_ids", ids) + tokenizer.encode("<|header_start|>assistant<|header_end|>")
-        out.append(list(ids))
-    return out
-
-
-def _load_tokenizer(model_dir: Path):
-    """llama4/llama4_jax/model.py:234-246."""
-    from transformers import AddedToken, PreTrainedTokenizerFast
-
-    cfg = json.loads((model_dir / "tokenizer_config.json").read_text())
-    cfg = {k: AddedToken(**v) if isinstance(v, dict) and str(k).endswith("token") else v for k, v in cfg.items()}
-    cfg["added_tokens_decoder"] = {int(k): AddedToken(**v) for k, v in cfg.get("added_tokens_decoder", {}).items()}
-    return PreTrainedTokenizerFast(tokenizer_file=str(model_dir / "tokenizer.json"), **cfg)
 
 
 def main(argv: list[str] | None = None) -> int:
@@ -86,8 +65,10 @@ def main(argv: list[str] | None = None) -> int:
     if args.prompt:
         if model_dir is None or not (model_dir / "tokenizer.json").is_file():
             ap.error("--prompt needs a model folder with tokenizer.json; use --prompt-ids or --random-prompts")
-        tokenizer = _load_tokenizer(model_dir)
-        prompts += _encode(tokenizer, args.prompt)
+        from .tokenizer import encode_chat, load_tokenizer
+
+        tokenizer = load_tokenizer(model_dir / "tokenizer.json", model_dir / "tokenizer_config.json")
+        prompts += [encode_chat(tokenizer, text) for text in args.prompt]
     rng = random.Random(args.seed)
     prompts += [[rng.randrange(model.vocab_size) for _ in range(args.prompt_len)] for _ in range(args.random_prompts)]
     if not prompts:
