@@ -98,6 +98,12 @@ class Llama4Config:
 
         if d.get("no_rope_layers"):
             no_rope = tuple(int(v) for v in read_key(d, "no_rope_layers", list))
+        elif d.get("layer_types"):
+            # newer HF files name the layer kinds instead: "chunked_attention" = a rotary layer, "full_attention" = none
+            kinds = read_key(d, "layer_types", list)
+            require(all(k in ("chunked_attention", "full_attention") for k in kinds),
+                    f"layer_types may hold 'chunked_attention' and 'full_attention', found {sorted(set(map(str, kinds)))}")
+            no_rope = tuple(int(k == "chunked_attention") for k in kinds)
         else:
             # model.py:203 fixes the interval at 4; the commented lines 201-202 show that
             # no_rope_layers[i] == 1 marks a layer that does use rotary embeddings.

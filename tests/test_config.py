@@ -79,3 +79,17 @@ def test_registry_names_and_errors():
         J.resolve({})
     with pytest.raises(J.ConfigError, match="no config.json"):
         load_config_json("/nonexistent/folder")
+
+
+def test_layer_kinds_from_layer_types():
+    """Newer HF files give ``layer_types`` instead of ``no_rope_layers``."""
+    from jax_llm_examples_b200 import preset, resolve
+
+    d = preset("tiny_a")
+    d.pop("no_rope_layers", None)
+    d["layer_types"] = ["chunked_attention", "full_attention", "chunked_attention", "chunked_attention"]
+    cfg = resolve(d).parse_config(d)
+    assert cfg.no_rope_layers == (1, 0, 1, 1) and not cfg.layer_uses_rope(1) and cfg.layer_uses_rope(0)
+    d["layer_types"][0] = "sliding_attention"
+    with pytest.raises(Exception, match="layer_types"):
+        resolve(d).parse_config(d)
