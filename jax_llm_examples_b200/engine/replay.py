@@ -60,7 +60,8 @@ def main(argv: list[str] | None = None) -> int:
             rid = str(e["id"])
             if rid not in slots:
                 slots[rid] = engine.new_request()
-            entries.append(StepEntry(slots[rid], e["tokens"], e.get("want", [])))
+            if e.get("tokens"):  # an entry without tokens only makes the request known
+                entries.append(StepEntry(slots[rid], e["tokens"], e.get("want", [])))
         if entries:
             logits = engine.step(entries)
             if logits.shape[0] > 0:
