@@ -563,7 +563,7 @@ __global__ void attention_combine_kernel(const AttnParams P) {
 }
 
 // ----------------------------------------------------------------------------------- prefill
-// grid (n_tiles, Hkv); G warps.  A tile is up to 16 consecutive tokens of one request; warp g owns the
+// grid (Hkv, n_tiles); G warps.  A tile is up to 16 consecutive tokens of one request; warp g owns the
 // 16 x DH rows of query head g.  Key tiles of 64 are double-buffered.
 template <int DH>
 __global__ void __launch_bounds__(256) attention_prefill_kernel(const AttnParams P) {
@@ -572,7 +572,7 @@ __global__ void __launch_bounds__(256) attention_prefill_kernel(const AttnParams
   constexpr int STAGES = 2;
   bf16* ks = reinterpret_cast<bf16*>(smem);          // [STAGES][KT][DH]
   bf16* vs = ks + STAGES * KT * DH;
-  const int tile = blockIdx.x, hk = blockIdx.y;
+  const int hk = blockIdx.x, tile = blockIdx.y;
   const int G = P.Hq / P.Hkv;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = P.tiles[2 * tile], cnt = P.tiles[2 * tile + 1];
@@ -744,7 +744,7 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap map, const Attn
   constexpr uint32_t STAGE_BYTES = 2 * HALVES * HALF_BYTES;
   __shared__ __align__(8) uint64_t full_bar[PRE_STAGES];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const int tile = blockIdx.x, hk = blockIdx.y;
+  const int hk = blockIdx.x, tile = blockIdx.y;
   const int G = P.Hq / P.Hkv;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = P.tiles[2 * tile], cnt = P.tiles[2 * tile + 1];
@@ -1038,7 +1038,9 @@ JLX_API int jlx_attention_prefill(const void* q, const void* pages, const int* b
   JLX_REQUIRE(Hkv <= 65535, "attention_prefill: too many KV heads");
   if (n_tiles == 0) return 0;
   P.tiles = tiles;
-  dim3 grid(n_tiles, Hkv);
+  // blocks are handed out by blockIdx.x first: every head of the list's first (heaviest) tile before lighter tiles
+  JLX_REQUIRE(n_tiles <= 65535, "attention_prefill: %d tiles; up to 65535 are supported", n_tiles);
+  dim3 grid(Hkv, n_tiles);
   const bool tma = (page_size % KT == 0 || KT % page_size == 0) && page_size >= 8 &&
                    (long long)num_pages * 2 * Hkv * page_size < (1ll << 31);
   if (tma) {

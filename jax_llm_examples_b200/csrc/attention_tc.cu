@@ -176,7 +176,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   auto BAR = [bar0](int i) { return bar0 + 8u * i; };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tile = blockIdx.x, head = blockIdx.y;
+  // blocks are handed out in the order of blockIdx.x, then y: all heads of the first tile of the list (the
+  // one with the most keys, see the engine's tile order) start before any head of a lighter tile
+  const int head = blockIdx.x, tile = blockIdx.y;
   const int G = P.Hq / P.Hkv, hk = head / G;
   const int n0 = P.tiles[2 * tile], cnt = P.tiles[2 * tile + 1];
   const int r = P.req_of_token[n0];
@@ -518,7 +520,8 @@ JLX_API int jlx_attention_prefill_tc(const void* q, const void* pages, const int
     JLX_CUDA(cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     cfg = true;
   }
-  attention_prefill_tc_kernel<<<dim3(n_tiles, Hq), NTHREADS, smem, stream>>>(map_q, map_kv, P);
+  JLX_REQUIRE(n_tiles <= 65535, "attention_prefill_tc: %d tiles; up to 65535 are supported", n_tiles);
+  attention_prefill_tc_kernel<<<dim3(Hq, n_tiles), NTHREADS, smem, stream>>>(map_q, map_kv, P);
   JLX_LAUNCH_CHECK("attention_prefill_tc");
   return 0;
 }
