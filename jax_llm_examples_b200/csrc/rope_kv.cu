@@ -202,11 +202,11 @@ JLX_API int jlx_rope_kv_store(const void* qkv, int in_dtype, int splits, long lo
   if (N == 0) return 0;
   const size_t smem = (size_t)dh * sizeof(float);
   const int heads = Hq + 2 * Hkv;
-  // many tokens (prompt portions): four heads per warp; few (decoding): one, for the most blocks
+  // many tokens (prompt portions): two heads per warp; few (decoding): one, for the most blocks
   const bool wide = N >= 256 && heads > 8;
   JLX_DISPATCH_DTYPE(in_dtype, TI, JLX_DISPATCH_DTYPE(dtype, T, {
     if (wide) {
-      JLX_CUDA(jlx_launch_pdl(rope_kv_store_kernel<TI, T, 4>, dim3(N, (heads + 31) / 32), dim3(256), smem, stream,
+      JLX_CUDA(jlx_launch_pdl(rope_kv_store_kernel<TI, T, 2>, dim3(N, (heads + 15) / 16), dim3(256), smem, stream,
                               (const TI*)qkv, splits, split_stride, (T*)q_out, (T*)pages, block_table, bt_stride, req_of_token,
                               positions, inv_freq, l2norm, eps, Hq, Hkv, dh, page_size, num_pages, store_kv, status));
     } else {
