@@ -45,7 +45,7 @@ class ClockSampler:
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200"],
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
@@ -193,7 +193,8 @@ def run_ours(args) -> dict:
         eng.record_routing = True  # one more step, untimed, to see which experts a step touches
         one_step()
         torch.cuda.synchronize()
-        nbytes = _decode_bytes(model, eng, b, ctx_len - 1, eng.last_routing)
+        # the cache that a timed step reads: the requests' mean length over the timed steps
+        nbytes = _decode_bytes(model, eng, b, start_len + warmup + (steps + 1) // 2, eng.last_routing)
         desc_bytes = 4 * J.CacheManager.packed_size(len(eng.manager.groups), b, b, b, -(-ctx_len // page))
         for s in slots:
             eng.finish(s)
@@ -323,7 +324,7 @@ def run_ours(args) -> dict:
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--preset", default="scout16", help="named configuration (the default is the benchmark's: 16 Scout-sized layers)")
