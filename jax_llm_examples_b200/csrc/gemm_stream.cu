@@ -59,6 +59,16 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
 __device__ __forceinline__ void prefetch_map(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
+// The same for a wait that is expected to be long (the epilogue warps' wait for the whole main loop): between polls
+// the warp sleeps, so that eight waiting warps per block do not compete for issue slots, or for power, with the
+// two that work.
+__device__ __forceinline__ bool mbar_wait_long(uint32_t bar, uint32_t parity) {
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    __nanosleep(128);
+  }
+  return false;
+}
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
@@ -181,7 +191,7 @@ __device__ __forceinline__ void stream_epilogue(const StreamArgs& args, int warp
   const int quarter = warp & 3;         // tensor-memory lanes [32 * quarter, 32 * quarter + 32): fixed by the warp's number
   const int half = (warp - 2) >> 2;     // the two warps of a quarter take alternate blocks of 16 token columns
   pdl_wait();  // the output buffer may still be read by a predecessor
-  bool ok = mbar_wait(bar_acc, 0);
+  bool ok = mbar_wait_long(bar_acc, 0);
   if (*(volatile int*)failed) ok = false;
   ok = __all_sync(0xffffffffu, ok);  // the tensor-memory loads below need the whole warp
   if (ok) {
