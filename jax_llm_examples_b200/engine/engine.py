@@ -62,14 +62,22 @@ class Engine:
     """Owns the cache (manager, pages, state slabs) of one model on one GPU and steps batches through it.
 
     ``max_tokens``: tokens that all live requests may hold together (each request's count rounded
-    up to whole pages); every group's pool has ``ceil(max_tokens / page_size)`` pages.
-    ``max_seq_len``: longest request (sets the block-table width); default ``max_tokens``.
+    up to whole pages); every group's pool has ``ceil(max_tokens / page_size)`` pages.  None: as many
+    as fit into ``memory_fraction`` of the GPU memory that is free when the engine is made.
+    ``max_seq_len``: longest request (sets the block-table width); default ``max_tokens`` (131072 when the
+    pool is sized from free memory).
     """
 
-    def __init__(self, model: DecoderModel, *, max_tokens: int, page_size: int = 64, max_slots: int = 64,
-                 max_seq_len: int | None = None, use_graphs: bool | None = None):
+    DEFAULT_MAX_SEQ_LEN = 131072  # longest request when neither max_tokens nor max_seq_len says otherwise
+
+    def __init__(self, model: DecoderModel, *, max_tokens: int | None, page_size: int = 64, max_slots: int = 64,
+                 max_seq_len: int | None = None, use_graphs: bool | None = None, memory_fraction: float = 0.9):
         if not torch.cuda.is_available():
             raise EngineError("no CUDA device: this engine runs on a GPU only and has no CPU path")
+        if max_tokens is None:
+            max_tokens = self.tokens_that_fit(model, page_size, memory_fraction)
+            if max_seq_len is None:  # a pool of millions of tokens: the block tables need not be that wide
+                max_seq_len = min(max_tokens, self.DEFAULT_MAX_SEQ_LEN)
         if page_size <= 0 or max_tokens <= 0:
             raise EngineError("page_size and max_tokens must be positive")
         self.model, self.runtime = model, model.runtime
@@ -99,6 +107,16 @@ class Engine:
         self._graphs: dict[tuple[int, int], dict] = {}
         self.graph_replays = 0
         self.graph_kernel_launches = 0  # kernels of this package launched through graph replays
+
+    @staticmethod
+    def tokens_that_fit(model: DecoderModel, page_size: int = 64, memory_fraction: float = 0.9) -> int:
+        """Tokens of cache (whole pages) that fit into this fraction of the device memory now free."""
+        elem = 4 if model.runtime.dtype == torch.float32 else 2
+        per_token = sum(2 * c.num_kv_heads * c.head_dim * elem for c in model.plan.caches)
+        if per_token == 0:
+            raise EngineError("this model keeps no keys and values: give max_tokens")
+        free, _ = torch.cuda.mem_get_info(model.runtime.device)
+        return int(free * memory_fraction / per_token) // page_size * page_size
 
     # ------------------------------------------------------------------ requests
     def new_request(self) -> int:

@@ -160,3 +160,17 @@ def test_prefill_then_decode_steps_as_the_reference_calls_them(model_dirs, dtype
     assert got == want
     eng = batch.engine
     assert all(eng.manager.free_pages(g) == eng.num_pages for g in range(len(eng.manager.groups)))
+
+
+def test_engine_sizes_its_pool_from_free_memory(model_dirs):
+    import jax_llm_examples_b200 as J
+
+    model = J.load_model(model_dirs["tiny_a"], "bfloat16", "cuda")
+    fit = J.Engine.tokens_that_fit(model, page_size=16, memory_fraction=0.001)
+    assert fit > 0 and fit % 16 == 0
+    eng = J.Engine(model, max_tokens=None, page_size=16, max_slots=2, memory_fraction=0.001)
+    assert eng.num_pages * 16 <= fit + 16 and eng.max_seq_len <= J.Engine.DEFAULT_MAX_SEQ_LEN
+    s = eng.new_request()
+    logits = eng.step([J.StepEntry(s, [1, 2, 3], [2])])
+    assert logits.shape == (1, 256)
+    eng.finish(s)
