@@ -60,5 +60,12 @@ def resolve(config_json: Mapping[str, Any]) -> Architecture:
 
 
 def _ensure_builtin() -> None:
-    # Imported late: the model module imports parts, which import this package.
-    from ..models import llama4  # noqa: F401
+    """Imports every module of the ``models`` package (each registers its architectures when imported), so an
+    architecture added in-tree is one new file there.  Late: model modules import parts, which import this package."""
+    import importlib
+    import pkgutil
+
+    from .. import models
+
+    for m in pkgutil.iter_modules(models.__path__):
+        importlib.import_module(f"{models.__name__}.{m.name}")

@@ -950,6 +950,18 @@ JLX_API int jlx_attention_mma_supported(int Hq, int Hkv, int dh, int decode) {
   return (dh == 64 || dh == 128) && G <= (decode ? 16 : 8);
 }
 
+// Multiprocessors of the current device (asked once per device).
+static int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0, n = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
 // Keys per decode split for `pairs` (request, KV head) pairs that read up to max_kv_len keys: a multiple
 // of SPLIT_UNIT chosen so that all blocks are resident at once (two per SM): a second, partly filled round of
 // blocks costs more than longer splits do.
@@ -957,7 +969,7 @@ JLX_API int jlx_attention_decode_split_keys(int max_kv_len, int chunk, int windo
   int span = max_kv_len;
   if (chunk > 0 && chunk < span) span = chunk;
   if (window > 0 && window < span) span = window;
-  int want_splits = 2 * 148 / (pairs > 0 ? pairs : 1);
+  int want_splits = 2 * sm_count() / (pairs > 0 ? pairs : 1);
   if (want_splits < 1) want_splits = 1;
   int keys = (span + want_splits - 1) / (want_splits > 0 ? want_splits : 1);
   keys = (keys + SPLIT_UNIT - 1) / SPLIT_UNIT * SPLIT_UNIT;

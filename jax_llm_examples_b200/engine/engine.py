@@ -18,7 +18,7 @@ import torch
 
 from ..cache.manager import CacheManager, OutOfPages
 from ..kernels import api as K
-from ..parts.base import StepContext, Workspace
+from ..parts.base import StepContext, StepShape, Workspace
 from ..parts.decoder import DecoderModel
 
 
@@ -33,6 +33,16 @@ class StepEntry:
     slot: int
     tokens: Sequence[int]
     want: Sequence[int] = ()
+
+
+class _NotInAGraph:
+    """Stands where a step's host copies would be while the step is captured in a CUDA graph."""
+
+    def _refuse(self, *a, **k):
+        raise EngineError("a part read the step's host copies (ctx.host_*) while the step was captured in a CUDA graph, "
+                          "which would freeze this step's values into later steps: set `capturable = False` on that part")
+
+    __iter__ = __len__ = __getitem__ = __bool__ = _refuse
 
 
 class _HostRing:
@@ -102,9 +112,15 @@ class Engine:
         self.record_routing = False  # True: keep each routed layer's expert choices of the last step
         self.last_routing: list[torch.Tensor] = []
         # Decode-only steps (one token per request) are launch-bound: from the second step of a batch
-        # shape on, the step's kernels are captured once in a CUDA graph and replayed.
+        # shape on, the step's kernels are captured once in a CUDA graph and replayed.  Per-request state lives
+        # in static slabs indexed by the descriptor's slot ids, so a model with state is captured as well, unless
+        # one of its parts says that it plans on the host (Part.capturable).
         self.use_graphs = (self.runtime.dtype == torch.bfloat16) if use_graphs is None else use_graphs
-        self._graphs: dict[tuple[int, int], dict] = {}
+        self._graphs: dict[tuple[int, int, int], dict] = {}
+        self._graph_pool = torch.cuda.graph_pool_handle() if self.use_graphs else None  # one pool for all graphs
+        self._planners = model.step_planners()
+        self._capturable = model.capturable
+        self.last_scratch: dict = {}
         self.graph_replays = 0
         self.graph_kernel_launches = 0  # kernels of this package launched through graph replays
 
@@ -144,7 +160,8 @@ class Engine:
 
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """Runs one batch.  Returns float32 logits [M, vocab] on the device, M = all wanted places in
-        the order of the entries and of each entry's ``want``."""
+        the order of the entries and of each entry's ``want``.  The tensor may be a buffer that the next
+        step overwrites (a replayed graph's): read or copy it before stepping again."""
         if not entries:
             raise EngineError("a step needs at least one entry")
         R = len(entries)
@@ -167,38 +184,34 @@ class Engine:
         starts = [self.manager.committed(e.slot) for e in entries]
         max_kv = max(s + int(n) for s, n in zip(starts, n_tok))
         G = len(self.manager.groups)
+        # what the parts' planners make of this step (tile lists and the like); it travels with the descriptor
+        shape = StepShape(tuple(int(n) for n in n_tok), tuple(starts), self.page_size, max_kv)
+        extra: dict[str, np.ndarray] = {}
+        for planner in self._planners:
+            for name, a in planner(shape).items():
+                extra[name] = np.ascontiguousarray(a, dtype=np.int32)
+        extra_sizes = tuple((name, a.size) for name, a in extra.items())
         graph = None
-        if self.use_graphs and N == R and not self.record_routing and not self.states:
-            graph = self._graphs.setdefault((R, M), {"seen": 0})
+        if self.use_graphs and N == R and not self.record_routing and self._capturable:
+            # A graph freezes the launch shapes, among them the split plan of decode attention, which is laid out
+            # for a longest request: one graph per (requests, wanted rows, bucket of the longest request in the step).
+            bucket = self.kv_bucket(max_kv)
+            graph = self._graphs.setdefault((R, M, bucket), {"seen": 0, "extra": extra_sizes})
             graph["seen"] += 1
+            if graph["extra"] != extra_sizes:
+                graph = None  # a planner gave other sizes than the captured step had: run this step uncaptured
         static = graph is not None and graph["seen"] >= 2
-        # a graph's descriptor is laid out for the longest request the engine allows, so that it fits every replay
-        width = self.max_pages_per_request if static else -(-max_kv // self.page_size)
+        plan_kv = bucket if static else max_kv
+        width = -(-plan_kv // self.page_size)
         packed = CacheManager.packed_size(G, N, R, M, width)
-        # query tiles for the flash kernels: up to 16 consecutive tokens of one request that brings several
-        tiles = tiles_big = tiles_rest = single_rows = None
-        if int(n_tok.max()) > 1:
-            firsts = np.concatenate([[0], np.cumsum(n_tok)[:-1]])
-
-            def cut_tiles(rows: int, which) -> np.ndarray:
-                t = [(f + o, min(rows, n - o)) for f, n in zip(firsts, n_tok) if which(n) for o in range(0, n, rows)]
-                # late tiles of a causal prompt read the most keys: launch them first so that the tail is short
-                return np.ascontiguousarray(np.array(t, dtype=np.int32).reshape(-1, 2)[::-1])
-
-            tiles = cut_tiles(16, lambda n: n > 1)
-            tiles_big = cut_tiles(128, lambda n: n >= 64)
-            tiles_rest = cut_tiles(16, lambda n: 1 < n < 64)
-            # requests that bring a single (decoded) token beside the portions: their rows, for the split-KV kernel
-            single_rows = np.ascontiguousarray(firsts[n_tok == 1].astype(np.int32))
-        extra = [t for t in (tiles, tiles_big, tiles_rest, single_rows) if t is not None]
-        size = packed + sum(t.size for t in extra)
+        size = packed + sum(a.size for a in extra.values())
         host, ring_i = self._ring.next(size)
         host_np = host.numpy()
         self.manager.pack_step(slots, n_tok, tokens, want_off, want, width, N, R, M, host_np)
         at = packed
-        for t in extra:
-            host_np[at:at + t.size] = t.reshape(-1)
-            at += t.size
+        for a in extra.values():
+            host_np[at:at + a.size] = a.reshape(-1)
+            at += a.size
         if static:
             if "desc" not in graph:
                 graph["desc"] = torch.empty(size, dtype=torch.int32, device=self.runtime.device)
@@ -224,26 +237,26 @@ class Engine:
                 o += n
                 return v
 
+            # a captured step must not depend on this step's host copies: it is replayed for other steps
+            host_view = (lambda v: _NotInAGraph()) if static else (lambda v: v)
             ctx = StepContext(
                 runtime=self.runtime, n_tokens=N, n_requests=R,
                 token_ids=cut(N), positions=cut(N), req_of_token=cut(N), cu_q=cut(R + 1), q_start=cut(R), kv_len=cut(R),
                 slot_ids=cut(R), logit_rows=cut(M), n_logit_rows=M, status=self.status,
-                host_q_lens=[int(n) for n in n_tok], host_q_start=starts, host_slot_ids=[int(s) for s in slots],
-                max_q_len=int(n_tok.max()), max_kv_len=self.max_seq_len if static else max_kv, workspace=self.workspace,
+                host_q_lens=host_view([int(n) for n in n_tok]), host_q_start=host_view(starts),
+                host_slot_ids=host_view([int(s) for s in slots]),
+                max_q_len=int(n_tok.max()), max_kv_len=plan_kv, workspace=self.workspace,
             )
             block_tables = [cut(R * width).view(R, width) for _ in range(G)]
-            if tiles is not None:
-                ctx.attn_tiles, ctx.n_attn_tiles = cut(tiles.size).view(-1, 2), tiles.shape[0]
-                ctx.attn_tiles_big, ctx.n_attn_tiles_big = cut(tiles_big.size).view(-1, 2), tiles_big.shape[0]
-                ctx.attn_tiles_rest, ctx.n_attn_tiles_rest = cut(tiles_rest.size).view(-1, 2), tiles_rest.shape[0]
-                ctx.attn_single_rows, ctx.n_attn_single_rows = cut(single_rows.size), single_rows.shape[0]
+            for name, a in extra.items():
+                ctx.host_arrays[name], ctx.arrays[name] = a, cut(a.size)
             if self.record_routing:
                 ctx.scratch["record_routing"] = []
             if static:
                 g = torch.cuda.CUDAGraph()
                 torch.cuda.synchronize()
                 before = K.launch_count()
-                with torch.cuda.graph(g):
+                with torch.cuda.graph(g, pool=self._graph_pool):
                     logits = self.model.forward(ctx, self.kv, self.states, block_tables)
                 graph["graph"], graph["logits"], graph["kernels"] = g, logits, K.launch_count() - before
                 g.replay()
@@ -252,10 +265,23 @@ class Engine:
             else:
                 logits = self.model.forward(ctx, self.kv, self.states, block_tables)
             self.last_routing = ctx.scratch.get("record_routing", [])
+            self.last_scratch = ctx.scratch
         for e, s, n in zip(entries, starts, n_tok):
             self.manager.commit(e.slot, s + int(n))
         self.steps_run += 1
         return logits
+
+    KV_BUCKET_MIN = 1024  # below this many keys a decode step's attention is too short to be worth a plan of its own
+
+    def kv_bucket(self, max_kv: int) -> int:
+        """The longest-request length that a captured decode step is planned for: the step's own longest request
+        rounded up to an eighth of its power of two (so a plan is at most an eighth too wide, and a request
+        that grows from n to 2n tokens meets eight plans), within [KV_BUCKET_MIN, max_seq_len]."""
+        b = self.KV_BUCKET_MIN
+        if max_kv > b:
+            step = (1 << (max_kv - 1).bit_length()) // 8
+            b = -(-max_kv // step) * step
+        return min(b, max(self.max_seq_len, 1))
 
     def check_status(self) -> None:
         """Reads the kernels' status word (synchronises) and raises if any kernel refused something."""

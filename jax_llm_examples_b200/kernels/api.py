@@ -34,6 +34,18 @@ def launch_count() -> int:
     return _launches
 
 
+_sm_counts: dict[int, int] = {}
+
+
+def sm_count() -> int:
+    """Multiprocessors of the current device (asked once per device)."""
+    dev = torch.cuda.current_device()
+    n = _sm_counts.get(dev)
+    if n is None:
+        n = _sm_counts[dev] = torch.cuda.get_device_properties(dev).multi_processor_count
+    return n
+
+
 def library(name: str) -> ctypes.CDLL:
     lib = _libs.get(name)
     if lib is None:

@@ -2,12 +2,43 @@
 
 from __future__ import annotations
 
+import numpy as np
 import torch
 
 from ..cache.manager import Retention
 from ..kernels import api as K
-from .base import KVNeed, LayerCache, Mixer, PositionEncoding, Runtime, StepContext, register_part
+from .base import KVNeed, LayerCache, Mixer, PositionEncoding, Runtime, StepContext, StepShape, register_part
 from .linear import linear
+
+# How this part's kernels cut a step's tokens (the planner below is theirs alone; nothing else knows these numbers).
+FLASH_TILE = 16  # query rows per block of the mma.sync flash kernel
+TC_TILE = 128  # query rows per block of the tcgen05 flash kernel
+TC_MIN_TOKENS = 64  # a request that brings at least this many tokens goes to the tcgen05 kernel
+
+
+def plan_attention_tiles(shape: StepShape) -> dict[str, np.ndarray]:
+    """The step's tokens cut for the three attention kernels, once per step on the host.  A step of single
+    tokens only needs no lists.  Otherwise, as int32 arrays of (first token row, count) pairs, each within one
+    request: ``attn_tiles_all`` = every request that brings several tokens in tiles of FLASH_TILE;
+    ``attn_tiles_long`` = requests that bring at least TC_MIN_TOKENS in tiles of TC_TILE; ``attn_tiles_short`` =
+    the other requests with several tokens in tiles of FLASH_TILE; and ``attn_single_rows`` = the token rows of
+    the requests that bring one token (decoded tokens beside the portions), which the split-KV kernel serves."""
+    n_tok = np.asarray(shape.q_lens, dtype=np.int64)
+    if n_tok.max() <= 1:
+        return {}
+    firsts = np.concatenate([[0], np.cumsum(n_tok)[:-1]])
+
+    def cut(rows: int, which) -> np.ndarray:
+        t = [(f + o, min(rows, n - o)) for f, n in zip(firsts, n_tok) if which(n) for o in range(0, n, rows)]
+        # late tiles of a causal prompt read the most keys: launch them first so that the tail is short
+        return np.ascontiguousarray(np.array(t, dtype=np.int32).reshape(-1, 2)[::-1])
+
+    return {
+        "attn_tiles_all": cut(FLASH_TILE, lambda n: n > 1),
+        "attn_tiles_long": cut(TC_TILE, lambda n: n >= TC_MIN_TOKENS),
+        "attn_tiles_short": cut(FLASH_TILE, lambda n: 1 < n < TC_MIN_TOKENS),
+        "attn_single_rows": np.ascontiguousarray(firsts[n_tok == 1].astype(np.int32)),
+    }
 
 
 class PagedAttention(Mixer):
@@ -21,7 +52,8 @@ class PagedAttention(Mixer):
     A layer with ``shares_cache`` projects only q and reads pages that another layer wrote.
     """
 
-    kernel_libraries = ("attention_generic", "attention_mma", "attention_tc", "rope_kv", "gemm_simt", "gemm_stream")
+    kernel_libraries = ("attention_generic", "gemm_simt")
+    kernel_libraries_bf16 = ("attention_mma", "attention_tc", "gemm_stream")
 
     def __init__(self, w_qkv: torch.Tensor, w_o: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
                  position: PositionEncoding, qk_norm_eps: float | None = None, chunk: int | None = None,
@@ -45,10 +77,15 @@ class PagedAttention(Mixer):
     TC_HEAD_SIZES = (128,)
 
     def required_libraries(self, runtime: Runtime):
-        mine = [n for n in super().required_libraries(runtime)
-                if not (n == "attention_mma" and self.head_dim not in self.MMA_HEAD_SIZES)
-                and not (n == "attention_tc" and self.head_dim not in self.TC_HEAD_SIZES)]
-        return tuple(dict.fromkeys(tuple(mine) + self.position.required_libraries(runtime)))
+        return tuple(n for n in super().required_libraries(runtime)
+                     if not (n == "attention_mma" and self.head_dim not in self.MMA_HEAD_SIZES)
+                     and not (n == "attention_tc" and self.head_dim not in self.TC_HEAD_SIZES))
+
+    def sub_parts(self):
+        return (self.position,)
+
+    def step_planners(self):
+        return (plan_attention_tiles,)
 
     def kv_need(self) -> KVNeed:
         if self.chunk is not None and self.window is None:
@@ -90,18 +127,23 @@ class PagedAttention(Mixer):
             if decode:
                 self._split_kv(ctx, q, cache, out, attn_scale, floor_scale, None, q.shape[0])
                 return
-            if ctx.attn_tiles is not None:
-                if ctx.n_attn_single_rows:
+            tiles_all = ctx.arrays.get("attn_tiles_all")
+            if tiles_all is not None:
+                count = {name: len(a) for name, a in ctx.host_arrays.items()}
+                if count["attn_single_rows"]:
                     # the single decoded tokens of a mixed step go to the split-KV kernel, by their row list
-                    self._split_kv(ctx, q, cache, out, attn_scale, floor_scale, ctx.attn_single_rows, ctx.n_attn_single_rows)
-                tiles, n_tiles = ctx.attn_tiles, ctx.n_attn_tiles  # every request that brings more than one token
-                if ctx.n_attn_tiles_big and self.head_dim in self.TC_HEAD_SIZES and K.attention_prefill_tc_supported(
+                    self._split_kv(ctx, q, cache, out, attn_scale, floor_scale, ctx.arrays["attn_single_rows"],
+                                   count["attn_single_rows"])
+                tiles, n_tiles = tiles_all, count["attn_tiles_all"]  # every request that brings more than one token
+                if count["attn_tiles_long"] and self.head_dim in self.TC_HEAD_SIZES and K.attention_prefill_tc_supported(
                         q.dtype, self.n_heads, self.n_kv_heads, self.head_dim, cache.pages.shape[3]):
                     # long portions on the tcgen05 kernel (128-token tiles), the short ones below
                     K.attention_prefill_tc(q, cache.pages, cache.block_table, ctx.req_of_token, ctx.positions, out,
-                                           ctx.attn_tiles_big, ctx.n_attn_tiles_big, self.scale, chunk, window,
+                                           ctx.arrays["attn_tiles_long"], count["attn_tiles_long"], self.scale, chunk, window,
                                            attn_scale, floor_scale, ctx.status)
-                    tiles, n_tiles = ctx.attn_tiles_rest, ctx.n_attn_tiles_rest
+                    tiles, n_tiles = ctx.arrays["attn_tiles_short"], count["attn_tiles_short"]
+                    kinds = ("tc", "flash" if n_tiles else "", "split_kv" if count["attn_single_rows"] else "")
+                    ctx.scratch.setdefault("attention_kernels", set()).add(tuple(k for k in kinds if k))
                 if n_tiles:
                     K.attention_prefill(q, cache.pages, cache.block_table, ctx.req_of_token, ctx.positions, out, tiles,
                                         n_tiles, self.scale, chunk, window, attn_scale, floor_scale, ctx.status)

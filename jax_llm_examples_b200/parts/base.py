@@ -126,32 +126,72 @@ class StepContext:
     max_kv_len: int = 0
     scratch: dict[str, Any] = dataclasses.field(default_factory=dict)  # per-step memo shared by parts
     workspace: Workspace | None = None  # buffers that outlive the step
-    attn_tiles: torch.Tensor | None = None  # int32 [n, 2]: (first token row, count <= 16) tiles of the requests that bring several tokens
-    n_attn_tiles: int = 0
-    # the same tokens cut three ways for a mixer with several kernels: requests that bring at least 64 tokens in
-    # tiles of up to 128; requests that bring 2..63 tokens in tiles of up to 16; and the token rows of the
-    # requests that bring a single token (int32 [n]), which a split-KV kernel serves best
-    attn_tiles_big: torch.Tensor | None = None
-    n_attn_tiles_big: int = 0
-    attn_tiles_rest: torch.Tensor | None = None
-    n_attn_tiles_rest: int = 0
-    attn_single_rows: torch.Tensor | None = None
-    n_attn_single_rows: int = 0
+    # What the model's step planners (see :meth:`Part.step_planners`) made of this step, by name: int32 arrays
+    # on the host, and the same arrays on the device (they travel with the step's descriptor, in its one copy).
+    host_arrays: dict[str, Any] = dataclasses.field(default_factory=dict)
+    arrays: dict[str, torch.Tensor] = dataclasses.field(default_factory=dict)
+
+    def plan_with(self, planners, page_size: int) -> None:
+        """Runs step planners for a context made by hand (a test of one part): what the engine does while it
+        packs a step, with one small copy per array instead of the descriptor's single one."""
+        shape = StepShape(tuple(self.host_q_lens), tuple(self.host_q_start), page_size, self.max_kv_len)
+        for planner in planners:
+            for name, a in planner(shape).items():
+                self.host_arrays[name] = a
+                self.arrays[name] = torch.tensor(a.tolist(), dtype=torch.int32).reshape(-1).to(self.token_ids.device)
 
 
-BF16_ONLY_LIBRARIES = ("gemm_stream", "attention_mma", "attention_tc")
+@dataclasses.dataclass(frozen=True)
+class StepShape:
+    """What a step planner sees of a step, on the host, before anything runs."""
+
+    q_lens: tuple[int, ...]  # tokens each request brings
+    q_start: tuple[int, ...]  # tokens each request held before
+    page_size: int
+    max_kv_len: int
+
+
+StepPlanner = Callable[["StepShape"], "dict[str, Any]"]
 
 
 class Part:
-    """Base of all parts.  ``tensors()`` lists device tensors for memory accounting."""
+    """Base of all parts.
 
-    kernel_libraries: tuple[str, ...] = ()  # kernel libraries this part launches (built on first use)
+    ``kernel_libraries``: the kernel libraries (``csrc/<name>.cu``) this part launches in every precision;
+    ``kernel_libraries_bf16``: those it launches only with bfloat16 activations (tensor-core kernels: the
+    32-bit path never builds or loads them).  Libraries are built on first use.
+    """
+
+    kernel_libraries: tuple[str, ...] = ()
+    kernel_libraries_bf16: tuple[str, ...] = ()
+    # False: forward() reads the step's host copies (``ctx.host_*``) or otherwise does work that a captured
+    # CUDA graph would freeze; a model with such a part is never replayed from a graph.
+    capturable: bool = True
 
     def required_libraries(self, runtime: Runtime) -> tuple[str, ...]:
-        """What this part launches in this precision (the 32-bit path needs no tensor-core kernels)."""
-        if runtime.dtype == torch.float32:
-            return tuple(n for n in self.kernel_libraries if n not in BF16_ONLY_LIBRARIES)
+        """What this part launches in this precision."""
+        if runtime.dtype == torch.bfloat16:
+            return tuple(dict.fromkeys(self.kernel_libraries + self.kernel_libraries_bf16))
         return self.kernel_libraries
+
+    def step_planners(self) -> "tuple[StepPlanner, ...]":
+        """Functions ``planner(shape: StepShape) -> {name: int32 numpy array}`` that this part wants run once per
+        step on the host (tile lists, row lists and the like).  The model collects the distinct planners of all
+        its parts; the engine runs each once per step and sends the arrays to the device together with the step's
+        descriptor: ``ctx.arrays[name]`` (device) and ``ctx.host_arrays[name]``.  A planner is a module-level
+        function (parts of the same kind share it, so it runs once however many layers use it) and must return
+        the same names with the same sizes for steps of the same shape when it wants to be replayed from a graph."""
+        return ()
+
+    def sub_parts(self) -> "tuple[Part, ...]":
+        """Parts inside this one (a block's norms, mixer and feed-forward; an attention's position encoding)."""
+        return ()
+
+
+def walk_parts(part: "Part"):
+    yield part
+    for p in part.sub_parts():
+        yield from walk_parts(p)
 
 
 class Norm(Part):

@@ -4,7 +4,7 @@ from __future__ import annotations
 
 import torch
 
-from .base import Block, FeedForward, LayerCache, Mixer, Norm, Runtime, StepContext, register_part
+from .base import Block, FeedForward, LayerCache, Mixer, Norm, StepContext, register_part
 
 
 class PreNormBlock(Block):
@@ -16,11 +16,8 @@ class PreNormBlock(Block):
     def __init__(self, norm1: Norm, mixer: Mixer, norm2: Norm, feed_forward: FeedForward):
         self.norm1, self.mixer, self.norm2, self.feed_forward = norm1, mixer, norm2, feed_forward
 
-    def required_libraries(self, runtime: Runtime):
-        libs: list[str] = []
-        for p in (self.norm1, self.mixer, self.norm2, self.feed_forward):
-            libs.extend(p.required_libraries(runtime))
-        return tuple(dict.fromkeys(libs))
+    def sub_parts(self):
+        return (self.norm1, self.mixer, self.norm2, self.feed_forward)
 
     def forward(self, ctx: StepContext, x: torch.Tensor, delta, cache: LayerCache) -> torch.Tensor:
         dt = ctx.runtime.dtype

@@ -13,7 +13,7 @@ import torch
 
 from ..cache.manager import Retention
 from ..kernels import api as K
-from .base import Block, KVNeed, LayerCache, Norm, Runtime, StateNeed, StepContext
+from .base import Block, KVNeed, LayerCache, Norm, Runtime, StateNeed, StepContext, walk_parts
 from .linear import linear
 
 
@@ -97,10 +97,23 @@ class DecoderModel:
 
     def required_libraries(self) -> tuple[str, ...]:
         libs = ["elementwise", "gemm_simt"] + ([] if self.runtime.dtype == torch.float32 else ["gemm_stream"])
-        for b in self.blocks:
-            libs.extend(b.required_libraries(self.runtime))
-        libs.extend(self.final_norm.required_libraries(self.runtime))
+        for p in self.parts():
+            libs.extend(p.required_libraries(self.runtime))
         return tuple(dict.fromkeys(libs))
+
+    def parts(self):
+        """Every part of the model, parts inside parts included."""
+        for top in (*self.blocks, self.final_norm):
+            yield from walk_parts(top)
+
+    def step_planners(self) -> tuple:
+        """The distinct host planners of all parts, in a fixed order (see Part.step_planners)."""
+        return tuple(dict.fromkeys(f for p in self.parts() for f in p.step_planners()))
+
+    @property
+    def capturable(self) -> bool:
+        """False if a part does host work per step that a captured CUDA graph would freeze."""
+        return all(p.capturable for p in self.parts())
 
     def weight_bytes(self) -> int:
         seen, total = set(), 0

@@ -19,7 +19,8 @@ class DenseSwiGLU(FeedForward):
     ``w_gate_up``: [2F, D], gate rows then up rows; ``w_down``: [D, F].  bfloat16 weights are re-laid in
     blocks of [16 gate rows, 16 up rows] so that the product's epilogue can apply the activation."""
 
-    kernel_libraries = ("elementwise", "gemm_simt", "gemm_stream")
+    kernel_libraries = ("elementwise", "gemm_simt")
+    kernel_libraries_bf16 = ("gemm_stream",)
 
     def __init__(self, w_gate_up: torch.Tensor, w_down: torch.Tensor):
         if w_gate_up.shape[0] != 2 * w_down.shape[1] or w_gate_up.shape[1] != w_down.shape[0]:
@@ -42,7 +43,8 @@ class RoutedExperts(FeedForward):
     shared expert's output on the unscaled h is added (model.py:1111, 1137-1139).
     ``w_router``: [E, D]; ``we_gate_up``: [E, 2F, D] (gate rows then up rows); ``we_down``: [E, D, F]."""
 
-    kernel_libraries = ("moe", "elementwise", "gemm_simt", "gemm_stream")
+    kernel_libraries = ("moe", "elementwise", "gemm_simt")
+    kernel_libraries_bf16 = ("gemm_stream",)
     needs_f32_input = True
 
     def __init__(self, w_router: torch.Tensor, we_gate_up: torch.Tensor, we_down: torch.Tensor, top_k: int,
@@ -69,6 +71,9 @@ class RoutedExperts(FeedForward):
             self.we_gate_up = torch.cat([self.we_gate_up, shared.w_gate_up[None]])
             self.we_down = torch.cat([self.we_down, shared.w_down[None]])
             shared.w_gate_up, shared.w_down = self.we_gate_up[E], self.we_down[E]
+
+    def sub_parts(self):
+        return () if self.shared is None else (self.shared,)
 
     def router_request(self):
         return (self.w_router, self.top_k)

@@ -22,11 +22,16 @@ import torch
 from ..kernels import api as K
 from .base import Rows, StepContext
 
+# Every product of this package accumulates in float32.  The library's bfloat16 GEMM may otherwise add its
+# split-K partial sums in bfloat16 (torch's default lets it): switched off for the process when this package loads.
+torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
+
 STREAM_MAX_ROWS = 256  # above this a dense product is compute-bound and goes to the library
-_SM_COUNT = 148
 
 
-_RESIDENT = 2 * _SM_COUNT  # blocks of the streaming kernel that the GPU holds at once (two per SM)
+def _resident_blocks() -> int:
+    """Blocks of the streaming kernel that the GPU holds at once (two per multiprocessor)."""
+    return 2 * K.sm_count()
 
 
 def _splits_for(n_out: int, k: int, groups: int = 1, partials: bool = True) -> int:
@@ -37,7 +42,8 @@ def _splits_for(n_out: int, k: int, groups: int = 1, partials: bool = True) -> i
     the consumer adds the partials itself (`partials`): a separate pass over them costs more than the tail.
     Each cut keeps at least 512 of K."""
     busy = -(-n_out // 128) * max(groups, 1)
-    want = _RESIDENT // busy if busy <= _RESIDENT else (k // 2048 if partials else 1)
+    resident = _resident_blocks()
+    want = resident // busy if busy <= resident else (k // 2048 if partials else 1)
     return max(1, min(want, k // 512, 8))
 
 

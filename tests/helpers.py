@@ -123,7 +123,12 @@ def trace_portions(requests, rng: random.Random):
     return steps
 
 
-def trace_mixed(requests, rng: random.Random, max_live=4):
+SHORT_PORTIONS = (2, 2, 3, 5, 8, 17, 33)
+# around the sizes at which the attention part changes kernels (64 tokens) and tiles (128 rows)
+LONG_PORTIONS = (2, 17, 63, 64, 65, 127, 128, 129, 200, 300)
+
+
+def trace_mixed(requests, rng: random.Random, max_live=4, portions=SHORT_PORTIONS):
     """Up to `max_live` live requests: portions of some beside single tokens of others; a request
     may sit out a step; finished requests make room (and pages) for the next ones."""
     pending = list(requests.items())
@@ -142,7 +147,7 @@ def trace_mixed(requests, rng: random.Random, max_live=4):
             if rng.random() < 0.5 or left == 1:
                 n = 1
             else:
-                n = min(left, rng.choice([2, 2, 3, 5, 8, 17, 33]))
+                n = min(left, rng.choice(portions))
             entries.append({"id": rid, "tokens": toks[at:at + n], "want": list(range(n))})
             live[rid] = at + n
             if live[rid] == len(toks):
@@ -176,6 +181,8 @@ def run_trace(engine, steps):
             at[rid] += len(e["tokens"])
         logits = engine.step(entries).cpu().numpy()
         engine.check_status()
+        # which attention kernels served the step together (a set of tuples, kept on the engine for the tests)
+        engine.__dict__.setdefault("attention_kernels_seen", set()).update(engine.last_scratch.get("attention_kernels", ()))
         assert logits.shape[0] == len(places)
         for row, key in zip(logits, places):
             out[key] = row
@@ -230,3 +237,20 @@ def compare_plain_only(model_dir, requests, got, dtype: str):
             if (rid, pos) in got:
                 err = rel_err(got[(rid, pos)], ref[pos])
                 assert err < TOL[dtype], f"{dtype}: request {rid} position {pos}: relative error {err:.3e}"
+
+
+def plain_greedy_checked(folder, prompt, got, dtype: str):
+    """`got` must be the plain implementation's greedy continuation, except that a step whose two best
+    logits nearly tie (closer than the precision can tell apart) may go either way; after such a step the
+    comparison follows the engine's choice."""
+    cfg, w = _plain_model(str(folder))
+    toks = list(prompt)
+    tol = 1e-5 if dtype == "float32" else 2e-2
+    with torch.no_grad():
+        for step, g in enumerate(got):
+            logits = plain.forward(cfg, w, toks)[-1]
+            best = int(torch.argmax(logits))
+            if g != best:
+                gap = float(logits[best] - logits[g]) / float(logits.abs().max())
+                assert gap < tol, f"{dtype}: step {step}: engine chose {g}, plain {best}, relative logit gap {gap:.2e}"
+            toks.append(g)

@@ -16,20 +16,7 @@ from tests.plain import llama4_plain as plain
 pytestmark = pytest.mark.gpu
 
 
-def _plain_greedy_checked(folder, prompt, got, dtype):
-    """`got` must be the plain implementation's greedy continuation, except that a step whose two best
-    logits nearly tie (closer than the precision can tell apart) may go either way; after such a step the
-    comparison follows the engine's choice."""
-    cfg, w = plain.load_config(folder), plain.load_weights(folder)
-    toks = list(prompt)
-    tol = 1e-5 if dtype == "float32" else 2e-2
-    for step, g in enumerate(got):
-        logits = plain.forward(cfg, w, toks)[-1]
-        best = int(torch.argmax(logits))
-        if g != best:
-            gap = float(logits[best] - logits[g]) / float(logits.abs().max())
-            assert gap < tol, f"{dtype}: step {step}: engine chose {g}, plain {best}, relative logit gap {gap:.2e}"
-        toks.append(g)
+_plain_greedy_checked = H.plain_greedy_checked
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -67,6 +54,27 @@ def test_long_decoding_stays_right(model_dirs, dtype):
     seq = prompts[0] + outs[0]
     got, routing = H.run_trace(eng, H.trace_tail_decode({"r": seq}, 32))
     H.compare_with_plain(folder, {"r": seq}, got, routing, dtype)
+
+
+def test_replayed_graphs_follow_the_growing_context(model_dirs):
+    """A captured decode step is planned for a bucket of context lengths; as the requests grow the engine moves
+    from one bucket's graph to the next.  With buckets made small, 150 decoded tokens cross many of them."""
+    import jax_llm_examples_b200 as J
+
+    folder = model_dirs["tiny_c"]
+    model = J.load_model(folder, "bfloat16")
+    gen = J.Generator(model, max_tokens=3 * 256, page_size=16, max_slots=3, max_tokens_per_step=64)
+    gen.engine.KV_BUCKET_MIN = 32
+    assert [gen.engine.kv_bucket(n) for n in (1, 32, 33, 36, 37, 64, 65, 100, 128, 129, 700)] == [32, 32, 40, 40, 40, 64, 80, 112, 128, 160, 768]
+    prompts = [[5, 6, 7], [9] * 40, [200, 100] * 9]
+    outs = gen.generate(prompts, J.SamplingParams(max_new_tokens=150))
+    buckets = {key[2] for key, g in gen.engine._graphs.items() if "graph" in g}
+    assert len(buckets) >= 8 and gen.engine.graph_replays > 100, (buckets, gen.engine.graph_replays)
+    for p, o in zip(prompts, outs):
+        H.plain_greedy_checked(folder, p, o, "bfloat16")
+    # a wide engine (the default when the pool is sized from free memory) plans for the context in use all the same
+    wide = J.Engine(model, max_tokens=4096, page_size=16, max_slots=2, max_seq_len=131072)
+    assert wide.kv_bucket(700) == 1024 and wide.kv_bucket(9000) == 10240 and wide.kv_bucket(131072) == 131072
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

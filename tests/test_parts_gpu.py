@@ -22,7 +22,7 @@ DEV = "cuda"
 # ------------------------------------------------------------------------------- parts alone
 def _ctx(J, runtime, q_lens, starts, page_size=16, n_pages=32, vocab=100):
     """A step context for hand-made batches (what Engine.step builds), with one block table."""
-    from jax_llm_examples_b200.parts import StepContext, Workspace
+    from jax_llm_examples_b200.parts import StepContext, Workspace, plan_attention_tiles
 
     pos = [s + i for n, s in zip(q_lens, starts) for i in range(n)]
     req = [r for r, n in enumerate(q_lens) for _ in range(n)]
@@ -30,7 +30,6 @@ def _ctx(J, runtime, q_lens, starts, page_size=16, n_pages=32, vocab=100):
     width = max(-(-(s + n) // page_size) for n, s in zip(q_lens, starts))
     perm = torch.randperm(n_pages)[: len(q_lens) * width].reshape(len(q_lens), width).to(torch.int32).to(DEV)
     N = sum(q_lens)
-    tiles = [(f + o, min(16, n - o)) for f, n in zip(np.concatenate([[0], np.cumsum(q_lens)[:-1]]), q_lens) for o in range(0, n, 16)]
     ctx = StepContext(runtime=runtime, n_tokens=N, n_requests=len(q_lens), token_ids=t([0] * N), positions=t(pos),
                       req_of_token=t(req), cu_q=t(list(np.concatenate([[0], np.cumsum(q_lens)]))), q_start=t(starts),
                       kv_len=t([s + n for n, s in zip(q_lens, starts)]), slot_ids=t(list(range(len(q_lens)))),
@@ -38,8 +37,7 @@ def _ctx(J, runtime, q_lens, starts, page_size=16, n_pages=32, vocab=100):
                       host_q_lens=list(q_lens), host_q_start=list(starts), host_slot_ids=list(range(len(q_lens))),
                       max_q_len=max(q_lens), max_kv_len=max(s + n for n, s in zip(q_lens, starts)),
                       workspace=Workspace(torch.device(DEV)))
-    if max(q_lens) > 1:
-        ctx.attn_tiles, ctx.n_attn_tiles = t(tiles), len(tiles)
+    ctx.plan_with((plan_attention_tiles,), page_size)
     return ctx, perm
 
 
@@ -393,3 +391,70 @@ def test_a_block_run_twice_and_a_layer_reading_another_layers_cache(model_dirs):
     with pytest.raises(ValueError, match="already has a writer"):
         DecoderModel(base.runtime, base.embedding, base.blocks, base.final_norm, base.lm_head,
                      [LayerRun(0, 0, True), LayerRun(1, 0, True)], base.config)
+
+
+# ------------------------------------------------------- per-request state under replayed CUDA graphs
+def test_a_state_mixer_decodes_through_replayed_graphs():
+    """A recurrent mixer whose decode step indexes its state slab by the descriptor's slot ids (device data) is
+    captured and replayed like any other model: the replayed steps give the same logits, bit for bit, as the
+    uncaptured ones.  A mixer that reads the step's host copies while being captured is refused loudly, and one
+    that says so (``capturable = False``) is simply never captured."""
+    import jax_llm_examples_b200 as J
+    from jax_llm_examples_b200.parts import DecoderModel, DenseSwiGLU, Mixer, PreNormBlock, RMSNorm, Runtime, StateNeed
+
+    class DecayState(Mixer):
+        def __init__(self, w, decay, mode):
+            self.w, self.decay, self.mode = w.float(), float(decay), mode
+            self.capturable = mode != "opts_out"
+
+        def state_need(self):
+            return StateNeed((self.w.shape[0],), torch.float32)
+
+        def forward(self, ctx, h, cache):
+            u = h.float() @ self.w.T
+            if ctx.max_q_len == 1 and self.mode == "device":  # a decode step: state rows by the device's slot ids
+                slots = ctx.slot_ids.long()
+                s = self.decay * cache.state.index_select(0, slots) + u
+                cache.state.index_copy_(0, slots, s)
+                return s
+            out, at = torch.empty_like(u), 0
+            for n, slot in zip(ctx.host_q_lens, ctx.host_slot_ids):  # portions: planned on the host (never captured)
+                s = cache.state[slot]
+                for i in range(n):
+                    s = self.decay * s + u[at + i]
+                    out[at + i] = s
+                cache.state[slot] = s
+                at += n
+            return out
+
+    D, F, V = 64, 128, 50
+    g = torch.Generator().manual_seed(4)
+    r = lambda *shape: (torch.randn(*shape, generator=g) * 0.1).to(torch.bfloat16).to(DEV)
+    rt = Runtime(torch.bfloat16, torch.device(DEV))
+
+    def model(mode):
+        torch.manual_seed(0)
+        blocks = [PreNormBlock(RMSNorm(torch.ones(D, device=DEV), 1e-5), DecayState(w, 0.7, mode), RMSNorm(torch.ones(D, device=DEV), 1e-5),
+                               DenseSwiGLU(gu, dn)) for w, gu, dn in weights]
+        return DecoderModel(rt, emb, blocks, RMSNorm(torch.ones(D, device=DEV), 1e-5), head)
+
+    weights = [(r(D, D), r(2 * F, D), r(D, F)) for _ in range(2)]
+    emb, head = r(V, D), r(V, D)
+
+    def run(mode, use_graphs, steps=12):
+        eng = J.Engine(model(mode), max_tokens=64, page_size=16, max_slots=4, use_graphs=use_graphs)
+        slots = [eng.new_request() for _ in range(3)]
+        rows = [eng.step([J.StepEntry(s, [1 + i, 2, 3 + i], [2]) for i, s in enumerate(slots)]).clone()]
+        for t in range(steps):
+            rows.append(eng.step([J.StepEntry(s, [(5 * t + i) % V], [0]) for i, s in enumerate(slots)]).clone())
+        eng.check_status()
+        return torch.stack(rows), eng
+
+    plain_rows, _ = run("device", False)
+    graph_rows, eng = run("device", True)
+    assert eng.graph_replays >= 10
+    assert torch.equal(plain_rows, graph_rows)
+    with pytest.raises(J.EngineError, match="capturable"):
+        run("host", True)
+    rows, eng = run("opts_out", True)
+    assert eng.graph_replays == 0 and torch.equal(rows, plain_rows)
