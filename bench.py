@@ -43,9 +43,19 @@ class ClockSampler:
         self.rows: list[list[str]] = []
         self.proc = None
 
+    @staticmethod
+    def _device_id() -> str:
+        """The running device as nvidia-smi knows it: its UUID (index 0 of this process may be another index there)."""
+        try:
+            import torch
+
+            return "GPU-" + str(torch.cuda.get_device_properties(torch.cuda.current_device()).uuid)
+        except Exception:
+            return "0"
+
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100"],
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", self._device_id(), f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:

@@ -1,7 +1,7 @@
 """Cache manager: pages, block tables and request slots (host side, C++ underneath).
 
 See ``csrc/host/cache_manager.cpp`` for the rules.  This wrapper adds typed errors and numpy
-views of the block tables; it holds no device memory (that is :mod:`.storage`).
+views of the block tables; it holds no device memory (the engine owns the pages and the state slabs).
 """
 
 from __future__ import annotations

@@ -23,6 +23,7 @@
 #include <cuda.h>
 
 #include "common.cuh"
+#include "mbarrier.cuh"
 
 #define KT 64            // keys per tile
 #define SPLIT_UNIT 64    // decode splits are multiples of this many keys (one tile), aligned to absolute positions
@@ -31,7 +32,6 @@
 #define DEC_STAGES 3     // key/value tiles in flight per decode block (96 KB at head size 128: two blocks per SM)
 #define NEG_BIG (-1.0e30f)
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
   const int n = valid ? 16 : 0;  // 0 bytes read: the 16 bytes are filled with zeros
@@ -58,25 +58,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 // ---- TMA and mbarrier (decode kernel: whole [rows, 64-element] boxes of a page per instruction)
-#define WAIT_LIMIT (1u << 22)
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {  // bounded: false = gave up
-  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.b32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    if (ok) return true;
-  }
-  return false;
-}
+#define WAIT_LIMIT JLX_WAIT_LIMIT
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"

@@ -25,38 +25,15 @@
 #include <cuda.h>
 
 #include "common.cuh"
+#include "mbarrier.cuh"
 
 #define DH 128
 #define BQ 128           // query rows per block
 #define BKV 128          // keys per tile
 #define NTHREADS 320     // warp 0: TMA, warp 1: MMA, warps 2..9: softmax (two per quarter of the query rows)
-#define WAIT_LIMIT (1u << 22)
+#define WAIT_LIMIT JLX_WAIT_LIMIT
 #define NEG_BIG (-1.0e30f)
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.b32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-  return ok != 0;
-}
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {  // bounded: false = gave up
-  for (uint32_t i = 0; i < WAIT_LIMIT; ++i)
-    if (mbar_try_wait(bar, parity)) return true;
-  return false;
-}
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");

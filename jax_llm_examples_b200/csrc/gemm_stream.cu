@@ -22,52 +22,18 @@
 #include <cuda.h>
 
 #include "common.cuh"
+#include "mbarrier.cuh"
 
 #define WN 128          // weight rows per tile (MMA M)
 #define BK 64           // K elements per stage (128 bytes of bfloat16)
 #define UMMA_K 16
 #define NTHREADS 320     // warp 0: TMA, warp 1: MMA, warps 2..9: epilogue (two per quarter of the tensor-memory lanes)
-#define WAIT_LIMIT (1u << 22)
+#define WAIT_LIMIT JLX_WAIT_LIMIT
 
 // ------------------------------------------------------------------------------------ PTX wrappers
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.b32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait: false after WAIT_LIMIT polls (each poll itself waits a bounded time in hardware).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  for (uint32_t i = 0; i < WAIT_LIMIT; ++i)
-    if (mbar_try_wait(bar, parity)) return true;
-  return false;
-}
 // Fetches a tensor map's descriptor ahead of its first use by a copy.
 __device__ __forceinline__ void prefetch_map(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
-}
-// The same for a wait that is expected to be long (the epilogue warps' wait for the whole main loop): between polls
-// the warp sleeps, so that eight waiting warps per block do not compete for issue slots, or for power, with the
-// two that work.
-__device__ __forceinline__ bool mbar_wait_long(uint32_t bar, uint32_t parity) {
-  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    __nanosleep(128);
-  }
-  return false;
 }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
   asm volatile(

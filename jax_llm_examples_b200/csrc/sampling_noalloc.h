@@ -22,7 +22,8 @@
 //    what the last call left, and that is harmless: every slot a call reads it has written itself first,
 //    so nothing has to be cleared.
 //  * The first call on each device looks up the array's device address (cudaGetSymbolAddress).  Make that
-//    first call once, ordinarily, before any stream capture is started on that device.
+//    first call once, ordinarily, before any stream capture is started on that device.  Host threads that
+//    make their first calls at the same time are safe: each looks the address up and stores the same value.
 //  * It calls no cudaMalloc, cudaFree or any allocating library routine.
 #pragma once
 #include <cuda_runtime.h>

@@ -14,7 +14,7 @@ from typing import Sequence
 import torch
 
 from ..parts.decoder import DecoderModel
-from ..sampling.sampler import Sampler, SamplingParams
+from ..sampling.sampler import Sampler, SamplingParams, stream_of
 from .engine import Engine, StepEntry
 from .scheduler import PlannedEntry, Request, Scheduler
 
@@ -62,7 +62,7 @@ class Generator:
             return []
         toks = self.sampler.sample(
             logits, [r.params.temperature for r in want], [r.params.top_k for r in want],
-            [r.request_id for r in want], [len(r.output) for r in want])
+            [stream_of(r.request_id, r.params) for r in want], [len(r.output) for r in want])
         host = toks.cpu()
         self.d2h_bytes += 4 * host.numel()
         self.engine.check_status()

@@ -28,7 +28,7 @@ def main(argv: list[str] | None = None) -> int:
     ap.add_argument("--out", required=True, help="folder for <step>.f32 files")
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens that live requests hold at any time (each rounded up to whole pages)")
-    ap.add_argument("--page-size", type=int, default=64, help="tokens per cache page (64 or a divisor of it)")
+    ap.add_argument("--page-size", type=int, default=64, help="tokens per cache page")
     ap.add_argument("--max-requests", type=int, default=16, help="most requests live at a time")
     args = ap.parse_args(argv)
 
@@ -44,7 +44,10 @@ def main(argv: list[str] | None = None) -> int:
     out_dir = Path(args.out)
     out_dir.mkdir(parents=True, exist_ok=True)
     model = load_model(args.model, args.dtype, "cuda")
-    pool_tokens = -(-args.max_tokens // 64) * 64  # requests are counted in multiples of 64 tokens
+    # --max-tokens counts each live request rounded up to a multiple of 64 tokens.  Pages that are larger than
+    # that round a request up further: by up to (page - 64) tokens for each live request.
+    ps = args.page_size
+    pool_tokens = -(-args.max_tokens // max(ps, 64)) * max(ps, 64) + args.max_requests * max(ps - 64, 0)
     engine = Engine(model, max_tokens=pool_tokens, page_size=args.page_size, max_slots=args.max_requests,
                     max_seq_len=pool_tokens)
     print("[trace_run] ready", file=sys.stderr, flush=True)

@@ -140,6 +140,26 @@ def ensure_built(names: list[str] | tuple[str, ...]) -> dict[str, Path]:
         return {n: _built[n] for n in names}
 
 
+def build_source(src: str | Path) -> Path:
+    """Builds one .cu file from anywhere (a test's own kernel) with the package's flags and headers."""
+    src = Path(src).resolve()
+    with _lock:
+        key = f"@{src}"
+        if key not in _built:
+            out = build_dir() / f"{src.stem}-{_hash([src] + _headers(), NVCC_FLAGS)}.so"
+            if not out.is_file():
+                tmp = Path(f"{out}.{os.getpid()}.tmp")
+                cmd = [_nvcc(), *NVCC_FLAGS, "-I", str(CSRC), "-o", str(tmp), str(src)]
+                _say(f"compiling {src.name} ...")
+                proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+                if proc.returncode != 0:
+                    tmp.unlink(missing_ok=True)
+                    raise KernelBuildError(f"building {src} failed:\n{' '.join(cmd)}\n{proc.stdout}")
+                os.replace(tmp, out)
+            _built[key] = out
+        return _built[key]
+
+
 def all_kernel_names() -> list[str]:
     return sorted(p.stem for p in CSRC.glob("*.cu"))
 

@@ -59,8 +59,16 @@ def load_model(model_dir: str | Path, dtype: str | torch.dtype = "bfloat16", dev
 
 def random_model(config_json: Mapping[str, Any], seed: int, dtype: str | torch.dtype = "bfloat16",
                  device: str | torch.device = "cuda", std: float = 0.02, norm_noise: float = 0.0,
-                 weight_dtype: torch.dtype = torch.bfloat16) -> DecoderModel:
-    """A model with seeded random weights made directly on the device (no folder is written)."""
+                 weight_dtype: torch.dtype = torch.bfloat16, draw_on: str = "device") -> DecoderModel:
+    """A model with seeded random weights made directly on the device (no folder is written).
+
+    NOT the tensors of ``write_random_model`` for the same seed, unless ``draw_on="cpu"``: a tensor's values
+    depend on (seed, tensor name) AND on the generator that draws them, and by default each tensor is drawn by
+    the device's generator (a large model is made without a host copy), while a folder is written from the
+    CPU's.  With ``draw_on="cpu"`` every tensor is drawn on the CPU and copied over: the model that
+    ``load_model`` gives for a folder written with the same configuration, seed, std and norm_noise."""
+    if draw_on not in ("device", "cpu"):
+        raise ValueError(f"draw_on must be 'device' or 'cpu', not {draw_on!r}")
     dt = parse_dtype(dtype)
     arch = resolve(config_json)
     cfg = arch.parse_config(config_json)
@@ -71,7 +79,7 @@ def random_model(config_json: Mapping[str, Any], seed: int, dtype: str | torch.d
         """Makes each tensor when the builder takes it, so that only one is unfused at a time."""
 
         def pop(self, name, *a):
-            return random_tensor(specs[name], seed, store, device, std, norm_noise)
+            return random_tensor(specs[name], seed, store, "cpu" if draw_on == "cpu" else device, std, norm_noise).to(device)
 
         def __contains__(self, name):
             return name in specs and not specs[name].optional

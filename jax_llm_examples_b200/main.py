@@ -39,7 +39,6 @@ def main(argv: list[str] | None = None) -> int:
     ap.add_argument("--page-size", type=int, default=64)
     ap.add_argument("--max-tokens", type=int, default=None, help="cache pool in tokens (default: what the prompts need)")
     ap.add_argument("--num-pages", type=int, default=None, help="the same pool given in pages of --page-size tokens")
-    ap.add_argument("--random-weights", action="store_true", help="with --preset (which always has random weights): accepted for clarity")
     ap.add_argument("--max-tokens-per-step", type=int, default=2048, help="token budget of one step")
     ap.add_argument("--max-live", type=int, default=None, help="most requests in the cache at a time")
     ap.add_argument("--verbose", action="store_true")

@@ -20,7 +20,7 @@ from ..kernels import api as K
 class SamplingParams:
     temperature: float = 0.0  # <= 1e-3: greedy
     top_k: int = 0  # 0: the whole vocabulary
-    seed: int = 0
+    seed: int = 0  # varies this request's random stream (see stream_of); the run's own seed is the Sampler's
     max_new_tokens: int = 32
     eos_token_ids: tuple[int, ...] = ()
 
@@ -31,6 +31,11 @@ class SamplingParams:
             raise ValueError("top_k must be >= 0")
         if self.max_new_tokens < 1:
             raise ValueError("max_new_tokens must be >= 1")
+
+
+def stream_of(request_id: int, params: SamplingParams) -> int:
+    """The random stream of a request: its id, moved by the seed of its sampling parameters (seed 0: the id)."""
+    return (request_id ^ (params.seed * 0x9E3779B97F4A7C15)) & 0x7FFFFFFFFFFFFFFF
 
 
 class Sampler:

@@ -55,7 +55,8 @@ def random_tensors(specs: Mapping[str, TensorSpec], seed: int, dtype: torch.dtyp
 
 def write_random_model(model_dir: str | Path, config_json: Mapping[str, Any], seed: int,
                        dtype: torch.dtype = torch.bfloat16, std: float = 0.02, norm_noise: float = 0.0) -> Path:
-    """Writes ``config.json`` and ``model.safetensors`` for the architecture that config_json names."""
+    """Writes ``config.json`` and ``model.safetensors`` for the architecture that config_json names.  The
+    tensors are drawn by the CPU's generator: ``random_model`` gives the same ones only with ``draw_on="cpu"``."""
     from safetensors.torch import save_file
 
     from ..config.registry import resolve

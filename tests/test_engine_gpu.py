@@ -150,3 +150,21 @@ def test_renumbering_the_experts_changes_nothing(model_dirs, name, dtype, tol):
     assert rows[0].keys() == rows[1].keys() and len(rows[0]) > 0
     worst = max(H.rel_err(rows[1][k], rows[0][k]) for k in rows[0])
     assert worst < tol, f"{name} {dtype}: relative difference {worst:.2e} after renumbering the experts"
+
+
+def test_random_model_on_the_device_and_the_written_folder(tmp_path):
+    """``random_model(draw_on="cpu")`` is the model of the folder that ``write_random_model`` writes for the same
+    seed; drawn on the device (the default) it is another model, as its docstring says."""
+    import jax_llm_examples_b200 as J
+
+    cfg = J.preset("tiny_b")
+    folder = J.write_random_model(tmp_path / "m", cfg, seed=9, norm_noise=0.1)
+    from_folder = J.load_model(folder, "bfloat16", "cuda")
+    same = J.random_model(cfg, 9, "bfloat16", "cuda", norm_noise=0.1, draw_on="cpu")
+    other = J.random_model(cfg, 9, "bfloat16", "cuda", norm_noise=0.1)
+    assert torch.equal(same.embedding, from_folder.embedding) and torch.equal(same.lm_head, from_folder.lm_head)
+    assert torch.equal(same.blocks[3].mixer.w_qkv, from_folder.blocks[3].mixer.w_qkv)
+    assert torch.equal(same.blocks[1].feed_forward.we_down, from_folder.blocks[1].feed_forward.we_down)
+    assert not torch.equal(other.embedding, from_folder.embedding)
+    with pytest.raises(ValueError, match="draw_on"):
+        J.random_model(cfg, 9, draw_on="gpu")
