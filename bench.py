@@ -157,32 +157,40 @@ def run_ours(args) -> dict:
     cfg = model.config
     torch.cuda.synchronize()
     print(f"[bench] model of {cfg.num_hidden_layers} layers ({model.weight_bytes() / 1e9:.1f} GB) made in {time.time() - t0:.0f} s", file=sys.stderr)
-    max_batch = max(batch, 64 if not args.skip_points else batch)
+    extra = set(filter(None, args.extra_points.split(",")))
+    known = {"wide", "past_chunk", "ref_table", "prefill4", "long"}
+    if extra - known:
+        raise SystemExit(f"bench.py: unknown --extra-points {sorted(extra - known)}; known: {sorted(known)}")
     gen = torch.Generator(device="cuda")
     gen.manual_seed(1)
     import random as pyrandom
 
     rng = pyrandom.Random(0)
 
-    def decode_run(b: int, steps: int, warmup: int, e2e: bool):
-        """b requests with ctx_len - (steps + warmup) tokens of cache decode steps + warmup tokens."""
+    def decode_run(b: int, steps: int, warmup: int, e2e: bool = False, ctx_len: int = ctx_len, start_len: int | None = None,
+                   max_seq_len: int | None = None):
+        """b requests decode steps + warmup tokens; they end just below ctx_len tokens, or start at start_len.
+        ``max_seq_len``: the longest request the engine allows (default: ctx_len)."""
         g = J.Generator(model, max_tokens=b * ctx_len, page_size=page, max_slots=b, max_tokens_per_step=max(b, 2048),
-                        max_seq_len=ctx_len)
+                        max_seq_len=max_seq_len or ctx_len)
         eng = g.engine
         slots = [eng.new_request() for _ in range(b)]
-        start_len = ctx_len - (steps + warmup) - 2
+        if start_len is None:
+            start_len = ctx_len - (steps + warmup) - 10
         _fill_cache(eng, slots, start_len, gen)
-        toks = torch.tensor([rng.randrange(cfg.vocab_size) for _ in range(b)], dtype=torch.int32).pin_memory()
+        extra_steps = 8  # untimed steps after the timed ones, to see which experts a step touches
+        # fresh token ids for every step (drawn beforehand), so that every step routes its own way
+        all_toks = [[rng.randrange(cfg.vocab_size) for _ in range(b)] for _ in range(steps + warmup + extra_steps)]
         out_host = torch.empty(b, dtype=torch.int32).pin_memory()
         sampler = J.Sampler(0)
+        at = [0]
 
         def one_step():
-            entries = [J.StepEntry(s, [int(t)], [0]) for s, t in zip(slots, toks.tolist())]
+            entries = [J.StepEntry(s, [t], [0]) for s, t in zip(slots, all_toks[at[0]])]
+            at[0] += 1
             logits = eng.step(entries)
             nxt = sampler.sample(logits, [0.0] * b, [0] * b, [0] * b, [0] * b)
-            out_host.copy_(nxt, non_blocking=not e2e)
-            if e2e:
-                toks.copy_(out_host)  # the next step's input is this step's output, on the host
+            out_host.copy_(nxt, non_blocking=True)
             return nxt
 
         for _ in range(warmup):
@@ -200,11 +208,14 @@ def run_ours(args) -> dict:
         dev_ms = ev0.elapsed_time(ev1)
         eng.check_status()
         launches = api.launch_count() + eng.graph_kernel_launches - launches0
-        eng.record_routing = True  # one more step, untimed, to see which experts a step touches
-        one_step()
-        torch.cuda.synchronize()
-        # the cache that a timed step reads: the requests' mean length over the timed steps
-        nbytes = _decode_bytes(model, eng, b, start_len + warmup + (steps + 1) // 2, eng.last_routing)
+        # which experts a step touches: a few more steps, untimed, with the choices recorded; the bytes of a step
+        # are the mean over them (the cache that a timed step reads: the requests' mean length over the timed steps)
+        eng.record_routing = True
+        nbytes = 0.0
+        for _ in range(extra_steps):
+            one_step()
+            torch.cuda.synchronize()
+            nbytes += _decode_bytes(model, eng, b, start_len + warmup + (steps + 1) // 2, eng.last_routing) / extra_steps
         desc_bytes = 4 * J.CacheManager.packed_size(len(eng.manager.groups), b, b, b, -(-ctx_len // page))
         for s in slots:
             eng.finish(s)
@@ -252,11 +263,28 @@ def run_ours(args) -> dict:
     e2e = e2e_run(batch, args.steps, args.warmup) if not args.skip_e2e else {"ms": float("nan"), "h2d": 0, "d2h": 0}
 
     points = {}
+    few = max(3, min(args.steps, 20))
+
+    def point(name: str, b: int, **kw):
+        r = decode_run(b, few, 3, **kw)
+        points[name] = round(b / (r["ms"] / 1e3), 1)
+        points[name + "_hbm_frac"] = round(r["bytes"] / (r["ms"] / 1e3) / 1e9 / peaks["hbm_gbs"], 3)
+
     if not args.skip_points:
         for b in (1, 64):
-            r = decode_run(b, max(3, min(args.steps, 10)), 3, e2e=False)
-            points[f"decode_b{b}"] = round(b / (r["ms"] / 1e3), 1)
-            points[f"decode_b{b}_hbm_frac"] = round(r["bytes"] / (r["ms"] / 1e3) / 1e9 / peaks["hbm_gbs"], 3)
+            point(f"decode_b{b}", b)
+    if "wide" in extra:
+        # the same decode steps on an engine that allows requests of 131072 tokens (the default when the pool is
+        # sized from free memory): the captured graphs are planned for the context in use, not for the widest request
+        point(f"decode_b{batch}_max_seq_131072", batch, max_seq_len=131072)
+    if "past_chunk" in extra and cfg.attention_chunk_size:
+        # just past a chunk start the rotary layers read almost no cache; only the NoPE layers read the history
+        C = cfg.attention_chunk_size
+        point(f"decode_b{batch}_just_past_{C}", batch, ctx_len=C + 512, start_len=C + 16)
+    if "ref_table" in extra:
+        # the settings of the reference's published table (llama4/README.md:73-77): context 4096, batch 1, 16, 32
+        for b in (1, 16, 32):
+            point(f"decode_b{b}_ctx4096", b, ctx_len=4096)
 
     # prefill of one 2,048-token prompt
     T = args.prefill_tokens
@@ -302,6 +330,51 @@ def run_ours(args) -> dict:
         del g, eng
         torch.cuda.empty_cache()
 
+    if "prefill4" in extra:
+        # four 2048-token prompts in one step: the routed experts get four times the rows each
+        g = J.Generator(model, max_tokens=4 * (T + page), page_size=page, max_slots=4, max_tokens_per_step=4 * T)
+        eng, ms = g.engine, []
+        for it in range(3 + 3):
+            ss = [eng.new_request() for _ in range(4)]
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ev0.record()
+            eng.step([J.StepEntry(x, [rng.randrange(cfg.vocab_size) for _ in range(T)], [T - 1]) for x in ss])
+            ev1.record()
+            torch.cuda.synchronize()
+            if it >= 3:
+                ms.append(ev0.elapsed_time(ev1))
+            for x in ss:
+                eng.finish(x)
+        eng.check_status()
+        m = sorted(ms)[len(ms) // 2]
+        points[f"prefill_4x{T}_tok_s"] = round(4 * T / (m / 1e3), 1)
+        points[f"prefill_4x{T}_ms"] = round(m, 3)
+        del g, eng
+        torch.cuda.empty_cache()
+    if "long" in extra:
+        # one long prompt in portions of T tokens (chunk starts crossed, pages of dead chunks given back), then 256
+        # decoded tokens; device-timed
+        L, n_dec = args.long_tokens, 256
+        g = J.Generator(model, max_tokens=L + n_dec + page, page_size=page, max_slots=1, max_tokens_per_step=T)
+        eng = g.engine
+        s = eng.new_request()
+        toks = [rng.randrange(cfg.vocab_size) for _ in range(L + n_dec)]
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        ev[0].record()
+        for a in range(0, L, T):
+            eng.step([J.StepEntry(s, toks[a:a + T], [T - 1] if a + T >= L else [])])
+        ev[1].record()
+        for i in range(n_dec):
+            eng.step([J.StepEntry(s, [toks[L + i]], [0])])
+        ev[2].record()
+        torch.cuda.synchronize()
+        eng.check_status()
+        points[f"long_{L}_prefill_tok_s"] = round(L / (ev[0].elapsed_time(ev[1]) / 1e3), 1)
+        points[f"long_{L}_decode_b1_tok_s"] = round(n_dec / (ev[1].elapsed_time(ev[2]) / 1e3), 1)
+        eng.finish(s)
+        del g, eng
+        torch.cuda.empty_cache()
+
     tok_s = batch / (main["ms"] / 1e3)
     achieved = main["bytes"] / (main["ms"] / 1e3) / 1e9
     return {
@@ -309,7 +382,7 @@ def run_ours(args) -> dict:
         "value": round(tok_s, 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(main["ms"], 3), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16",
-        "data": "synthetic: random N(0,0.02) weights, seeded uniform token ids, random cache contents",
+        "data": "synthetic: random N(0,0.02) weights, seeded uniform token ids (fresh ones every step), random cache contents",
         "config": {
             "model": "llama4-scout-layer-sizes" if args.preset == "scout16" else f"llama4-{args.preset}", "layers": cfg.num_hidden_layers, "layers_full_config": full_layers,
             "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
@@ -331,6 +404,60 @@ def run_ours(args) -> dict:
     }
 
 
+def run_reference(args) -> dict:
+    """The reference arm: the UNMODIFIED reference installed under baseline/_ref, through its own public calls
+    (``prefill`` then ``decode_step`` over a fixed batch, llama4/llama4_jax/model.py:1243-1277, the loop of
+    llama4/main.py:68-75), at the same layer sizes, batch and context, with its own random initialisation
+    (``Weights.init``) and its cache in bfloat16.  Nothing of this repository's engine is on that path.  Where the
+    reference cannot be imported or run here, the line says why, with the exception it raised."""
+    ref_root = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_root, "llama4_jax")):
+        return {"impl": "reference", "unavailable": f"the reference is not installed under {os.path.relpath(ref_root, ROOT)}"}
+    sys.path.insert(0, ref_root)
+    try:
+        import dataclasses
+
+        import jax
+        import jax.numpy as jnp
+        import numpy as np
+        from jax import random
+        from jax.sharding import AxisType
+        from llama4_jax import model as l4jax
+    except Exception as e:  # on this image: No module named 'jax' (not in the image, not in the offline wheelhouse)
+        return {"impl": "reference", "unavailable": f"import of llama4_jax from baseline/_ref failed: {type(e).__name__}: {e}"}
+    try:
+        import jax_llm_examples_b200 as J
+
+        text = J.preset(args.preset, num_hidden_layers=args.layers) if args.layers else J.preset(args.preset)
+        batch, ctx_len, steps, warmup = args.batch, args.context, args.steps, max(args.warmup, 3)
+        mesh = jax.make_mesh((1, 1, 1), ("x", "y", "z"), devices=jax.devices()[:1], axis_types=(AxisType.Explicit,) * 3)
+        cfg = l4jax.hf_to_jax_config(text)
+        cfg = dataclasses.replace(cfg, mesh=mesh, max_seq_len=ctx_len, quant_attn=False, quant_moe=False, quant_mlp=False,
+                                  quant_cache=False)
+        with jax.sharding.set_mesh(cfg.mesh):
+            weights = l4jax.Weights.init(random.key(0), cfg)
+            cache = l4jax.KVCache.init(random.key(1), cfg, batch, cfg.max_seq_len)
+            prompt = np.random.default_rng(0).integers(1, cfg.vocab_size, size=(batch, ctx_len - steps - warmup - 2))
+            next_tokens, _, cache = l4jax.prefill(jnp.asarray(prompt, dtype=jnp.int32), weights, cache, cfg)
+            cur = next_tokens[:, cache.iter - 1: cache.iter]
+            for _ in range(warmup):
+                cur, cache = l4jax.decode_step(cur, weights, cache, cfg)
+            np.asarray(cur)
+            t0 = time.perf_counter()
+            for _ in range(steps):
+                cur, cache = l4jax.decode_step(cur, weights, cache, cfg)
+                np.asarray(cur)  # the step's tokens on the host, as the reference's loop collects them
+            ms = (time.perf_counter() - t0) * 1e3 / steps
+        value = round(batch / (ms / 1e3), 1)
+        return {"impl": "reference", "metric": f"decode tok/s at batch {batch}, context {ctx_len}", "value": value, "unit": "tok/s",
+                "n_gpus": 1, "steps": steps, "warmup": warmup, "ms_per_step": round(ms, 3), "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic: the reference's own random weights, uniform token ids",
+                "config": {"model": args.preset, "layers": cfg.num_layers, "global_batch": batch, "seq_len": ctx_len, "parallelism": "none (1 GPU)"},
+                "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 4 * batch}}
+    except Exception as e:
+        return {"impl": "reference", "unavailable": f"the reference was imported but did not run: {type(e).__name__}: {str(e)[:300]}"}
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -343,12 +470,15 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=8192)
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--skip-points", action="store_true", help="skip the batch 1 and 64 points")
+    ap.add_argument("--extra-points", default="", help="comma list of further points: wide (an engine that allows 131072-token "
+                    "requests), past_chunk (decode just past a chunk start), ref_table (context 4096, batch 1/16/32), "
+                    "prefill4 (four prompts in one step), long (one --long-tokens prompt in portions, then 256 decoded tokens)")
+    ap.add_argument("--long-tokens", type=int, default=32768)
     ap.add_argument("--skip-e2e", action="store_true", help="skip the end-to-end run (for profiling captures)")
     ap.add_argument("--skip-prefill", action="store_true", help="skip the prefill measurement (for profiling captures)")
     args = ap.parse_args()
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable": "the reference (llama4_jax) installs offline only with --no-deps and "
-                          "cannot be imported: it needs jax, which is neither in this image nor in the offline wheelhouse"}))
+        print(json.dumps(run_reference(args)))
         return 0
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")

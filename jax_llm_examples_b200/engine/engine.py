@@ -17,6 +17,7 @@ import numpy as np
 import torch
 
 from ..cache.manager import CacheManager, OutOfPages
+from .. import tracing
 from ..kernels import api as K
 from ..parts.base import StepContext, StepShape, Workspace
 from ..parts.decoder import DecoderModel
@@ -192,7 +193,7 @@ class Engine:
                 extra[name] = np.ascontiguousarray(a, dtype=np.int32)
         extra_sizes = tuple((name, a.size) for name, a in extra.items())
         graph = None
-        if self.use_graphs and N == R and not self.record_routing and self._capturable:
+        if self.use_graphs and N == R and not self.record_routing and self._capturable and not tracing.active():
             # A graph freezes the launch shapes, among them the split plan of decode attention, which is laid out
             # for a longest request: one graph per (requests, wanted rows, bucket of the longest request in the step).
             bucket = self.kv_bucket(max_kv)

@@ -15,6 +15,7 @@ import torch
 
 from ..parts.decoder import DecoderModel
 from ..sampling.sampler import Sampler, SamplingParams, stream_of
+from ..tracing import KernelTimer
 from .engine import Engine, StepEntry
 from .scheduler import PlannedEntry, Request, Scheduler
 
@@ -24,7 +25,7 @@ class Generator:
 
     def __init__(self, model: DecoderModel, *, max_tokens: int, page_size: int = 64, max_slots: int = 64,
                  max_tokens_per_step: int = 2048, max_live: int | None = None, max_seq_len: int | None = None,
-                 seed: int = 0, profile: bool = False):
+                 seed: int = 0, profile: "bool | str" = False):
         self.engine = Engine(model, max_tokens=max_tokens, page_size=page_size, max_slots=max_slots,
                              max_seq_len=max_seq_len)
         self.sampler = Sampler(seed)
@@ -33,8 +34,11 @@ class Generator:
         self.h2d_bytes = 0
         self.d2h_bytes = 0
         self._next_id = 0
-        # profile=True: every step is timed on the host (the read of the sampled tokens ends it)
-        self.profile = profile
+        # profile=True: every step is timed on the host (the read of the sampled tokens ends it).
+        # profile="kernels": also, every kernel launch is bracketed with CUDA events (no graph replay meanwhile);
+        # ``kernel_timer.report()`` / ``.report("scope")`` give the times by kernel and by op group.
+        self.profile = bool(profile)
+        self.kernel_timer = KernelTimer() if profile == "kernels" else None
         self.step_times: list[tuple[int, int, float]] = []  # (prompt tokens, decode tokens, seconds)
 
     def _admit(self, r: Request) -> None:
@@ -47,6 +51,9 @@ class Generator:
             torch.cuda.synchronize()
             t0 = time.perf_counter()
         try:
+            if self.kernel_timer is not None:
+                with self.kernel_timer:
+                    return self._run_batch(entries, batch)
             return self._run_batch(entries, batch)
         finally:
             if self.profile:

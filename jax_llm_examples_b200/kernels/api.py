@@ -9,6 +9,7 @@ from ctypes import c_float, c_int, c_longlong, c_ulonglong, c_void_p
 
 import torch
 
+from .. import tracing
 from . import build
 
 F32, BF16 = 0, 1
@@ -89,7 +90,13 @@ def _stream():
 def _run(libname: str, fn: str, *args) -> None:
     global _launches
     lib = library(libname)
-    rc = getattr(lib, fn)(*args)
+    timer = tracing.current_timer()
+    if timer is None:
+        rc = getattr(lib, fn)(*args)
+    else:  # Generator(profile="kernels"): CUDA events around the launch
+        rc_box = []
+        timer.around(fn, lambda: rc_box.append(getattr(lib, fn)(*args)))
+        rc = rc_box[0]
     if rc != 0:
         raise KernelError(f"{fn}: {lib.jlx_last_error().decode()}")
     _launches += 1

@@ -42,6 +42,8 @@ def main(argv: list[str] | None = None) -> int:
     ap.add_argument("--max-tokens-per-step", type=int, default=2048, help="token budget of one step")
     ap.add_argument("--max-live", type=int, default=None, help="most requests in the cache at a time")
     ap.add_argument("--verbose", action="store_true")
+    ap.add_argument("--profile-kernels", action="store_true",
+                    help="time every kernel launch with CUDA events and print the times by kernel and by op group")
     args = ap.parse_args(argv)
 
     import jax_llm_examples_b200 as J
@@ -82,7 +84,7 @@ def main(argv: list[str] | None = None) -> int:
     max_tokens = args.max_tokens or sum(-(-(len(p) + args.max_new_tokens) // ps) * ps for p in prompts)
     gen = J.Generator(model, max_tokens=max_tokens, page_size=ps, max_slots=max(len(prompts), 1),
                       max_tokens_per_step=args.max_tokens_per_step, max_live=args.max_live, seed=args.seed,
-                      profile=args.verbose)
+                      profile="kernels" if args.profile_kernels else args.verbose)
     t0 = time.time()
     outputs = gen.generate(prompts, params)
     dt = time.time() - t0
@@ -90,6 +92,9 @@ def main(argv: list[str] | None = None) -> int:
     for p, o in zip(prompts, outputs):
         print(tokenizer.decode(o) if tokenizer else " ".join(map(str, o)))
         print("-" * 80)
+    if args.profile_kernels:
+        print("time by kernel entry point:\n" + gen.kernel_timer.report("kernel"), file=sys.stderr)
+        print("time by op group:\n" + gen.kernel_timer.report("scope"), file=sys.stderr)
     if args.verbose:
         n = sum(map(len, outputs))
         print(f"{n} tokens in {dt:.3f} s ({n / dt:.1f} tok/s), {gen.scheduler.step_count} steps, "

@@ -7,6 +7,7 @@ import torch
 
 from ..cache.manager import Retention
 from ..kernels import api as K
+from ..tracing import scope
 from .base import KVNeed, LayerCache, Mixer, PositionEncoding, Runtime, StepContext, StepShape, register_part
 from .linear import linear
 
@@ -98,12 +99,16 @@ class PagedAttention(Mixer):
 
     def forward(self, ctx: StepContext, h: torch.Tensor, cache: LayerCache) -> torch.Tensor:
         rt = ctx.runtime
-        qkv = linear(ctx, h, self.w_qkv, rt.dtype, partials=self.position.accepts_partials)
-        q = self.position.encode_and_store(ctx, qkv, self.n_heads, self.n_kv_heads, self.head_dim, cache, self.qk_norm_eps)
+        with scope("qkv_matmul"):  # the scopes carry the reference's names (model.py:906-954)
+            qkv = linear(ctx, h, self.w_qkv, rt.dtype, partials=self.position.accepts_partials)
+        with scope("rope"):  # with the q/k norm and the cache update (the reference's "cache_update") in one kernel
+            q = self.position.encode_and_store(ctx, qkv, self.n_heads, self.n_kv_heads, self.head_dim, cache, self.qk_norm_eps)
         attn_scale, floor_scale = self.position.query_temperature()
         out = torch.empty_like(q)
-        self.attend(ctx, q, cache, out, attn_scale, floor_scale)
-        return linear(ctx, out.view(q.shape[0], -1), self.w_o, torch.float32, partials=True)
+        with scope("attention"):
+            self.attend(ctx, q, cache, out, attn_scale, floor_scale)
+        with scope("projection"):
+            return linear(ctx, out.view(q.shape[0], -1), self.w_o, torch.float32, partials=True)
 
     def _split_kv(self, ctx: StepContext, q, cache: LayerCache, out, attn_scale, floor_scale, rows, n_rows: int) -> None:
         """Split-KV attention for requests that bring one token: all rows of q, or the listed ones."""

@@ -4,6 +4,7 @@ from __future__ import annotations
 
 import torch
 
+from ..tracing import scope
 from .base import Block, FeedForward, LayerCache, Mixer, Norm, StepContext, register_part
 
 
@@ -21,12 +22,15 @@ class PreNormBlock(Block):
 
     def forward(self, ctx: StepContext, x: torch.Tensor, delta, cache: LayerCache) -> torch.Tensor:
         dt = ctx.runtime.dtype
-        h = self.norm1.forward(ctx, x, delta, out_dtype=dt)[0]
+        with scope("attn_pre_norm"):  # the reference's names (model.py:1169-1180); each norm also adds the residual
+            h = self.norm1.forward(ctx, x, delta, out_dtype=dt)[0]
         a = self.mixer.forward(ctx, h, cache)
         want32 = self.feed_forward.needs_f32_input
         router = self.feed_forward.router_request() if self.norm2.fuses_router else None
-        h, h32, routing = self.norm2.forward(ctx, x, a, out_dtype=dt, want_f32=want32, router=router)
-        return self.feed_forward.forward(ctx, h, h32, routing)
+        with scope("attn_post_norm"):
+            h, h32, routing = self.norm2.forward(ctx, x, a, out_dtype=dt, want_f32=want32, router=router)
+        with scope("ffn"):
+            return self.feed_forward.forward(ctx, h, h32, routing)
 
 
 register_part("block", "pre_norm", PreNormBlock)

@@ -5,6 +5,7 @@ from __future__ import annotations
 import torch
 
 from ..kernels import api as K
+from ..tracing import scope
 from .base import FeedForward, Rows, StepContext, as_rows, register_part
 from .linear import (STREAM_MAX_ROWS, group_rows_hint, grouped_linear, grouped_swiglu_linear, interleave_gate_up, linear,
                      swiglu_linear)
@@ -30,8 +31,10 @@ class DenseSwiGLU(FeedForward):
         self.w_down = w_down
 
     def forward(self, ctx: StepContext, h, h32=None, routing=None):
-        act = swiglu_linear(ctx, h, self.w_gate_up, self.interleaved, ctx.runtime.dtype)
-        return linear(ctx, act, self.w_down, torch.float32, partials=True)
+        with scope("gate_up_proj"):  # the reference's "gate" and "up_proj" (model.py:1145-1149) as one product
+            act = swiglu_linear(ctx, h, self.w_gate_up, self.interleaved, ctx.runtime.dtype)
+        with scope("down_proj"):
+            return linear(ctx, act, self.w_down, torch.float32, partials=True)
 
 
 class RoutedExperts(FeedForward):
@@ -112,19 +115,25 @@ class RoutedExperts(FeedForward):
             ctx.scratch["record_routing"].append(topk_idx)
         merged = self.merged and n <= STREAM_MAX_ROWS
         extra = n if merged else 0
-        offsets, sorted_pair, sorted_pos, tiles = self.sort(ctx, topk_idx, extra)
-        a_sorted = torch.empty((n * k + extra, D), dtype=rt.dtype, device=h.device)
-        K.permute_scale(h32, sorted_pair, topk_w, a_sorted, k, extra)
-        groups = E + 1 if merged else E
-        act = grouped_swiglu_linear(ctx, a_sorted, self.we_gate_up[:groups], offsets, self.interleaved, rt.dtype, extra, tiles)
-        y = grouped_linear(ctx, act, self.we_down[:groups], offsets, torch.float32, partials=True, largest_group=extra,
-                           tiles=tiles)
+        with scope("moe_routed_expert"):  # the reference's names (model.py:1076-1138)
+            with scope("permute"):
+                offsets, sorted_pair, sorted_pos, tiles = self.sort(ctx, topk_idx, extra)
+                a_sorted = torch.empty((n * k + extra, D), dtype=rt.dtype, device=h.device)
+                K.permute_scale(h32, sorted_pair, topk_w, a_sorted, k, extra)
+            groups = E + 1 if merged else E
+            with scope("we_gate_up"):
+                act = grouped_swiglu_linear(ctx, a_sorted, self.we_gate_up[:groups], offsets, self.interleaved, rt.dtype, extra, tiles)
+            with scope("we_down"):
+                y = grouped_linear(ctx, act, self.we_down[:groups], offsets, torch.float32, partials=True, largest_group=extra,
+                                   tiles=tiles)
         shared = None
         if self.shared is not None and not merged:
-            shared = as_rows(self.shared.forward(ctx, h, None))
+            with scope("moe_shared_expert"):
+                shared = as_rows(self.shared.forward(ctx, h, None))
         delta = torch.empty((n, D), dtype=torch.float32, device=h.device)
-        K.moe_combine(y.data, None if shared is None else shared.data, sorted_pos, delta, k,
-                      1 if shared is None else shared.splits, y.splits, n * k if merged else -1)
+        with scope("unpermute"):  # with the reference's "expert_summing" in the same kernel
+            K.moe_combine(y.data, None if shared is None else shared.data, sorted_pos, delta, k,
+                          1 if shared is None else shared.splits, y.splits, n * k if merged else -1)
         return delta
 
 

@@ -182,3 +182,31 @@ def test_engine_sizes_its_pool_from_free_memory(model_dirs):
     logits = eng.step([J.StepEntry(s, [1, 2, 3], [2])])
     assert logits.shape == (1, 256)
     eng.finish(s)
+
+
+def test_kernel_timer_and_named_ranges(model_dirs):
+    """``Generator(profile="kernels")`` times every launch by kernel and by op group (under the reference's scope
+    names) and gives the same tokens; NVTX ranges can be switched on around the same scopes."""
+    import jax_llm_examples_b200 as J
+    from jax_llm_examples_b200 import tracing
+
+    model = J.load_model(model_dirs["tiny_c"], "float32")  # 32-bit: the same sums in the same order, traced or not
+    prompts = [[3, 4, 5] * 30, [7, 8]]
+    params = J.SamplingParams(max_new_tokens=6)
+    want = J.generate(model, prompts, params, page_size=16)
+    gen = J.Generator(model, max_tokens=512, page_size=16, max_slots=2, profile="kernels")
+    gen.engine.use_graphs = True
+    assert gen.generate(prompts, params) == want
+    assert gen.engine.graph_replays == 0  # a replayed graph would hide its launches from the timer
+    t = gen.kernel_timer
+    assert t.by_kernel["jlx_add_rmsnorm"][0] > 0 and t.by_kernel["jlx_add_rmsnorm"][1] > 0
+    for name in ("qkv_matmul", "rope", "attention", "projection", "attn_pre_norm", "attn_post_norm", "we_gate_up", "we_down", "unpermute"):
+        assert t.by_scope[name][0] > 0, name
+    assert "jlx_embed" in t.report() and "attention" in t.report("scope")
+    assert not tracing.active()
+    tracing.enable_nvtx(True)
+    try:
+        assert tracing.active()
+        assert J.generate(model, prompts, params, page_size=16) == want
+    finally:
+        tracing.enable_nvtx(False)
