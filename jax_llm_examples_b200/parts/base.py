@@ -80,6 +80,13 @@ class Workspace:
         self.device = device
         self._bufs: dict[str, torch.Tensor] = {}
         self._outgrown: list[torch.Tensor] = []
+        self._side: torch.cuda.Stream | None = None
+
+    def side_stream(self) -> torch.cuda.Stream:
+        """A second stream for work that is independent of what the step's own stream does next (made on first use)."""
+        if self._side is None:
+            self._side = torch.cuda.Stream(device=self.device)
+        return self._side
 
     def get(self, name: str, numel: int, dtype: torch.dtype) -> torch.Tensor:
         t = self._bufs.get(name)

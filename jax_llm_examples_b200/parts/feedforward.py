@@ -49,6 +49,7 @@ class RoutedExperts(FeedForward):
     kernel_libraries = ("moe", "elementwise", "gemm_simt")
     kernel_libraries_bf16 = ("gemm_stream",)
     needs_f32_input = True
+    OVERLAP_MIN_ROWS = 512  # from this many rows on, the shared expert runs on a second stream beside the routed ones
 
     def __init__(self, w_router: torch.Tensor, we_gate_up: torch.Tensor, we_down: torch.Tensor, top_k: int,
                  shared: DenseSwiGLU | None = None):
@@ -115,6 +116,16 @@ class RoutedExperts(FeedForward):
             ctx.scratch["record_routing"].append(topk_idx)
         merged = self.merged and n <= STREAM_MAX_ROWS
         extra = n if merged else 0
+        # Prompt portions: the routed experts stream their weights once for about a hundred rows each (bound by HBM),
+        # the shared expert's products are dense (bound by the tensor cores).  The shared expert runs on a second
+        # stream beside them, so that the tails and the small kernels of either side hide behind the other.
+        shared, side = None, None
+        if self.shared is not None and not merged and n >= self.OVERLAP_MIN_ROWS and ctx.workspace is not None:
+            main, side = torch.cuda.current_stream(), ctx.workspace.side_stream()
+            side.wait_stream(main)
+            with torch.cuda.stream(side), scope("moe_shared_expert"):
+                shared = as_rows(self.shared.forward(ctx, h, None))
+            shared.data.record_stream(main)  # made on the side stream, read (and freed) on the step's own
         with scope("moe_routed_expert"):  # the reference's names (model.py:1076-1138)
             with scope("permute"):
                 offsets, sorted_pair, sorted_pos, tiles = self.sort(ctx, topk_idx, extra)
@@ -126,8 +137,9 @@ class RoutedExperts(FeedForward):
             with scope("we_down"):
                 y = grouped_linear(ctx, act, self.we_down[:groups], offsets, torch.float32, partials=True, largest_group=extra,
                                    tiles=tiles)
-        shared = None
-        if self.shared is not None and not merged:
+        if side is not None:
+            torch.cuda.current_stream().wait_stream(side)
+        elif self.shared is not None and not merged:
             with scope("moe_shared_expert"):
                 shared = as_rows(self.shared.forward(ctx, h, None))
         delta = torch.empty((n, D), dtype=torch.float32, device=h.device)
