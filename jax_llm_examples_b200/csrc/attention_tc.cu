@@ -3,7 +3,7 @@
 // One block = 128 consecutive query tokens of one request and one query head.  Keys and values come from
 // the paged cache in tiles of 128 keys.  Per tile:
 //   S = Q K^T        tcgen05.mma, Q and K from shared memory (TMA, 128-byte swizzle), S in tensor memory
-//   P = softmax part two threads per query row read the halves of its row of S from tensor memory, keep the running
+//   P = softmax part PARTS threads per query row read their parts of its row of S from tensor memory, keep the running
 //                    max and sum in 32-bit, and write P (bfloat16, two keys per 32-bit column) back over the
 //                    first half of the same S buffer; when a row's maximum moved they rescale O
 //   O += P V         tcgen05.mma with P as the operand in tensor memory and V from shared memory as an MN-major
@@ -12,8 +12,8 @@
 // S is double-buffered in tensor memory, so the product of the next tile runs while this tile's softmax does.
 // MMAs run in the order of their issue: the score product of tile j+2, which overwrites the buffer of S_j and
 // P_j, is issued after O += P_j V_j and so needs no barrier of its own;
-// K and V tiles are double-buffered in shared memory.  Warp 0 issues TMA copies, warp 1 issues the MMAs,
-// warps 2..9 (two threads per query row = per tensor-memory lane, each half of the tile's keys) do softmax,
+// K and V tiles are double-buffered in shared memory.  Warp 0 issues TMA copies, warp 1 issues the MMAs, the other
+// warps (PARTS threads per query row = per tensor-memory lane, each a part of the tile's keys) do softmax,
 // rescaling and the final store.
 //
 // Mask, scale and softmax are those of llama4/llama4_jax/model.py:731-794 (causal, same chunk, optional
@@ -30,7 +30,9 @@
 #define DH 128
 #define BQ 128           // query rows per block
 #define BKV 128          // keys per tile
-#define NTHREADS 320     // warp 0: TMA, warp 1: MMA, warps 2..9: softmax (two per quarter of the query rows)
+#define PARTS 4          // softmax threads per query row: each takes BKV / PARTS of a tile's keys and DH / PARTS of O's columns
+#define NTHREADS (64 + 128 * PARTS)  // warp 0: TMA, warp 1: MMA, then PARTS softmax warps for each quarter of the query rows
+#define CP (BKV / PARTS)  // key columns of a tile per softmax thread
 #define WAIT_LIMIT JLX_WAIT_LIMIT
 #define NEG_BIG (-1.0e30f)
 
@@ -86,6 +88,13 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
         "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]),
         "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
         "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
       : "memory");
 }
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -147,8 +156,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   __shared__ __align__(8) uint64_t bars[19];
   __shared__ uint32_t tmem_slot;
   __shared__ int failed;
-  __shared__ float xmax[2][2][BQ];  // [tile parity][half of the keys][row]: what the two warps of a row exchange
-  __shared__ float xsum[2][BQ];
+  __shared__ float xmax[2][PARTS][BQ];  // [tile parity][part of the keys][row]: what the threads of a row exchange
+  __shared__ float xsum[PARTS][BQ];
   const uint32_t bar0 = smem_u32(&bars[0]);
   auto BAR = [bar0](int i) { return bar0 + 8u * i; };
 
@@ -169,11 +178,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     for (int i = 0; i < 9; ++i) mbar_init(BAR(i), 1);
     mbar_init(BAR(9), 1);
     mbar_init(BAR(10), 1);
-    mbar_init(BAR(11), 256);
+    mbar_init(BAR(11), 128 * PARTS);
     mbar_init(BAR(12), 1);
     mbar_init(BAR(13), 1);
     mbar_init(BAR(14), 1);
-    for (int i = 15; i < 19; ++i) mbar_init(BAR(i), 64);
+    for (int i = 15; i < 19; ++i) mbar_init(BAR(i), 32 * PARTS);
     failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -275,19 +284,21 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     }
   } else {
     // ------------------------------------------------------------------------------ softmax, rescale, store
-    // Warps 2..9: a warp reaches the tensor-memory lanes [32 * (warp & 3), +32), so two warps share each
-    // quarter of the query rows and split the tile's 128 key columns (and the output's 128 columns) in halves
-    // of 64.  The two meet once per tile to agree on the row's maximum; each keeps the sum of its own half.
-    const int quarter = warp & 3, half = (warp - 2) >> 2;
+    // A warp reaches the tensor-memory lanes [32 * (warp & 3), +32), so PARTS warps share each quarter of the query
+    // rows and split the tile's 128 key columns (and the output's 128 columns) among them.  The threads of a row
+    // meet once per tile to agree on the row's maximum; each keeps the sum of its own part.  More, narrower threads
+    // per row keep four warps on every scheduler: the chain load -> max -> exponentials -> store of one warp is
+    // full of waits that the others fill.
+    const int quarter = warp & 3, part = (warp - 2) >> 2;
     const int row = quarter * 32 + lane;             // query row = tensor-memory lane
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-    const int col0 = half * (BKV / 2);
+    const int col0 = part * CP;
     const bool live = row < cnt;
     const int p_row = p_first + min(row, cnt - 1);
     const int lo_row = first_key(p_row, P.chunk, P.window);
-    float sc = P.scale_log2;
+    float sc = P.scale_log2;  // positive: raw scores and scaled scores have their maximum at the same key
     if (P.attn_scale != 0.f) sc *= 1.f + P.attn_scale * log1pf(floorf(((float)p_row + 1.f) / P.floor_scale));
-    float m = NEG_BIG, l = 0.f;
+    float m = NEG_BIG, l = 0.f;  // the running maximum (of scaled scores, in powers of two) and this thread's sum
     bool ok = true;
     for (int j = 0; j < n_kv; ++j) {
       const int st = j & 1;
@@ -299,67 +310,68 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       const int tile_key = key_begin + j * BKV + col0;
       const bool need_mask = key_begin + j * BKV + BKV - 1 > p_first || key_begin + j * BKV < first_key(p_last, P.chunk, P.window);
       const uint32_t s_addr = tm_s0 + st * 128 + lane_addr + col0;
-      // this warp's 64 scores of the row come into registers once
-      uint32_t v[BKV / 2];
-      tmem_ld32(s_addr, v);
-      tmem_ld32(s_addr + 32, v + 32);
+      // this thread's raw scores of the row come into registers once
+      uint32_t v[CP];
+#pragma unroll
+      for (int c = 0; c < CP; c += 32) tmem_ld32(s_addr + c, v + c);
       tmem_ld_wait();
-      float mx4[4] = {NEG_BIG, NEG_BIG, NEG_BIG, NEG_BIG};  // four chains instead of one of 64 dependent steps
+      float mx4[4] = {NEG_BIG, NEG_BIG, NEG_BIG, NEG_BIG};  // four chains instead of one long chain of dependent steps
       if (need_mask) {
 #pragma unroll
-        for (int i = 0; i < BKV / 2; ++i) {
+        for (int i = 0; i < CP; ++i) {
           const int key = tile_key + i;
-          const float sv = (key >= lo_row && key <= p_row) ? __uint_as_float(v[i]) * sc : NEG_BIG;
+          const float sv = (key >= lo_row && key <= p_row) ? __uint_as_float(v[i]) : NEG_BIG;
           v[i] = __float_as_uint(sv);
           mx4[i & 3] = fmaxf(mx4[i & 3], sv);
         }
       } else {
 #pragma unroll
-        for (int i = 0; i < BKV / 2; ++i) {
-          const float sv = __uint_as_float(v[i]) * sc;
-          v[i] = __float_as_uint(sv);
-          mx4[i & 3] = fmaxf(mx4[i & 3], sv);
-        }
+        for (int i = 0; i < CP; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(v[i]));
       }
       float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      // the row's maximum over both halves (double-buffered by tile parity: the partner may be a tile ahead)
-      xmax[st][half][row] = mx;
+      // the row's maximum over all parts (double-buffered by tile parity: a partner may be a tile ahead)
+      xmax[st][part][row] = mx;
       mbar_arrive(BAR(15 + quarter));
       ok = mbar_wait(BAR(15 + quarter), j & 1);
       if (*(volatile int*)&failed) ok = false;
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
-      mx = fmaxf(m, fmaxf(mx, xmax[st][half ^ 1][row]));
+#pragma unroll
+      for (int q = 0; q < PARTS; ++q) mx = fmaxf(mx, xmax[st][q][row]);
+      // raw -> scaled; a row whose keys are all masked so far keeps NEG_BIG (NEG_BIG * sc does not overflow)
+      mx = fmaxf(m, mx > 0.5f * NEG_BIG ? mx * sc : NEG_BIG);
       const float corr = fast_exp2(m - mx);
-      // probabilities and their sum; a masked score is NEG_BIG and gives exactly 0, also in a row whose scores
-      // are all masked so far (mx = NEG_BIG)
+      // probabilities 2^(s * sc - mx) and their sum; a masked score gives exactly 0, also in a row whose scores are
+      // all masked so far (mx = NEG_BIG)
       float rs4[4] = {0.f, 0.f, 0.f, 0.f};
-      uint32_t packed[BKV / 4];
+      uint32_t packed[CP / 2];
       if (need_mask) {
 #pragma unroll
-        for (int i = 0; i < BKV / 2; i += 2) {
+        for (int i = 0; i < CP; i += 2) {
           const float s0 = __uint_as_float(v[i]), s1 = __uint_as_float(v[i + 1]);
-          const float p0 = s0 > 0.5f * NEG_BIG ? fast_exp2(s0 - mx) : 0.f, p1 = s1 > 0.5f * NEG_BIG ? fast_exp2(s1 - mx) : 0.f;
+          const float p0 = s0 > 0.5f * NEG_BIG ? fast_exp2(fmaf(s0, sc, -mx)) : 0.f;
+          const float p1 = s1 > 0.5f * NEG_BIG ? fast_exp2(fmaf(s1, sc, -mx)) : 0.f;
           rs4[(i >> 1) & 3] += p0 + p1;
           __nv_bfloat162 b2 = __floats2bfloat162_rn(p0, p1);
           packed[i >> 1] = *reinterpret_cast<uint32_t*>(&b2);
         }
       } else {
 #pragma unroll
-        for (int i = 0; i < BKV / 2; i += 2) {
-          const float p0 = fast_exp2(__uint_as_float(v[i]) - mx), p1 = fast_exp2(__uint_as_float(v[i + 1]) - mx);
+        for (int i = 0; i < CP; i += 2) {
+          const float p0 = fast_exp2(fmaf(__uint_as_float(v[i]), sc, -mx)), p1 = fast_exp2(fmaf(__uint_as_float(v[i + 1]), sc, -mx));
           rs4[(i >> 1) & 3] += p0 + p1;
           __nv_bfloat162 b2 = __floats2bfloat162_rn(p0, p1);
           packed[i >> 1] = *reinterpret_cast<uint32_t*>(&b2);
         }
       }
       const float rs = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
-      // P over the first half of this S buffer: keys 2c and 2c+1 in column c (the partner has read its scores:
-      // the two met after their loads)
-      tmem_st32(tm_s0 + st * 128 + lane_addr + half * (BKV / 4), packed);
+      // P over the first half of this S buffer: keys 2c and 2c+1 in column c (the partners have read their scores:
+      // they met after their loads)
+      if (CP == 64) tmem_st32(tm_s0 + st * 128 + lane_addr + part * (CP / 2), packed);
+      else tmem_st16(tm_s0 + st * 128 + lane_addr + part * (CP / 2), packed);
       l = l * corr + rs;
       m = mx;
-      // Rescale this warp's half of O's columns when a row of the warp moved its maximum; the product of the
+      // Rescale this thread's part of O's columns when a row of the warp moved its maximum; the product of the
       // previous tile must be complete first (nothing to rescale before the first product).
       if (j > 0 && !__all_sync(0xffffffffu, corr == 1.f)) {
         ok = mbar_wait(BAR(12), (j - 1) & 1);
@@ -369,7 +381,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         tc_fence_after();
         uint32_t o[32];
 #pragma unroll 1
-        for (int c0 = half * (DH / 2); c0 < (half + 1) * (DH / 2); c0 += 32) {
+        for (int c0 = part * (DH / PARTS); c0 < (part + 1) * (DH / PARTS); c0 += 32) {
           tmem_ld32(tm_o + lane_addr + c0, o);
           tmem_ld_wait();
 #pragma unroll
@@ -388,17 +400,20 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     }
     if (ok) {
       tc_fence_after();
-      // the row's sum is the sum of the halves' sums
-      xsum[half][row] = l;
+      // the row's sum is the sum of the parts' sums
+      xsum[part][row] = l;
       mbar_arrive(BAR(15 + quarter));
       ok = __all_sync(0xffffffffu, mbar_wait(BAR(15 + quarter), n_kv & 1));
     }
     if (ok) {
-      const float inv = 1.f / (xsum[0][row] + xsum[1][row]);
+      float total = 0.f;
+#pragma unroll
+      for (int q = 0; q < PARTS; ++q) total += xsum[q][row];
+      const float inv = 1.f / total;
       bf16* dst = P.out + ((size_t)(n0 + row) * P.Hq + head) * DH;
       uint32_t v[32];
 #pragma unroll 1
-      for (int c0 = half * (DH / 2); c0 < (half + 1) * (DH / 2); c0 += 32) {
+      for (int c0 = part * (DH / PARTS); c0 < (part + 1) * (DH / PARTS); c0 += 32) {
         tmem_ld32(tm_o + lane_addr + c0, v);
         tmem_ld_wait();
         if (live) {
