@@ -111,9 +111,56 @@ __device__ __forceinline__ void router_topk(float* scores, int E, int k, size_t 
   }
 }
 
+// What a norm adds to the residual stream before it normalises: up to DELTA_MAX_TERMS terms, added in the order given.
+// A term is `splits` float32 partials [z][rows][D] (z ascending, `stride` elements apart), of which token r takes row
+// base + r, or, with `index`, the k rows index[r * k + j], j ascending (an expert layer's rows in expert order: the
+// norm then does the un-permute and the sum over a token's experts that a kernel of its own would do).
+#define DELTA_MAX_TERMS 3
+struct DeltaTerm {
+  const float* p;
+  long long stride;
+  const int* index;
+  int splits, k, base;
+};
+struct DeltaSpec {
+  int n;
+  DeltaTerm t[DELTA_MAX_TERMS];
+};
+
+// The rows that token r adds, resolved once per block into shared memory: source i is `splits[i]` partials that lie
+// `stride[i]` elements apart, the first at ptr[i].  The kernels then walk the sources with several loads in flight.
+#define DELTA_MAX_SOURCES (DELTA_MAX_TERMS - 1 + 16)
+struct DeltaSources {
+  const float* ptr[DELTA_MAX_SOURCES];
+  long long stride[DELTA_MAX_SOURCES];
+  int splits[DELTA_MAX_SOURCES];
+  int n;
+};
+// Called by every thread; thread 0 fills `src`, a barrier follows.
+__device__ __forceinline__ void resolve_delta(DeltaSources& src, const DeltaSpec& ds, size_t r, int D) {
+  if (threadIdx.x == 0) {
+    int n = 0;
+#pragma unroll
+    for (int q = 0; q < DELTA_MAX_TERMS; ++q) {  // unrolled: the terms stay in the kernel's parameter space
+      if (q >= ds.n) break;
+      const DeltaTerm& t = ds.t[q];
+      const int rows = t.index ? t.k : 1;
+      for (int j = 0; j < rows && n < DELTA_MAX_SOURCES; ++j) {
+        const size_t row = t.index ? (size_t)t.index[r * t.k + j] : (size_t)t.base + r;
+        src.ptr[n] = t.p + row * D;
+        src.stride[n] = t.stride;
+        src.splits[n] = t.splits;
+        ++n;
+      }
+    }
+    src.n = n;
+  }
+  __syncthreads();
+}
+
 template <typename TO>
 __global__ void __launch_bounds__(1024)
-add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, int delta_splits, long long delta_stride,
+add_rmsnorm_kernel(float* __restrict__ x, const DeltaSpec ds,
                    const float* __restrict__ gamma, float eps, TO* __restrict__ out, float* __restrict__ out32,
                    const int* __restrict__ row_index, int D, int row_in_smem, const float* __restrict__ w_router, int E,
                    int k, int* __restrict__ topk_idx, float* __restrict__ topk_w) {
@@ -126,16 +173,18 @@ add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, int d
   const int n = blockIdx.x;
   const size_t r = row_index ? (size_t)row_index[n] : (size_t)n;
   float* xr = x + r * D;
-  const float* dr = delta ? delta + r * D : nullptr;
+  const bool has_delta = ds.n > 0;
+  __shared__ DeltaSources src;
+  if (has_delta) resolve_delta(src, ds, r, D);
   float ss = 0.f;
   // 16-byte accesses when the row allows it (width a multiple of 4, row kept in shared memory)
-  const bool vec = row_in_smem && (D & 3) == 0 && (delta_stride & 3) == 0;
+  bool vec = row_in_smem && (D & 3) == 0;
+#pragma unroll
+  for (int q = 0; q < DELTA_MAX_TERMS; ++q) vec = vec && (q >= ds.n || (ds.t[q].stride & 3) == 0);
   if (vec) {
     const int D4 = D >> 2;
     float4* x4 = reinterpret_cast<float4*>(xr);
-    const float4* d4 = reinterpret_cast<const float4*>(dr);
     float4* row4 = reinterpret_cast<float4*>(rowbuf);
-    const long long stride4 = delta_stride >> 2;
     // four 16-byte loads of the residual (and of each partial) in flight per thread
     for (int i0 = threadIdx.x; i0 < D4; i0 += 4 * blockDim.x) {
       float4 s[4];
@@ -144,14 +193,18 @@ add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, int d
         const int i = i0 + u * blockDim.x;
         s[u] = i < D4 ? x4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
       }
-      if (dr) {
-        for (int z = 0; z < delta_splits; ++z) {
+      if (has_delta) {
+        for (int q = 0; q < src.n; ++q) {
+          const float4* d4 = reinterpret_cast<const float4*>(src.ptr[q]);
+          const long long stride4 = src.stride[q] >> 2;
+          for (int z = 0; z < src.splits[q]; ++z) {
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const int i = i0 + u * blockDim.x;
-            if (i < D4) {
-              const float4 v = d4[(size_t)z * stride4 + i];
-              s[u].x += v.x; s[u].y += v.y; s[u].z += v.z; s[u].w += v.w;
+            for (int u = 0; u < 4; ++u) {
+              const int i = i0 + u * blockDim.x;
+              if (i < D4) {
+                const float4 v = d4[(size_t)z * stride4 + i];
+                s[u].x += v.x; s[u].y += v.y; s[u].z += v.z; s[u].w += v.w;
+              }
             }
           }
         }
@@ -160,7 +213,7 @@ add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, int d
       for (int u = 0; u < 4; ++u) {
         const int i = i0 + u * blockDim.x;
         if (i < D4) {
-          if (dr && !row_index) x4[i] = s[u];
+          if (has_delta && !row_index) x4[i] = s[u];
           row4[i] = s[u];
           ss += (s[u].x * s[u].x + s[u].y * s[u].y) + (s[u].z * s[u].z + s[u].w * s[u].w);
         }
@@ -180,8 +233,9 @@ add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, int d
   } else {
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
       float s = xr[d];
-      if (dr) {
-        for (int z = 0; z < delta_splits; ++z) s += dr[(size_t)z * delta_stride + d];
+      if (has_delta) {
+        for (int q = 0; q < src.n; ++q)
+          for (int z = 0; z < src.splits[q]; ++z) s += src.ptr[q][(size_t)z * src.stride[q] + d];
         if (!row_index) xr[d] = s;
       }
       if (row_in_smem) rowbuf[d] = s;
@@ -195,8 +249,9 @@ add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, int d
         s = rowbuf[d];
       } else {
         s = xr[d];
-        if (dr && row_index)
-          for (int z = 0; z < delta_splits; ++z) s += dr[(size_t)z * delta_stride + d];
+        if (has_delta && row_index)
+          for (int q = 0; q < src.n; ++q)
+            for (int z = 0; z < src.splits[q]; ++z) s += src.ptr[q][(size_t)z * src.stride[q] + d];
       }
       const float v = (gamma ? gamma[d] * s : s) / rms;
       if (out) out[(size_t)n * D + d] = from_f32<TO>(v);
@@ -224,7 +279,7 @@ add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, int d
 // the order of the sums differs from the one-block kernel's, which the 32-bit path must not depend on.
 template <typename TO>
 __global__ void __launch_bounds__(512)
-add_rmsnorm_router_cluster_kernel(float* __restrict__ x, const float* __restrict__ delta, int delta_splits, long long delta_stride,
+add_rmsnorm_router_cluster_kernel(float* __restrict__ x, const DeltaSpec ds,
                                   const float* __restrict__ gamma, float eps, TO* __restrict__ out, float* __restrict__ out32, int D,
                                   int slice,
                                   const float* __restrict__ w_router, int E, int k, int* __restrict__ topk_idx,
@@ -243,16 +298,20 @@ add_rmsnorm_router_cluster_kernel(float* __restrict__ x, const float* __restrict
   const int n = blockIdx.x / C;
   const int lo = min(D, rank * slice), hi = min(D, lo + slice);  // multiples of 4
   float4* x4 = reinterpret_cast<float4*>(x + (size_t)n * D);
-  const float4* d4 = delta ? reinterpret_cast<const float4*>(delta + (size_t)n * D) : nullptr;
   float4* row4 = reinterpret_cast<float4*>(rowbuf);
-  const long long stride4 = delta_stride >> 2;
+  __shared__ DeltaSources src;
+  if (ds.n > 0) resolve_delta(src, ds, (size_t)n, D);
   float ss = 0.f;
   for (int i = (lo >> 2) + threadIdx.x; i < (hi >> 2); i += blockDim.x) {
     float4 s = x4[i];
-    if (d4) {
-      for (int z = 0; z < delta_splits; ++z) {
-        const float4 v = d4[(size_t)z * stride4 + i];
-        s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+    if (ds.n > 0) {
+      for (int q = 0; q < src.n; ++q) {
+        const float4* d4 = reinterpret_cast<const float4*>(src.ptr[q]);
+        const long long stride4 = src.stride[q] >> 2;
+        for (int z = 0; z < src.splits[q]; ++z) {
+          const float4 v = d4[(size_t)z * stride4 + i];
+          s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+        }
       }
       x4[i] = s;
     }
@@ -295,12 +354,20 @@ add_rmsnorm_router_cluster_kernel(float* __restrict__ x, const float* __restrict
   cluster.sync();  // every block's shared memory stays alive until block 0 has read it
 }
 
-JLX_API int jlx_add_rmsnorm(float* x, const float* delta, int delta_splits, long long delta_stride, const float* gamma,
+// delta: what to add to x first (null: nothing), see DeltaSpec; the struct is read on the host.
+JLX_API int jlx_add_rmsnorm(float* x, const DeltaSpec* delta, const float* gamma,
                             float eps, void* out, int out_dtype, float* out32, const int* row_index, int N, int D,
                             const float* w_router, int E, int k, int* topk_idx, float* topk_w, cudaStream_t stream) {
   JLX_REQUIRE(N >= 0 && D > 0, "add_rmsnorm: bad sizes N=%d D=%d", N, D);
   JLX_REQUIRE(eps > 0.f, "add_rmsnorm: eps must be positive");
-  JLX_REQUIRE(!delta || delta_splits >= 1, "add_rmsnorm: bad split count");
+  DeltaSpec ds = {};
+  if (delta) ds = *delta;
+  JLX_REQUIRE(ds.n >= 0 && ds.n <= DELTA_MAX_TERMS, "add_rmsnorm: %d terms to add; up to %d are supported", ds.n, DELTA_MAX_TERMS);
+  bool aligned = true;
+  for (int q = 0; q < ds.n; ++q) {
+    JLX_REQUIRE(ds.t[q].p && ds.t[q].splits >= 1 && (!ds.t[q].index || (ds.t[q].k >= 1 && ds.t[q].k <= 16)), "add_rmsnorm: bad term %d", q);
+    aligned = aligned && (ds.t[q].stride & 3) == 0 && ((uintptr_t)ds.t[q].p & 15) == 0;
+  }
   if (N == 0) return 0;
   const int row_in_smem = (size_t)D * 4 <= 64 * 1024;
   if (w_router) {
@@ -311,8 +378,8 @@ JLX_API int jlx_add_rmsnorm(float* x, const float* delta, int delta_splits, long
   }
   const size_t smem = row_in_smem ? (size_t)D * 4 : 0;
   // A few rows with a router: a cluster of 8 blocks per row (all rows resident at once), bfloat16 output only.
-  if (w_router && out_dtype == JLX_BF16 && !row_index && out && N <= 32 && (D & 3) == 0 && D >= 1024 && (delta_stride & 3) == 0 &&
-      (((uintptr_t)x | (uintptr_t)delta | (uintptr_t)gamma | (uintptr_t)out | (uintptr_t)out32) & 15) == 0) {
+  if (w_router && out_dtype == JLX_BF16 && !row_index && out && N <= 32 && (D & 3) == 0 && D >= 1024 && aligned &&
+      (((uintptr_t)x | (uintptr_t)gamma | (uintptr_t)out | (uintptr_t)out32) & 15) == 0) {
     const int C = 8;
     const int slice = ((D / 4 + C - 1) / C) * 4;
     cudaLaunchConfig_t cfg = {};
@@ -329,7 +396,7 @@ JLX_API int jlx_add_rmsnorm(float* x, const float* delta, int delta_splits, long
     attr[1].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 2;
-    JLX_CUDA(cudaLaunchKernelEx(&cfg, add_rmsnorm_router_cluster_kernel<bf16>, x, delta, delta_splits, delta_stride, gamma, eps,
+    JLX_CUDA(cudaLaunchKernelEx(&cfg, add_rmsnorm_router_cluster_kernel<bf16>, x, ds, gamma, eps,
                                 (bf16*)out, out32, D, slice, w_router, E, k, topk_idx, topk_w));
     JLX_LAUNCH_CHECK("add_rmsnorm (cluster)");
     return 0;
@@ -345,7 +412,7 @@ JLX_API int jlx_add_rmsnorm(float* x, const float* delta, int delta_splits, long
     // not change with the number of rows that happen to share its step.
     const bool exact = out_dtype == JLX_F32;
     const int threads = (D >= 2048 && (exact || N <= 256)) ? 1024 : 256;
-    JLX_CUDA(jlx_launch_pdl(add_rmsnorm_kernel<TO>, dim3(N), dim3(threads), smem, stream, x, delta, delta_splits, delta_stride,
+    JLX_CUDA(jlx_launch_pdl(add_rmsnorm_kernel<TO>, dim3(N), dim3(threads), smem, stream, x, ds,
                             gamma, eps, (TO*)out, out32, row_index, D, row_in_smem, w_router, E, k, topk_idx, topk_w));
   });
   JLX_LAUNCH_CHECK("add_rmsnorm");

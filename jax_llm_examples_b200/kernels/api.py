@@ -123,28 +123,49 @@ def _splits(t: torch.Tensor | None, splits: int) -> tuple[int, int]:
     return splits, t.numel() // splits
 
 
-def add_rmsnorm(x: torch.Tensor, delta: torch.Tensor | None, gamma: torch.Tensor | None, eps: float,
+DELTA_MAX_TERMS = 3
+
+
+class _DeltaTerm(ctypes.Structure):
+    _fields_ = [("p", c_void_p), ("stride", c_longlong), ("index", c_void_p), ("splits", c_int), ("k", c_int), ("base", c_int)]
+
+
+class _DeltaSpec(ctypes.Structure):
+    _fields_ = [("n", c_int), ("t", _DeltaTerm * DELTA_MAX_TERMS)]
+
+
+def add_rmsnorm(x: torch.Tensor, delta, gamma: torch.Tensor | None, eps: float,
                 out: torch.Tensor | None, out32: torch.Tensor | None = None, row_index: torch.Tensor | None = None,
                 delta_splits: int = 1, w_router: torch.Tensor | None = None, topk_idx: torch.Tensor | None = None,
                 topk_w: torch.Tensor | None = None) -> None:
-    """x (+= delta); out = gamma * x / sqrt(mean(x^2) + eps).  ``delta`` may hold ``delta_splits`` split-K
-    partials [splits, N, D] that are added in order.  With row_index, row n reads source row row_index[n]
-    and x is not written back.  With w_router [E, D] the token is routed in the same kernel:
-    topk_idx / topk_w [N, k]."""
-    _contig(x, delta, gamma, out, out32, row_index, w_router, topk_idx, topk_w)
+    """x (+= delta); out = gamma * x / sqrt(mean(x^2) + eps).  ``delta``: a float32 tensor that may hold
+    ``delta_splits`` split-K partials [splits, N, D], added in order; or a list of up to DELTA_MAX_TERMS terms
+    ``(data, splits, index, k, base)`` added in the order given: of the float32 partials ``data`` [splits, rows, D]
+    token r takes row ``base + r`` or, with ``index`` (int32 [N * k]), the k rows ``index[r * k + j]``.
+    With row_index, row n reads source row row_index[n] and x is not written back.  With w_router [E, D] the token
+    is routed in the same kernel: topk_idx / topk_w [N, k]."""
+    terms = [] if delta is None else (list(delta) if isinstance(delta, (list, tuple)) else [(delta, delta_splits, None, 1, 0)])
+    _contig(x, gamma, out, out32, row_index, w_router, topk_idx, topk_w, *(t[0] for t in terms), *(t[2] for t in terms))
     D = x.shape[-1]
     n = row_index.numel() if row_index is not None else x.numel() // D
-    if x.dtype != torch.float32 or (delta is not None and delta.dtype != torch.float32):
+    if x.dtype != torch.float32 or any(t[0].dtype != torch.float32 for t in terms):
         raise KernelError("add_rmsnorm: the residual stream must be float32")
     if gamma is not None and gamma.dtype != torch.float32:
         raise KernelError("add_rmsnorm: the norm weight must be float32")
-    ds, dstride = _splits(delta, delta_splits)
+    if len(terms) > DELTA_MAX_TERMS:
+        raise KernelError(f"add_rmsnorm: {len(terms)} terms to add; up to {DELTA_MAX_TERMS} are supported")
+    spec = _DeltaSpec()
+    spec.n = len(terms)
+    for q, (data, splits, index, k_rows, base) in enumerate(terms):
+        sp, stride = _splits(data, splits)
+        spec.t[q].p, spec.t[q].stride, spec.t[q].splits = data.data_ptr(), stride, sp
+        spec.t[q].index, spec.t[q].k, spec.t[q].base = (index.data_ptr() if index is not None else None), k_rows, base
     E = k = 0
     if w_router is not None:
         if w_router.dtype != torch.float32 or topk_idx is None or topk_w is None:
             raise KernelError("router: float32 weight and outputs are needed")
         E, k = w_router.shape[0], topk_idx.shape[1]
-    _run("elementwise", "jlx_add_rmsnorm", _ptr(x), _ptr(delta), c_int(ds), c_longlong(dstride), _ptr(gamma), c_float(eps),
+    _run("elementwise", "jlx_add_rmsnorm", _ptr(x), ctypes.byref(spec) if terms else None, _ptr(gamma), c_float(eps),
          _ptr(out), c_int(code(out.dtype) if out is not None else F32), _ptr(out32), _ptr(row_index), c_int(n), c_int(D),
          _ptr(w_router), c_int(E), c_int(k), _ptr(topk_idx), _ptr(topk_w), _stream())
 

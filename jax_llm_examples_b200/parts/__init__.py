@@ -1,5 +1,5 @@
 from .attention import PagedAttention, plan_attention_tiles
-from .base import (Block, FeedForward, KVNeed, LayerCache, Mixer, Norm, Part, PositionEncoding, Rows, Runtime, StateNeed,
+from .base import (Block, FeedForward, KVNeed, LayerCache, Mixer, Norm, Part, PositionEncoding, Rows, RowSum, Runtime, StateNeed,
                    StepContext, StepShape, Workspace, as_rows, known_parts, make_part, register_part)
 from .block import PreNormBlock
 from .decoder import CachePlan, DecoderModel, LayerRun
@@ -11,6 +11,6 @@ from .positions import InterleavedRope, NoPositionWithTemperature, UnfusedEncodi
 __all__ = [
     "Block", "CachePlan", "DecoderModel", "DenseSwiGLU", "FeedForward", "InterleavedRope", "KVNeed", "LayerCache",
     "LayerRun", "Mixer", "NoPositionWithTemperature", "Norm", "PagedAttention", "Part", "PositionEncoding",
-    "PreNormBlock", "RMSNorm", "RoutedExperts", "Rows", "Runtime", "Workspace", "as_rows", "grouped_swiglu_linear", "interleave_gate_up", "swiglu_linear", "StateNeed", "StepContext", "StepShape", "plan_attention_tiles", "UnfusedEncoding",
+    "PreNormBlock", "RMSNorm", "RoutedExperts", "Rows", "RowSum", "Runtime", "Workspace", "as_rows", "grouped_swiglu_linear", "interleave_gate_up", "swiglu_linear", "StateNeed", "StepContext", "StepShape", "plan_attention_tiles", "UnfusedEncoding",
     "grouped_linear", "known_parts", "linear", "llama3_scaled_frequencies", "make_part", "register_part",
 ]

@@ -59,15 +59,33 @@ class StateNeed:
 @dataclasses.dataclass
 class Rows:
     """Token rows that may still be split-K partials: ``data`` is [N, D], or float32 [splits, N, D] whose
-    slices the consumer adds in ascending order (saving the launch that would add them)."""
+    slices the consumer adds in ascending order (saving the launch that would add them).
+
+    As a term of a :class:`RowSum` the rows may also lie elsewhere in ``data``: token r's row is ``base + r``, or,
+    with ``index`` (int32 [N * k]), the sum of the k rows ``index[r * k + j]``, j ascending."""
 
     data: torch.Tensor
     splits: int = 1
+    index: torch.Tensor | None = None
+    k: int = 1
+    base: int = 0
 
 
-def as_rows(x: "torch.Tensor | Rows | None") -> "Rows | None":
+@dataclasses.dataclass
+class RowSum:
+    """A delta that is still a sum of terms, added in this order by a consumer that can (the RMSNorm kernel: it then
+    does an expert layer's un-permute and sum, and no kernel runs for them alone).  ``materialize()`` makes the plain
+    [N, D] float32 tensor for a consumer that cannot: :func:`as_rows` calls it."""
+
+    terms: list[Rows]
+    materialize: Callable[[], torch.Tensor]
+
+
+def as_rows(x: "torch.Tensor | Rows | RowSum | None") -> "Rows | None":
     if x is None or isinstance(x, Rows):
         return x
+    if isinstance(x, RowSum):
+        return Rows(x.materialize(), 1)
     return Rows(x, 1)
 
 

@@ -6,7 +6,7 @@ import torch
 
 from ..kernels import api as K
 from ..tracing import scope
-from .base import FeedForward, Rows, StepContext, as_rows, register_part
+from .base import FeedForward, Rows, RowSum, StepContext, as_rows, register_part
 from .linear import (STREAM_MAX_ROWS, group_rows_hint, grouped_linear, grouped_swiglu_linear, interleave_gate_up, linear,
                      swiglu_linear)
 
@@ -142,11 +142,22 @@ class RoutedExperts(FeedForward):
         elif self.shared is not None and not merged:
             with scope("moe_shared_expert"):
                 shared = as_rows(self.shared.forward(ctx, h, None))
-        delta = torch.empty((n, D), dtype=torch.float32, device=h.device)
-        with scope("unpermute"):  # with the reference's "expert_summing" in the same kernel
-            K.moe_combine(y.data, None if shared is None else shared.data, sorted_pos, delta, k,
-                          1 if shared is None else shared.splits, y.splits, n * k if merged else -1)
-        return delta
+        def combine() -> torch.Tensor:
+            delta = torch.empty((n, D), dtype=torch.float32, device=h.device)
+            with scope("unpermute"):  # with the reference's "expert_summing" in the same kernel
+                K.moe_combine(y.data, None if shared is None else shared.data, sorted_pos, delta, k,
+                              1 if shared is None else shared.splits, y.splits, n * k if merged else -1)
+            return delta
+
+        # The un-permute and the sum over a token's experts are left to the consumer (the next norm adds the rows
+        # where it adds the residual); the order is the combine kernel's: shared expert, then the experts by choice.
+        if y.data.dtype != torch.float32 or (shared is not None and shared.data.dtype != torch.float32):
+            return combine()
+        terms = [shared] if shared is not None else []
+        if merged:
+            terms.append(Rows(y.data, y.splits, None, 1, n * k))
+        terms.append(Rows(y.data, y.splits, sorted_pos, k, 0))
+        return RowSum(terms, combine)
 
 
 register_part("feed_forward", "dense_swiglu", DenseSwiGLU)

@@ -5,7 +5,7 @@ from __future__ import annotations
 import torch
 
 from ..kernels import api as K
-from .base import Norm, StepContext, as_rows, register_part
+from .base import Norm, RowSum, StepContext, as_rows, register_part
 
 
 class RMSNorm(Norm):
@@ -26,7 +26,12 @@ class RMSNorm(Norm):
         dev = x.device
         out = torch.empty((n, x.shape[1]), dtype=out_dtype, device=dev)
         out32 = torch.empty((n, x.shape[1]), dtype=torch.float32, device=dev) if want_f32 else None
-        d = as_rows(delta)
+        # a sum of terms (an expert layer's rows still in expert order) is added term by term in the kernel
+        if isinstance(delta, RowSum) and len(delta.terms) <= K.DELTA_MAX_TERMS:
+            terms = [(t.data, t.splits, t.index, t.k, t.base) for t in delta.terms]
+        else:
+            d = as_rows(delta)
+            terms = None if d is None else [(d.data, d.splits, None, 1, 0)]
         routing = None
         w_router = idx = wt = None
         unfused = False
@@ -41,8 +46,7 @@ class RMSNorm(Norm):
             unfused = out_dtype == torch.bfloat16 and n > self.FUSED_ROUTER_MAX_ROWS and x.shape[1] % 4 == 0
             if unfused and out32 is None:
                 out32 = torch.empty((n, x.shape[1]), dtype=torch.float32, device=dev)
-        K.add_rmsnorm(x, None if d is None else d.data, self.weight, self.eps, out, out32, row_index,
-                      1 if d is None else d.splits, None if unfused else w_router, idx, wt)
+        K.add_rmsnorm(x, terms, self.weight, self.eps, out, out32, row_index, 1, None if unfused else w_router, idx, wt)
         if unfused:
             K.router(out32, w_router, idx, wt, many_rows=True)
         return out, out32, routing

@@ -67,7 +67,9 @@ def plain_logits(model_dir, tokens, routing: dict[int, np.ndarray] | None = None
 
 
 def as_rows_sum(x) -> torch.Tensor:
-    """What a part returned, as one tensor: split-K partials are added."""
+    """What a part returned, as one tensor: split-K partials are added, a sum of terms is made."""
+    if hasattr(x, "materialize"):
+        return x.materialize()
     data, splits = (x.data, x.splits) if hasattr(x, "splits") else (x, 1)
     return data.sum(0) if splits > 1 or data.dim() == 3 else data
 

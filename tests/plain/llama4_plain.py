@@ -96,8 +96,12 @@ def apply_rope_interleaved(x: torch.Tensor, positions: torch.Tensor, inv_freq: t
 
 
 def attention_temperature(positions: torch.Tensor, floor_scale: float, attn_scale: float) -> torch.Tensor:
-    """DEVIATION (not in the reference): query scale on NoPE layers,
-    1 + attn_scale * ln(1 + floor((p + 1) / floor_scale)), p the query's absolute position."""
+    """DEVIATION (the reference has no temperature): query scale on NoPE layers,
+    1 + attn_scale * ln(1 + floor((p + 1) / floor_scale)), p the query's absolute position.
+    Where the definition comes from: this build's task statement names attention-temperature tuning on the NoPE
+    layers with the constants floor_scale and attn_scale (config.json's ``attn_temperature_tuning``,
+    ``floor_scale``, ``attn_scale``; Llama 4 Scout ships 8192 and 0.1); the formula is the one published with the
+    Llama 4 models for those keys.  No line of jax-ml/jax-llm-examples states it, so nothing there can be cited."""
     p = positions.to(torch.float32)
     return torch.log1p(torch.floor((p + 1.0) / floor_scale)) * attn_scale + 1.0
 

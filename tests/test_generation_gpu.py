@@ -200,7 +200,7 @@ def test_kernel_timer_and_named_ranges(model_dirs):
     assert gen.engine.graph_replays == 0  # a replayed graph would hide its launches from the timer
     t = gen.kernel_timer
     assert t.by_kernel["jlx_add_rmsnorm"][0] > 0 and t.by_kernel["jlx_add_rmsnorm"][1] > 0
-    for name in ("qkv_matmul", "rope", "attention", "projection", "attn_pre_norm", "attn_post_norm", "we_gate_up", "we_down", "unpermute"):
+    for name in ("qkv_matmul", "rope", "attention", "projection", "attn_pre_norm", "attn_post_norm", "we_gate_up", "we_down", "permute"):
         assert t.by_scope[name][0] > 0, name
     assert "jlx_embed" in t.report() and "attention" in t.report("scope")
     assert not tracing.active()

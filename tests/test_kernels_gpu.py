@@ -721,3 +721,44 @@ def test_attention_prefill_tc(Hq, Hkv, page, chunk, window, temp):
         ref = _attention_ref(q[at:at + n], ks[r], vs[r], pos[at:at + n].long(), chunk, window, dh ** -0.5, attn_scale, floor_scale)
         close(out[at:at + n], ref, 1.5e-2)
         at += n
+
+
+@pytest.mark.parametrize("out_dtype, tol", [(torch.float32, 2e-6), (torch.bfloat16, 5e-3)])
+@pytest.mark.parametrize("N, D, k, E", [(5, 5120, 1, 16), (70, 200, 2, 8), (3, 1030, 3, 4)])
+def test_add_rmsnorm_adds_a_sum_of_terms_with_gathered_rows(out_dtype, tol, N, D, k, E):
+    """The norm adds an expert layer's output while it is still in expert order: a plain term with split-K partials
+    (a shared expert), a term at a row offset (a shared expert riding as the last group), and a term whose k rows per
+    token are gathered by an index; in that order, as the combine kernel would."""
+    g = torch.Generator(device=DEV).manual_seed(N)
+    x = torch.randn(N, D, device=DEV, generator=g)
+    gamma = 1 + 0.1 * torch.randn(D, device=DEV, generator=g)
+    shared = torch.randn(2, N, D, device=DEV, generator=g)
+    rows = N * k + N
+    y = torch.randn(3, rows, D, device=DEV, generator=g)
+    pos = torch.randperm(N * k, device=DEV).to(torch.int32)  # sorted row of each (token, choice) pair
+    terms = [(shared, 2, None, 1, 0), (y, 3, None, 1, N * k), (y, 3, pos, k, 0)]
+    ref = x + shared.sum(0) + y.sum(0)[N * k:] + y.sum(0)[pos.long()].reshape(N, k, D).sum(1)
+    want = gamma * ref / torch.sqrt((ref * ref).mean(-1, keepdim=True) + 1e-5)
+    out = torch.empty(N, D, device=DEV, dtype=out_dtype)
+    out32 = torch.empty(N, D, device=DEV)
+    x1 = x.clone()
+    K().add_rmsnorm(x1, terms, gamma, 1e-5, out, out32)
+    close(x1, ref, 2e-6)
+    close(out, want, tol)
+    close(out32, want, 2e-6)
+    # the wanted rows only (the final norm): x is left alone
+    idx = torch.tensor([N - 1, 0], device=DEV, dtype=torch.int32)
+    x2, out2 = x.clone(), torch.empty(2, D, device=DEV, dtype=out_dtype)
+    K().add_rmsnorm(x2, terms, gamma, 1e-5, out2, None, idx)
+    assert torch.equal(x2, x)
+    close(out2, want[idx.long()], tol)
+    # with the router in the same kernel (a cluster of blocks per row for few wide rows in bfloat16)
+    w_router = torch.randn(E, D, device=DEV, generator=g)
+    ti, tw = torch.empty(N, 1, device=DEV, dtype=torch.int32), torch.empty(N, 1, device=DEV)
+    x3 = x.clone()
+    K().add_rmsnorm(x3, terms, gamma, 1e-5, out, out32, None, 1, w_router, ti, tw)
+    close(x3, ref, 2e-6)
+    close(out32, want, 2e-6)
+    scores = want @ w_router.T
+    chosen = torch.gather(scores, 1, ti.long())
+    assert float((scores.max(-1, keepdim=True).values - chosen).max()) < 1e-3 * float(scores.abs().max())

@@ -1,9 +1,9 @@
 """Layers of Llama 4 Scout's sizes (width 5120, 40 query / 8 KV heads of 128, expert width 8192) against
-the plain implementation: four layers (rotary and chunked, but the third, which is NoPE with temperature), 4
-experts and a small vocabulary so that the plain implementation stays affordable on the CPU; the chunk (256)
-and the temperature floor (128) are small so that a 600-token prompt crosses them.  Whole, with the tail decoded
-one by one, and mixed (decoded tokens beside portions of up to 300 tokens); in 32-bit and in bfloat16.  And one
-4096-token prompt in 32-bit, whole and in portions of 512."""
+the plain implementation: two layers (one rotary and chunked, one NoPE with temperature), 4 experts and a small
+vocabulary so that the plain implementation stays affordable on the CPU; the chunk (256) and the temperature
+floor (128) are small so that a 600-token prompt crosses them.  Whole, with the tail decoded one by one, and
+mixed (decoded tokens beside portions of up to 300 tokens); in 32-bit and in bfloat16.  And, on four such layers,
+one 4096-token prompt in 32-bit, whole and in portions of 512."""
 
 import random
 
@@ -16,12 +16,12 @@ pytestmark = pytest.mark.gpu
 
 SCOUT_LAYERS = {
     "architectures": ["Llama4ForCausalLM"], "model_type": "llama4_text",
-    "num_hidden_layers": 4, "hidden_size": 5120, "num_attention_heads": 40, "num_key_value_heads": 8, "head_dim": 128,
+    "num_hidden_layers": 2, "hidden_size": 5120, "num_attention_heads": 40, "num_key_value_heads": 8, "head_dim": 128,
     "interleave_moe_layer_step": 1, "num_local_experts": 4, "num_experts_per_tok": 1, "intermediate_size": 8192,
     "intermediate_size_mlp": 16384, "vocab_size": 1000, "rope_theta": 500000.0,
     "rope_scaling": {"rope_type": "llama3", "factor": 16.0, "low_freq_factor": 1.0, "high_freq_factor": 1.0,
                      "original_max_position_embeddings": 8192},
-    "use_qk_norm": True, "attention_chunk_size": 256, "no_rope_layers": [1, 1, 0, 1], "attn_temperature_tuning": True,
+    "use_qk_norm": True, "attention_chunk_size": 256, "no_rope_layers": [1, 0], "attn_temperature_tuning": True,
     "floor_scale": 128.0, "attn_scale": 0.1, "rms_norm_eps": 1e-5, "tie_word_embeddings": False,
 }
 
@@ -55,7 +55,16 @@ def test_scout_sized_layers_under_every_cut(scout_dir, dtype):
         assert any("tc" in k and "split_kv" in k for k in eng.attention_kernels_seen), eng.attention_kernels_seen
 
 
-def test_scout_sized_layers_4096_tokens_in_float32(scout_dir):
+@pytest.fixture(scope="module")
+def scout4_dir(tmp_path_factory):
+    import jax_llm_examples_b200 as J
+
+    four = dict(SCOUT_LAYERS, num_hidden_layers=4, no_rope_layers=[1, 1, 0, 1])
+    return J.write_random_model(tmp_path_factory.mktemp("scout4") / "m", four, seed=8)
+
+
+def test_scout_sized_layers_4096_tokens_in_float32(scout4_dir):
+    scout_dir = scout4_dir
     """The 32-bit path at length: one 4096-token prompt whole and in portions of 512 tokens (sixteen chunks, the
     temperature factor up to ln(33)), every position against the plain implementation."""
     import jax_llm_examples_b200 as J
