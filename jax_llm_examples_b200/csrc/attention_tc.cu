@@ -35,6 +35,7 @@
 #define CP (BKV / PARTS)  // key columns of a tile per softmax thread
 #define WAIT_LIMIT JLX_WAIT_LIMIT
 #define NEG_BIG (-1.0e30f)
+#define LAZY_GROWTH 6.0f  // see the softmax warps: how far a row's maximum may outgrow its reference before O is rescaled
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
@@ -146,43 +147,71 @@ __device__ __forceinline__ int first_key(int p, int chunk, int window) {
 #define TILE_BYTES (2 * 128 * 128)  // one [128 rows][128 elements] operand: two halves of 16 KB
 #define HALF_BYTES (128 * 128)
 
+// A work item: one tile of up to 128 query tokens of one request, and one query head.
+struct Item {
+  int head, hk, n0, cnt, p_first, p_last, key_begin, n_kv;
+  const int* table;
+};
+
+// The kernel is persistent: one block per SM walks a list of work items.  Items are numbered heaviest first (the tile
+// list's order, heads fastest), and block c takes, of every round of gridDim.x items, the c-th in even rounds and the
+// c-th from the end in odd ones, so that all blocks get about the same number of key tiles.  The key tiles of a block's
+// items form one stream: barriers, rings and buffers are indexed by a tile's number g in that stream, and the score
+// product of the next item's first tile is issued while the softmax of this item's last tile runs.  What an item costs
+// beyond its tiles (the block's start, set-up, the first loads, the pipeline's fill) is so paid once per block, not
+// once per item; only the wait for the last product and the store of the output remain between two items.
 __global__ void __launch_bounds__(NTHREADS, 1)
-attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv, const TcParams P) {
+attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv, const TcParams P,
+                            int n_items) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t q_s = base, k_s = base + TILE_BYTES, v_s = k_s + 2 * TILE_BYTES;
-  // barriers: 0 q_full | 1,2 k_full | 3,4 v_full | 5,6 v_empty | 7,8 s_full | 9,10 free | 11 p_ready | 12 o_done | 13,14 k_empty |
-  // 15..18 the meeting of the two softmax warps of each quarter of the rows
-  __shared__ __align__(8) uint64_t bars[19];
+  // barriers (each use flips a phase bit; g = a tile's number in the block's stream, i = an item's number in the block)
+  enum { B_QFULL = 0,    // Q of item i has landed                      phase i
+         B_QEMPTY = 1,   // the last score product of item i is done    phase i
+         B_KFULL = 2,    // [2] K of tile g has landed                  stage g % 2, phase g / 2
+         B_KEMPTY = 4,   // [2] the score product of tile g is done
+         B_VFULL = 6,    // [2] V of tile g has landed
+         B_VEMPTY = 8,   // [2] the product with P of tile g is done
+         B_SFULL = 10,   // [2] S of tile g is complete
+         B_PREADY = 12,  // P of tile g is in tensor memory, O rescaled  phase g
+         B_ODONE = 13,   // O holds the item's tiles up to g            phase g
+         B_MEET = 14,    // [4] the threads of a quarter of the rows have met
+         N_BARS = 18 };
+  __shared__ __align__(8) uint64_t bars[N_BARS];
   __shared__ uint32_t tmem_slot;
   __shared__ int failed;
-  __shared__ float xmax[2][PARTS][BQ];  // [tile parity][part of the keys][row]: what the threads of a row exchange
-  __shared__ float xsum[PARTS][BQ];
+  __shared__ float xmax[2][PARTS][BQ];  // [meeting parity][part of the keys][row]: what the threads of a row exchange
+  __shared__ float xsum[2][PARTS][BQ];
   const uint32_t bar0 = smem_u32(&bars[0]);
   auto BAR = [bar0](int i) { return bar0 + 8u * i; };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // blocks are handed out in the order of blockIdx.x, then y: all heads of the first tile of the list (the
-  // one with the most keys, see the engine's tile order) start before any head of a lighter tile
-  const int head = blockIdx.x, tile = blockIdx.y;
-  const int G = P.Hq / P.Hkv, hk = head / G;
-  const int n0 = P.tiles[2 * tile], cnt = P.tiles[2 * tile + 1];
-  const int r = P.req_of_token[n0];
-  const int p_first = P.positions[n0], p_last = p_first + cnt - 1;
-  const int lo_tile = first_key(p_first, P.chunk, P.window);
-  const int key_begin = lo_tile / BKV * BKV;
-  const int n_kv = (p_last - key_begin) / BKV + 1;
-  const int* table = P.block_table + (size_t)r * P.bt_stride;
+  const int G = P.Hq / P.Hkv;
+  // the block's i-th item, or n_kv = 0 when it has no more
+  auto item = [&](int i) {
+    Item it;
+    it.n_kv = 0;
+    const int rank = (i & 1) ? (int)gridDim.x - 1 - (int)blockIdx.x : (int)blockIdx.x;
+    const long long w = (long long)i * gridDim.x + rank;
+    if (w >= n_items) return it;
+    const int tile = (int)(w / P.Hq);
+    it.head = (int)(w % P.Hq);
+    it.hk = it.head / G;
+    it.n0 = P.tiles[2 * tile];
+    it.cnt = P.tiles[2 * tile + 1];
+    it.p_first = P.positions[it.n0];
+    it.p_last = it.p_first + it.cnt - 1;
+    it.key_begin = first_key(it.p_first, P.chunk, P.window) / BKV * BKV;
+    it.n_kv = (it.p_last - it.key_begin) / BKV + 1;
+    it.table = P.block_table + (size_t)P.req_of_token[it.n0] * P.bt_stride;
+    return it;
+  };
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 9; ++i) mbar_init(BAR(i), 1);
-    mbar_init(BAR(9), 1);
-    mbar_init(BAR(10), 1);
-    mbar_init(BAR(11), 128 * PARTS);
-    mbar_init(BAR(12), 1);
-    mbar_init(BAR(13), 1);
-    mbar_init(BAR(14), 1);
-    for (int i = 15; i < 19; ++i) mbar_init(BAR(i), 32 * PARTS);
+    for (int i = 0; i < N_BARS; ++i) mbar_init(BAR(i), 1);  // a TMA transaction count or a tcgen05.commit each, but:
+    mbar_init(BAR(B_PREADY), 128 * PARTS);
+    for (int i = 0; i < 4; ++i) mbar_init(BAR(B_MEET + i), 32 * PARTS);
     failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -196,86 +225,106 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   if (warp == 0) {
     // ------------------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      mbar_expect_tx(BAR(0), TILE_BYTES);
-      tma_load_3d(q_s, &map_q, 0, head, n0, BAR(0));
-      tma_load_3d(q_s + HALF_BYTES, &map_q, 64, head, n0, BAR(0));
-      // One tile of keys (which = 0) or values (which = 1) into stage j & 1: four boxes of 64 rows x 64 elements.
-      auto load_tile = [&](int j, int which) {
-        const int st = j & 1;
-        const uint32_t bar = BAR((which ? 3 : 1) + st);
-        const uint32_t dst = (which ? v_s : k_s) + st * TILE_BYTES;
-        mbar_expect_tx(bar, TILE_BYTES);
-        for (int b = 0; b < BKV / 64; ++b) {  // pages hold whole 64-key blocks
-          const int pos = key_begin + j * BKV + b * 64;
-          const int pi = pos / P.page_size;
-          int page = pi < P.bt_stride ? table[pi] : -1;
-          if (page >= P.num_pages) { atomicOr(P.status, JLX_STATUS_BAD_PAGE); page = 0; }
-          if (page < 0) page = 0;  // no page there: every key of the block is masked
-          const int row = ((page * 2 + which) * P.Hkv + hk) * P.page_size + (pos - pi * P.page_size);
-          for (int h = 0; h < 2; ++h) tma_load_2d(dst + h * HALF_BYTES + b * 64 * 128, &map_kv, h * 64, row, bar);
-        }
-      };
-      // Keys are free again after their score product, values after the product with P, which comes a tile
-      // later: each ring advances as soon as its own stage is free.
-      int ik = 0, iv = 0;
-      uint32_t idle = 0;
+      int g0 = 0;  // stream number of the item's first tile
       bool ok = true;
-      while ((ik < n_kv || iv < n_kv) && ok) {
-        bool moved = false;
-        if (ik < n_kv && (ik < 2 || mbar_try_wait(BAR(13 + (ik & 1)), ((ik >> 1) - 1) & 1))) { load_tile(ik, 0); ++ik; moved = true; }
-        if (iv < n_kv && (iv < 2 || mbar_try_wait(BAR(5 + (iv & 1)), ((iv >> 1) - 1) & 1))) { load_tile(iv, 1); ++iv; moved = true; }
-        if (moved) idle = 0;
-        else if (++idle >= WAIT_LIMIT || *(volatile int*)&failed) ok = false;
+      for (int i = 0; ok; ++i) {
+        const Item it = item(i);
+        if (it.n_kv == 0) break;
+        // Q's buffer is free when the previous item's last score product is done
+        if (i > 0) ok = mbar_wait(BAR(B_QEMPTY), (i - 1) & 1);
+        if (!ok || *(volatile int*)&failed) { ok = false; break; }
+        mbar_expect_tx(BAR(B_QFULL), TILE_BYTES);
+        tma_load_3d(q_s, &map_q, 0, it.head, it.n0, BAR(B_QFULL));
+        tma_load_3d(q_s + HALF_BYTES, &map_q, 64, it.head, it.n0, BAR(B_QFULL));
+        // One tile of keys (which = 0) or values (which = 1) into stage g & 1: four boxes of 64 rows x 64 elements.
+        auto load_tile = [&](int j, int which) {
+          const int st = (g0 + j) & 1;
+          const uint32_t bar = BAR((which ? B_VFULL : B_KFULL) + st);
+          const uint32_t dst = (which ? v_s : k_s) + st * TILE_BYTES;
+          mbar_expect_tx(bar, TILE_BYTES);
+          for (int b = 0; b < BKV / 64; ++b) {  // pages hold whole 64-key blocks
+            const int pos = it.key_begin + j * BKV + b * 64;
+            const int pi = pos / P.page_size;
+            int page = pi < P.bt_stride ? it.table[pi] : -1;
+            if (page >= P.num_pages) { atomicOr(P.status, JLX_STATUS_BAD_PAGE); page = 0; }
+            if (page < 0) page = 0;  // no page there: every key of the block is masked
+            const int row = ((page * 2 + which) * P.Hkv + it.hk) * P.page_size + (pos - pi * P.page_size);
+            for (int h = 0; h < 2; ++h) tma_load_2d(dst + h * HALF_BYTES + b * 64 * 128, &map_kv, h * 64, row, bar);
+          }
+        };
+        // Keys are free again after their score product, values after the product with P, which comes a tile
+        // later: each ring advances as soon as its own stage is free.
+        int ik = 0, iv = 0;
+        uint32_t idle = 0;
+        while ((ik < it.n_kv || iv < it.n_kv) && ok) {
+          bool moved = false;
+          const int gk = g0 + ik, gv = g0 + iv;
+          if (ik < it.n_kv && (gk < 2 || mbar_try_wait(BAR(B_KEMPTY + (gk & 1)), ((gk >> 1) - 1) & 1))) { load_tile(ik, 0); ++ik; moved = true; }
+          if (iv < it.n_kv && (gv < 2 || mbar_try_wait(BAR(B_VEMPTY + (gv & 1)), ((gv >> 1) - 1) & 1))) { load_tile(iv, 1); ++iv; moved = true; }
+          if (moved) idle = 0;
+          else if (++idle >= WAIT_LIMIT || *(volatile int*)&failed) ok = false;
+        }
+        g0 += it.n_kv;
+        if (!ok) {  // let the copies in flight land before the block's shared memory is given up
+          for (int j = max(0, ik - 2); j < ik; ++j) mbar_wait(BAR(B_KFULL + ((g0 - it.n_kv + j) & 1)), ((g0 - it.n_kv + j) >> 1) & 1);
+          for (int j = max(0, iv - 2); j < iv; ++j) mbar_wait(BAR(B_VFULL + ((g0 - it.n_kv + j) & 1)), ((g0 - it.n_kv + j) >> 1) & 1);
+        }
       }
       if (!ok) {
         atomicOr(P.status, JLX_STATUS_WAIT_TIMEOUT);
         failed = 1;
-        for (int j = max(0, ik - 2); j < ik; ++j) mbar_wait(BAR(1 + (j & 1)), (j >> 1) & 1);
-        for (int j = max(0, iv - 2); j < iv; ++j) mbar_wait(BAR(3 + (j & 1)), (j >> 1) & 1);
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------------------ MMA issuer
+    // One thread issues all products, in the order of the stream: the score product of the tile after next... of
+    // the NEXT tile (which may be the next item's first) goes out before this tile's product with P is waited for.
+    // Products run in the order of their issue: the score product of tile g + 1 overwrites the buffer of S and P of
+    // tile g - 1, whose product with P was issued before it.
     if (lane == 0) {
       constexpr uint32_t idesc_qk = make_idesc(BKV, 0), idesc_pv = make_idesc(DH, 1);
-      bool ok = mbar_wait(BAR(0), 0);
-      auto issue_qk = [&](int j) {  // S[j & 1] = Q K_j^T
-        const int st = j & 1;
+      bool ok = true;
+      // S[g & 1] = Q K^T for tile g; `first` / `last`: the item's first / last tile; i: the item's number
+      auto issue_qk = [&](int g, int i, bool first, bool last) {
+        const int st = g & 1;
+        if (first) ok = mbar_wait(BAR(B_QFULL), i & 1);
+        if (ok) ok = mbar_wait(BAR(B_KFULL + st), (g >> 1) & 1);
+        if (!ok || *(volatile int*)&failed) { ok = false; return; }
+        tc_fence_after();
         const uint32_t kb = k_s + st * TILE_BYTES;
 #pragma unroll
         for (int kk = 0; kk < DH / 16; ++kk) {
           const uint32_t off = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;  // 16 elements = 32 bytes along the row
           umma_bf16(tm_s0 + st * 128, desc_k_major(q_s + off), desc_k_major(kb + off), idesc_qk, kk != 0);
         }
-        umma_commit(BAR(7 + st));   // S is complete
-        umma_commit(BAR(13 + st));  // K_j may be overwritten
+        umma_commit(BAR(B_SFULL + st));   // S is complete
+        umma_commit(BAR(B_KEMPTY + st));  // K may be overwritten
+        if (last) umma_commit(BAR(B_QEMPTY));  // and so may Q
       };
-      if (ok) ok = mbar_wait(BAR(1), 0);
-      if (ok) {
-        tc_fence_after();
-        issue_qk(0);
-      }
-      for (int j = 0; j < n_kv && ok; ++j) {
-        const int st = j & 1;
-        if (j + 1 < n_kv) {
-          const int s1 = (j + 1) & 1;
-          ok = mbar_wait(BAR(1 + s1), ((j + 1) >> 1) & 1);  // K_{j+1} has landed
+      Item cur = item(0);
+      int g = 0;
+      if (cur.n_kv > 0) issue_qk(0, 0, true, cur.n_kv == 1);
+      for (int i = 0; cur.n_kv > 0 && ok; ++i) {
+        const Item nxt = item(i + 1);
+        for (int j = 0; j < cur.n_kv && ok; ++j, ++g) {
+          const int st = g & 1;
+          if (j + 1 < cur.n_kv) issue_qk(g + 1, i, false, j + 2 == cur.n_kv);
+          else if (nxt.n_kv > 0) issue_qk(g + 1, i + 1, true, nxt.n_kv == 1);
+          if (!ok) break;
+          ok = mbar_wait(BAR(B_PREADY), g & 1);                    // P is in tensor memory, O is rescaled
+          if (ok) ok = mbar_wait(BAR(B_VFULL + st), (g >> 1) & 1);  // V has landed
           if (!ok || *(volatile int*)&failed) { ok = false; break; }
           tc_fence_after();
-          issue_qk(j + 1);
-        }
-        ok = mbar_wait(BAR(11), j & 1);                   // P_j is in tensor memory, O is rescaled
-        if (ok) ok = mbar_wait(BAR(3 + st), (j >> 1) & 1);  // V_j has landed
-        if (!ok || *(volatile int*)&failed) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t vb = v_s + st * TILE_BYTES;
+          const uint32_t vb = v_s + st * TILE_BYTES;
 #pragma unroll
-        for (int kk = 0; kk < BKV / 16; ++kk) {
-          // P: 16 keys = 8 columns of tensor memory; V: MN-major, 16 keys = 16 rows of 128 bytes
-          umma_bf16_a_tmem(tm_o, tm_s0 + st * 128 + kk * 8, desc_mn_major(vb + kk * 16 * 128, HALF_BYTES), idesc_pv, (j | kk) != 0);
+          for (int kk = 0; kk < BKV / 16; ++kk) {
+            // P: 16 keys = 8 columns of tensor memory; V: MN-major, 16 keys = 16 rows of 128 bytes
+            umma_bf16_a_tmem(tm_o, tm_s0 + st * 128 + kk * 8, desc_mn_major(vb + kk * 16 * 128, HALF_BYTES), idesc_pv, (j | kk) != 0);
+          }
+          umma_commit(BAR(B_VEMPTY + st));  // V may be overwritten
+          umma_commit(BAR(B_ODONE));        // O holds the item's tiles up to this one
         }
-        umma_commit(BAR(5 + st));  // V_j may be overwritten
-        umma_commit(BAR(12));      // O holds tiles 0..j
+        cur = nxt;
       }
       if (!ok) {
         atomicOr(P.status, JLX_STATUS_WAIT_TIMEOUT);
@@ -293,124 +342,142 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int row = quarter * 32 + lane;             // query row = tensor-memory lane
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     const int col0 = part * CP;
-    const bool live = row < cnt;
-    const int p_row = p_first + min(row, cnt - 1);
-    const int lo_row = first_key(p_row, P.chunk, P.window);
-    float sc = P.scale_log2;  // positive: raw scores and scaled scores have their maximum at the same key
-    if (P.attn_scale != 0.f) sc *= 1.f + P.attn_scale * log1pf(floorf(((float)p_row + 1.f) / P.floor_scale));
-    float m = NEG_BIG, l = 0.f;  // the running maximum (of scaled scores, in powers of two) and this thread's sum
     bool ok = true;
-    for (int j = 0; j < n_kv; ++j) {
-      const int st = j & 1;
-      ok = mbar_wait(BAR(7 + st), (j >> 1) & 1);
-      if (*(volatile int*)&failed) ok = false;
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      tc_fence_after();
-      const int tile_key = key_begin + j * BKV + col0;
-      const bool need_mask = key_begin + j * BKV + BKV - 1 > p_first || key_begin + j * BKV < first_key(p_last, P.chunk, P.window);
-      const uint32_t s_addr = tm_s0 + st * 128 + lane_addr + col0;
-      // this thread's raw scores of the row come into registers once
-      uint32_t v[CP];
-#pragma unroll
-      for (int c = 0; c < CP; c += 32) tmem_ld32(s_addr + c, v + c);
-      tmem_ld_wait();
-      float mx4[4] = {NEG_BIG, NEG_BIG, NEG_BIG, NEG_BIG};  // four chains instead of one long chain of dependent steps
-      if (need_mask) {
-#pragma unroll
-        for (int i = 0; i < CP; ++i) {
-          const int key = tile_key + i;
-          const float sv = (key >= lo_row && key <= p_row) ? __uint_as_float(v[i]) : NEG_BIG;
-          v[i] = __float_as_uint(sv);
-          mx4[i & 3] = fmaxf(mx4[i & 3], sv);
-        }
-      } else {
-#pragma unroll
-        for (int i = 0; i < CP; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(v[i]));
-      }
-      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      // the row's maximum over all parts (double-buffered by tile parity: a partner may be a tile ahead)
-      xmax[st][part][row] = mx;
-      mbar_arrive(BAR(15 + quarter));
-      ok = mbar_wait(BAR(15 + quarter), j & 1);
-      if (*(volatile int*)&failed) ok = false;
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-#pragma unroll
-      for (int q = 0; q < PARTS; ++q) mx = fmaxf(mx, xmax[st][q][row]);
-      // raw -> scaled; a row whose keys are all masked so far keeps NEG_BIG (NEG_BIG * sc does not overflow)
-      mx = fmaxf(m, mx > 0.5f * NEG_BIG ? mx * sc : NEG_BIG);
-      const float corr = fast_exp2(m - mx);
-      // probabilities 2^(s * sc - mx) and their sum; a masked score gives exactly 0, also in a row whose scores are
-      // all masked so far (mx = NEG_BIG)
-      float rs4[4] = {0.f, 0.f, 0.f, 0.f};
-      uint32_t packed[CP / 2];
-      if (need_mask) {
-#pragma unroll
-        for (int i = 0; i < CP; i += 2) {
-          const float s0 = __uint_as_float(v[i]), s1 = __uint_as_float(v[i + 1]);
-          const float p0 = s0 > 0.5f * NEG_BIG ? fast_exp2(fmaf(s0, sc, -mx)) : 0.f;
-          const float p1 = s1 > 0.5f * NEG_BIG ? fast_exp2(fmaf(s1, sc, -mx)) : 0.f;
-          rs4[(i >> 1) & 3] += p0 + p1;
-          __nv_bfloat162 b2 = __floats2bfloat162_rn(p0, p1);
-          packed[i >> 1] = *reinterpret_cast<uint32_t*>(&b2);
-        }
-      } else {
-#pragma unroll
-        for (int i = 0; i < CP; i += 2) {
-          const float p0 = fast_exp2(fmaf(__uint_as_float(v[i]), sc, -mx)), p1 = fast_exp2(fmaf(__uint_as_float(v[i + 1]), sc, -mx));
-          rs4[(i >> 1) & 3] += p0 + p1;
-          __nv_bfloat162 b2 = __floats2bfloat162_rn(p0, p1);
-          packed[i >> 1] = *reinterpret_cast<uint32_t*>(&b2);
-        }
-      }
-      const float rs = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
-      // P over the first half of this S buffer: keys 2c and 2c+1 in column c (the partners have read their scores:
-      // they met after their loads)
-      if (CP == 64) tmem_st32(tm_s0 + st * 128 + lane_addr + part * (CP / 2), packed);
-      else tmem_st16(tm_s0 + st * 128 + lane_addr + part * (CP / 2), packed);
-      l = l * corr + rs;
-      m = mx;
-      // Rescale this thread's part of O's columns when a row of the warp moved its maximum; the product of the
-      // previous tile must be complete first (nothing to rescale before the first product).
-      if (j > 0 && !__all_sync(0xffffffffu, corr == 1.f)) {
-        ok = mbar_wait(BAR(12), (j - 1) & 1);
+    int g = 0;      // the tile's number in the block's stream
+    int meets = 0;  // meetings of this quarter's threads so far (the phase of their barrier)
+    for (int i = 0; ok; ++i) {
+      const Item it = item(i);
+      if (it.n_kv == 0) break;
+      const bool live = row < it.cnt;
+      const int p_row = it.p_first + min(row, it.cnt - 1);
+      const int lo_row = first_key(p_row, P.chunk, P.window);
+      const int lo_last = first_key(it.p_last, P.chunk, P.window);
+      float sc = P.scale_log2;  // positive: raw scores and scaled scores have their maximum at the same key
+      if (P.attn_scale != 0.f) sc *= 1.f + P.attn_scale * log1pf(floorf(((float)p_row + 1.f) / P.floor_scale));
+      float m = NEG_BIG, l = 0.f;  // the running maximum (of scaled scores, in powers of two) and this thread's sum
+      for (int j = 0; j < it.n_kv; ++j, ++g) {
+        const int st = g & 1;
+        ok = mbar_wait(BAR(B_SFULL + st), (g >> 1) & 1);
         if (*(volatile int*)&failed) ok = false;
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
-        uint32_t o[32];
-#pragma unroll 1
-        for (int c0 = part * (DH / PARTS); c0 < (part + 1) * (DH / PARTS); c0 += 32) {
-          tmem_ld32(tm_o + lane_addr + c0, o);
-          tmem_ld_wait();
+        const int tile_key = it.key_begin + j * BKV + col0;
+        const bool need_mask = it.key_begin + j * BKV + BKV - 1 > it.p_first || it.key_begin + j * BKV < lo_last;
+        const uint32_t s_addr = tm_s0 + st * 128 + lane_addr + col0;
+        // this thread's raw scores of the row come into registers once
+        uint32_t v[CP];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
-          tmem_st32(tm_o + lane_addr + c0, o);
+        for (int c = 0; c < CP; c += 32) tmem_ld32(s_addr + c, v + c);
+        tmem_ld_wait();
+        float mx4[4] = {NEG_BIG, NEG_BIG, NEG_BIG, NEG_BIG};  // four chains instead of one long chain of dependent steps
+        if (need_mask) {
+#pragma unroll
+          for (int c = 0; c < CP; ++c) {
+            const int key = tile_key + c;
+            const float sv = (key >= lo_row && key <= p_row) ? __uint_as_float(v[c]) : NEG_BIG;
+            v[c] = __float_as_uint(sv);
+            mx4[c & 3] = fmaxf(mx4[c & 3], sv);
+          }
+        } else {
+#pragma unroll
+          for (int c = 0; c < CP; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(v[c]));
         }
+        float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+        // the row's maximum over all parts (double-buffered by the meeting's parity: a partner may be a tile ahead)
+        const int mp = meets & 1;
+        xmax[mp][part][row] = mx;
+        mbar_arrive(BAR(B_MEET + quarter));
+        ok = mbar_wait(BAR(B_MEET + quarter), mp);
+        ++meets;
+        if (*(volatile int*)&failed) ok = false;
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+#pragma unroll
+        for (int q = 0; q < PARTS; ++q) mx = fmaxf(mx, xmax[mp][q][row]);
+        // raw -> scaled; a row whose keys are all masked so far keeps NEG_BIG (NEG_BIG * sc does not overflow)
+        mx = fmaxf(m, mx > 0.5f * NEG_BIG ? mx * sc : NEG_BIG);
+        // The reference point of the exponents need not be the maximum itself: while no row of this quarter has grown
+        // by more than LAZY_GROWTH (in powers of two) beyond its reference, the references stay, the probabilities
+        // may exceed 1 (up to 2^LAZY_GROWTH: no trouble for a 32-bit sum or a bfloat16 P), and O is not rescaled.
+        // All threads of these rows decide alike: they hold the same references and have just exchanged the maxima.
+        if (__all_sync(0xffffffffu, mx - m <= LAZY_GROWTH)) mx = m;
+        const float corr = fast_exp2(m - mx);
+        // probabilities 2^(s * sc - mx) and their sum; a masked score gives exactly 0, also in a row whose scores are
+        // all masked so far (mx = NEG_BIG)
+        float rs4[4] = {0.f, 0.f, 0.f, 0.f};
+        uint32_t packed[CP / 2];
+        if (need_mask) {
+#pragma unroll
+          for (int c = 0; c < CP; c += 2) {
+            const float s0 = __uint_as_float(v[c]), s1 = __uint_as_float(v[c + 1]);
+            const float p0 = s0 > 0.5f * NEG_BIG ? fast_exp2(fmaf(s0, sc, -mx)) : 0.f;
+            const float p1 = s1 > 0.5f * NEG_BIG ? fast_exp2(fmaf(s1, sc, -mx)) : 0.f;
+            rs4[(c >> 1) & 3] += p0 + p1;
+            __nv_bfloat162 b2 = __floats2bfloat162_rn(p0, p1);
+            packed[c >> 1] = *reinterpret_cast<uint32_t*>(&b2);
+          }
+        } else {
+#pragma unroll
+          for (int c = 0; c < CP; c += 2) {
+            const float p0 = fast_exp2(fmaf(__uint_as_float(v[c]), sc, -mx)), p1 = fast_exp2(fmaf(__uint_as_float(v[c + 1]), sc, -mx));
+            rs4[(c >> 1) & 3] += p0 + p1;
+            __nv_bfloat162 b2 = __floats2bfloat162_rn(p0, p1);
+            packed[c >> 1] = *reinterpret_cast<uint32_t*>(&b2);
+          }
+        }
+        const float rs = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
+        // P over the first half of this S buffer: keys 2c and 2c+1 in column c (the partners have read their scores:
+        // they met after their loads)
+        if (CP == 64) tmem_st32(tm_s0 + st * 128 + lane_addr + part * (CP / 2), packed);
+        else tmem_st16(tm_s0 + st * 128 + lane_addr + part * (CP / 2), packed);
+        l = l * corr + rs;
+        m = mx;
+        // The product of the previous tile must be complete before O is rescaled, and every thread waits for it
+        // whether it rescales or not: a barrier's phase bit tells a waiter the truth only if the waiter has seen
+        // the phase before, so no phase of this barrier is skipped.  (Nothing to wait for before an item's first
+        // product: the phase before it was seen at the previous item's end.)
+        if (j > 0) {
+          ok = mbar_wait(BAR(B_ODONE), (g - 1) & 1);
+          if (*(volatile int*)&failed) ok = false;
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+        }
+        // Rescale this thread's part of O's columns when a row of the warp moved its maximum.
+        if (j > 0 && !__all_sync(0xffffffffu, corr == 1.f)) {
+          tc_fence_after();
+          uint32_t o[32];
+#pragma unroll 1
+          for (int c0 = part * (DH / PARTS); c0 < (part + 1) * (DH / PARTS); c0 += 32) {
+            tmem_ld32(tm_o + lane_addr + c0, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * corr);
+            tmem_st32(tm_o + lane_addr + c0, o);
+          }
+        }
+        tmem_st_wait();
+        tc_fence_before();
+        mbar_arrive(BAR(B_PREADY));
       }
-      tmem_st_wait();
-      tc_fence_before();
-      mbar_arrive(BAR(11));
-    }
-    if (ok) {
-      ok = mbar_wait(BAR(12), (n_kv - 1) & 1);
+      if (!ok) break;
+      // the item's end: its last product, the row's sum (the sum of the parts' sums), the store
+      ok = mbar_wait(BAR(B_ODONE), (g - 1) & 1);
       if (*(volatile int*)&failed) ok = false;
       ok = __all_sync(0xffffffffu, ok);
-    }
-    if (ok) {
+      if (!ok) break;
       tc_fence_after();
-      // the row's sum is the sum of the parts' sums
-      xsum[part][row] = l;
-      mbar_arrive(BAR(15 + quarter));
-      ok = __all_sync(0xffffffffu, mbar_wait(BAR(15 + quarter), n_kv & 1));
-    }
-    if (ok) {
+      const int mp = meets & 1;
+      xsum[mp][part][row] = l;
+      mbar_arrive(BAR(B_MEET + quarter));
+      ok = __all_sync(0xffffffffu, mbar_wait(BAR(B_MEET + quarter), mp));
+      ++meets;
+      if (!ok) break;
       float total = 0.f;
 #pragma unroll
-      for (int q = 0; q < PARTS; ++q) total += xsum[q][row];
+      for (int q = 0; q < PARTS; ++q) total += xsum[mp][q][row];
       const float inv = 1.f / total;
-      bf16* dst = P.out + ((size_t)(n0 + row) * P.Hq + head) * DH;
+      bf16* dst = P.out + ((size_t)(it.n0 + row) * P.Hq + it.head) * DH;
       uint32_t v[32];
 #pragma unroll 1
       for (int c0 = part * (DH / PARTS); c0 < (part + 1) * (DH / PARTS); c0 += 32) {
@@ -418,17 +485,21 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         tmem_ld_wait();
         if (live) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 8) {
+          for (int c = 0; c < 32; c += 8) {
             uint4 o;
             __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
             for (int u = 0; u < 4; ++u)
-              op[u] = __floats2bfloat162_rn(__uint_as_float(v[i + 2 * u]) * inv, __uint_as_float(v[i + 2 * u + 1]) * inv);
-            *reinterpret_cast<uint4*>(dst + c0 + i) = o;
+              op[u] = __floats2bfloat162_rn(__uint_as_float(v[c + 2 * u]) * inv, __uint_as_float(v[c + 2 * u + 1]) * inv);
+            *reinterpret_cast<uint4*>(dst + c0 + c) = o;
           }
         }
       }
-    } else if (lane == 0) {
+      // (the next item's first product with P overwrites O; it waits for this warp's arrival at that tile's barrier,
+      // which comes after these loads)
+      tc_fence_before();
+    }
+    if (!ok && lane == 0) {
       atomicOr(P.status, JLX_STATUS_WAIT_TIMEOUT);
       failed = 1;
     }
@@ -512,8 +583,15 @@ JLX_API int jlx_attention_prefill_tc(const void* q, const void* pages, const int
     JLX_CUDA(cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     cfg = true;
   }
-  JLX_REQUIRE(n_tiles <= 65535, "attention_prefill_tc: %d tiles; up to 65535 are supported", n_tiles);
-  attention_prefill_tc_kernel<<<dim3(Hq, n_tiles), NTHREADS, smem, stream>>>(map_q, map_kv, P);
+  JLX_REQUIRE((long long)n_tiles * Hq < (1ll << 31), "attention_prefill_tc: too many tiles");
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    JLX_CUDA(cudaGetDevice(&dev));
+    JLX_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  }
+  const int n_items = n_tiles * Hq;
+  attention_prefill_tc_kernel<<<dim3(n_items < sms ? n_items : sms), NTHREADS, smem, stream>>>(map_q, map_kv, P, n_items);
   JLX_LAUNCH_CHECK("attention_prefill_tc");
   return 0;
 }
