@@ -345,8 +345,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     bool ok = true;
     int g = 0;      // the tile's number in the block's stream
     int meets = 0;  // meetings of this quarter's threads so far (the phase of their barrier)
+    Item upcoming = item(0);
     for (int i = 0; ok; ++i) {
-      const Item it = item(i);
+      const Item it = upcoming;
       if (it.n_kv == 0) break;
       const bool live = row < it.cnt;
       const int p_row = it.p_first + min(row, it.cnt - 1);
@@ -461,6 +462,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         mbar_arrive(BAR(B_PREADY));
       }
       if (!ok) break;
+      // the next item's description is fetched now (a chain of dependent loads), behind the wait for the last product
+      upcoming = item(i + 1);
       // the item's end: its last product, the row's sum (the sum of the parts' sums), the store
       ok = mbar_wait(BAR(B_ODONE), (g - 1) & 1);
       if (*(volatile int*)&failed) ok = false;
