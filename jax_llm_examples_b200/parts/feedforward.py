@@ -49,7 +49,8 @@ class RoutedExperts(FeedForward):
     kernel_libraries = ("moe", "elementwise", "gemm_simt")
     kernel_libraries_bf16 = ("gemm_stream",)
     needs_f32_input = True
-    OVERLAP_MIN_ROWS = 512  # from this many rows on, the shared expert runs on a second stream beside the routed ones
+    OVERLAP_MIN_ROWS = 512  # from this many rows on (prompt portions), the shared expert runs on a second stream beside the routed ones
+    FORK_MIN_ROWS = 3  # and in steps of few rows (decoding) from this many on; below, it rides as a group of the routed products
 
     def __init__(self, w_router: torch.Tensor, we_gate_up: torch.Tensor, we_down: torch.Tensor, top_k: int,
                  shared: DenseSwiGLU | None = None):
@@ -114,13 +115,19 @@ class RoutedExperts(FeedForward):
         topk_idx, topk_w = routing if routing is not None else self.route(ctx, h32)
         if "record_routing" in ctx.scratch:  # tests compare the choices with a plain router's
             ctx.scratch["record_routing"].append(topk_idx)
-        merged = self.merged and n <= STREAM_MAX_ROWS
+        # Where the shared expert runs.  One or two rows: as one more group of the routed experts' two products (two
+        # launches fewer; with so few blocks one kernel streams better than two).  More rows: on a second stream, beside
+        # the sort, the gather and the routed products: its weights stream while those small kernels would leave the
+        # memory idle (decode at batch 8: +3.7 %, batch 64: +6.5 %; batch 1 would lose 4 %).  Prompt portions: the
+        # routed experts stream their weights once for about a hundred rows each (bound by HBM), the shared expert's
+        # products are dense (bound by the tensor cores); side by side, the tails and the small kernels of either
+        # hide behind the other.  Between STREAM_MAX_ROWS and OVERLAP_MIN_ROWS: one after the other.
+        beside = self.shared is not None and ctx.workspace is not None and (
+            self.FORK_MIN_ROWS <= n <= STREAM_MAX_ROWS or n >= self.OVERLAP_MIN_ROWS)
+        merged = self.merged and n <= STREAM_MAX_ROWS and not beside
         extra = n if merged else 0
-        # Prompt portions: the routed experts stream their weights once for about a hundred rows each (bound by HBM),
-        # the shared expert's products are dense (bound by the tensor cores).  The shared expert runs on a second
-        # stream beside them, so that the tails and the small kernels of either side hide behind the other.
         shared, side = None, None
-        if self.shared is not None and not merged and n >= self.OVERLAP_MIN_ROWS and ctx.workspace is not None:
+        if beside:
             main, side = torch.cuda.current_stream(), ctx.workspace.side_stream()
             side.wait_stream(main)
             with torch.cuda.stream(side), scope("moe_shared_expert"):
