@@ -634,7 +634,11 @@ JLX_API int jlx_gemm_stream(const void* A, const void* W, void* out, int out_is_
   a.tile_list = offsets ? tile_list : nullptr; a.n_tiles = n_tiles;
   a.out = (splits > 1 && mode == 0) ? (void*)scratch : out;
   a.out_is_f32 = out_is_f32; a.silu = mode == 2; a.splits = splits; a.k_per_split = kps; a.status = status;
-  const int row_tiles = (rows + bt - 1) / bt + (offsets ? E : 0);
+  // Row tiles to launch blocks for.  Grouped: a group of r rows has ceil(r / bt) <= r / bt + 1 tiles and only a group
+  // with rows has any, so there are at most rows / bt + min(E, rows) of them.  (A looser bound costs time: a block
+  // without a tile returns at once, but with the kernel's shared memory only two blocks fit an SM at a time, and with
+  // 128 experts and a handful of rows the blocks without work were a hundred times the blocks with.)
+  const int row_tiles = offsets ? rows / bt + (E < rows ? E : rows) : (rows + bt - 1) / bt;
   JLX_REQUIRE(row_tiles <= 65535, "gemm_stream: too many row tiles");
   int rc;
   // Wide token tiles (prompt portions): a pair of blocks per 256 weight rows, when the rows divide so.
