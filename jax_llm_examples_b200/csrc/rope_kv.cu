@@ -189,6 +189,103 @@ rope_kv_store_kernel(const TI* __restrict__ qkv, int splits, long long split_str
   }
 }
 
+// The same for many tokens in bfloat16 (a prompt portion): one block per token takes ALL its heads, eight elements
+// (four rotary pairs, 16 bytes) per thread and access, so that a token's angles are computed once (not once per
+// group of heads) and every load and store is 16 bytes wide.  A head's dh / 8 threads are neighbours in a warp and
+// add their squares by shuffles.  Needs dh / 8 a power of two up to 32 (head sizes 8, 16, 32, 64, 128, 256).
+// The arithmetic of an element is the general kernel's; only the order of the sum of squares differs.
+__global__ void __launch_bounds__(256)
+rope_kv_store_rows_kernel(const bf16* __restrict__ qkv, bf16* __restrict__ q_out, bf16* __restrict__ pages,
+                          const int* __restrict__ block_table, int bt_stride, const int* __restrict__ req_of_token,
+                          const int* __restrict__ positions, const float* __restrict__ inv_freq, int l2norm, float eps, int Hq,
+                          int Hkv, int dh, int page_size, int num_pages, int store_kv, int* status) {
+  extern __shared__ float sc[];  // [dh / 2][2]: sine and cosine of this token's angles
+  pdl_launch_dependents();
+  pdl_wait();
+  const int n = blockIdx.x;
+  const int heads = Hq + 2 * Hkv, per_head = dh >> 3, vectors = heads * per_head;
+  const uint4* row = reinterpret_cast<const uint4*>(qkv + (size_t)n * heads * dh);
+  // this thread's vectors first: the loads depend on nothing and fly during the dependent loads below
+  constexpr int MAXV = 4;
+  uint4 v[MAXV];
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int idx = threadIdx.x + i * 256;
+    if (idx < vectors) v[i] = row[idx];
+  }
+  const int pos = positions[n];
+  bf16* kdst = nullptr;
+  bf16* vdst = nullptr;
+  if (store_kv) {
+    const int r = req_of_token[n];
+    const int page = block_table[(size_t)r * bt_stride + pos / page_size];
+    if (page < 0 || page >= num_pages) {
+      if (threadIdx.x == 0) atomicOr(status, JLX_STATUS_BAD_PAGE);
+    } else {
+      bf16* base = pages + (size_t)page * 2 * Hkv * page_size * dh;
+      kdst = base + (size_t)(pos % page_size) * dh;
+      vdst = base + (size_t)Hkv * page_size * dh + (size_t)(pos % page_size) * dh;
+    }
+  }
+  if (inv_freq) {
+    for (int j = threadIdx.x; j < (dh >> 1); j += blockDim.x) sincosf((float)pos * inv_freq[j], &sc[2 * j], &sc[2 * j + 1]);
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int idx = threadIdx.x + i * 256;
+    const bool mine = idx < vectors;  // (no early exit: the shuffles below need the whole warp)
+    const int h = mine ? idx / per_head : 0, part = idx % per_head;
+    const bool is_v = h >= Hq + Hkv;
+    float f[8];
+    {
+      const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&v[i]);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const float2 t = mine ? __bfloat1622float2(p2[u]) : make_float2(0.f, 0.f);
+        f[2 * u] = t.x;
+        f[2 * u + 1] = t.y;
+      }
+    }
+    float ss = 0.f;
+    if (!is_v) {
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        float a = f[2 * u], b = f[2 * u + 1];
+        if (inv_freq) {
+          const int j = part * 4 + u;
+          const float s = sc[2 * j], c = sc[2 * j + 1];
+          const float ra = a * c - b * s, rb = b * c + a * s;
+          a = ra;
+          b = rb;
+        }
+        ss += a * a + b * b;
+        f[2 * u] = a;
+        f[2 * u + 1] = b;
+      }
+    }
+    float inv = 1.f;
+    if (l2norm) {  // uniform over the block
+      for (int o = per_head >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      if (!is_v) inv = 1.f / sqrtf(ss / (float)dh + eps);
+    }
+    if (!mine) continue;
+    bf16* dst = h < Hq ? q_out + ((size_t)n * Hq + h) * dh
+                       : (is_v ? (vdst ? vdst + (size_t)(h - Hq - Hkv) * page_size * dh : nullptr)
+                               : (kdst ? kdst + (size_t)(h - Hq) * page_size * dh : nullptr));
+    if (!dst) continue;
+    uint4 o;
+    if (is_v) {
+      o = v[i];  // values are copied as they are
+    } else {
+      __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) o2[u] = __floats2bfloat162_rn(f[2 * u] * inv, f[2 * u + 1] * inv);
+    }
+    *reinterpret_cast<uint4*>(dst + part * 8) = o;
+  }
+}
+
 JLX_API int jlx_rope_kv_store(const void* qkv, int in_dtype, int splits, long long split_stride, void* q_out, void* pages,
                               int dtype, const int* block_table, int bt_stride, const int* req_of_token,
                               const int* positions, const float* inv_freq, int l2norm, float eps, int N, int Hq, int Hkv,
@@ -204,6 +301,16 @@ JLX_API int jlx_rope_kv_store(const void* qkv, int in_dtype, int splits, long lo
   const int heads = Hq + 2 * Hkv;
   // many tokens (prompt portions): two heads per warp; few (decoding): one, for the most blocks
   const bool wide = N >= 256 && heads > 8;
+  // many tokens in bfloat16: the kernel that takes a token's heads 16 bytes at a time
+  const int per_head = dh / 8;
+  if (N >= 256 && in_dtype == JLX_BF16 && dtype == JLX_BF16 && splits == 1 && dh % 8 == 0 && per_head <= 32 &&
+      (per_head & (per_head - 1)) == 0 && heads * per_head <= 4 * 256 &&
+      (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)pages) & 15) == 0) {
+    JLX_CUDA(jlx_launch_pdl(rope_kv_store_rows_kernel, dim3(N), dim3(256), smem, stream, (const bf16*)qkv, (bf16*)q_out,
+                            (bf16*)pages, block_table, bt_stride, req_of_token, positions, inv_freq, l2norm, eps, Hq, Hkv, dh,
+                            page_size, num_pages, store_kv, status));
+    return 0;
+  }
   JLX_DISPATCH_DTYPE(in_dtype, TI, JLX_DISPATCH_DTYPE(dtype, T, {
     if (wide) {
       JLX_CUDA(jlx_launch_pdl(rope_kv_store_kernel<TI, T, 2>, dim3(N, (heads + 15) / 16), dim3(256), smem, stream,

@@ -118,9 +118,11 @@ def test_rope_kv_store(dtype, tol, Hq, Hkv, dh, page, rope, l2):
 
 
 @pytest.mark.parametrize("dtype, tol", [(torch.float32, 3e-6), (torch.bfloat16, 8e-3)])
-@pytest.mark.parametrize("Hq, Hkv, dh, page, l2", [(40, 8, 128, 64, True), (9, 3, 48, 16, False), (3, 1, 320, 32, True)])
+@pytest.mark.parametrize("Hq, Hkv, dh, page, l2", [(40, 8, 128, 64, True), (9, 3, 48, 16, False), (3, 1, 320, 32, True),
+                                                   (10, 2, 64, 16, True), (5, 5, 16, 8, False), (4, 1, 256, 64, True)])
 def test_rope_kv_store_many_tokens(dtype, tol, Hq, Hkv, dh, page, l2):
-    """A prompt portion: 300 tokens of one request from position 70 on (several heads per warp)."""
+    """A prompt portion: 300 tokens of one request from position 70 on (several heads per warp; in bfloat16 with a
+    head size of 8 times a power of two, the kernel that takes a token's heads 16 bytes at a time)."""
     N, eps, first = 300, 1e-5, 70
     qkv = torch.randn(N, (Hq + 2 * Hkv) * dh, device=DEV).to(dtype)
     pos = torch.arange(first, first + N, device=DEV, dtype=torch.int32)
