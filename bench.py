@@ -157,8 +157,9 @@ def run_ours(args) -> dict:
     cfg = model.config
     torch.cuda.synchronize()
     print(f"[bench] model of {cfg.num_hidden_layers} layers ({model.weight_bytes() / 1e9:.1f} GB) made in {time.time() - t0:.0f} s", file=sys.stderr)
-    extra = set(filter(None, args.extra_points.split(",")))
     known = {"wide", "past_chunk", "ref_table", "prefill4", "long"}
+    extra = set() if args.extra_points == "none" or args.skip_points else (
+        set(known) if args.extra_points == "all" else set(filter(None, args.extra_points.split(","))))
     if extra - known:
         raise SystemExit(f"bench.py: unknown --extra-points {sorted(extra - known)}; known: {sorted(known)}")
     gen = torch.Generator(device="cuda")
@@ -470,7 +471,7 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=8192)
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--skip-points", action="store_true", help="skip the batch 1 and 64 points")
-    ap.add_argument("--extra-points", default="", help="comma list of further points: wide (an engine that allows 131072-token "
+    ap.add_argument("--extra-points", default="all", help="'all' (the default), 'none', or a comma list of further points: wide (an engine that allows 131072-token "
                     "requests), past_chunk (decode just past a chunk start), ref_table (context 4096, batch 1/16/32), "
                     "prefill4 (four prompts in one step), long (one --long-tokens prompt in portions, then 256 decoded tokens)")
     ap.add_argument("--long-tokens", type=int, default=32768)
