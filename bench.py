@@ -257,36 +257,12 @@ def run_ours(args) -> dict:
                 eng.finish(r.slot)
         return {"ms": ms, "h2d": desc, "d2h": (g.d2h_bytes - d0) // steps}
 
-    clocks = ClockSampler()
-    clocks.start()
-    main = decode_run(batch, args.steps, args.warmup, e2e=False)
-    clock_rec = clocks.stop()
-    e2e = e2e_run(batch, args.steps, args.warmup) if not args.skip_e2e else {"ms": float("nan"), "h2d": 0, "d2h": 0}
-
     points = {}
-    few = max(3, min(args.steps, 20))
-
-    def point(name: str, b: int, **kw):
-        r = decode_run(b, few, 3, **kw)
-        points[name] = round(b / (r["ms"] / 1e3), 1)
-        points[name + "_hbm_frac"] = round(r["bytes"] / (r["ms"] / 1e3) / 1e9 / peaks["hbm_gbs"], 3)
-
-    if not args.skip_points:
-        for b in (1, 64):
-            point(f"decode_b{b}", b)
-    if "wide" in extra:
-        # the same decode steps on an engine that allows requests of 131072 tokens (the default when the pool is
-        # sized from free memory): the captured graphs are planned for the context in use, not for the widest request
-        point(f"decode_b{batch}_max_seq_131072", batch, max_seq_len=131072)
-    if "past_chunk" in extra and cfg.attention_chunk_size:
-        # just past a chunk start the rotary layers read almost no cache; only the NoPE layers read the history
-        C = cfg.attention_chunk_size
-        point(f"decode_b{batch}_just_past_{C}", batch, ctx_len=C + 512, start_len=C + 16)
-    if "ref_table" in extra:
-        # the settings of the reference's published table (llama4/README.md:73-77): context 4096, batch 1, 16, 32
-        for b in (1, 16, 32):
-            point(f"decode_b{b}_ctx4096", b, ctx_len=4096)
-
+    # The order of the measurements follows what each is sensitive to.  The prompt measurements run the library's dense
+    # products, whose rate goes with the power the GPU may draw: they come first, while it is cool, as the peak they are
+    # set against was measured (a burst).  Then the headline: the decode steps, with the clocks sampled.  Decoding at
+    # batch 1 is a chain of short kernels and goes with the SM clock: it is the first of the further points.  The
+    # decode points at larger batches are bound by HBM and mind neither: they come last.
     # prefill of one 2,048-token prompt
     T = args.prefill_tokens
     g = J.Generator(model, max_tokens=T + page, page_size=page, max_slots=1, max_tokens_per_step=T)
@@ -330,6 +306,36 @@ def run_ours(args) -> dict:
         points[f"mixed_b{batch}_plus_{T}_ms"] = round(sorted(mixed_ms)[len(mixed_ms) // 2], 3)
         del g, eng
         torch.cuda.empty_cache()
+
+    clocks = ClockSampler()
+    clocks.start()
+    main = decode_run(batch, args.steps, args.warmup, e2e=False)
+    clock_rec = clocks.stop()
+    e2e = e2e_run(batch, args.steps, args.warmup) if not args.skip_e2e else {"ms": float("nan"), "h2d": 0, "d2h": 0}
+
+    few = max(3, min(args.steps, 20))
+
+    def point(name: str, b: int, **kw):
+        r = decode_run(b, few, 3, **kw)
+        points[name] = round(b / (r["ms"] / 1e3), 1)
+        points[name + "_hbm_frac"] = round(r["bytes"] / (r["ms"] / 1e3) / 1e9 / peaks["hbm_gbs"], 3)
+
+    if not args.skip_points:
+        point("decode_b1", 1)
+    if not args.skip_points:
+        point("decode_b64", 64)
+    if "wide" in extra:
+        # the same decode steps on an engine that allows requests of 131072 tokens (the default when the pool is
+        # sized from free memory): the captured graphs are planned for the context in use, not for the widest request
+        point(f"decode_b{batch}_max_seq_131072", batch, max_seq_len=131072)
+    if "past_chunk" in extra and cfg.attention_chunk_size:
+        # just past a chunk start the rotary layers read almost no cache; only the NoPE layers read the history
+        C = cfg.attention_chunk_size
+        point(f"decode_b{batch}_just_past_{C}", batch, ctx_len=C + 512, start_len=C + 16)
+    if "ref_table" in extra:
+        # the settings of the reference's published table (llama4/README.md:73-77): context 4096, batch 1, 16, 32
+        for b in (1, 16, 32):
+            point(f"decode_b{b}_ctx4096", b, ctx_len=4096)
 
     if "prefill4" in extra:
         # four 2048-token prompts in one step: the routed experts get four times the rows each

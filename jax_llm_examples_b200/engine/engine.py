@@ -11,6 +11,7 @@ into pages, and returns float32 logits at the places asked for.
 from __future__ import annotations
 
 import dataclasses
+import gc
 from typing import Sequence
 
 import numpy as np
@@ -255,9 +256,13 @@ class Engine:
                 ctx.scratch["record_routing"] = []
             if static:
                 g = torch.cuda.CUDAGraph()
+                # Graphs of engines that are no longer used die when Python collects them, and destroying a graph
+                # is not allowed while another is being captured (it would spoil the capture): collect them now, and
+                # capture in the mode that tolerates such calls from this thread.
+                gc.collect()
                 torch.cuda.synchronize()
                 before = K.launch_count()
-                with torch.cuda.graph(g, pool=self._graph_pool):
+                with torch.cuda.graph(g, pool=self._graph_pool, capture_error_mode="relaxed"):
                     logits = self.model.forward(ctx, self.kv, self.states, block_tables)
                 graph["graph"], graph["logits"], graph["kernels"] = g, logits, K.launch_count() - before
                 g.replay()
