@@ -1,17 +1,19 @@
 // Flash attention for prompt portions on the 5th-generation tensor cores (tcgen05), bfloat16, head size 128.
 //
-// One block = 128 consecutive query tokens of one request and one query head.  Keys and values come from
-// the paged cache in tiles of 128 keys.  Per tile:
+// A work item = 128 consecutive query tokens of one request and one query head; a persistent block (one per SM)
+// walks its share of the items (see the kernel).  Keys and values come from the paged cache in tiles of 128 keys.
+// Per tile:
 //   S = Q K^T        tcgen05.mma, Q and K from shared memory (TMA, 128-byte swizzle), S in tensor memory
-//   P = softmax part PARTS threads per query row read their parts of its row of S from tensor memory, keep the running
-//                    max and sum in 32-bit, and write P (bfloat16, two keys per 32-bit column) back over the
-//                    first half of the same S buffer; when a row's maximum moved they rescale O
+//   P = softmax part PARTS threads per query row read their parts of its row of S from tensor memory, keep the
+//                    running reference (the maximum, updated lazily) and sum in 32-bit, and write P (bfloat16, two
+//                    keys per 32-bit column) back over the first half of the same S buffer; when a row's maximum
+//                    outgrew its reference by 2^LAZY_GROWTH they rescale O
 //   O += P V         tcgen05.mma with P as the operand in tensor memory and V from shared memory as an MN-major
 //                    operand (the cache keeps values as [key][dh], so dh is the contiguous direction), O in
 //                    tensor memory
 // S is double-buffered in tensor memory, so the product of the next tile runs while this tile's softmax does.
-// MMAs run in the order of their issue: the score product of tile j+2, which overwrites the buffer of S_j and
-// P_j, is issued after O += P_j V_j and so needs no barrier of its own;
+// MMAs run in the order of their issue: the score product of tile g+2, which overwrites the buffer of S_g and
+// P_g, is issued after O += P_g V_g and so needs no barrier of its own;
 // K and V tiles are double-buffered in shared memory.  Warp 0 issues TMA copies, warp 1 issues the MMAs, the other
 // warps (PARTS threads per query row = per tensor-memory lane, each a part of the tile's keys) do softmax,
 // rescaling and the final store.
