@@ -300,6 +300,7 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttnParams 
 template <int DH>
 __global__ void __launch_bounds__(128)
 attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map, const AttnParams P, int box_rows) {
+  JLX_TL(TL_ATTN_DECODE);
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   constexpr int HALVES = DH / 64;                 // 128-byte column blocks per row
   constexpr uint32_t HALF_BYTES = KT * 128;       // one [64 keys][64 elements] block
@@ -307,7 +308,8 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map, const AttnP
   __shared__ __align__(8) uint64_t full_bar[DEC_STAGES];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   pdl_launch_dependents();
-  pdl_wait();
+  // Until pdl_wait() below, only what no kernel of this step writes is read: the step's description (rows,
+  // positions, requests, block table: on the device before the step began) and keys and values of earlier steps.
   const int slot = blockIdx.z, n = P.rows ? P.rows[slot] : slot, hk = blockIdx.y, split = blockIdx.x;
   const int G = P.Hq / P.Hkv;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -360,8 +362,15 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map, const AttnP
       }
     }
   };
+  // The token's own key and value (position p) are written by the kernel before this one; every other key is older
+  // than the step.  Tiles that end below p are asked for at once, while the predecessor still runs; the query, and
+  // the tile that holds p, wait for it.
+  int issued = 0;
   if (threadIdx.x == 0)
-    for (int t = 0; t < DEC_STAGES && t < n_tiles; ++t) issue(t);
+    for (; issued < DEC_STAGES && issued < n_tiles && key_begin + (issued + 1) * KT <= p; ++issued) issue(issued);
+  pdl_wait();
+  if (threadIdx.x == 0)
+    for (; issued < DEC_STAGES && issued < n_tiles; ++issued) issue(issued);
 
   uint32_t qf[DH / 16][4];
   {
@@ -504,9 +513,11 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map, const AttnP
 #define COMBINE_CACHE 512
 template <int DH>
 __global__ void attention_combine_kernel(const AttnParams P) {
+  JLX_TL(TL_ATTN_COMBINE);
   __shared__ float ms[COMBINE_CACHE], wgt[COMBINE_CACHE];
   pdl_launch_dependents();
-  pdl_wait();
+  // the token's row and position belong to the step's description, which no kernel of the step writes: they are read
+  // while the split kernel still runs
   const int slot = blockIdx.x, n = P.rows ? P.rows[slot] : slot, h = blockIdx.y;
   const int p = P.positions[n];
   const int lo = first_key(p, P.chunk, P.window);
@@ -515,6 +526,7 @@ __global__ void attention_combine_kernel(const AttnParams P) {
   const float2* ml = reinterpret_cast<const float2*>(P.part_ml) + row;
   const bool cached = splits <= COMBINE_CACHE;
   float mm = NEG_BIG, ll = 0.f;
+  pdl_wait();
   if (cached) {
     for (int s = threadIdx.x; s < splits; s += blockDim.x) {
       const float2 v = ml[s];

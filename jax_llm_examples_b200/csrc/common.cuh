@@ -101,8 +101,84 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 // the stream still runs.  It must call pdl_wait() before it reads or writes anything that a predecessor
 // touches; what comes before (barrier set-up, tensor-memory allocation, loads of weights) overlaps the
 // predecessor's tail.  pdl_launch_dependents() lets the successor start the same way.
+// ---- device timeline (only when compiled with -DJLX_TIMELINE): thread 0 of every block notes the global timer when
+// the block starts, when its wait for the predecessor ends and when it leaves, so that the kernels of a replayed
+// graph, which no host-side timer can tell apart, can be laid out on one time axis.  A record is eight 64-bit
+// words: {kernel id | gridDim.x << 8 | gridDim.y << 24 | gridDim.z << 40 | (block 0 of the grid) << 63, start, waited
+// (0: the thread never waited), end, mark 0..3 (0: not passed)}; word 0 of the buffer counts the records asked for.  JLX_TL_MARK(i) notes
+// the time at a place inside a kernel (thread 0 only), to see which stretch of a short kernel takes its time.
+enum JlxTimelineId {
+  TL_EMBED = 1, TL_NORM, TL_NORM_ROUTER, TL_GEMM, TL_GEMM_PAIR, TL_ROPE, TL_ATTN_DECODE, TL_ATTN_COMBINE, TL_SORT, TL_PERMUTE,
+  TL_ARGMAX, TL_ATTN_PREFILL, TL_ROUTER, TL_OTHER
+};
+#ifdef JLX_TIMELINE
+__device__ unsigned long long* jlx_tl_buf = nullptr;
+__device__ unsigned int jlx_tl_cap = 0;
+JLX_API int jlx_timeline_set(unsigned long long* buf, unsigned int cap) {
+  if (cudaMemcpyToSymbol(jlx_tl_buf, &buf, sizeof(buf)) != cudaSuccess) return 1;
+  return cudaMemcpyToSymbol(jlx_tl_cap, &cap, sizeof(cap)) != cudaSuccess;
+}
+__device__ __forceinline__ unsigned long long jlx_now() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ unsigned long long* jlx_tl_waited() {
+  __shared__ unsigned long long t[5];  // the end of the wait, then the marks
+  return t;
+}
+struct JlxTimelineScope {
+  unsigned long long t0;
+  int id;
+  __device__ __forceinline__ explicit JlxTimelineScope(int id_) : t0(jlx_now()), id(id_) {
+    if (threadIdx.x == 0 && threadIdx.y == 0)
+      for (int i = 0; i < 5; ++i) jlx_tl_waited()[i] = 0;
+  }
+  __device__ __forceinline__ ~JlxTimelineScope() {
+    if (threadIdx.x != 0 || threadIdx.y != 0 || jlx_tl_buf == nullptr) return;
+    const unsigned long long t_end = jlx_now();  // before the atomic below, whose round trip is no part of the kernel
+    const unsigned long long slot = atomicAdd(jlx_tl_buf, 1ull);
+    if (slot >= jlx_tl_cap) return;
+    unsigned long long* r = jlx_tl_buf + 1 + 8 * slot;
+    const bool first = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+    r[0] = (unsigned long long)id | ((unsigned long long)(gridDim.x & 0xffff) << 8) | ((unsigned long long)(gridDim.y & 0xffff) << 24) |
+           ((unsigned long long)(gridDim.z & 0xff) << 40) | ((unsigned long long)first << 63);
+    r[1] = t0;
+    r[2] = *jlx_tl_waited();
+    r[3] = t_end;
+    for (int i = 0; i < 4; ++i) r[4 + i] = jlx_tl_waited()[1 + i];
+  }
+};
+#define JLX_TL(id) JlxTimelineScope jlx_tl_scope(id)
+#define JLX_TL_MARK(i) do { if (threadIdx.x == 0 && threadIdx.y == 0) jlx_tl_waited()[1 + (i)] = jlx_now(); } while (0)
+__device__ __forceinline__ void pdl_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (threadIdx.x == 0 && threadIdx.y == 0) *jlx_tl_waited() = jlx_now();
+}
+#else
+#define JLX_TL(id) do { } while (0)
+#define JLX_TL_MARK(i) do { } while (0)
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+#endif
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// Rehearsal.  A short kernel of a decode step runs on a block or a handful, once per layer, on whichever SM is free:
+// it finds none of its code in that SM's instruction cache, and fetching it line by line after the wait for the
+// predecessor took as long as the kernel's work.  Such a kernel starts while its predecessor still runs (programmatic
+// dependent launch) and has nothing to do until that ends, so it spends the wait running its own code once with
+// every load of a predecessor's data and every store switched off (a pass of a loop that the compiler may not
+// unroll, so that both passes are the same instructions), which brings the code in.  Only small grids do this: with
+// many blocks the code is warm after the first and the second pass would only cost time.
+#define JLX_REHEARSAL_MAX_BLOCKS 512
+__device__ __forceinline__ bool jlx_rehearses() { return gridDim.x * gridDim.y * gridDim.z <= JLX_REHEARSAL_MAX_BLOCKS; }
+
+// Asks [p, p + bytes) into L2, the block's threads taking a line each; nothing waits for it.  For weights that a
+// short kernel reads right after its wait for the predecessor: asked for before the wait, they arrive during it.
+__device__ __forceinline__ void l2_prefetch_block(const void* p, size_t bytes) {
+  const char* c = reinterpret_cast<const char*>(p);
+  for (size_t off = (size_t)threadIdx.x * 128; off < bytes; off += (size_t)blockDim.x * 128)
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(c + off));
+}
 
 template <typename... KArgs, typename... Args>
 static cudaError_t jlx_launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {

@@ -11,6 +11,7 @@
 template <typename TW>
 __global__ void embed_kernel(const int* __restrict__ ids, const TW* __restrict__ table, float* __restrict__ x,
                              int D, int V, int* status) {
+  JLX_TL(TL_EMBED);
   pdl_launch_dependents();
   pdl_wait();
   const int n = blockIdx.x;
@@ -21,6 +22,30 @@ __global__ void embed_kernel(const int* __restrict__ ids, const TW* __restrict__
   }
   const TW* row = table + (size_t)id * D;
   float* out = x + (size_t)n * D;
+  if (sizeof(TW) == 2 && (D & 7) == 0 && (((uintptr_t)table | (uintptr_t)x) & 15) == 0) {
+    // eight bfloat16 values per access, and a thread's accesses all in flight before the first is used: with one
+    // row a step this kernel is a chain of memory latencies (the row comes from HBM), not a stream
+    constexpr int AHEAD = 4;
+    const uint4* row8 = reinterpret_cast<const uint4*>(row);
+    const int D8 = D >> 3;
+    for (int i0 = threadIdx.x; i0 < D8; i0 += AHEAD * blockDim.x) {
+      uint4 v[AHEAD];
+#pragma unroll
+      for (int u = 0; u < AHEAD; ++u)
+        if (i0 + u * blockDim.x < D8) v[u] = row8[i0 + u * blockDim.x];
+#pragma unroll
+      for (int u = 0; u < AHEAD; ++u) {
+        const int i = i0 + u * blockDim.x;
+        if (i < D8) {
+          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[u]);
+          const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]), c = __bfloat1622float2(h[2]), e = __bfloat1622float2(h[3]);
+          reinterpret_cast<float4*>(out)[2 * i] = make_float4(a.x, a.y, b.x, b.y);
+          reinterpret_cast<float4*>(out)[2 * i + 1] = make_float4(c.x, c.y, e.x, e.y);
+        }
+      }
+    }
+    return;
+  }
   for (int d = threadIdx.x; d < D; d += blockDim.x) out[d] = to_f32<TW>(row[d]);
 }
 
@@ -127,13 +152,14 @@ struct DeltaSpec {
   DeltaTerm t[DELTA_MAX_TERMS];
 };
 
-// The rows that token r adds, resolved once per block into shared memory: source i is `splits[i]` partials that lie
-// `stride[i]` elements apart, the first at ptr[i].  The kernels then walk the sources with several loads in flight.
-#define DELTA_MAX_SOURCES (DELTA_MAX_TERMS - 1 + 16)
+// The rows that token r adds, resolved once per block into shared memory as a flat list of streams: one per (term,
+// row of the term, split) in that order, which is the order in which they are added.  The kernels then fetch a thread's
+// element from up to DELTA_CHUNK streams at once: with one or a few rows a step the norm is a chain of memory
+// latencies, and a loop that added stream after stream paid one latency per stream.
+#define DELTA_MAX_STREAMS 64
+#define DELTA_CHUNK 8
 struct DeltaSources {
-  const float* ptr[DELTA_MAX_SOURCES];
-  long long stride[DELTA_MAX_SOURCES];
-  int splits[DELTA_MAX_SOURCES];
+  const float* ptr[DELTA_MAX_STREAMS];
   int n;
 };
 // Called by every thread; thread 0 fills `src`, a barrier follows.
@@ -145,17 +171,27 @@ __device__ __forceinline__ void resolve_delta(DeltaSources& src, const DeltaSpec
       if (q >= ds.n) break;
       const DeltaTerm& t = ds.t[q];
       const int rows = t.index ? t.k : 1;
-      for (int j = 0; j < rows && n < DELTA_MAX_SOURCES; ++j) {
+      for (int j = 0; j < rows; ++j) {
         const size_t row = t.index ? (size_t)t.index[r * t.k + j] : (size_t)t.base + r;
-        src.ptr[n] = t.p + row * D;
-        src.stride[n] = t.stride;
-        src.splits[n] = t.splits;
-        ++n;
+        for (int z = 0; z < t.splits && n < DELTA_MAX_STREAMS; ++z) src.ptr[n++] = t.p + (size_t)z * t.stride + row * D;
       }
     }
     src.n = n;
   }
   __syncthreads();
+}
+
+// s += the streams' 16-byte element i, in stream order; a chunk of streams is in flight at once.
+__device__ __forceinline__ void add_streams4(float4& s, const DeltaSources& src, int i) {
+  for (int q0 = 0; q0 < src.n; q0 += DELTA_CHUNK) {
+    float4 v[DELTA_CHUNK];
+#pragma unroll
+    for (int u = 0; u < DELTA_CHUNK; ++u)
+      if (q0 + u < src.n) v[u] = reinterpret_cast<const float4*>(src.ptr[q0 + u])[i];
+#pragma unroll
+    for (int u = 0; u < DELTA_CHUNK; ++u)
+      if (q0 + u < src.n) { s.x += v[u].x; s.y += v[u].y; s.z += v[u].z; s.w += v[u].w; }
+  }
 }
 
 template <typename TO>
@@ -164,68 +200,55 @@ add_rmsnorm_kernel(float* __restrict__ x, const DeltaSpec ds,
                    const float* __restrict__ gamma, float eps, TO* __restrict__ out, float* __restrict__ out32,
                    const int* __restrict__ row_index, int D, int row_in_smem, const float* __restrict__ w_router, int E,
                    int k, int* __restrict__ topk_idx, float* __restrict__ topk_w) {
+  JLX_TL(TL_NORM);
   extern __shared__ __align__(16) float rowbuf[];  // [D] when row_in_smem
   __shared__ float scratch[33];
   __shared__ float scores[ROUTER_MAX_E];
   __shared__ float partial[ROUTER_MAX_E * ROUTER_MAX_PARTS];
   pdl_launch_dependents();
-  pdl_wait();
-  const int n = blockIdx.x;
-  const size_t r = row_index ? (size_t)row_index[n] : (size_t)n;
-  float* xr = x + r * D;
-  const bool has_delta = ds.n > 0;
-  __shared__ DeltaSources src;
-  if (has_delta) resolve_delta(src, ds, r, D);
-  float ss = 0.f;
   // 16-byte accesses when the row allows it (width a multiple of 4, row kept in shared memory)
   bool vec = row_in_smem && (D & 3) == 0;
 #pragma unroll
   for (int q = 0; q < DELTA_MAX_TERMS; ++q) vec = vec && (q >= ds.n || (ds.t[q].stride & 3) == 0);
+  // The norm's weights depend on no kernel: a thread's first elements of them are fetched before the wait for the
+  // predecessor.
+  const float4 g_ahead = vec && gamma && (int)threadIdx.x < (D >> 2) ? reinterpret_cast<const float4*>(gamma)[threadIdx.x]
+                                                                      : make_float4(1.f, 1.f, 1.f, 1.f);
+  if (w_router && gridDim.x <= 64) l2_prefetch_block(w_router, (size_t)E * D * 4);  // they have left L2 since the layer before
+  const int n = blockIdx.x;
+  const bool has_delta = ds.n > 0;
+  __shared__ DeltaSources src;
+  // (No rehearsal here, see jlx_rehearses: measured, it made this kernel slower, whether its block started just before
+  // the end of the matrix product in front of it or, with fewer threads, long before.)
+  pdl_wait();
+  const size_t r = row_index ? (size_t)row_index[n] : (size_t)n;
+  float* xr = x + r * D;
+  if (has_delta) resolve_delta(src, ds, r, D);
+  JLX_TL_MARK(0);
+  float ss = 0.f;
   if (vec) {
     const int D4 = D >> 2;
     float4* x4 = reinterpret_cast<float4*>(xr);
     float4* row4 = reinterpret_cast<float4*>(rowbuf);
-    // four 16-byte loads of the residual (and of each partial) in flight per thread
-    for (int i0 = threadIdx.x; i0 < D4; i0 += 4 * blockDim.x) {
-      float4 s[4];
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int i = i0 + u * blockDim.x;
-        s[u] = i < D4 ? x4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
-      }
+    for (int i = threadIdx.x; i < D4; i += blockDim.x) {
+      float4 t = x4[i];  // in flight together with the first chunk of streams
       if (has_delta) {
-        for (int q = 0; q < src.n; ++q) {
-          const float4* d4 = reinterpret_cast<const float4*>(src.ptr[q]);
-          const long long stride4 = src.stride[q] >> 2;
-          for (int z = 0; z < src.splits[q]; ++z) {
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              const int i = i0 + u * blockDim.x;
-              if (i < D4) {
-                const float4 v = d4[(size_t)z * stride4 + i];
-                s[u].x += v.x; s[u].y += v.y; s[u].z += v.z; s[u].w += v.w;
-              }
-            }
-          }
-        }
+        add_streams4(t, src, i);
+        if (!row_index) x4[i] = t;
       }
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int i = i0 + u * blockDim.x;
-        if (i < D4) {
-          if (has_delta && !row_index) x4[i] = s[u];
-          row4[i] = s[u];
-          ss += (s[u].x * s[u].x + s[u].y * s[u].y) + (s[u].z * s[u].z + s[u].w * s[u].w);
-        }
-      }
+      row4[i] = t;
+      ss += (t.x * t.x + t.y * t.y) + (t.z * t.z + t.w * t.w);
     }
+    JLX_TL_MARK(1);
     ss = block_sum(ss, scratch);
+    JLX_TL_MARK(2);
     const float rms = sqrtf(ss / (float)D + eps);
     const float4* g4 = reinterpret_cast<const float4*>(gamma);
-    for (int i = threadIdx.x; i < D4; i += blockDim.x) {
-      const float4 s = row4[i];
-      const float4 g = gamma ? g4[i] : make_float4(1.f, 1.f, 1.f, 1.f);
-      const float4 v = make_float4(g.x * s.x / rms, g.y * s.y / rms, g.z * s.z / rms, g.w * s.w / rms);
+    int turn = 0;
+    for (int i = threadIdx.x; i < D4; i += blockDim.x, ++turn) {
+      const float4 t = row4[i];
+      const float4 g = turn == 0 ? g_ahead : (gamma ? g4[i] : make_float4(1.f, 1.f, 1.f, 1.f));
+      const float4 v = make_float4(g.x * t.x / rms, g.y * t.y / rms, g.z * t.z / rms, g.w * t.w / rms);
       if (out) store4<TO>(out + (size_t)n * D + 4 * i, v);
       if (out32) reinterpret_cast<float4*>(out32 + (size_t)n * D)[i] = v;
       row4[i] = v;
@@ -234,8 +257,7 @@ add_rmsnorm_kernel(float* __restrict__ x, const DeltaSpec ds,
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
       float s = xr[d];
       if (has_delta) {
-        for (int q = 0; q < src.n; ++q)
-          for (int z = 0; z < src.splits[q]; ++z) s += src.ptr[q][(size_t)z * src.stride[q] + d];
+        for (int q = 0; q < src.n; ++q) s += src.ptr[q][d];
         if (!row_index) xr[d] = s;
       }
       if (row_in_smem) rowbuf[d] = s;
@@ -250,8 +272,7 @@ add_rmsnorm_kernel(float* __restrict__ x, const DeltaSpec ds,
       } else {
         s = xr[d];
         if (has_delta && row_index)
-          for (int q = 0; q < src.n; ++q)
-            for (int z = 0; z < src.splits[q]; ++z) s += src.ptr[q][(size_t)z * src.stride[q] + d];
+          for (int q = 0; q < src.n; ++q) s += src.ptr[q][d];
       }
       const float v = (gamma ? gamma[d] * s : s) / rms;
       if (out) out[(size_t)n * D + d] = from_f32<TO>(v);
@@ -259,17 +280,19 @@ add_rmsnorm_kernel(float* __restrict__ x, const DeltaSpec ds,
       if (row_in_smem) rowbuf[d] = v;
     }
   }
-  if (!w_router) return;
-  __syncthreads();
-  const int parts = router_partials(rowbuf, w_router, D, 0, D, E, partial);
-  __syncthreads();
-  for (int e = threadIdx.x; e < E; e += blockDim.x) {
-    float s = 0.f;
-    for (int part = 0; part < parts; ++part) s += partial[e * ROUTER_MAX_PARTS + part];
-    scores[e] = s;
+  JLX_TL_MARK(3);
+  if (w_router) {
+    __syncthreads();
+    const int parts = router_partials(rowbuf, w_router, D, 0, D, E, partial);
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+      float s = 0.f;
+      for (int part = 0; part < parts; ++part) s += partial[e * ROUTER_MAX_PARTS + part];
+      scores[e] = s;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) router_topk(scores, E, k, (size_t)n, topk_idx, topk_w);
   }
-  __syncthreads();
-  if (threadIdx.x == 0) router_topk(scores, E, k, (size_t)n, topk_idx, topk_w);
 }
 
 // The same for a handful of rows (a decode step), where one block per row would leave the row's router
@@ -277,6 +300,7 @@ add_rmsnorm_kernel(float* __restrict__ x, const DeltaSpec ds,
 // the columns: its part of the sum of squares and of every expert's score goes through distributed shared
 // memory, block 0 of the cluster adds the parts in rank order and chooses the experts.  bfloat16 output only:
 // the order of the sums differs from the one-block kernel's, which the 32-bit path must not depend on.
+#define NORM_CLUSTER 8
 template <typename TO>
 __global__ void __launch_bounds__(512)
 add_rmsnorm_router_cluster_kernel(float* __restrict__ x, const DeltaSpec ds,
@@ -284,9 +308,11 @@ add_rmsnorm_router_cluster_kernel(float* __restrict__ x, const DeltaSpec ds,
                                   int slice,
                                   const float* __restrict__ w_router, int E, int k, int* __restrict__ topk_idx,
                                   float* __restrict__ topk_w) {
+  JLX_TL(TL_NORM_ROUTER);
   namespace cg = cooperative_groups;
   cg::cluster_group cluster = cg::this_cluster();
-  const int rank = (int)cluster.block_rank(), C = (int)cluster.num_blocks();
+  const int rank = (int)cluster.block_rank();
+  constexpr int C = NORM_CLUSTER;  // known at compile time: the loops over the ranks' shared memory unroll, their loads overlap
   extern __shared__ __align__(16) float rowbuf[];  // [slice]
   __shared__ float scratch[33];
   __shared__ float cl_ss;                      // this block's part of the sum of squares
@@ -294,34 +320,36 @@ add_rmsnorm_router_cluster_kernel(float* __restrict__ x, const DeltaSpec ds,
   __shared__ float scores[ROUTER_MAX_E];
   __shared__ float partial[ROUTER_MAX_E * ROUTER_MAX_PARTS];
   pdl_launch_dependents();
-  pdl_wait();
   const int n = blockIdx.x / C;
   const int lo = min(D, rank * slice), hi = min(D, lo + slice);  // multiples of 4
   float4* x4 = reinterpret_cast<float4*>(x + (size_t)n * D);
   float4* row4 = reinterpret_cast<float4*>(rowbuf);
   __shared__ DeltaSources src;
+  // this block's slices of the norm's and the router's weights have left L2 since the layer before: they are asked
+  // back while the predecessor still runs.  (No rehearsal, see jlx_rehearses: the kernel follows a matrix product
+  // whose blocks fill the GPU, its cluster starts only microseconds before that ends, and a rehearsal then still runs
+  // when the real work could begin.)
+  if (gamma) l2_prefetch_block(gamma + lo, (size_t)(hi - lo) * 4);
+  for (int e = 0; e < E; ++e) l2_prefetch_block(w_router + (size_t)e * D + lo, (size_t)(hi - lo) * 4);
+  pdl_wait();
   if (ds.n > 0) resolve_delta(src, ds, (size_t)n, D);
   float ss = 0.f;
   for (int i = (lo >> 2) + threadIdx.x; i < (hi >> 2); i += blockDim.x) {
     float4 s = x4[i];
     if (ds.n > 0) {
-      for (int q = 0; q < src.n; ++q) {
-        const float4* d4 = reinterpret_cast<const float4*>(src.ptr[q]);
-        const long long stride4 = src.stride[q] >> 2;
-        for (int z = 0; z < src.splits[q]; ++z) {
-          const float4 v = d4[(size_t)z * stride4 + i];
-          s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
-        }
-      }
+      add_streams4(s, src, i);
       x4[i] = s;
     }
     row4[i - (lo >> 2)] = s;
     ss += (s.x * s.x + s.y * s.y) + (s.z * s.z + s.w * s.w);
   }
+  JLX_TL_MARK(0);
   ss = block_sum(ss, scratch);
   if (threadIdx.x == 0) cl_ss = ss;
   cluster.sync();
+  JLX_TL_MARK(1);
   float total = 0.f;
+#pragma unroll
   for (int r = 0; r < C; ++r) total += *cluster.map_shared_rank(&cl_ss, r);
   const float rms = sqrtf(total / (float)D + eps);
   const float4* g4 = reinterpret_cast<const float4*>(gamma);
@@ -341,10 +369,13 @@ add_rmsnorm_router_cluster_kernel(float* __restrict__ x, const DeltaSpec ds,
     for (int part = 0; part < parts; ++part) s += partial[e * ROUTER_MAX_PARTS + part];
     cl_scores[e] = s;
   }
+  JLX_TL_MARK(2);
   cluster.sync();
+  JLX_TL_MARK(3);
   if (rank == 0) {
     for (int e = threadIdx.x; e < E; e += blockDim.x) {
       float s = 0.f;
+#pragma unroll
       for (int r = 0; r < C; ++r) s += cluster.map_shared_rank(cl_scores, r)[e];
       scores[e] = s;
     }
@@ -364,10 +395,14 @@ JLX_API int jlx_add_rmsnorm(float* x, const DeltaSpec* delta, const float* gamma
   if (delta) ds = *delta;
   JLX_REQUIRE(ds.n >= 0 && ds.n <= DELTA_MAX_TERMS, "add_rmsnorm: %d terms to add; up to %d are supported", ds.n, DELTA_MAX_TERMS);
   bool aligned = true;
+  int streams = 0;
   for (int q = 0; q < ds.n; ++q) {
     JLX_REQUIRE(ds.t[q].p && ds.t[q].splits >= 1 && (!ds.t[q].index || (ds.t[q].k >= 1 && ds.t[q].k <= 16)), "add_rmsnorm: bad term %d", q);
     aligned = aligned && (ds.t[q].stride & 3) == 0 && ((uintptr_t)ds.t[q].p & 15) == 0;
+    streams += (ds.t[q].index ? ds.t[q].k : 1) * ds.t[q].splits;
   }
+  JLX_REQUIRE(streams <= DELTA_MAX_STREAMS, "add_rmsnorm: a token would add %d rows (terms x rows x split-K partials); up to %d are supported",
+              streams, DELTA_MAX_STREAMS);
   if (N == 0) return 0;
   const int row_in_smem = (size_t)D * 4 <= 64 * 1024;
   if (w_router) {
@@ -380,7 +415,7 @@ JLX_API int jlx_add_rmsnorm(float* x, const DeltaSpec* delta, const float* gamma
   // A few rows with a router: a cluster of 8 blocks per row (all rows resident at once), bfloat16 output only.
   if (w_router && out_dtype == JLX_BF16 && !row_index && out && N <= 32 && (D & 3) == 0 && D >= 1024 && aligned &&
       (((uintptr_t)x | (uintptr_t)gamma | (uintptr_t)out | (uintptr_t)out32) & 15) == 0) {
-    const int C = 8;
+    const int C = NORM_CLUSTER;
     const int slice = ((D / 4 + C - 1) / C) * 4;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(N * C);
@@ -425,6 +460,7 @@ JLX_API int jlx_add_rmsnorm(float* x, const DeltaSpec* delta, const float* gamma
 template <typename TI, typename TO>
 __global__ void silu_mul_kernel(const TI* __restrict__ gu, int splits, long long split_stride, TO* __restrict__ out,
                                 int F, int interleaved) {
+  JLX_TL(TL_OTHER);
   const int i = blockIdx.x;
   const TI* g = gu + (size_t)i * 2 * F;
   for (int f = threadIdx.x; f < F; f += blockDim.x) {
@@ -442,6 +478,7 @@ __global__ void silu_mul_kernel(const TI* __restrict__ gu, int splits, long long
 
 // The common case in prompts: bfloat16 in and out, no partials; eight outputs per thread with 16-byte accesses.
 __global__ void silu_mul_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int F, int interleaved) {
+  JLX_TL(TL_OTHER);
   const size_t i = blockIdx.x;
   const bf16* g = gu + i * 2 * F;
   for (int f0 = threadIdx.x * 8; f0 < F; f0 += blockDim.x * 8) {

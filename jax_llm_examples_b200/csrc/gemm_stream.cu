@@ -221,6 +221,7 @@ __device__ __forceinline__ void stream_epilogue(const StreamArgs& args, int warp
 template <int BT, int SW, int SA, int WT>
 __global__ void __launch_bounds__(NTHREADS)
 gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a, const StreamArgs args) {
+  JLX_TL(TL_GEMM);
   constexpr uint32_t W_TILE = WN * BK * 2, W_BYTES = WT * W_TILE, A_BYTES = BT * BK * 2;
   constexpr uint32_t TMEM_NEED = WT * BT;  // allocations are powers of two from 32 columns
   constexpr uint32_t TMEM_COLS = TMEM_NEED <= 32 ? 32 : TMEM_NEED <= 64 ? 64 : TMEM_NEED <= 128 ? 128 : TMEM_NEED <= 256 ? 256 : 512;
@@ -370,6 +371,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 template <int BT, int ST>
 __global__ void __launch_bounds__(NTHREADS)
 gemm_stream_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a, const StreamArgs args) {
+  JLX_TL(TL_GEMM_PAIR);
   constexpr uint32_t W_BYTES = WN * BK * 2, A_HALF = (BT / 2) * BK * 2;
   constexpr uint32_t TMEM_COLS = BT <= 32 ? 32 : BT <= 64 ? 64 : BT <= 128 ? 128 : 256;
   static_assert(BT % 16 == 0 && A_HALF % 1024 == 0, "half a token tile must be whole 8-row swizzle groups");

@@ -58,6 +58,7 @@ template <int EPW>
 __global__ void __launch_bounds__(256, 2)
 router_rows_kernel(const float* __restrict__ h, const float* __restrict__ w_router, int* __restrict__ topk_idx,
                    float* __restrict__ topk_w, int N, int D, int E, int k) {
+  JLX_TL(TL_ROUTER);
   __shared__ float scores[ROUTER_ROWS][ROUTER_MAX_E];
   pdl_launch_dependents();
   pdl_wait();
@@ -149,66 +150,104 @@ __global__ void expert_sort_kernel(const int* __restrict__ topk_idx, int* __rest
                                    int* __restrict__ sorted_pair, int* __restrict__ sorted_pos, int P, int E, int extra_rows,
                                    int tile_rows, int* __restrict__ tile_list, int* __restrict__ n_tiles, int* status,
                                    int in_smem) {
+  JLX_TL(TL_SORT);
   __shared__ int counts[ROUTER_MAX_E + 1];
   extern __shared__ int staged[];  // the choices, when `in_smem`: both passes below walk them once per expert
   pdl_launch_dependents();
-  pdl_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
-  if (in_smem) {
-    for (int i = threadIdx.x; i < P; i += blockDim.x) staged[i] = topk_idx[i];
+  // One block, once per layer: it rehearses (see jlx_rehearses): every load replaced by "no choice", every store left out.
+#pragma unroll 1
+  for (int pass = 0; pass < 2; ++pass) {
+    const bool real = pass == 1;
+    if (real) pdl_wait();
+    if (in_smem) {
+      for (int i = threadIdx.x; i < P; i += blockDim.x) staged[i] = real ? topk_idx[i] : -1;
+      __syncthreads();
+    }
+    if (real) JLX_TL_MARK(0);
+    const int* choice = in_smem ? staged : topk_idx;
+    for (int e = warp; e < E; e += nwarp) {
+      int c = 0;
+      for (int base = 0; base < P; base += 32) {
+        const int i = base + lane;
+        const int v = i < P && (real || in_smem) ? choice[i] : -1;
+        c += __popc(__ballot_sync(0xffffffffu, v == e));
+      }
+      if (lane == 0) counts[e] = c;
+    }
     __syncthreads();
-  }
-  const int* choice = in_smem ? staged : topk_idx;
-  for (int e = warp; e < E; e += nwarp) {
-    int c = 0;
-    for (int base = 0; base < P; base += 32) {
-      const int i = base + lane;
-      const int v = i < P ? choice[i] : -1;
-      c += __popc(__ballot_sync(0xffffffffu, v == e));
-    }
-    if (lane == 0) counts[e] = c;
-  }
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    int run = 0;
-    for (int e = 0; e < E; ++e) {
-      const int c = counts[e];
-      counts[e] = run;
-      offsets[e] = run;
-      run += c;
-    }
-    counts[E] = run;
-    offsets[E] = run;
-    if (extra_rows > 0) offsets[E + 1] = run + extra_rows;
-    if (run != P) atomicOr(status, JLX_STATUS_BAD_EXPERT);
-    if (tile_rows > 0) {
-      int t = 0;
-      const int groups = extra_rows > 0 ? E + 1 : E;
-      for (int e = 0; e < groups; ++e) {
-        const int lo = counts[e], hi = e < E ? counts[e + 1] : run + extra_rows;
-        for (int r = lo; r < hi; r += tile_rows) {
-          tile_list[2 * t] = e;
-          tile_list[2 * t + 1] = r;
-          ++t;
+    if (warp == 0) {
+      // offsets = exclusive prefix sums of the counts, 32 experts at a time by shuffles (a single thread walking
+      // the experts and then the tiles was a third of this kernel's time in a decode step)
+      int run = 0;
+      for (int e0 = 0; e0 < E; e0 += 32) {
+        const int e = e0 + lane;
+        const int c = e < E ? counts[e] : 0;
+        int incl = c;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+          const int v = __shfl_up_sync(0xffffffffu, incl, d);
+          if (lane >= d) incl += v;
+        }
+        __syncwarp();
+        if (e < E) {
+          counts[e] = run + incl - c;
+          if (real) offsets[e] = run + incl - c;
+        }
+        run += __shfl_sync(0xffffffffu, incl, 31);
+      }
+      if (lane == 0) {
+        counts[E] = run;
+        if (real) {
+          offsets[E] = run;
+          if (extra_rows > 0) offsets[E + 1] = run + extra_rows;
+          if (run != P) atomicOr(status, JLX_STATUS_BAD_EXPERT);
         }
       }
-      n_tiles[0] = t;
-    }
-  }
-  __syncthreads();
-  for (int e = warp; e < E; e += nwarp) {
-    int at = counts[e];
-    for (int base = 0; base < P; base += 32) {
-      const int i = base + lane;
-      const int v = i < P ? choice[i] : -1;
-      const unsigned mask = __ballot_sync(0xffffffffu, v == e);
-      if (v == e) {
-        const int dst = at + __popc(mask & ((1u << lane) - 1u));
-        sorted_pair[dst] = i;
-        sorted_pos[i] = dst;
+      __syncwarp();
+      if (tile_rows > 0) {
+        // the tiles of group g follow those of the groups before it: the same scan over the groups' tile counts
+        const int groups = extra_rows > 0 ? E + 1 : E;
+        int t_run = 0;
+        for (int g0 = 0; g0 < groups; g0 += 32) {
+          const int g = g0 + lane;
+          const int lo = g < groups ? counts[g] : 0, hi = g < E ? counts[g + 1] : (g == E ? run + extra_rows : 0);
+          const int tiles = g < groups ? (hi - lo + tile_rows - 1) / tile_rows : 0;
+          int incl = tiles;
+#pragma unroll
+          for (int d = 1; d < 32; d <<= 1) {
+            const int v = __shfl_up_sync(0xffffffffu, incl, d);
+            if (lane >= d) incl += v;
+          }
+          if (real) {
+            int t = t_run + incl - tiles;
+            for (int r = lo; r < hi; r += tile_rows, ++t) {
+              tile_list[2 * t] = g;
+              tile_list[2 * t + 1] = r;
+            }
+          }
+          t_run += __shfl_sync(0xffffffffu, incl, 31);
+        }
+        if (real && lane == 0) n_tiles[0] = t_run;
       }
-      at += __popc(mask);
+      if (real) JLX_TL_MARK(1);
     }
+    __syncthreads();
+    for (int e = warp; e < E; e += nwarp) {
+      int at = counts[e];
+      for (int base = 0; base < P; base += 32) {
+        const int i = base + lane;
+        const int v = i < P && (real || in_smem) ? choice[i] : -1;
+        const unsigned mask = __ballot_sync(0xffffffffu, v == e);
+        if (v == e) {
+          const int dst = at + __popc(mask & ((1u << lane) - 1u));
+          sorted_pair[dst] = i;
+          sorted_pos[i] = dst;
+        }
+        at += __popc(mask);
+      }
+    }
+    __syncthreads();
   }
 }
 
@@ -229,6 +268,7 @@ JLX_API int jlx_expert_sort(const int* topk_idx, int* offsets, int* sorted_pair,
 template <typename T>
 __global__ void permute_scale_kernel(const float* __restrict__ h, const int* __restrict__ sorted_pair,
                                      const float* __restrict__ topk_w, T* __restrict__ a_sorted, int D, int k, int P) {
+  JLX_TL(TL_PERMUTE);
   pdl_launch_dependents();
   pdl_wait();
   const int i = blockIdx.x;

@@ -176,15 +176,44 @@ sample_kernel(const float* __restrict__ logits, int V, long long ld, const float
 #define ARGMAX_CHUNKS 32
 __global__ void __launch_bounds__(256)
 argmax_chunk_kernel(const float* __restrict__ logits, int V, long long ld, float* __restrict__ part_v, int* __restrict__ part_i) {
+  JLX_TL(TL_ARGMAX);
   __shared__ ArgMax scratch[33];
   const int m = blockIdx.y, c = blockIdx.x;
-  const int span = (V + ARGMAX_CHUNKS - 1) / ARGMAX_CHUNKS;
-  const int lo = c * span, hi = min(V, lo + span);
+  const int span = ((V + ARGMAX_CHUNKS - 1) / ARGMAX_CHUNKS + 3) / 4 * 4;  // a multiple of 4: chunks start 16-byte aligned
+  const int lo = min(V, c * span), hi = min(V, lo + span);
   const float* row = logits + (size_t)m * ld;
   ArgMax best{0.f, -1};
-  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
-    const float v = row[i];
-    if (!isnan(v)) best = better(best, ArgMax{v, i});
+  if ((ld & 3) == 0 && ((uintptr_t)logits & 15) == 0) {
+    // four values per access and a thread's accesses in flight together: a step's one or few rows are read at the speed
+    // of a memory latency per round, so there should be few rounds
+    constexpr int AHEAD = 4;
+    const float4* row4 = reinterpret_cast<const float4*>(row);
+    const int lo4 = lo >> 2, hi4 = hi >> 2;  // whole vectors; the row's last 1..3 values follow below
+    for (int i0 = lo4 + threadIdx.x; i0 < hi4; i0 += AHEAD * blockDim.x) {
+      float4 v[AHEAD];
+#pragma unroll
+      for (int u = 0; u < AHEAD; ++u)
+        if (i0 + u * blockDim.x < hi4) v[u] = row4[i0 + u * blockDim.x];
+#pragma unroll
+      for (int u = 0; u < AHEAD; ++u) {
+        const int i = i0 + u * blockDim.x;
+        if (i < hi4) {
+          if (!isnan(v[u].x)) best = better(best, ArgMax{v[u].x, 4 * i});
+          if (!isnan(v[u].y)) best = better(best, ArgMax{v[u].y, 4 * i + 1});
+          if (!isnan(v[u].z)) best = better(best, ArgMax{v[u].z, 4 * i + 2});
+          if (!isnan(v[u].w)) best = better(best, ArgMax{v[u].w, 4 * i + 3});
+        }
+      }
+    }
+    for (int i = (hi4 << 2) + threadIdx.x; i < hi; i += blockDim.x) {
+      const float v = row[i];
+      if (!isnan(v)) best = better(best, ArgMax{v, i});
+    }
+  } else {
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+      const float v = row[i];
+      if (!isnan(v)) best = better(best, ArgMax{v, i});
+    }
   }
   best = block_argmax(best, scratch);
   if (threadIdx.x == 0) {
@@ -194,6 +223,7 @@ argmax_chunk_kernel(const float* __restrict__ logits, int V, long long ld, float
 }
 
 __global__ void argmax_final_kernel(const float* __restrict__ part_v, const int* __restrict__ part_i, int* __restrict__ out) {
+  JLX_TL(TL_ARGMAX);
   const int m = blockIdx.x, lane = threadIdx.x;
   ArgMax a{part_v[m * ARGMAX_CHUNKS + lane], part_i[m * ARGMAX_CHUNKS + lane]};
 #pragma unroll

@@ -98,8 +98,8 @@ def _target(name: str) -> tuple[Path, list[str]]:
     src = CSRC / f"{name}.cu"
     if not src.is_file():
         raise KernelBuildError(f"no kernel source {src}")
-    out = build_dir() / f"{name}-{_hash([src] + _headers(), NVCC_FLAGS)}.so"
     extra = os.environ.get("JLX_B200_NVCC_EXTRA", "").split()
+    out = build_dir() / f"{name}-{_hash([src] + _headers(), NVCC_FLAGS + extra)}.so"
     return out, [_nvcc(), *NVCC_FLAGS, *extra, "-I", str(CSRC), "-o", str(out) + ".tmp", str(src)]
 
 

@@ -109,3 +109,202 @@ class KernelTimer:
 
 def current_timer() -> "KernelTimer | None":
     return _timer
+
+
+# ------------------------------------------------------------------------------------------ device timeline
+TIMELINE_FLAG = "-DJLX_TIMELINE"
+TIMELINE_KERNELS = ("?", "embed", "add_rmsnorm", "add_rmsnorm_router", "gemm_stream", "gemm_stream_pair", "rope_kv_store",
+                    "attention_decode", "attention_combine", "expert_sort", "permute_scale", "argmax", "attention_prefill_tc",
+                    "router_rows", "other")
+
+
+class DeviceTimeline:
+    """Where the kernels of a step lie on the GPU's own clock, also inside a replayed graph.
+
+    Neither CUDA events nor a profiler's serialised replay show how the kernels of a captured decode step overlap
+    (programmatic dependent launch lets each start during its predecessor) or where the GPU waits.  Kernel
+    libraries compiled with ``-DJLX_TIMELINE`` (put it into ``JLX_B200_NVCC_EXTRA`` before the first kernel is
+    loaded; ``python -m jax_llm_examples_b200.tracing`` does) make thread 0 of every block record the global timer
+    at the block's start, at the end of its wait for the predecessor, at up to four marked places inside the
+    kernel, and at its exit.  This class owns the record buffer, hands it to every loaded library, and groups the
+    records into launches.
+    """
+
+    WORDS = 8  # per record: what, start, waited, end, four marks
+
+    def __init__(self, capacity: int = 1 << 16):
+        self.capacity = capacity
+        self.buf = torch.zeros(1 + self.WORDS * capacity, dtype=torch.int64, device="cuda")
+        self._attached: set[str] = set()
+
+    def attach(self) -> None:
+        """Gives the buffer to every kernel library loaded so far (call again after more were loaded)."""
+        import ctypes
+
+        from .kernels import api
+
+        for name in api.loaded_libraries():
+            if name in self._attached or name == "host":
+                continue
+            lib = api.library(name)
+            if not hasattr(lib, "jlx_timeline_set"):
+                raise RuntimeError(f"kernel library {name} was built without {TIMELINE_FLAG}")
+            if lib.jlx_timeline_set(ctypes.c_void_p(self.buf.data_ptr()), ctypes.c_uint(self.capacity)) != 0:
+                raise RuntimeError(f"jlx_timeline_set failed in {name}")
+            self._attached.add(name)
+
+    def reset(self) -> None:
+        self.buf[:1].zero_()
+
+    def records(self):
+        """[n, 8] int64 on the host: (what, start, waited, end, marks), times in ns of the GPU's global timer."""
+        torch.cuda.synchronize()
+        n = int(self.buf[0].item())
+        if n > self.capacity:
+            raise RuntimeError(f"the timeline holds {self.capacity} block records, {n} were written: shorten the run")
+        return self.buf[1:1 + self.WORDS * n].view(n, self.WORDS).cpu().numpy()
+
+    def launches(self) -> list[dict]:
+        """Records grouped into launches, in the order of their first block's start: a launch is complete when as many
+        blocks of its kernel and grid shape were seen as the grid has.  Per launch: ``start`` (first block in),
+        ``ready`` (the first block that waited for the predecessor got through: the predecessor had ended), ``end``
+        (last block out), ``marks`` (block 0's), in microseconds after the first record."""
+        rec = self.records()
+        if not len(rec):
+            return []
+        order = rec[:, 1].argsort(kind="stable")
+        t_zero = int(rec[:, 1].min())
+        open_by_key: dict[int, dict] = {}
+        seen: dict[int, int] = {}
+        out: list[dict] = []
+        for what, t0, t1, t3, *marks in rec[order].tolist():
+            key = what & 0xFFFFFFFFFFFF
+            g = open_by_key.get(key)
+            if g is None:
+                gx, gy, gz = (key >> 8) & 0xFFFF, (key >> 24) & 0xFFFF, (key >> 40) & 0xFF
+                g = {"kernel": TIMELINE_KERNELS[min(key & 0xFF, len(TIMELINE_KERNELS) - 1)], "grid": (gx, gy, gz), "blocks": 0,
+                     "occurrence": seen.get(key, 0), "start": t0, "ready": None, "end": t3, "marks": None, "_key": key}
+                seen[key] = g["occurrence"] + 1
+                open_by_key[key] = g
+                out.append(g)
+            g["blocks"] += 1
+            g["end"] = max(g["end"], t3)
+            if t1:
+                g["ready"] = t1 if g["ready"] is None else min(g["ready"], t1)
+            if what < 0 or what >> 63:  # the grid's block 0 (the word's top bit)
+                g["marks"] = marks if any(marks) else None
+            if g["blocks"] == g["grid"][0] * g["grid"][1] * g["grid"][2]:
+                del open_by_key[key]
+        for g in out:
+            for k in ("start", "ready", "end"):
+                g[k] = None if g[k] is None else (g[k] - t_zero) / 1e3
+            if g["marks"] is not None:
+                g["marks"] = [None if m == 0 else (m - t_zero) / 1e3 for m in g["marks"]]
+        return out
+
+    @staticmethod
+    def summary(steps: list[list[dict]]) -> list[dict]:
+        """Medians over several recordings of the same step.  The k-th launch of a kernel with a grid shape is the
+        same launch in every recording.  Per launch: ``at`` (when it was ready, or started, after the step's first
+        record; the rows are in this order), ``busy`` (from then to its end), ``adds`` (how much later it ended than
+        every launch that was ready before it: what it added to the chain; kernels of a second stream that hide
+        behind others add nothing), ``early`` (how long before it was ready its first block was in), and the marks
+        as microseconds after ``ready``."""
+        import statistics
+
+        per_launch: dict[tuple, list[dict]] = {}
+        for s in steps:
+            ordered = sorted(s, key=lambda g: g["ready"] if g["ready"] is not None else g["start"])
+            so_far = None
+            for g in ordered:
+                ready = g["ready"] if g["ready"] is not None else g["start"]
+                m = {"at": ready, "busy": g["end"] - ready, "early": ready - g["start"],
+                     "adds": max(0.0, g["end"] - (so_far if so_far is not None else g["start"])),
+                     "marks": None if g["marks"] is None else [None if x is None else x - ready for x in g["marks"]]}
+                so_far = g["end"] if so_far is None else max(so_far, g["end"])
+                per_launch.setdefault((g["_key"], g["occurrence"]), []).append({**g, **m})
+        rows = []
+        for (key, occ), ms in per_launch.items():
+            if len(ms) != len(steps):
+                continue  # a launch that not every recording has (another graph was replayed)
+            row = {"kernel": ms[0]["kernel"], "grid": ms[0]["grid"], "blocks": ms[0]["blocks"], "marks": None}
+            for k in ("at", "busy", "adds", "early"):
+                row[k] = statistics.median(m[k] for m in ms)
+            with_marks = [m["marks"] for m in ms if m["marks"] is not None]
+            if with_marks:
+                row["marks"] = [None if any(w[j] is None for w in with_marks) else statistics.median(w[j] for w in with_marks)
+                                for j in range(4)]
+            rows.append(row)
+        rows.sort(key=lambda r: r["at"])
+        return rows
+
+    @staticmethod
+    def table(rows: list[dict]) -> str:
+        """One line per launch of a summary."""
+        lines = [f"{'kernel':22s} {'grid':>12s} {'at':>8s} {'early':>7s} {'busy':>7s} {'adds':>7s}  marks after ready"]
+        for g in rows:
+            marks = "" if g["marks"] is None else " ".join("-" if m is None else f"{m:.2f}" for m in g["marks"])
+            lines.append(f"{g['kernel']:22s} {'x'.join(map(str, g['grid'])):>12s} {g['at']:8.2f} {g['early']:7.2f} "
+                         f"{g['busy']:7.2f} {g['adds']:7.2f}  {marks}")
+        return "\n".join(lines)
+
+
+def _timeline_main(argv=None) -> int:
+    """``python -m jax_llm_examples_b200.tracing --preset NAME [--layers L] --batch B --context C``: the timeline of
+    one decode step (replayed from its graph) with random weights."""
+    import argparse
+    import random
+
+    ap = argparse.ArgumentParser(description="device timeline of one decode step")
+    ap.add_argument("--preset", default="scout16")
+    ap.add_argument("--layers", type=int, default=0)
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--context", type=int, default=8192)
+    ap.add_argument("--steps", type=int, default=6, help="decode steps before the recorded ones")
+    ap.add_argument("--repeat", type=int, default=9, help="recorded steps (the table shows medians)")
+    args = ap.parse_args(argv)
+    extra = os.environ.get("JLX_B200_NVCC_EXTRA", "")
+    if TIMELINE_FLAG not in extra.split():
+        os.environ["JLX_B200_NVCC_EXTRA"] = (extra + " " + TIMELINE_FLAG).strip()
+    import jax_llm_examples_b200 as J
+
+    cfg_json = J.preset(args.preset, num_hidden_layers=args.layers) if args.layers else J.preset(args.preset)
+    model = J.random_model(cfg_json, seed=0, dtype="bfloat16")
+    b = args.batch
+    gen = J.Generator(model, max_tokens=b * args.context, page_size=64, max_slots=b, max_tokens_per_step=max(b, 64),
+                      max_seq_len=args.context)
+    eng = gen.engine
+    slots = [eng.new_request() for _ in range(b)]
+    start_len = args.context - args.steps - args.repeat - 8
+    for s in slots:
+        eng.manager.reserve(s, start_len)
+        eng.manager.commit(s, start_len)
+    for t in eng.kv:
+        t.normal_(0.0, 0.5)
+    rng = random.Random(0)
+    sampler = J.Sampler(0)
+    timeline = DeviceTimeline()
+
+    def one_step():
+        logits = eng.step([J.StepEntry(s, [rng.randrange(model.config.vocab_size)], [0]) for s in slots])
+        return sampler.sample(logits, [0.0] * b, [0] * b, [0] * b, [0] * b)
+
+    for _ in range(args.steps):
+        one_step()
+        timeline.attach()
+    recorded = []
+    for _ in range(args.repeat):
+        torch.cuda.synchronize()
+        timeline.reset()
+        one_step()
+        recorded.append(timeline.launches())
+    eng.check_status()
+    rows = DeviceTimeline.summary(recorded)
+    print(f"# one decode step, {args.preset}, {model.config.num_hidden_layers} layers, batch {b}, context {args.context}: "
+          f"{len(rows)} launches, {sum(r['adds'] for r in rows):.1f} us (medians of {args.repeat} steps, in us)")
+    print(DeviceTimeline.table(rows))
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(_timeline_main())
