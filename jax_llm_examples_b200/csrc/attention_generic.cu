@@ -23,6 +23,7 @@ __global__ void attention_generic_kernel(const T* __restrict__ q, const T* __res
                                          T* __restrict__ out, int Hq, int Hkv, int dh, int page_size, int num_pages,
                                          float scale, int chunk, int window, float attn_scale, float floor_scale,
                                          int* status) {
+  JLX_TL(TL_ATTN_GENERIC);
   extern __shared__ float smem[];
   const int n = blockIdx.x, hk = blockIdx.y;
   const int G = Hq / Hkv;

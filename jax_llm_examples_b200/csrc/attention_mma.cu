@@ -137,6 +137,7 @@ __device__ __forceinline__ void load_kv_tile(const AttnParams& P, int r, int hk,
 // few hundred blocks share the GPU: short-lived blocks would spend their time on set-up.
 template <int DH>
 __global__ void __launch_bounds__(128) attention_decode_kernel(const AttnParams P) {
+  JLX_TL(TL_ATTN_DECODE_PLAIN);
   extern __shared__ __align__(128) uint8_t smem[];
   constexpr int CH = DH / 8;
   bf16* ks = reinterpret_cast<bf16*>(smem);                  // [DEC_STAGES][KT][DH]
@@ -385,6 +386,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map, const AttnP
       qf[s][3] = g1 < G ? *reinterpret_cast<const uint32_t*>(q1 + s * 16 + kk + 8) : 0u;
     }
   }
+  JLX_TL_MARK(0);
   const float sc = P.scale_log2 * temperature(p, P.attn_scale, P.floor_scale);
   float m[2] = {NEG_BIG, NEG_BIG}, l[2] = {0.f, 0.f};
   float o[DH / 8][4];
@@ -468,6 +470,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map, const AttnP
       issue(t + DEC_STAGES);
     }
   }
+  JLX_TL_MARK(1);
   if (!ok) return;
   float* red = reinterpret_cast<float*>(smem_raw + (base - smem_u32(smem_raw)));
   constexpr int LD = DH + 2;
@@ -561,6 +564,7 @@ __global__ void attention_combine_kernel(const AttnParams P) {
 // 16 x DH rows of query head g.  Key tiles of 64 are double-buffered.
 template <int DH>
 __global__ void __launch_bounds__(256) attention_prefill_kernel(const AttnParams P) {
+  JLX_TL(TL_ATTN_PREFILL_MMA);
   extern __shared__ __align__(128) uint8_t smem[];
   constexpr int CH = DH / 8;
   constexpr int STAGES = 2;
@@ -732,6 +736,7 @@ __device__ __forceinline__ void tma_issue_tile(const CUtensorMap* map, const Att
 template <int DH, int MAXW, int MINB>
 __global__ void __launch_bounds__(MAXW * 32, MINB)
 attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap map, const AttnParams P, int box_rows) {
+  JLX_TL(TL_ATTN_PREFILL_MMA);
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   constexpr int HALVES = DH / 64;
   constexpr uint32_t HALF_BYTES = KT * 128;

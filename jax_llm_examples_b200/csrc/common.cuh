@@ -109,7 +109,8 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 // the time at a place inside a kernel (thread 0 only), to see which stretch of a short kernel takes its time.
 enum JlxTimelineId {
   TL_EMBED = 1, TL_NORM, TL_NORM_ROUTER, TL_GEMM, TL_GEMM_PAIR, TL_ROPE, TL_ATTN_DECODE, TL_ATTN_COMBINE, TL_SORT, TL_PERMUTE,
-  TL_ARGMAX, TL_ATTN_PREFILL, TL_ROUTER, TL_OTHER
+  TL_ARGMAX, TL_ATTN_PREFILL, TL_ROUTER, TL_OTHER, TL_ATTN_GENERIC, TL_GEMM_SIMT, TL_SAMPLE, TL_KV_STORE, TL_MOE_COMBINE,
+  TL_SPLITK_REDUCE, TL_SILU_MUL, TL_ATTN_PREFILL_MMA, TL_ATTN_DECODE_PLAIN
 };
 #ifdef JLX_TIMELINE
 __device__ unsigned long long* jlx_tl_buf = nullptr;

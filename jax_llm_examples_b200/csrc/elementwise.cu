@@ -214,7 +214,10 @@ add_rmsnorm_kernel(float* __restrict__ x, const DeltaSpec ds,
   // predecessor.
   const float4 g_ahead = vec && gamma && (int)threadIdx.x < (D >> 2) ? reinterpret_cast<const float4*>(gamma)[threadIdx.x]
                                                                       : make_float4(1.f, 1.f, 1.f, 1.f);
-  if (w_router && gridDim.x <= 64) l2_prefetch_block(w_router, (size_t)E * D * 4);  // they have left L2 since the layer before
+  if (gridDim.x <= 64) {  // a decode step's few rows: the weights have left L2 since the layer before
+    if (gamma) l2_prefetch_block(gamma, (size_t)D * 4);
+    if (w_router) l2_prefetch_block(w_router, (size_t)E * D * 4);
+  }
   const int n = blockIdx.x;
   const bool has_delta = ds.n > 0;
   __shared__ DeltaSources src;
@@ -460,7 +463,7 @@ JLX_API int jlx_add_rmsnorm(float* x, const DeltaSpec* delta, const float* gamma
 template <typename TI, typename TO>
 __global__ void silu_mul_kernel(const TI* __restrict__ gu, int splits, long long split_stride, TO* __restrict__ out,
                                 int F, int interleaved) {
-  JLX_TL(TL_OTHER);
+  JLX_TL(TL_SILU_MUL);
   const int i = blockIdx.x;
   const TI* g = gu + (size_t)i * 2 * F;
   for (int f = threadIdx.x; f < F; f += blockDim.x) {
@@ -478,7 +481,7 @@ __global__ void silu_mul_kernel(const TI* __restrict__ gu, int splits, long long
 
 // The common case in prompts: bfloat16 in and out, no partials; eight outputs per thread with 16-byte accesses.
 __global__ void silu_mul_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int F, int interleaved) {
-  JLX_TL(TL_OTHER);
+  JLX_TL(TL_SILU_MUL);
   const size_t i = blockIdx.x;
   const bf16* g = gu + i * 2 * F;
   for (int f0 = threadIdx.x * 8; f0 < F; f0 += blockDim.x * 8) {

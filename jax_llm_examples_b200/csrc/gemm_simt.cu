@@ -21,6 +21,7 @@ __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const TA* __restrict__ A, const TW* __restrict__ W, TC* __restrict__ C, int M, int N, int K,
                  long long lda, long long ldw, long long ldc, const int* __restrict__ offsets, int E,
                  long long w_group_stride) {
+  JLX_TL(TL_GEMM_SIMT);
   __shared__ __align__(16) float As[BK][LDS];
   __shared__ __align__(16) float Ws[BK][LDS];
 

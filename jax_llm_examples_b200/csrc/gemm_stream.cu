@@ -504,6 +504,7 @@ gemm_stream_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
 // out[m, n] = sum over splits (ascending) of partial[z][m][n]
 template <typename TO>
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, TO* __restrict__ out, long long total, int splits) {
+  JLX_TL(TL_SPLITK_REDUCE);
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
     float s = 0.f;
     for (int z = 0; z < splits; ++z) s += partial[(size_t)z * total + i];

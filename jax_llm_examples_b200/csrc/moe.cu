@@ -14,6 +14,7 @@
 // the D products per (token, expert), so a token's routing does not depend on the batch.
 __global__ void router_kernel(const float* __restrict__ h, const float* __restrict__ w_router, int* __restrict__ topk_idx,
                               float* __restrict__ topk_w, float* __restrict__ scores_out, int D, int E, int k) {
+  JLX_TL(TL_ROUTER);
   __shared__ float scores[ROUTER_MAX_E];
   const int n = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
@@ -306,6 +307,7 @@ JLX_API int jlx_permute_scale(const float* h, const int* sorted_pair, const floa
 __global__ void moe_combine_kernel(const float* __restrict__ y, int y_splits, long long y_stride, int extra_base,
                                    const float* __restrict__ shared, int splits, long long split_stride,
                                    const int* __restrict__ sorted_pos, float* __restrict__ delta, int D, int k) {
+  JLX_TL(TL_MOE_COMBINE);
   pdl_launch_dependents();
   pdl_wait();
   const int n = blockIdx.x;

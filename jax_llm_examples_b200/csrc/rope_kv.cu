@@ -348,6 +348,7 @@ __global__ void kv_store_kernel(const T* __restrict__ k, const T* __restrict__ v
                                 const int* __restrict__ block_table, int bt_stride,
                                 const int* __restrict__ req_of_token, const int* __restrict__ positions, int Hkv,
                                 int dh, int page_size, int num_pages, int* status) {
+  JLX_TL(TL_KV_STORE);
   const int n = blockIdx.x;
   const int pos = positions[n];
   const int page = block_table[(size_t)req_of_token[n] * bt_stride + pos / page_size];

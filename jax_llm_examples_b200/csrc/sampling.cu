@@ -69,6 +69,7 @@ __global__ void __launch_bounds__(1024)
 sample_kernel(const float* __restrict__ logits, int V, long long ld, const float* __restrict__ temperature,
               const int* __restrict__ top_k, const unsigned long long* __restrict__ streams,
               const unsigned long long* __restrict__ counters, unsigned long long seed, int* __restrict__ out) {
+  JLX_TL(TL_SAMPLE);
   __shared__ ArgMax scratch[33];
   __shared__ float fscratch[33];
   __shared__ float topv[SAMPLE_MAX_K];

@@ -115,7 +115,8 @@ def current_timer() -> "KernelTimer | None":
 TIMELINE_FLAG = "-DJLX_TIMELINE"
 TIMELINE_KERNELS = ("?", "embed", "add_rmsnorm", "add_rmsnorm_router", "gemm_stream", "gemm_stream_pair", "rope_kv_store",
                     "attention_decode", "attention_combine", "expert_sort", "permute_scale", "argmax", "attention_prefill_tc",
-                    "router_rows", "other")
+                    "router_rows", "other", "attention_generic", "gemm_simt", "sample", "kv_store", "moe_combine", "splitk_reduce",
+                    "silu_mul", "attention_prefill_mma", "attention_decode_plain")  # the order of JlxTimelineId in csrc/common.cuh
 
 
 class DeviceTimeline:
@@ -124,7 +125,7 @@ class DeviceTimeline:
     Neither CUDA events nor a profiler's serialised replay show how the kernels of a captured decode step overlap
     (programmatic dependent launch lets each start during its predecessor) or where the GPU waits.  Kernel
     libraries compiled with ``-DJLX_TIMELINE`` (put it into ``JLX_B200_NVCC_EXTRA`` before the first kernel is
-    loaded; ``python -m jax_llm_examples_b200.tracing`` does) make thread 0 of every block record the global timer
+    loaded; ``python -m jax_llm_examples_b200.timeline`` does) make thread 0 of every block record the global timer
     at the block's start, at the end of its wait for the predecessor, at up to four marked places inside the
     kernel, and at its exit.  This class owns the record buffer, hands it to every loaded library, and groups the
     records into launches.
@@ -247,64 +248,3 @@ class DeviceTimeline:
             lines.append(f"{g['kernel']:22s} {'x'.join(map(str, g['grid'])):>12s} {g['at']:8.2f} {g['early']:7.2f} "
                          f"{g['busy']:7.2f} {g['adds']:7.2f}  {marks}")
         return "\n".join(lines)
-
-
-def _timeline_main(argv=None) -> int:
-    """``python -m jax_llm_examples_b200.tracing --preset NAME [--layers L] --batch B --context C``: the timeline of
-    one decode step (replayed from its graph) with random weights."""
-    import argparse
-    import random
-
-    ap = argparse.ArgumentParser(description="device timeline of one decode step")
-    ap.add_argument("--preset", default="scout16")
-    ap.add_argument("--layers", type=int, default=0)
-    ap.add_argument("--batch", type=int, default=1)
-    ap.add_argument("--context", type=int, default=8192)
-    ap.add_argument("--steps", type=int, default=6, help="decode steps before the recorded ones")
-    ap.add_argument("--repeat", type=int, default=9, help="recorded steps (the table shows medians)")
-    args = ap.parse_args(argv)
-    extra = os.environ.get("JLX_B200_NVCC_EXTRA", "")
-    if TIMELINE_FLAG not in extra.split():
-        os.environ["JLX_B200_NVCC_EXTRA"] = (extra + " " + TIMELINE_FLAG).strip()
-    import jax_llm_examples_b200 as J
-
-    cfg_json = J.preset(args.preset, num_hidden_layers=args.layers) if args.layers else J.preset(args.preset)
-    model = J.random_model(cfg_json, seed=0, dtype="bfloat16")
-    b = args.batch
-    gen = J.Generator(model, max_tokens=b * args.context, page_size=64, max_slots=b, max_tokens_per_step=max(b, 64),
-                      max_seq_len=args.context)
-    eng = gen.engine
-    slots = [eng.new_request() for _ in range(b)]
-    start_len = args.context - args.steps - args.repeat - 8
-    for s in slots:
-        eng.manager.reserve(s, start_len)
-        eng.manager.commit(s, start_len)
-    for t in eng.kv:
-        t.normal_(0.0, 0.5)
-    rng = random.Random(0)
-    sampler = J.Sampler(0)
-    timeline = DeviceTimeline()
-
-    def one_step():
-        logits = eng.step([J.StepEntry(s, [rng.randrange(model.config.vocab_size)], [0]) for s in slots])
-        return sampler.sample(logits, [0.0] * b, [0] * b, [0] * b, [0] * b)
-
-    for _ in range(args.steps):
-        one_step()
-        timeline.attach()
-    recorded = []
-    for _ in range(args.repeat):
-        torch.cuda.synchronize()
-        timeline.reset()
-        one_step()
-        recorded.append(timeline.launches())
-    eng.check_status()
-    rows = DeviceTimeline.summary(recorded)
-    print(f"# one decode step, {args.preset}, {model.config.num_hidden_layers} layers, batch {b}, context {args.context}: "
-          f"{len(rows)} launches, {sum(r['adds'] for r in rows):.1f} us (medians of {args.repeat} steps, in us)")
-    print(DeviceTimeline.table(rows))
-    return 0
-
-
-if __name__ == "__main__":
-    raise SystemExit(_timeline_main())

@@ -210,3 +210,29 @@ def test_kernel_timer_and_named_ranges(model_dirs):
         assert J.generate(model, prompts, params, page_size=16) == want
     finally:
         tracing.enable_nvtx(False)
+
+
+def test_device_timeline_of_a_replayed_decode_step():
+    """``python -m jax_llm_examples_b200.timeline`` builds the kernels with their time stamps, replays decode steps
+    from a graph and lays their launches out in stream order: every kernel of a layer is there, and each ends after
+    it could start."""
+    import os
+    import subprocess
+    import sys
+
+    repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = subprocess.run([sys.executable, "-m", "jax_llm_examples_b200.timeline", "--preset", "tiny_a", "--batch", "2",
+                          "--context", "96", "--steps", "3", "--repeat", "3"], cwd=repo, capture_output=True, text=True, timeout=900)
+    assert out.returncode == 0, out.stderr[-2000:]
+    lines = out.stdout.strip().splitlines()
+    assert lines[0].startswith("# one decode step, tiny_a, 4 layers, batch 2") and "medians of 3 steps" in lines[0]
+    rows = [ln.split() for ln in lines[2:]]
+    names = [r[0] for r in rows]
+    for kernel, at_least in (("embed", 1), ("add_rmsnorm", 4), ("rope_kv_store", 4), ("expert_sort", 4), ("argmax", 2)):
+        assert names.count(kernel) >= at_least, (kernel, names)
+    assert sum(n.startswith("attention") for n in names) >= 4 and sum(n.startswith("gemm") for n in names) >= 16, names
+    assert "?" not in names
+    assert names[0] == "embed" and names[-1] == "argmax"
+    ats = [float(r[2]) for r in rows]
+    assert ats == sorted(ats)
+    assert all(float(r[4]) > 0 for r in rows)  # busy: every launch ends after it was ready
