@@ -163,7 +163,8 @@ struct DeltaSources {
   int n;
 };
 // Called by every thread; thread 0 fills `src`, a barrier follows.
-__device__ __forceinline__ void resolve_delta(DeltaSources& src, const DeltaSpec& ds, size_t r, int D) {
+// (`real` false: a rehearsal, which loads nothing that a predecessor writes; the pointers it makes are never used)
+__device__ __forceinline__ void resolve_delta(DeltaSources& src, const DeltaSpec& ds, size_t r, int D, bool real = true) {
   if (threadIdx.x == 0) {
     int n = 0;
 #pragma unroll
@@ -172,7 +173,7 @@ __device__ __forceinline__ void resolve_delta(DeltaSources& src, const DeltaSpec
       const DeltaTerm& t = ds.t[q];
       const int rows = t.index ? t.k : 1;
       for (int j = 0; j < rows; ++j) {
-        const size_t row = t.index ? (size_t)t.index[r * t.k + j] : (size_t)t.base + r;
+        const size_t row = t.index && real ? (size_t)t.index[r * t.k + j] : (size_t)t.base + r;
         for (int z = 0; z < t.splits && n < DELTA_MAX_STREAMS; ++z) src.ptr[n++] = t.p + (size_t)z * t.stride + row * D;
       }
     }
@@ -182,12 +183,14 @@ __device__ __forceinline__ void resolve_delta(DeltaSources& src, const DeltaSpec
 }
 
 // s += the streams' 16-byte element i, in stream order; a chunk of streams is in flight at once.
-__device__ __forceinline__ void add_streams4(float4& s, const DeltaSources& src, int i) {
+__device__ __forceinline__ void add_streams4(float4& s, const DeltaSources& src, int i, bool real = true) {
   for (int q0 = 0; q0 < src.n; q0 += DELTA_CHUNK) {
     float4 v[DELTA_CHUNK];
 #pragma unroll
-    for (int u = 0; u < DELTA_CHUNK; ++u)
-      if (q0 + u < src.n) v[u] = reinterpret_cast<const float4*>(src.ptr[q0 + u])[i];
+    for (int u = 0; u < DELTA_CHUNK; ++u) {
+      v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (real && q0 + u < src.n) v[u] = reinterpret_cast<const float4*>(src.ptr[q0 + u])[i];
+    }
 #pragma unroll
     for (int u = 0; u < DELTA_CHUNK; ++u)
       if (q0 + u < src.n) { s.x += v[u].x; s.y += v[u].y; s.z += v[u].z; s.w += v[u].w; }
@@ -298,14 +301,16 @@ add_rmsnorm_kernel(float* __restrict__ x, const DeltaSpec ds,
   }
 }
 
-// The same for a handful of rows (a decode step), where one block per row would leave the row's router
-// weights (E * D * 4 bytes) to a single SM: a cluster of blocks shares the row.  Each block takes a slice of
+// The same for a handful of rows (a decode step), with or without a router, where one block per row would leave the
+// row to a single SM: its instructions (32 warps through four schedulers) and the router's weights (E * D * 4
+// bytes) then take longer than the memory latencies.  A cluster of blocks shares the row.  Each block takes a slice of
 // the columns: its part of the sum of squares and of every expert's score goes through distributed shared
 // memory, block 0 of the cluster adds the parts in rank order and chooses the experts.  bfloat16 output only:
 // the order of the sums differs from the one-block kernel's, which the 32-bit path must not depend on.
 #define NORM_CLUSTER 8
-template <typename TO>
-__global__ void __launch_bounds__(512)
+// ROUTER: with the router (else w_router is not used, and the kernel is two of everything leaner).
+template <typename TO, bool ROUTER>
+__global__ void __launch_bounds__(ROUTER ? 512 : 256, 1)
 add_rmsnorm_router_cluster_kernel(float* __restrict__ x, const DeltaSpec ds,
                                   const float* __restrict__ gamma, float eps, TO* __restrict__ out, float* __restrict__ out32, int D,
                                   int slice,
@@ -318,8 +323,8 @@ add_rmsnorm_router_cluster_kernel(float* __restrict__ x, const DeltaSpec ds,
   constexpr int C = NORM_CLUSTER;  // known at compile time: the loops over the ranks' shared memory unroll, their loads overlap
   extern __shared__ __align__(16) float rowbuf[];  // [slice]
   __shared__ float scratch[33];
-  __shared__ float cl_ss;                      // this block's part of the sum of squares
-  __shared__ float cl_scores[ROUTER_MAX_E];    // this block's part of every expert's score
+  __shared__ float cl_ss[NORM_CLUSTER];                       // every block's part of the sum of squares (each block has all)
+  __shared__ float cl_scores[NORM_CLUSTER][ROUTER_MAX_E];    // every block's part of every expert's score (used in block 0)
   __shared__ float scores[ROUTER_MAX_E];
   __shared__ float partial[ROUTER_MAX_E * ROUTER_MAX_PARTS];
   pdl_launch_dependents();
@@ -333,36 +338,60 @@ add_rmsnorm_router_cluster_kernel(float* __restrict__ x, const DeltaSpec ds,
   // whose blocks fill the GPU, its cluster starts only microseconds before that ends, and a rehearsal then still runs
   // when the real work could begin.)
   if (gamma) l2_prefetch_block(gamma + lo, (size_t)(hi - lo) * 4);
-  for (int e = 0; e < E; ++e) l2_prefetch_block(w_router + (size_t)e * D + lo, (size_t)(hi - lo) * 4);
-  pdl_wait();
-  if (ds.n > 0) resolve_delta(src, ds, (size_t)n, D);
+  if (ROUTER)
+    for (int e = 0; e < E; ++e) l2_prefetch_block(w_router + (size_t)e * D + lo, (size_t)(hi - lo) * 4);
+  // A thread's norm weights wait in a register.  The blocks of the cluster meet once here, where it costs nothing:
+  // from then on all of them run, so that a block may WRITE its partial results into the others' shared memory
+  // before the barriers below instead of reading theirs after (a remote read is a round trip on the critical path,
+  // a remote write is not), and block 0 needs nobody after the last barrier.
+  const int mine = (lo >> 2) + threadIdx.x;
+  const float4 g_ahead = gamma && mine < (hi >> 2) ? reinterpret_cast<const float4*>(gamma)[mine] : make_float4(1.f, 1.f, 1.f, 1.f);
+  cluster.sync();
+  // Without a router the blocks are lean enough to sit beside the blocks of the matrix product before, so they start
+  // long before it ends and rehearse (see jlx_rehearses).  With one they start only microseconds before, and do not.
+#pragma unroll 1
+  for (int pass = ROUTER ? 1 : 0; pass < 2; ++pass) {
+  const bool real = pass == 1;
+  if (real) pdl_wait();
+  if (ds.n > 0) resolve_delta(src, ds, (size_t)n, D, real);
   float ss = 0.f;
   for (int i = (lo >> 2) + threadIdx.x; i < (hi >> 2); i += blockDim.x) {
-    float4 s = x4[i];
+    float4 s = make_float4(1.f, 1.f, 1.f, 1.f);
+    if (real) s = x4[i];
     if (ds.n > 0) {
-      add_streams4(s, src, i);
-      x4[i] = s;
+      add_streams4(s, src, i, real);
+      if (real) x4[i] = s;
     }
     row4[i - (lo >> 2)] = s;
     ss += (s.x * s.x + s.y * s.y) + (s.z * s.z + s.w * s.w);
   }
   JLX_TL_MARK(0);
-  ss = block_sum(ss, scratch);
-  if (threadIdx.x == 0) cl_ss = ss;
+  ss = block_sum(ss, scratch);  // (every thread has the sum)
+  if (threadIdx.x < C) *cluster.map_shared_rank(&cl_ss[rank], threadIdx.x) = ss;
   cluster.sync();
   JLX_TL_MARK(1);
   float total = 0.f;
 #pragma unroll
-  for (int r = 0; r < C; ++r) total += *cluster.map_shared_rank(&cl_ss, r);
-  const float rms = sqrtf(total / (float)D + eps);
+  for (int r = 0; r < C; ++r) total += cl_ss[r];
+  // One division, then products: four exact divisions per thread are some fifty instructions with branches, and in a
+  // block that runs this code once, cold, instructions cost more than arithmetic.  (The result differs from the
+  // quotient's by a rounding of 32-bit; this kernel's output is bfloat16.)
+  const float inv_rms = 1.f / sqrtf(total / (float)D + eps);
   const float4* g4 = reinterpret_cast<const float4*>(gamma);
+  if (!ROUTER) JLX_TL_MARK(2);
   for (int i = (lo >> 2) + threadIdx.x; i < (hi >> 2); i += blockDim.x) {
     const float4 s = row4[i - (lo >> 2)];
-    const float4 g = gamma ? g4[i] : make_float4(1.f, 1.f, 1.f, 1.f);
-    const float4 v = make_float4(g.x * s.x / rms, g.y * s.y / rms, g.z * s.z / rms, g.w * s.w / rms);
-    store4<TO>(out + (size_t)n * D + 4 * i, v);
-    if (out32) reinterpret_cast<float4*>(out32 + (size_t)n * D)[i] = v;
+    const float4 g = i == mine ? g_ahead : (gamma ? g4[i] : make_float4(1.f, 1.f, 1.f, 1.f));
+    const float4 v = make_float4(g.x * s.x * inv_rms, g.y * s.y * inv_rms, g.z * s.z * inv_rms, g.w * s.w * inv_rms);
+    if (real) store4<TO>(out + (size_t)n * D + 4 * i, v);
+    if (real && out32) reinterpret_cast<float4*>(out32 + (size_t)n * D)[i] = v;
     row4[i - (lo >> 2)] = v;
+  }
+  if (!ROUTER) JLX_TL_MARK(3);
+  if (!ROUTER) {  // a norm without a router: no remote access after the barrier above
+    if (real) return;
+    cluster.sync();  // ... of the rehearsal, whose values nobody may still be reading when the real ones are written
+    continue;
   }
   __syncthreads();
   const int parts = router_partials(rowbuf, w_router, D, lo, hi, E, partial);
@@ -370,22 +399,22 @@ add_rmsnorm_router_cluster_kernel(float* __restrict__ x, const DeltaSpec ds,
   for (int e = threadIdx.x; e < E; e += blockDim.x) {
     float s = 0.f;
     for (int part = 0; part < parts; ++part) s += partial[e * ROUTER_MAX_PARTS + part];
-    cl_scores[e] = s;
+    cluster.map_shared_rank(&cl_scores[rank][0], 0)[e] = s;  // into block 0's shared memory
   }
   JLX_TL_MARK(2);
-  cluster.sync();
+  cluster.sync();  // the last remote access of the kernel is before this barrier: the other blocks may leave
   JLX_TL_MARK(3);
   if (rank == 0) {
     for (int e = threadIdx.x; e < E; e += blockDim.x) {
       float s = 0.f;
 #pragma unroll
-      for (int r = 0; r < C; ++r) s += cluster.map_shared_rank(cl_scores, r)[e];
+      for (int r = 0; r < C; ++r) s += cl_scores[r][e];
       scores[e] = s;
     }
     __syncthreads();
     if (threadIdx.x == 0) router_topk(scores, E, k, (size_t)n, topk_idx, topk_w);
   }
-  cluster.sync();  // every block's shared memory stays alive until block 0 has read it
+  }
 }
 
 // delta: what to add to x first (null: nothing), see DeltaSpec; the struct is read on the host.
@@ -415,14 +444,16 @@ JLX_API int jlx_add_rmsnorm(float* x, const DeltaSpec* delta, const float* gamma
     JLX_REQUIRE(topk_idx && topk_w, "router: outputs missing");
   }
   const size_t smem = row_in_smem ? (size_t)D * 4 : 0;
-  // A few rows with a router: a cluster of 8 blocks per row (all rows resident at once), bfloat16 output only.
-  if (w_router && out_dtype == JLX_BF16 && !row_index && out && N <= 32 && (D & 3) == 0 && D >= 1024 && aligned &&
+  // A few rows: a cluster of 8 blocks per row (all rows resident at once), bfloat16 output only.
+  if (out_dtype == JLX_BF16 && !row_index && out && N <= 32 && (D & 3) == 0 && D >= 1024 && aligned &&
       (((uintptr_t)x | (uintptr_t)gamma | (uintptr_t)out | (uintptr_t)out32) & 15) == 0) {
     const int C = NORM_CLUSTER;
     const int slice = ((D / 4 + C - 1) / C) * 4;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(N * C);
-    cfg.blockDim = dim3(512);
+    // with a router the experts' rows are spread over 16 warps; without, a thread per 16 bytes of the slice is enough
+    const int lean = ((slice / 4 + 31) / 32) * 32;
+    cfg.blockDim = dim3(w_router ? 512 : (lean < 64 ? 64 : (lean > 256 ? 256 : lean)));
     cfg.dynamicSmemBytes = (size_t)slice * 4;
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
@@ -434,8 +465,12 @@ JLX_API int jlx_add_rmsnorm(float* x, const DeltaSpec* delta, const float* gamma
     attr[1].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 2;
-    JLX_CUDA(cudaLaunchKernelEx(&cfg, add_rmsnorm_router_cluster_kernel<bf16>, x, ds, gamma, eps,
-                                (bf16*)out, out32, D, slice, w_router, E, k, topk_idx, topk_w));
+    if (w_router)
+      JLX_CUDA(cudaLaunchKernelEx(&cfg, add_rmsnorm_router_cluster_kernel<bf16, true>, x, ds, gamma, eps,
+                                  (bf16*)out, out32, D, slice, w_router, E, k, topk_idx, topk_w));
+    else
+      JLX_CUDA(cudaLaunchKernelEx(&cfg, add_rmsnorm_router_cluster_kernel<bf16, false>, x, ds, gamma, eps,
+                                  (bf16*)out, out32, D, slice, w_router, E, k, topk_idx, topk_w));
     JLX_LAUNCH_CHECK("add_rmsnorm (cluster)");
     return 0;
   }
