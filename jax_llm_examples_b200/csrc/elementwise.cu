@@ -347,10 +347,12 @@ add_rmsnorm_router_cluster_kernel(float* __restrict__ x, const DeltaSpec ds,
   const int mine = (lo >> 2) + threadIdx.x;
   const float4 g_ahead = gamma && mine < (hi >> 2) ? reinterpret_cast<const float4*>(gamma)[mine] : make_float4(1.f, 1.f, 1.f, 1.f);
   cluster.sync();
-  // Without a router the blocks are lean enough to sit beside the blocks of the matrix product before, so they start
-  // long before it ends and rehearse (see jlx_rehearses).  With one they start only microseconds before, and do not.
+  // Without a router the blocks are lean enough to sit beside the blocks of the matrix product before; with one row
+  // in the step that product leaves room on the SMs (240 blocks at Scout's sizes), the cluster starts long before it
+  // ends, and rehearses (see jlx_rehearses).  With more rows the product fills the GPU to its end, with a router
+  // the blocks are not lean: the cluster then starts only microseconds before its work, and does not rehearse.
 #pragma unroll 1
-  for (int pass = ROUTER ? 1 : 0; pass < 2; ++pass) {
+  for (int pass = ROUTER || gridDim.x > C ? 1 : 0; pass < 2; ++pass) {
   const bool real = pass == 1;
   if (real) pdl_wait();
   if (ds.n > 0) resolve_delta(src, ds, (size_t)n, D, real);
