@@ -32,6 +32,9 @@ def main(argv=None) -> int:
     ap.add_argument("--context", type=int, default=8192)
     ap.add_argument("--steps", type=int, default=6, help="decode steps before the recorded ones")
     ap.add_argument("--repeat", type=int, default=9, help="recorded steps (the table shows medians)")
+    ap.add_argument("--prompt", type=int, default=0, metavar="T",
+                    help="instead of decode steps: steps of one T-token prompt portion each (run eagerly, as prompts are; "
+                         "library kernels, which carry no stamps, show as gaps)")
     args = ap.parse_args(argv)
     extra = os.environ.get("JLX_B200_NVCC_EXTRA", "")
     if TIMELINE_FLAG not in extra.split():  # before the first kernel library is built or loaded
@@ -42,6 +45,8 @@ def main(argv=None) -> int:
     model = J.random_model(cfg_json, seed=0, dtype="bfloat16")
     b = args.batch
     page = 64
+    if args.prompt:
+        return _prompt_steps(J, model, args, page)
     gen = J.Generator(model, max_tokens=b * (-(-args.context // page) * page), page_size=page, max_slots=b, max_tokens_per_step=max(b, 64),
                       max_seq_len=args.context)
     eng = gen.engine
@@ -73,6 +78,38 @@ def main(argv=None) -> int:
     rows = DeviceTimeline.summary(recorded)
     print(f"# one decode step, {args.preset}, {model.config.num_hidden_layers} layers, batch {b}, context {args.context}: "
           f"{len(rows)} launches, {sum(r['adds'] for r in rows):.1f} us (medians of {args.repeat} steps, in us)")
+    print(DeviceTimeline.table(rows))
+    return 0
+
+
+def _prompt_steps(J, model, args, page) -> int:
+    import random
+
+    T = args.prompt
+    rng = random.Random(0)
+    gen = J.Generator(model, max_tokens=(args.steps + args.repeat + 1) * (-(-T // page) * page), page_size=page,
+                      max_slots=args.steps + args.repeat + 1, max_tokens_per_step=T, max_seq_len=max(T, page))
+    eng = gen.engine
+    timeline = DeviceTimeline(capacity=1 << 18)
+
+    def one_step():
+        s = eng.new_request()
+        eng.step([J.StepEntry(s, [rng.randrange(model.config.vocab_size) for _ in range(T)], [T - 1])])
+        torch.cuda.synchronize()
+        eng.finish(s)
+
+    for _ in range(args.steps):
+        one_step()
+        timeline.attach()
+    recorded = []
+    for _ in range(args.repeat):
+        timeline.reset()
+        one_step()
+        recorded.append(timeline.launches())
+    eng.check_status()
+    rows = DeviceTimeline.summary(recorded)
+    print(f"# one step of a {T}-token prompt, {args.preset}, {model.config.num_hidden_layers} layers: {len(rows)} stamped launches "
+          f"(medians of {args.repeat} steps, in us)")
     print(DeviceTimeline.table(rows))
     return 0
 
