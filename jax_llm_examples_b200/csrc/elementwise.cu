@@ -6,6 +6,7 @@
 #include <cooperative_groups.h>
 
 #include "common.cuh"
+#include "expert_sort.cuh"
 
 // x[n, :] = table[ids[n], :]                                     (model.py:1191)
 template <typename TW>
@@ -117,7 +118,9 @@ __device__ __forceinline__ int router_partials(const float* __restrict__ row, co
 
 // Top-k of the raw scores by one thread (lower index wins ties; NaN never wins), weight = sigmoid of the score.
 // Destroys `scores`.
-__device__ __forceinline__ void router_topk(float* scores, int E, int k, size_t n, int* topk_idx, float* topk_w) {
+// With keep_idx / keep_w the choices are also left there (shared memory of the caller).
+__device__ __forceinline__ void router_topk(float* scores, int E, int k, size_t n, int* topk_idx, float* topk_w,
+                                            int* keep_idx = nullptr, float* keep_w = nullptr) {
   for (int j = 0; j < k; ++j) {
     int best = -1;
     float bv = 0.f;
@@ -130,8 +133,13 @@ __device__ __forceinline__ void router_topk(float* scores, int E, int k, size_t 
       }
     }
     if (best < 0) best = j;
+    const float weight = 1.f / (1.f + expf(-bv));
     topk_idx[n * k + j] = best;
-    topk_w[n * k + j] = 1.f / (1.f + expf(-bv));
+    topk_w[n * k + j] = weight;
+    if (keep_idx) {
+      keep_idx[j] = best;
+      keep_w[j] = weight;
+    }
     scores[best] = NAN;
   }
 }
@@ -307,6 +315,25 @@ add_rmsnorm_kernel(float* __restrict__ x, const DeltaSpec ds,
 // the columns: its part of the sum of squares and of every expert's score goes through distributed shared
 // memory, block 0 of the cluster adds the parts in rank order and chooses the experts.  bfloat16 output only:
 // the order of the sums differs from the one-block kernel's, which the 32-bit path must not depend on.
+// What a decode step's routed feed-forward needs after the router, done by the same kernel when it is asked to (`counter`
+// not null): the sort of the step's (token, choice) pairs by expert and the gather of the scaled rows in expert order,
+// which as kernels of their own are two more links in the step's chain of dependent launches.  See expert_sort_kernel
+// and permute_scale_kernel (moe.cu) for the outputs' meaning.  The rows' clusters take a ticket each from `counter`
+// (zero before the launch and after it); the cluster that takes the last one does the work for all rows.
+#define DISPATCH_MAX_ROWS 16    // tokens
+#define DISPATCH_MAX_PAIRS 64   // tokens x choices
+struct DispatchArgs {
+  int* counter;
+  int* offsets;
+  int* sorted_pair;
+  int* sorted_pos;
+  int* tile_list;   // with tile_rows > 0
+  int* n_tiles;
+  void* a_sorted;   // [pairs + extra_rows, D], the kernel's output type
+  int extra_rows, tile_rows;
+  int* status;
+};
+
 #define NORM_CLUSTER 8
 // ROUTER: with the router (else w_router is not used, and the kernel is two of everything leaner).
 template <typename TO, bool ROUTER>
@@ -315,7 +342,7 @@ add_rmsnorm_router_cluster_kernel(float* __restrict__ x, const DeltaSpec ds,
                                   const float* __restrict__ gamma, float eps, TO* __restrict__ out, float* __restrict__ out32, int D,
                                   int slice,
                                   const float* __restrict__ w_router, int E, int k, int* __restrict__ topk_idx,
-                                  float* __restrict__ topk_w) {
+                                  float* __restrict__ topk_w, const DispatchArgs dp) {
   JLX_TL(TL_NORM_ROUTER);
   namespace cg = cooperative_groups;
   cg::cluster_group cluster = cg::this_cluster();
@@ -327,6 +354,9 @@ add_rmsnorm_router_cluster_kernel(float* __restrict__ x, const DeltaSpec ds,
   __shared__ float cl_scores[NORM_CLUSTER][ROUTER_MAX_E];    // every block's part of every expert's score (used in block 0)
   __shared__ float scores[ROUTER_MAX_E];
   __shared__ float partial[ROUTER_MAX_E * ROUTER_MAX_PARTS];
+  __shared__ int choice[DISPATCH_MAX_PAIRS], order[DISPATCH_MAX_PAIRS];  // for the sort and gather (see DispatchArgs)
+  __shared__ float choice_w[DISPATCH_MAX_PAIRS], order_w[DISPATCH_MAX_PAIRS];
+  __shared__ int counts[ROUTER_MAX_E + 1];
   pdl_launch_dependents();
   const int n = blockIdx.x / C;
   const int lo = min(D, rank * slice), hi = min(D, lo + slice);  // multiples of 4
@@ -414,15 +444,79 @@ add_rmsnorm_router_cluster_kernel(float* __restrict__ x, const DeltaSpec ds,
       scores[e] = s;
     }
     __syncthreads();
-    if (threadIdx.x == 0) router_topk(scores, E, k, (size_t)n, topk_idx, topk_w);
+    if (threadIdx.x == 0) router_topk(scores, E, k, (size_t)n, topk_idx, topk_w, k <= DISPATCH_MAX_PAIRS ? choice : nullptr, choice_w);
+  }
+  if (ROUTER && dp.counter) {
+    // ---- the sort and the gather.  One row in the step: this cluster, from the choices that block 0 still holds.
+    // More rows: the cluster whose row is the last to have its experts, from all rows' choices in global memory.
+    __shared__ int cl_last;
+    const int rows = gridDim.x / C, P = rows * k;
+    if (rows > 1) {
+      if (rank == 0 && threadIdx.x == 0) {
+        __threadfence();  // this row's normed values (all blocks', by way of the barrier above) and choices, before the ticket
+        const int last = atomicAdd(dp.counter, 1) == rows - 1;
+        if (last) *dp.counter = 0;  // as the next launch expects it
+        __threadfence();  // ... and the other rows' after it
+#pragma unroll
+        for (int r = 0; r < C; ++r) *cluster.map_shared_rank(&cl_last, r) = last;
+      }
+      cluster.sync();
+      if (!cl_last) return;
+    }
+    if (rank == 0) {
+      __syncthreads();  // (one row: the choices that thread 0 kept)
+      if (rows > 1)
+        for (int i = threadIdx.x; i < P; i += blockDim.x) {  // other clusters' writes: past L1
+          choice[i] = __ldcg(topk_idx + i);
+          choice_w[i] = __ldcg(topk_w + i);
+        }
+      __syncthreads();
+      for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        int c = 0;
+        for (int i = 0; i < P; ++i) c += choice[i] == e;
+        counts[e] = c;
+      }
+      __syncthreads();
+      if (threadIdx.x < 32) expert_offsets_and_tiles(counts, E, P, dp.extra_rows, dp.tile_rows, dp.offsets, dp.tile_list, dp.n_tiles, dp.status, true);
+      __syncthreads();
+      for (int i = threadIdx.x; i < P; i += blockDim.x) {  // stable: a pair follows the earlier pairs of its expert
+        const int e = choice[i];
+        if (e < 0 || e >= E) continue;  // (never chosen by the router above; the count check has raised the status)
+        int dst = counts[e];
+        for (int j = 0; j < i; ++j) dst += choice[j] == e;
+        dp.sorted_pair[dst] = i;
+        dp.sorted_pos[i] = dst;
+        // the sorted order and the weights go into every block's shared memory: the gather below waits for no load
+#pragma unroll
+        for (int r = 0; r < C; ++r) {
+          cluster.map_shared_rank(order, r)[dst] = i;
+          cluster.map_shared_rank(order_w, r)[dst] = choice_w[i];
+        }
+      }
+    }
+    cluster.sync();
+    // every block: its columns of every sorted row (see permute_scale_kernel); this row's own values are still in rowbuf
+    const int n4 = (hi - lo) >> 2;
+    for (int item = threadIdx.x; item < (P + dp.extra_rows) * n4; item += blockDim.x) {
+      const int i = item / n4, c = item - i * n4;
+      const int pair = i < P ? order[i] : 0;
+      const float w = i < P ? order_w[i] : 1.f;
+      const int tok = i < P ? pair / k : i - P;
+      const float4 v = tok == n ? row4[c] : __ldcg(reinterpret_cast<const float4*>(out32 + (size_t)tok * D + lo) + c);
+      store4<TO>(reinterpret_cast<TO*>(dp.a_sorted) + (size_t)i * D + lo + 4 * c, make_float4(w * v.x, w * v.y, w * v.z, w * v.w));
+    }
   }
   }
 }
 
 // delta: what to add to x first (null: nothing), see DeltaSpec; the struct is read on the host.
+// dispatch (optional, with a router): the sort and gather that a routed feed-forward would launch next, see DispatchArgs;
+// *dispatched tells whether this call did them (it does when it runs the cluster kernel and the step is small enough).
 JLX_API int jlx_add_rmsnorm(float* x, const DeltaSpec* delta, const float* gamma,
                             float eps, void* out, int out_dtype, float* out32, const int* row_index, int N, int D,
-                            const float* w_router, int E, int k, int* topk_idx, float* topk_w, cudaStream_t stream) {
+                            const float* w_router, int E, int k, int* topk_idx, float* topk_w, const DispatchArgs* dispatch,
+                            int* dispatched, cudaStream_t stream) {
+  if (dispatched) *dispatched = 0;
   JLX_REQUIRE(N >= 0 && D > 0, "add_rmsnorm: bad sizes N=%d D=%d", N, D);
   JLX_REQUIRE(eps > 0.f, "add_rmsnorm: eps must be positive");
   DeltaSpec ds = {};
@@ -467,12 +561,21 @@ JLX_API int jlx_add_rmsnorm(float* x, const DeltaSpec* delta, const float* gamma
     attr[1].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 2;
+    DispatchArgs dp = {};
+    if (w_router && dispatch && dispatch->counter && out32 && N <= DISPATCH_MAX_ROWS && N * k <= DISPATCH_MAX_PAIRS) {
+      JLX_REQUIRE(dispatch->offsets && dispatch->sorted_pair && dispatch->sorted_pos && dispatch->a_sorted && dispatch->status &&
+                  dispatch->extra_rows >= 0 && (dispatch->tile_rows == 0 || (dispatch->tile_list && dispatch->n_tiles)),
+                  "add_rmsnorm: incomplete dispatch request");
+      JLX_REQUIRE(((uintptr_t)dispatch->a_sorted & 15) == 0, "add_rmsnorm: the gathered rows must be 16-byte aligned");
+      dp = *dispatch;
+      if (dispatched) *dispatched = 1;
+    }
     if (w_router)
       JLX_CUDA(cudaLaunchKernelEx(&cfg, add_rmsnorm_router_cluster_kernel<bf16, true>, x, ds, gamma, eps,
-                                  (bf16*)out, out32, D, slice, w_router, E, k, topk_idx, topk_w));
+                                  (bf16*)out, out32, D, slice, w_router, E, k, topk_idx, topk_w, dp));
     else
       JLX_CUDA(cudaLaunchKernelEx(&cfg, add_rmsnorm_router_cluster_kernel<bf16, false>, x, ds, gamma, eps,
-                                  (bf16*)out, out32, D, slice, w_router, E, k, topk_idx, topk_w));
+                                  (bf16*)out, out32, D, slice, w_router, E, k, topk_idx, topk_w, dp));
     JLX_LAUNCH_CHECK("add_rmsnorm (cluster)");
     return 0;
   }

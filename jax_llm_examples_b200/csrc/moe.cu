@@ -6,6 +6,7 @@
 // INPUT row by its router weight, group sizes), model.py:1109-1111 (unsort, sum over k),
 // model.py:1139 (add the shared expert).  Ties go to the lower expert index (jax.lax.top_k order).
 #include "common.cuh"
+#include "expert_sort.cuh"
 
 #define ROUTER_MAX_E 256
 #define ROUTER_MAX_K 16
@@ -178,59 +179,7 @@ __global__ void expert_sort_kernel(const int* __restrict__ topk_idx, int* __rest
     }
     __syncthreads();
     if (warp == 0) {
-      // offsets = exclusive prefix sums of the counts, 32 experts at a time by shuffles (a single thread walking
-      // the experts and then the tiles was a third of this kernel's time in a decode step)
-      int run = 0;
-      for (int e0 = 0; e0 < E; e0 += 32) {
-        const int e = e0 + lane;
-        const int c = e < E ? counts[e] : 0;
-        int incl = c;
-#pragma unroll
-        for (int d = 1; d < 32; d <<= 1) {
-          const int v = __shfl_up_sync(0xffffffffu, incl, d);
-          if (lane >= d) incl += v;
-        }
-        __syncwarp();
-        if (e < E) {
-          counts[e] = run + incl - c;
-          if (real) offsets[e] = run + incl - c;
-        }
-        run += __shfl_sync(0xffffffffu, incl, 31);
-      }
-      if (lane == 0) {
-        counts[E] = run;
-        if (real) {
-          offsets[E] = run;
-          if (extra_rows > 0) offsets[E + 1] = run + extra_rows;
-          if (run != P) atomicOr(status, JLX_STATUS_BAD_EXPERT);
-        }
-      }
-      __syncwarp();
-      if (tile_rows > 0) {
-        // the tiles of group g follow those of the groups before it: the same scan over the groups' tile counts
-        const int groups = extra_rows > 0 ? E + 1 : E;
-        int t_run = 0;
-        for (int g0 = 0; g0 < groups; g0 += 32) {
-          const int g = g0 + lane;
-          const int lo = g < groups ? counts[g] : 0, hi = g < E ? counts[g + 1] : (g == E ? run + extra_rows : 0);
-          const int tiles = g < groups ? (hi - lo + tile_rows - 1) / tile_rows : 0;
-          int incl = tiles;
-#pragma unroll
-          for (int d = 1; d < 32; d <<= 1) {
-            const int v = __shfl_up_sync(0xffffffffu, incl, d);
-            if (lane >= d) incl += v;
-          }
-          if (real) {
-            int t = t_run + incl - tiles;
-            for (int r = lo; r < hi; r += tile_rows, ++t) {
-              tile_list[2 * t] = g;
-              tile_list[2 * t + 1] = r;
-            }
-          }
-          t_run += __shfl_sync(0xffffffffu, incl, 31);
-        }
-        if (real && lane == 0) n_tiles[0] = t_run;
-      }
+      expert_offsets_and_tiles(counts, E, P, extra_rows, tile_rows, offsets, tile_list, n_tiles, status, real);
       if (real) JLX_TL_MARK(1);
     }
     __syncthreads();

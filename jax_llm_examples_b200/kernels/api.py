@@ -124,6 +124,7 @@ def _splits(t: torch.Tensor | None, splits: int) -> tuple[int, int]:
 
 
 DELTA_MAX_TERMS = 3
+DISPATCH_MAX_ROWS, DISPATCH_MAX_PAIRS = 16, 64  # csrc/elementwise.cu
 
 
 class _DeltaTerm(ctypes.Structure):
@@ -134,16 +135,25 @@ class _DeltaSpec(ctypes.Structure):
     _fields_ = [("n", c_int), ("t", _DeltaTerm * DELTA_MAX_TERMS)]
 
 
+class _DispatchArgs(ctypes.Structure):  # DispatchArgs in csrc/elementwise.cu
+    _fields_ = [("counter", c_void_p), ("offsets", c_void_p), ("sorted_pair", c_void_p), ("sorted_pos", c_void_p),
+                ("tile_list", c_void_p), ("n_tiles", c_void_p), ("a_sorted", c_void_p), ("extra_rows", c_int),
+                ("tile_rows", c_int), ("status", c_void_p)]
+
+
 def add_rmsnorm(x: torch.Tensor, delta, gamma: torch.Tensor | None, eps: float,
                 out: torch.Tensor | None, out32: torch.Tensor | None = None, row_index: torch.Tensor | None = None,
                 delta_splits: int = 1, w_router: torch.Tensor | None = None, topk_idx: torch.Tensor | None = None,
-                topk_w: torch.Tensor | None = None) -> None:
+                topk_w: torch.Tensor | None = None, dispatch=None) -> bool:
     """x (+= delta); out = gamma * x / sqrt(mean(x^2) + eps).  ``delta``: a float32 tensor that may hold
     ``delta_splits`` split-K partials [splits, N, D], added in order; or a list of up to DELTA_MAX_TERMS terms
     ``(data, splits, index, k, base)`` added in the order given: of the float32 partials ``data`` [splits, rows, D]
     token r takes row ``base + r`` or, with ``index`` (int32 [N * k]), the k rows ``index[r * k + j]``.
     With row_index, row n reads source row row_index[n] and x is not written back.  With w_router [E, D] the token
-    is routed in the same kernel: topk_idx / topk_w [N, k]."""
+    is routed in the same kernel: topk_idx / topk_w [N, k].  ``dispatch`` (with w_router; an object with the tensors
+    counter, offsets, sorted_pair, sorted_pos, a_sorted, status, the optional pair tiles = (tile_list, n_tiles) and
+    the numbers extra_rows, tile_rows): what ``expert_sort`` and ``permute_scale`` would write next; the kernel does
+    their work too when the step is small enough for that, and the call returns whether it did."""
     terms = [] if delta is None else (list(delta) if isinstance(delta, (list, tuple)) else [(delta, delta_splits, None, 1, 0)])
     _contig(x, gamma, out, out32, row_index, w_router, topk_idx, topk_w, *(t[0] for t in terms), *(t[2] for t in terms))
     D = x.shape[-1]
@@ -165,9 +175,20 @@ def add_rmsnorm(x: torch.Tensor, delta, gamma: torch.Tensor | None, eps: float,
         if w_router.dtype != torch.float32 or topk_idx is None or topk_w is None:
             raise KernelError("router: float32 weight and outputs are needed")
         E, k = w_router.shape[0], topk_idx.shape[1]
+    dp, did = None, c_int(0)
+    if dispatch is not None and w_router is not None:
+        tile_list, n_tiles = dispatch.tiles if dispatch.tiles is not None else (None, None)
+        _contig(dispatch.offsets, dispatch.sorted_pair, dispatch.sorted_pos, dispatch.a_sorted, tile_list, n_tiles)
+        if out is None or dispatch.a_sorted.dtype != out.dtype:
+            raise KernelError("add_rmsnorm: the gathered rows must have the output's type")
+        dp = _DispatchArgs(_ptr(dispatch.counter), _ptr(dispatch.offsets), _ptr(dispatch.sorted_pair), _ptr(dispatch.sorted_pos),
+                           _ptr(tile_list), _ptr(n_tiles), _ptr(dispatch.a_sorted), dispatch.extra_rows,
+                           dispatch.tile_rows if tile_list is not None else 0, _ptr(dispatch.status))
     _run("elementwise", "jlx_add_rmsnorm", _ptr(x), ctypes.byref(spec) if terms else None, _ptr(gamma), c_float(eps),
          _ptr(out), c_int(code(out.dtype) if out is not None else F32), _ptr(out32), _ptr(row_index), c_int(n), c_int(D),
-         _ptr(w_router), c_int(E), c_int(k), _ptr(topk_idx), _ptr(topk_w), _stream())
+         _ptr(w_router), c_int(E), c_int(k), _ptr(topk_idx), _ptr(topk_w), ctypes.byref(dp) if dp is not None else None,
+         ctypes.byref(did), _stream())
+    return bool(did.value)
 
 
 def silu_mul(gu: torch.Tensor, out: torch.Tensor, splits: int = 1, interleaved: bool = False) -> None:

@@ -106,6 +106,18 @@ class Workspace:
             self._side = torch.cuda.Stream(device=self.device)
         return self._side
 
+    def zeros(self, name: str, numel: int, dtype: torch.dtype) -> torch.Tensor:
+        """A buffer that is zero when first handed out and is never handed out as scratch: for kernels that keep a
+        small state across launches (a ticket counter that every launch leaves at zero)."""
+        key = "zeros:" + name
+        t = self._bufs.get(key)
+        if t is None or t.numel() < numel or t.dtype != dtype:
+            if t is not None:
+                self._outgrown.append(t)
+            t = torch.zeros(max(numel, 1), dtype=dtype, device=self.device)
+            self._bufs[key] = t
+        return t[:numel]
+
     def get(self, name: str, numel: int, dtype: torch.dtype) -> torch.Tensor:
         t = self._bufs.get(name)
         if t is None or t.numel() < numel or t.dtype != dtype:
@@ -219,6 +231,24 @@ def walk_parts(part: "Part"):
         yield from walk_parts(p)
 
 
+@dataclasses.dataclass
+class Dispatch:
+    """What a routed feed-forward needs between the router and its experts' products: the step's (token, choice)
+    pairs sorted by expert and the tokens' rows gathered (and scaled) in that order.  A feed-forward that can use
+    them offers the buffers through ``router_request()``; a norm that routes for it may fill them in the same kernel
+    and hands them back with the routing, which saves a decode step two dependent launches per layer."""
+
+    counter: torch.Tensor  # int32 [1], zero between launches
+    offsets: torch.Tensor  # int32 [groups + 1]
+    sorted_pair: torch.Tensor  # int32 [pairs]
+    sorted_pos: torch.Tensor  # int32 [pairs]
+    tiles: "tuple[torch.Tensor, torch.Tensor] | None"  # (tile list, count) for the grouped streaming products
+    a_sorted: torch.Tensor  # [pairs + extra_rows, D]
+    extra_rows: int  # rows of a group appended after the experts (a shared expert that takes every token)
+    tile_rows: int
+    status: torch.Tensor
+
+
 class Norm(Part):
     fuses_router: bool = False  # True: forward(router=...) also routes the tokens in its kernel
 
@@ -226,7 +256,9 @@ class Norm(Part):
                 want_f32: bool = False, row_index: torch.Tensor | None = None, router=None):
         """x += delta (if given); returns (normed rows in out_dtype, the same in float32 if asked,
         routing).  ``router`` = (w_router [E, D] float32, top_k) asks a norm with ``fuses_router`` to
-        route as well: routing = (expert indices [N, k] int32, weights [N, k] float32); else None."""
+        route as well: routing = (expert indices [N, k] int32, weights [N, k] float32); else None.  The request
+        may have a third element, a function (ctx, n_rows) -> Dispatch or None; a norm that fills the Dispatch too
+        returns it as the routing's third element."""
         raise NotImplementedError
 
 
@@ -260,7 +292,8 @@ class FeedForward(Part):
     needs_f32_input: bool = False  # True: forward() also gets the normed rows unrounded
 
     def router_request(self):
-        """(w_router, top_k) if the preceding norm may route the tokens for this part, else None."""
+        """(w_router, top_k) if the preceding norm may route the tokens for this part, else None; optionally a third
+        element, see Norm.forward."""
         return None
 
     def forward(self, ctx: StepContext, h: torch.Tensor, h32: torch.Tensor | None, routing=None) -> "torch.Tensor | Rows":

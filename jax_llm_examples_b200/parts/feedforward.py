@@ -6,7 +6,7 @@ import torch
 
 from ..kernels import api as K
 from ..tracing import scope
-from .base import FeedForward, Rows, RowSum, StepContext, as_rows, register_part
+from .base import Dispatch, FeedForward, Rows, RowSum, StepContext, as_rows, register_part
 from .linear import (STREAM_MAX_ROWS, group_rows_hint, grouped_linear, grouped_swiglu_linear, interleave_gate_up, linear,
                      swiglu_linear)
 
@@ -81,7 +81,45 @@ class RoutedExperts(FeedForward):
         return () if self.shared is None else (self.shared,)
 
     def router_request(self):
-        return (self.w_router, self.top_k)
+        return (self.w_router, self.top_k, self.offer_dispatch)
+
+    def placement(self, ctx: StepContext, n: int) -> tuple[bool, bool]:
+        """Where the shared expert runs in a step of n rows: (on a second stream beside the routed experts, as one more
+        group of the routed experts' products).  One or two rows: as a group (two launches fewer; with so few blocks one
+        kernel streams better than two).  More rows: on a second stream, beside the sort, the gather and the routed
+        products: its weights stream while those small kernels would leave the memory idle (decode at batch 8: +3.7 %,
+        batch 64: +6.5 %; batch 1 would lose 4 %).  Prompt portions: the routed experts stream their weights once for
+        about a hundred rows each (bound by HBM), the shared expert's products are dense (bound by the tensor cores);
+        side by side, the tails and the small kernels of either hide behind the other.  Between STREAM_MAX_ROWS and
+        OVERLAP_MIN_ROWS: one after the other."""
+        beside = self.shared is not None and ctx.workspace is not None and (
+            self.FORK_MIN_ROWS <= n <= STREAM_MAX_ROWS or n >= self.OVERLAP_MIN_ROWS)
+        return beside, self.merged and n <= STREAM_MAX_ROWS and not beside
+
+    def sort_buffers(self, ctx: StepContext, n: int, extra_rows: int):
+        """(offsets, sorted_pair, sorted_pos, tiles, tile_rows) for a step of n rows, not yet filled."""
+        k, dev = self.top_k, self.w_router.device
+        offsets = torch.empty(self.num_experts + 2, dtype=torch.int32, device=dev)
+        sorted_pair = torch.empty(n * k, dtype=torch.int32, device=dev)
+        sorted_pos = torch.empty(n * k, dtype=torch.int32, device=dev)
+        tiles, tile_rows = None, 0
+        if self.we_gate_up.dtype == torch.bfloat16 and ctx.runtime.dtype == torch.bfloat16:
+            # the grouped products will run on the streaming kernel: their row tiles are listed once, by the sort
+            rows, groups = n * k + extra_rows, self.num_experts + (extra_rows > 0)
+            tile_rows = K.gemm_stream_token_tile(group_rows_hint(rows, groups, extra_rows))
+            tiles = (torch.empty(2 * (-(-rows // tile_rows) + groups), dtype=torch.int32, device=dev),
+                     torch.empty(1, dtype=torch.int32, device=dev))
+        return offsets, sorted_pair, sorted_pos, tiles, tile_rows
+
+    def offer_dispatch(self, ctx: StepContext, n: int) -> Dispatch | None:
+        """The buffers that a norm which routes for this part may fill as well (see Dispatch)."""
+        if ctx.workspace is None:
+            return None
+        extra = n if self.placement(ctx, n)[1] else 0
+        offsets, sorted_pair, sorted_pos, tiles, tile_rows = self.sort_buffers(ctx, n, extra)
+        a_sorted = torch.empty((n * self.top_k + extra, self.w_router.shape[1]), dtype=ctx.runtime.dtype, device=self.w_router.device)
+        return Dispatch(ctx.workspace.zeros("dispatch_counter", 1, torch.int32), offsets, sorted_pair, sorted_pos, tiles, a_sorted,
+                        extra, tile_rows, ctx.status)
 
     def route(self, ctx: StepContext, h32: torch.Tensor):
         """The router as a kernel of its own (when the norm before this part does not route)."""
@@ -92,17 +130,8 @@ class RoutedExperts(FeedForward):
         return topk_idx, topk_w
 
     def sort(self, ctx: StepContext, topk_idx: torch.Tensor, extra_rows: int = 0):
-        n, k, dev = topk_idx.shape[0], self.top_k, topk_idx.device
-        offsets = torch.empty(self.num_experts + 2, dtype=torch.int32, device=dev)
-        sorted_pair = torch.empty(n * k, dtype=torch.int32, device=dev)
-        sorted_pos = torch.empty(n * k, dtype=torch.int32, device=dev)
-        tiles = None
-        if self.we_gate_up.dtype == torch.bfloat16 and ctx.runtime.dtype == torch.bfloat16:
-            # the grouped products will run on the streaming kernel: list their row tiles once, here
-            rows, groups = n * k + extra_rows, self.num_experts + (extra_rows > 0)
-            tile_rows = K.gemm_stream_token_tile(group_rows_hint(rows, groups, extra_rows))
-            tiles = (torch.empty(2 * (-(-rows // tile_rows) + groups), dtype=torch.int32, device=dev),
-                     torch.empty(1, dtype=torch.int32, device=dev))
+        offsets, sorted_pair, sorted_pos, tiles, tile_rows = self.sort_buffers(ctx, topk_idx.shape[0], extra_rows)
+        if tiles is not None:
             K.expert_sort(topk_idx, offsets, sorted_pair, sorted_pos, self.num_experts, ctx.status, extra_rows, tile_rows, *tiles)
         else:
             K.expert_sort(topk_idx, offsets, sorted_pair, sorted_pos, self.num_experts, ctx.status, extra_rows)
@@ -112,19 +141,11 @@ class RoutedExperts(FeedForward):
         rt = ctx.runtime
         n, D = h32.shape
         k, E = self.top_k, self.num_experts
-        topk_idx, topk_w = routing if routing is not None else self.route(ctx, h32)
+        topk_idx, topk_w, *dispatched = routing if routing is not None else self.route(ctx, h32)
+        done = dispatched[0] if dispatched else None  # sorted and gathered already, by the norm that routed
         if "record_routing" in ctx.scratch:  # tests compare the choices with a plain router's
             ctx.scratch["record_routing"].append(topk_idx)
-        # Where the shared expert runs.  One or two rows: as one more group of the routed experts' two products (two
-        # launches fewer; with so few blocks one kernel streams better than two).  More rows: on a second stream, beside
-        # the sort, the gather and the routed products: its weights stream while those small kernels would leave the
-        # memory idle (decode at batch 8: +3.7 %, batch 64: +6.5 %; batch 1 would lose 4 %).  Prompt portions: the
-        # routed experts stream their weights once for about a hundred rows each (bound by HBM), the shared expert's
-        # products are dense (bound by the tensor cores); side by side, the tails and the small kernels of either
-        # hide behind the other.  Between STREAM_MAX_ROWS and OVERLAP_MIN_ROWS: one after the other.
-        beside = self.shared is not None and ctx.workspace is not None and (
-            self.FORK_MIN_ROWS <= n <= STREAM_MAX_ROWS or n >= self.OVERLAP_MIN_ROWS)
-        merged = self.merged and n <= STREAM_MAX_ROWS and not beside
+        beside, merged = self.placement(ctx, n)
         extra = n if merged else 0
         shared, side = None, None
         if beside:
@@ -134,10 +155,15 @@ class RoutedExperts(FeedForward):
                 shared = as_rows(self.shared.forward(ctx, h, None))
             shared.data.record_stream(main)  # made on the side stream, read (and freed) on the step's own
         with scope("moe_routed_expert"):  # the reference's names (model.py:1076-1138)
-            with scope("permute"):
-                offsets, sorted_pair, sorted_pos, tiles = self.sort(ctx, topk_idx, extra)
-                a_sorted = torch.empty((n * k + extra, D), dtype=rt.dtype, device=h.device)
-                K.permute_scale(h32, sorted_pair, topk_w, a_sorted, k, extra)
+            if done is not None:
+                if done.extra_rows != extra:
+                    raise RuntimeError("the rows gathered with the routing do not fit this step's placement of the shared expert")
+                offsets, sorted_pos, tiles, a_sorted = done.offsets, done.sorted_pos, done.tiles, done.a_sorted
+            else:
+                with scope("permute"):
+                    offsets, sorted_pair, sorted_pos, tiles = self.sort(ctx, topk_idx, extra)
+                    a_sorted = torch.empty((n * k + extra, D), dtype=rt.dtype, device=h.device)
+                    K.permute_scale(h32, sorted_pair, topk_w, a_sorted, k, extra)
             groups = E + 1 if merged else E
             with scope("we_gate_up"):
                 act = grouped_swiglu_linear(ctx, a_sorted, self.we_gate_up[:groups], offsets, self.interleaved, rt.dtype, extra, tiles)

@@ -36,7 +36,7 @@ class RMSNorm(Norm):
         w_router = idx = wt = None
         unfused = False
         if router is not None and x.shape[1] <= 16384:
-            w_router, k = router
+            w_router, k, *offer = router
             idx = torch.empty((n, k), dtype=torch.int32, device=dev)
             wt = torch.empty((n, k), dtype=torch.float32, device=dev)
             routing = (idx, wt)
@@ -46,7 +46,15 @@ class RMSNorm(Norm):
             unfused = out_dtype == torch.bfloat16 and n > self.FUSED_ROUTER_MAX_ROWS and x.shape[1] % 4 == 0
             if unfused and out32 is None:
                 out32 = torch.empty((n, x.shape[1]), dtype=torch.float32, device=dev)
-        K.add_rmsnorm(x, terms, self.weight, self.eps, out, out32, row_index, 1, None if unfused else w_router, idx, wt)
+        # a decode step's few rows: the kernel can also sort the choices and gather the rows for the experts
+        dispatch = None
+        if routing is not None and not unfused and offer and offer[0] is not None and row_index is None \
+                and out_dtype == torch.bfloat16 and n <= K.DISPATCH_MAX_ROWS and n * k <= K.DISPATCH_MAX_PAIRS:
+            dispatch = offer[0](ctx, n)
+        did = K.add_rmsnorm(x, terms, self.weight, self.eps, out, out32, row_index, 1, None if unfused else w_router, idx, wt,
+                            dispatch)
+        if did:
+            routing = (idx, wt, dispatch)
         if unfused:
             K.router(out32, w_router, idx, wt, many_rows=True)
         return out, out32, routing
