@@ -582,6 +582,47 @@ def test_add_rmsnorm_router_on_few_rows_by_a_cluster(N, D, E, k, splits, want32)
     close(wt, torch.sigmoid(chosen), 1e-4)
 
 
+@pytest.mark.parametrize("N,D,E,k,extra,tile_rows", [(1, 1024, 16, 1, 1, 16), (1, 1280, 4, 2, 0, 0), (5, 1024, 16, 1, 0, 16),
+                                                      (16, 2048, 40, 2, 16, 32), (3, 1024, 130, 4, 3, 16)])
+def test_add_rmsnorm_router_that_also_sorts_and_gathers(N, D, E, k, extra, tile_rows):
+    """A decode step's norm + router kernel can do what expert_sort and permute_scale would do next (one launch for
+    three).  Its sort and its gathered rows must be exactly theirs, from the same choices; launch after launch (the
+    ticket counter returns to zero)."""
+    from types import SimpleNamespace
+
+    eps, P = 1e-5, N * k
+    g, w = 1 + 0.1 * torch.randn(D, device=DEV), torch.randn(E, D, device=DEV)
+    counter, st = torch.zeros(1, device=DEV, dtype=torch.int32), status()
+    groups = E + (extra > 0)
+    for launch in range(3):
+        x, parts = torch.randn(N, D, device=DEV), torch.randn(2, N, D, device=DEV)
+        out, out32 = torch.empty(N, D, device=DEV, dtype=torch.bfloat16), torch.empty(N, D, device=DEV)
+        idx, wt = torch.full((N, k), -1, device=DEV, dtype=torch.int32), torch.empty(N, k, device=DEV)
+        tiles = (torch.full((2 * (-(-(P + extra) // tile_rows) + groups),), -7, device=DEV, dtype=torch.int32),
+                 torch.full((1,), -7, device=DEV, dtype=torch.int32)) if tile_rows else None
+        d = SimpleNamespace(counter=counter, offsets=torch.full((E + 2,), -7, device=DEV, dtype=torch.int32),
+                            sorted_pair=torch.full((P,), -7, device=DEV, dtype=torch.int32),
+                            sorted_pos=torch.full((P,), -7, device=DEV, dtype=torch.int32), tiles=tiles,
+                            a_sorted=torch.full((P + extra, D), float("nan"), device=DEV, dtype=torch.bfloat16),
+                            extra_rows=extra, tile_rows=tile_rows, status=st)
+        assert K().add_rmsnorm(x, parts, g, eps, out, out32, None, 2, w, idx, wt, d)
+        torch.cuda.synchronize()
+        assert int(counter) == 0 and int(st) == 0
+        # the separate kernels, from the same choices and the same normed rows
+        offsets, pair, pos = (torch.full_like(t, -9) for t in (d.offsets, d.sorted_pair, d.sorted_pos))
+        tiles2 = tuple(torch.full_like(t, -9) for t in tiles) if tiles else ()
+        K().expert_sort(idx, offsets, pair, pos, E, st, extra, tile_rows, *tiles2)
+        a2 = torch.empty_like(d.a_sorted)
+        K().permute_scale(out32, pair, wt, a2, k, extra)
+        torch.cuda.synchronize()
+        n_off = E + 2 if extra else E + 1
+        assert torch.equal(d.offsets[:n_off], offsets[:n_off]) and torch.equal(d.sorted_pair, pair) and torch.equal(d.sorted_pos, pos)
+        if tiles:
+            nt = int(tiles2[1])
+            assert int(tiles[1]) == nt and torch.equal(tiles[0][:2 * nt], tiles2[0][:2 * nt])
+        assert torch.equal(d.a_sorted, a2)
+
+
 def test_rope_kv_store_from_float32_partials():
     N, Hq, Hkv, dh, page, P, eps = 5, 4, 2, 64, 16, 4, 1e-5
     parts = torch.randn(2, N, (Hq + 2 * Hkv) * dh, device=DEV)
