@@ -45,8 +45,9 @@ __device__ __forceinline__ void expert_offsets_and_tiles(int* counts, int E, int
     int t_run = 0;
     for (int g0 = 0; g0 < groups; g0 += 32) {
       const int g = g0 + lane;
-      const int lo = g < groups ? counts[g] : 0, hi = g < E ? counts[g + 1] : (g == E ? run + extra_rows : 0);
-      const int tiles = g < groups ? (hi - lo + tile_rows - 1) / tile_rows : 0;
+      // (a lane beyond the last group has no rows: lo = hi = 0, so that it lists nothing below)
+      const int lo = g < groups ? counts[g] : 0, hi = g >= groups ? 0 : (g < E ? counts[g + 1] : run + extra_rows);
+      const int tiles = (hi - lo + tile_rows - 1) / tile_rows;
       int incl = tiles;
 #pragma unroll
       for (int d = 1; d < 32; d <<= 1) {

@@ -313,6 +313,28 @@ def test_router_and_sort(N, D, E, k):
     assert torch.equal(pos.long()[pair.long()], torch.arange(N * k, device=DEV)) and int(st) == 0
 
 
+@pytest.mark.parametrize("N, E, k, extra, tile_rows", [(353, 40, 2, 0, 32), (64, 16, 1, 0, 16), (7, 40, 2, 7, 16), (200, 130, 3, 0, 16),
+                                                       (300, 32, 1, 300, 64), (1, 31, 1, 1, 16)])
+def test_expert_sort_lists_the_row_tiles_and_nothing_else(N, E, k, extra, tile_rows):
+    """offsets, the stable order, and the list of row tiles (group, first row) of every group that has rows, with the
+    appended group of a shared expert last; the entries of the list past the last tile stay untouched."""
+    idx = torch.stack([torch.randperm(E, device=DEV)[:k] for _ in range(N)]).to(torch.int32)
+    P, groups = N * k, E + (extra > 0)
+    off = torch.full((E + 2,), -7, device=DEV, dtype=torch.int32)
+    pair, pos, st = torch.full((P,), -7, device=DEV, dtype=torch.int32), torch.full((P,), -7, device=DEV, dtype=torch.int32), status()
+    tl = torch.full((2 * (-(-(P + extra) // tile_rows) + groups),), -7, device=DEV, dtype=torch.int32)
+    nt = torch.full((1,), -7, device=DEV, dtype=torch.int32)
+    K().expert_sort(idx, off, pair, pos, E, st, extra, tile_rows, tl, nt)
+    flat = idx.flatten().long()
+    bounds = [0] + torch.bincount(flat, minlength=E).cumsum(0).tolist() + ([P + extra] if extra else [])
+    assert off[:len(bounds)].tolist() == bounds and int(st) == 0
+    assert torch.equal(pair.long(), torch.sort(flat, stable=True).indices)
+    assert torch.equal(pos.long()[pair.long()], torch.arange(P, device=DEV))
+    want = [v for g in range(groups) for r in range(bounds[g], bounds[g + 1], tile_rows) for v in (g, r)]
+    assert int(nt) == len(want) // 2 and tl[:len(want)].tolist() == want
+    assert bool((tl[len(want):] == -7).all())
+
+
 @pytest.mark.parametrize("N, D, E, k", [(301, 5120, 16, 1), (70, 96, 8, 2), (1000, 200, 128, 4), (9, 64, 3, 3)])
 def test_router_for_many_rows(N, D, E, k):
     """The kernel that shares each router row among eight tokens: the same choices as float64 makes, except
@@ -620,6 +642,8 @@ def test_add_rmsnorm_router_that_also_sorts_and_gathers(N, D, E, k, extra, tile_
         if tiles:
             nt = int(tiles2[1])
             assert int(tiles[1]) == nt and torch.equal(tiles[0][:2 * nt], tiles2[0][:2 * nt])
+            # nothing is written past the list (a lane of the scan beyond the last group once listed tiles of its own)
+            assert bool((tiles[0][2 * nt:] == -7).all()) and bool((tiles2[0][2 * nt:] == -9).all())
         assert torch.equal(d.a_sorted, a2)
 
 
