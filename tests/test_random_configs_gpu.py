@@ -14,7 +14,7 @@ from tests import helpers as H
 pytestmark = pytest.mark.gpu
 
 
-def random_config(rng: random.Random) -> dict:
+def random_config(rng: random.Random, wide: bool = False) -> dict:
     dh = rng.choice([16, 32, 48, 64, 64, 96, 112, 128, 128, 144, 256])
     hkv = rng.choice([1, 2, 3, 4])
     group = rng.choice([1, 2, 3, 5, 8, 10, 16, 20]) if dh in (64, 128) else rng.choice([1, 2, 3])
@@ -36,6 +36,14 @@ def random_config(rng: random.Random) -> dict:
     if rng.random() < 0.5:
         cfg["rope_scaling"] = {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
                                "high_freq_factor": rng.choice([1.0, 4.0]), "original_max_position_embeddings": rng.choice([32, 64])}
+    if wide:
+        # widths from 1024 on take the kernels that a decode step of the real sizes takes (a cluster of blocks per row
+        # for the norms, the norm that also sorts and gathers); a shared expert of the experts' shape rides as a group
+        # of the experts' products when a step has one or two rows
+        cfg["hidden_size"] = rng.choice([1024, 1032, 1280, 2048])
+        cfg["intermediate_size"] = rng.choice([32, 64, 96, 128])
+        if rng.random() < 0.6:
+            cfg["intermediate_size_mlp"] = cfg["intermediate_size"]
     return cfg
 
 
@@ -58,3 +66,40 @@ def test_a_random_configuration(tmp_path, seed):
         got, routing = H.run_trace(eng, H.trace_tail_decode(reqs, 32))
         H.compare_with_plain(folder, reqs, got, routing, dtype)
         assert all(eng.manager.free_pages(g) == eng.num_pages for g in range(len(eng.manager.groups)))
+
+
+@pytest.mark.parametrize("seed", [500, 503, 511, 517])
+def test_a_random_wide_configuration(tmp_path, seed):
+    import jax_llm_examples_b200 as J
+
+    rng = random.Random(seed)
+    cfg = random_config(rng, wide=True)
+    page = 64
+    folder = J.write_random_model(tmp_path / "m", cfg, seed, dtype=torch.bfloat16, norm_noise=0.1)
+    lengths = [rng.randint(1, 200) for _ in range(4)] + [rng.choice([129, 300])]
+    reqs = H.random_requests(rng, cfg["vocab_size"], lengths)
+    for dtype in ("float32", "bfloat16"):
+        model = J.load_model(folder, dtype, "cuda")
+        need = sum(-(-n // page) * page for n in sorted(lengths)[-4:])
+        eng = J.Engine(model, max_tokens=need, page_size=page, max_slots=4)
+        got, routing = H.run_trace(eng, H.trace_mixed(reqs, random.Random(seed), max_live=4, portions=H.LONG_PORTIONS))
+        H.compare_with_plain(folder, reqs, got, routing, dtype)
+        got, routing = H.run_trace(eng, H.trace_tail_decode(reqs, 32))
+        H.compare_with_plain(folder, reqs, got, routing, dtype)
+
+
+def test_forty_experts_top_two_and_prompts_of_hundreds_of_tokens(tmp_path):
+    """More groups than a warp has lanes, two choices per token, and hundreds of (token, choice) pairs in a step: the
+    sort's list of row tiles is long here, and once ran past its end."""
+    import jax_llm_examples_b200 as J
+
+    rng = random.Random(232)
+    cfg = random_config(rng)
+    cfg.update(num_hidden_layers=2, hidden_size=64, num_attention_heads=5, num_key_value_heads=1, head_dim=128, moe_layers=[0, 1],
+               num_local_experts=40, num_experts_per_tok=2, intermediate_size=40, intermediate_size_mlp=64, no_rope_layers=[1, 1])
+    folder = J.write_random_model(tmp_path / "m", cfg, 232, dtype=torch.bfloat16, norm_noise=0.1)
+    reqs = H.random_requests(rng, cfg["vocab_size"], [353, 202, 144])
+    for dtype in ("float32", "bfloat16"):
+        eng = J.Engine(J.load_model(folder, dtype, "cuda"), max_tokens=1024, page_size=64, max_slots=3)
+        got, routing = H.run_trace(eng, H.trace_whole(reqs))
+        H.compare_with_plain(folder, reqs, got, routing, dtype)
