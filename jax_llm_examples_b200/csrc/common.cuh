@@ -169,7 +169,9 @@ __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepc
 // dependent launch) and has nothing to do until that ends, so it spends the wait running its own code once with
 // every load of a predecessor's data and every store switched off (a pass of a loop that the compiler may not
 // unroll, so that both passes are the same instructions), which brings the code in.  Only small grids do this: with
-// many blocks the code is warm after the first and the second pass would only cost time.
+// many blocks the code is warm after the first and the second pass would only cost time.  And only kernels that start
+// well before their predecessor ends: one that follows a matrix product whose blocks fill every SM gets its SMs
+// microseconds before its work, and a rehearsal would then delay it (measured; see the norm kernels).
 #define JLX_REHEARSAL_MAX_BLOCKS 512
 __device__ __forceinline__ bool jlx_rehearses() { return gridDim.x * gridDim.y * gridDim.z <= JLX_REHEARSAL_MAX_BLOCKS; }
 

@@ -124,6 +124,7 @@ def _splits(t: torch.Tensor | None, splits: int) -> tuple[int, int]:
 
 
 DELTA_MAX_TERMS = 3
+DELTA_MAX_STREAMS = 64  # rows x split-K partials that one token may add (csrc/elementwise.cu)
 DISPATCH_MAX_ROWS, DISPATCH_MAX_PAIRS = 16, 64  # csrc/elementwise.cu
 
 

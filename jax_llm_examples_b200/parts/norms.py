@@ -27,7 +27,9 @@ class RMSNorm(Norm):
         out = torch.empty((n, x.shape[1]), dtype=out_dtype, device=dev)
         out32 = torch.empty((n, x.shape[1]), dtype=torch.float32, device=dev) if want_f32 else None
         # a sum of terms (an expert layer's rows still in expert order) is added term by term in the kernel
-        if isinstance(delta, RowSum) and len(delta.terms) <= K.DELTA_MAX_TERMS:
+        # (the kernel takes so many terms, rows per token and partials; beyond that the sum is made by its producer)
+        if isinstance(delta, RowSum) and len(delta.terms) <= K.DELTA_MAX_TERMS and all(t.k <= 16 for t in delta.terms) and \
+                sum((t.k if t.index is not None else 1) * t.splits for t in delta.terms) <= K.DELTA_MAX_STREAMS:
             terms = [(t.data, t.splits, t.index, t.k, t.base) for t in delta.terms]
         else:
             d = as_rows(delta)

@@ -56,6 +56,33 @@ def test_norm_part(dtype, tol):
     assert H.rel_err(h32.cpu().numpy(), ref.numpy()) < 3e-6
 
 
+@pytest.mark.parametrize("k, splits", [(2, 3), (16, 5)])
+def test_norm_part_adds_an_expert_layers_rows_in_the_kernel_or_lets_their_producer(k, splits):
+    """A sum of terms (rows still in expert order) is added by the norm's kernel as long as a token adds no more rows and
+    partials than the kernel takes (64); beyond that the norm asks the producer for the finished sum."""
+    import jax_llm_examples_b200 as J
+    from jax_llm_examples_b200.kernels import api as K
+    from jax_llm_examples_b200.parts import RMSNorm, Rows, RowSum, Runtime
+
+    N, D = 5, 1024
+    rt = Runtime(torch.bfloat16, torch.device(DEV))
+    ctx, _ = _ctx(J, rt, [N], [0])
+    g = 1 + 0.1 * torch.randn(D, device=DEV)
+    x, y = torch.randn(N, D, device=DEV), torch.randn(splits, N * k, D, device=DEV)
+    pos = torch.randperm(N * k, device=DEV).to(torch.int32)
+    total = y.sum(0)[pos.long()].reshape(N, k, D).sum(1)
+    asked = []
+
+    def materialize():
+        asked.append(True)
+        return total.clone()
+
+    h, _, _ = RMSNorm(g, 1e-6).forward(ctx, x.clone(), RowSum([Rows(y, splits, pos, k, 0)], materialize), out_dtype=torch.bfloat16)
+    ref = plain.rms_norm((x + total).cpu(), g.cpu(), 1e-6)
+    assert H.rel_err(h.float().cpu().numpy(), ref.numpy()) < 1e-2
+    assert bool(asked) == (k * splits > K.DELTA_MAX_STREAMS)
+
+
 @pytest.mark.parametrize("dtype, tol", [(torch.float32, 1e-5), (torch.bfloat16, 2e-2)])
 @pytest.mark.parametrize("rope, chunk, dh", [(True, 24, 32), (False, None, 64)])
 def test_attention_part_with_its_position_encoding(dtype, tol, rope, chunk, dh):
