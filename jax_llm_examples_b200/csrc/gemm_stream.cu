@@ -146,6 +146,7 @@ struct StreamArgs {
   int silu;              // 1: rows come in blocks of [16 gate, 16 up]; out[m, j] = silu(gate_j) * up_j, [rows, N / 2]
   int splits;
   int k_per_split;       // multiple of BK
+  int offsets_settled;   // grouped: offsets and tile list were complete before the kernel in front of this one began its work
   int* status;
 };
 
@@ -232,26 +233,36 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   __shared__ int failed;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  pdl_launch_dependents();
+  // A grouped product lets its successor start only after its own wait for its predecessor (below): the successor
+  // then knows, before its own wait, that everything older than this product is complete.  That is what
+  // `offsets_settled` of the NEXT grouped product over the same offsets (an expert layer's down product after its
+  // gate/up product) rests on: it reads the offsets and the tile list at once and asks for its first weight tiles
+  // while this product still runs, as a dense product does.
+  if (!args.offsets) pdl_launch_dependents();
   if (threadIdx.x == 0) {
     prefetch_map(&map_w);
     prefetch_map(&map_a);
   }
 
-  // ---- which tile.  The group offsets are written by an earlier kernel of the stream: wait for it first.
+  // ---- which tile.  The group offsets are written by an earlier kernel of the stream: wait for it first, unless
+  // they are known to be settled (then they are read past L1, which may hold lines of an earlier step).
   int row_lo, row_hi, group = 0;
+  const bool settled = args.offsets && args.offsets_settled;
   if (args.offsets) {
-    pdl_wait();
+    if (!settled) {
+      pdl_wait();
+      pdl_launch_dependents();
+    }
     int t = blockIdx.y, found = 0;
     if (args.tile_list) {
-      if (t >= args.n_tiles[0]) return;
-      group = args.tile_list[2 * t];
-      row_lo = args.tile_list[2 * t + 1];
-      row_hi = args.offsets[group + 1];
+      if (t >= __ldcg(args.n_tiles)) return;
+      group = __ldcg(args.tile_list + 2 * t);
+      row_lo = __ldcg(args.tile_list + 2 * t + 1);
+      row_hi = __ldcg(args.offsets + group + 1);
       found = 1;
     }
     for (int e = 0; !found && e < args.E; ++e) {
-      const int lo = args.offsets[e], hi = args.offsets[e + 1];
+      const int lo = __ldcg(args.offsets + e), hi = __ldcg(args.offsets + e + 1);
       const int tiles = (hi - lo + BT - 1) / BT;
       if (t < tiles) { row_lo = lo + t * BT; row_hi = hi; group = e; found = 1; break; }
       t -= tiles;
@@ -300,6 +311,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       int iw = 0, ia = 0;
       for (; iw < k_iters && iw < SW; ++iw) load_w(iw);
       pdl_wait();
+      if (settled) pdl_launch_dependents();  // (see the top of the kernel)
       for (; ia < k_iters && ia < SA; ++ia) load_a(ia);
       // both rings advance as their stages come free; neither waits for the other
       uint32_t idle = 0;
@@ -383,7 +395,7 @@ gemm_stream_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_rank();  // 0 or 1: blockIdx.x is even or odd
-  pdl_launch_dependents();
+  if (!args.offsets) pdl_launch_dependents();  // grouped: after the wait, as in gemm_stream_kernel
   if (threadIdx.x == 0) {
     prefetch_map(&map_w);
     prefetch_map(&map_a);
@@ -393,6 +405,7 @@ gemm_stream_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
   int row_lo, row_hi, group = 0;
   if (args.offsets) {
     pdl_wait();
+    pdl_launch_dependents();
     int t = blockIdx.y, found = 0;
     if (args.tile_list) {
       if (t >= args.n_tiles[0]) return;
@@ -605,10 +618,12 @@ JLX_API int jlx_gemm_stream_token_tile(int rows_hint) { return pick_bt(rows_hint
 //         [rows, N / 2] = silu(gate) * up; no split-K.
 // tile_list / n_tiles (optional, grouped only): the row tiles that have rows, made by jlx_expert_sort for the
 // tile width jlx_gemm_stream_token_tile(rows_hint); without them every block walks the offsets.
+// offsets_settled (grouped only): the caller's word that the kernel launched just before this one on the stream is a
+// grouped product of this library over the same offsets and tile list (so that these were complete before it began).
 // Returns the split count used through *splits_used (it may be lower than asked).
 JLX_API int jlx_gemm_stream(const void* A, const void* W, void* out, int out_is_f32, int rows, int N, int K,
                             const int* offsets, int E, int rows_hint, int splits, float* scratch, int mode,
-                            const int* tile_list, const int* n_tiles, int* splits_used, int* status,
+                            const int* tile_list, const int* n_tiles, int offsets_settled, int* splits_used, int* status,
                             cudaStream_t stream) {
   JLX_REQUIRE(rows >= 0 && N > 0 && K > 0, "gemm_stream: bad sizes rows=%d N=%d K=%d", rows, N, K);
   JLX_REQUIRE(K % 8 == 0, "gemm_stream: K = %d is no multiple of 8 (TMA needs 16-byte row strides); use the SIMT product", K);
@@ -637,6 +652,7 @@ JLX_API int jlx_gemm_stream(const void* A, const void* W, void* out, int out_is_
   a.tile_list = offsets ? tile_list : nullptr; a.n_tiles = n_tiles;
   a.out = (splits > 1 && mode == 0) ? (void*)scratch : out;
   a.out_is_f32 = out_is_f32; a.silu = mode == 2; a.splits = splits; a.k_per_split = kps; a.status = status;
+  a.offsets_settled = offsets && offsets_settled;
   // Row tiles to launch blocks for.  Grouped: a group of r rows has ceil(r / bt) <= r / bt + 1 tiles and only a group
   // with rows has any, so there are at most rows / bt + min(E, rows) of them.  (A looser bound costs time: a block
   // without a tile returns at once, but with the kernel's shared memory only two blocks fit an SM at a time, and with

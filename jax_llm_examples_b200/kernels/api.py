@@ -346,13 +346,15 @@ def gemm_stream_token_tile(rows_hint: int) -> int:
 def gemm_stream(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: torch.Tensor,
                 offsets: torch.Tensor | None = None, rows_hint: int = 0, splits: int = 1,
                 scratch: torch.Tensor | None = None, mode: int = GEMM_PLAIN,
-                tiles: tuple[torch.Tensor, torch.Tensor] | None = None) -> int:
+                tiles: tuple[torch.Tensor, torch.Tensor] | None = None, offsets_settled: bool = False) -> int:
     """a @ w^T on the tcgen05 tensor cores (bfloat16 in, float32 accumulate).  a: [M, K]; w: [N, K] or,
     with row-group offsets [E + 1], [E, N, K].
     GEMM_PLAIN: out [M, N] bfloat16 or float32; splits > 1 cuts K across blocks (scratch: float32
     [splits * M * N]) and adds the partials.  GEMM_PARTIALS: out is float32 [splits, M, N], left for the
     consumer to add.  GEMM_SWIGLU: w's rows are interleaved [16 gate, 16 up]; out [M, N / 2] =
     silu(gate) * up.  ``tiles`` = (tile_list, n_tiles) from expert_sort for the same rows_hint.
+    ``offsets_settled``: the kernel launched just before this call on the stream was a grouped gemm_stream over the
+    same offsets and tiles (this one then finds its tile and asks for its weights without waiting for that one).
     Returns the split count used."""
     _contig(a, w, out, offsets, scratch)
     M, K = a.shape
@@ -370,7 +372,8 @@ def gemm_stream(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: tor
     used = c_int(1)
     _run("gemm_stream", "jlx_gemm_stream", _ptr(a), _ptr(w), _ptr(out), c_int(int(out.dtype == torch.float32)), c_int(M),
          c_int(N), c_int(K), _ptr(offsets), c_int(E), c_int(rows_hint), c_int(splits), _ptr(scratch), c_int(mode),
-         _ptr(tiles[0]) if tiles else None, _ptr(tiles[1]) if tiles else None, ctypes.byref(used), _ptr(status), _stream())
+         _ptr(tiles[0]) if tiles else None, _ptr(tiles[1]) if tiles else None, c_int(int(offsets_settled and offsets is not None)),
+         ctypes.byref(used), _ptr(status), _stream())
     return used.value
 
 

@@ -5,9 +5,11 @@ from __future__ import annotations
 import torch
 
 from ..kernels import api as K
+from ..tracing import active as tracing_active
 from ..tracing import scope
 from .base import Dispatch, FeedForward, Rows, RowSum, StepContext, as_rows, register_part
-from .linear import (STREAM_MAX_ROWS, group_rows_hint, grouped_linear, grouped_swiglu_linear, interleave_gate_up, linear,
+from .linear import (STREAM_MAX_ROWS, group_rows_hint, grouped_linear, grouped_swiglu_linear, grouped_swiglu_streams,
+                     interleave_gate_up, linear,
                      swiglu_linear)
 
 
@@ -166,10 +168,11 @@ class RoutedExperts(FeedForward):
                     K.permute_scale(h32, sorted_pair, topk_w, a_sorted, k, extra)
             groups = E + 1 if merged else E
             with scope("we_gate_up"):
+                one_product = grouped_swiglu_streams(a_sorted, self.we_gate_up[:groups], self.interleaved)
                 act = grouped_swiglu_linear(ctx, a_sorted, self.we_gate_up[:groups], offsets, self.interleaved, rt.dtype, extra, tiles)
-            with scope("we_down"):
+            with scope("we_down"):  # (a timer's events between the two launches would come between them on the stream)
                 y = grouped_linear(ctx, act, self.we_down[:groups], offsets, torch.float32, partials=True, largest_group=extra,
-                                   tiles=tiles)
+                                   tiles=tiles, after_grouped=one_product and not tracing_active())
         if side is not None:
             torch.cuda.current_stream().wait_stream(side)
         elif self.shared is not None and not merged:

@@ -112,9 +112,11 @@ def group_rows_hint(rows: int, groups: int, largest_group: int = 0) -> int:
 
 
 def grouped_linear(ctx: StepContext, a_sorted: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor,
-                   out_dtype: torch.dtype, partials: bool = False, largest_group: int = 0, tiles=None):
+                   out_dtype: torch.dtype, partials: bool = False, largest_group: int = 0, tiles=None, after_grouped: bool = False):
     """Rows [offsets[e], offsets[e+1]) of a_sorted times w[e]^T.  w: [E, N, K].  With ``partials`` the result
-    is float32 :class:`Rows`; few rows (few groups in use) then get K cut across blocks to fill the GPU."""
+    is float32 :class:`Rows`; few rows (few groups in use) then get K cut across blocks to fill the GPU.
+    ``after_grouped``: a_sorted was made by the call just before this one, ``grouped_swiglu_linear`` over the same
+    offsets and tiles, which ran as one streaming product (``grouped_swiglu_streams``; see ``K.gemm_stream``)."""
     rows, E, N = a_sorted.shape[0], w.shape[0], w.shape[1]
     if _streams(a_sorted, w, False):
         hint = _group_rows_hint(rows, E, largest_group)
@@ -123,14 +125,19 @@ def grouped_linear(ctx: StepContext, a_sorted: torch.Tensor, w: torch.Tensor, of
             splits = _splits_for(N, a_sorted.shape[1], min(E, rows)) if rows <= STREAM_MAX_ROWS else 1
             out = torch.empty((splits, rows, N), dtype=torch.float32, device=a_sorted.device)
             used = K.gemm_stream(a_sorted, w, out, ctx.status, offsets=offsets, rows_hint=hint, splits=splits, mode=K.GEMM_PARTIALS,
-                                 tiles=tiles)
+                                 tiles=tiles, offsets_settled=after_grouped)
             return Rows(out[:used], used)
         out = torch.empty((rows, N), dtype=out_dtype, device=a_sorted.device)
-        K.gemm_stream(a_sorted, w, out, ctx.status, offsets=offsets, rows_hint=hint, tiles=tiles)
+        K.gemm_stream(a_sorted, w, out, ctx.status, offsets=offsets, rows_hint=hint, tiles=tiles, offsets_settled=after_grouped)
         return out
     out = torch.empty((rows, N), dtype=torch.float32 if partials else out_dtype, device=a_sorted.device)
     K.gemm_simt(a_sorted, w, out, offsets)
     return Rows(out, 1) if partials else out
+
+
+def grouped_swiglu_streams(a_sorted: torch.Tensor, w_gate_up: torch.Tensor, interleaved: bool) -> bool:
+    """Whether ``grouped_swiglu_linear`` runs as ONE streaming product (activation in its epilogue), nothing after it."""
+    return interleaved and _streams(a_sorted, w_gate_up, False)
 
 
 def grouped_swiglu_linear(ctx: StepContext, a_sorted: torch.Tensor, w_gate_up: torch.Tensor, offsets: torch.Tensor,
@@ -138,7 +145,7 @@ def grouped_swiglu_linear(ctx: StepContext, a_sorted: torch.Tensor, w_gate_up: t
     """``largest_group``: rows of a group known to be large (a shared expert's), so that one tile holds it."""
     rows, E, F = a_sorted.shape[0], w_gate_up.shape[0], w_gate_up.shape[1] // 2
     act = torch.empty((rows, F), dtype=out_dtype, device=a_sorted.device)
-    if interleaved and _streams(a_sorted, w_gate_up, False):
+    if grouped_swiglu_streams(a_sorted, w_gate_up, interleaved):
         hint = _group_rows_hint(rows, E, largest_group)
         K.gemm_stream(a_sorted, w_gate_up, act, ctx.status, offsets=offsets, rows_hint=hint, mode=K.GEMM_SWIGLU, tiles=tiles)
         return act
