@@ -722,6 +722,40 @@ def test_grouped_product_with_the_sort_kernels_tile_list(E, N, k, extra):
             close(out[lo:hi], a[lo:hi].double() @ w[e].double().T, 1e-5)
 
 
+@pytest.mark.parametrize("E, N, k, extra", [(16, 1, 1, 1), (16, 8, 1, 0), (40, 30, 2, 0)])
+def test_a_grouped_product_right_after_another_over_the_same_groups(E, N, k, extra):
+    """An expert layer's down product follows its gate/up product over the same offsets and tile list; told so, it
+    finds its tile and asks for its weights before it waits for the gate/up product.  The result is the one of the
+    product that waits first, every time (the pair is launched back to back, programmatic dependent launch and all)."""
+    api = K()
+    D, F = 256, 512
+    idx = torch.stack([torch.randperm(E, device=DEV)[:k] for _ in range(N)]).to(torch.int32)
+    groups, rows = E + (extra > 0), N * k + extra
+    hint = max(3, extra)
+    tile_rows = api.gemm_stream_token_tile(hint)
+    off = torch.empty(E + 2, device=DEV, dtype=torch.int32)
+    pair, pos, st = torch.empty(N * k, device=DEV, dtype=torch.int32), torch.empty(N * k, device=DEV, dtype=torch.int32), status()
+    tl = torch.full((2 * (-(-rows // tile_rows) + groups),), -1, device=DEV, dtype=torch.int32)
+    nt = torch.zeros(1, device=DEV, dtype=torch.int32)
+    a = torch.randn(rows, D, device=DEV).bfloat16()
+    w_gu = (0.1 * torch.randn(groups, 2 * F, D, device=DEV)).bfloat16()
+    w_dn = (0.1 * torch.randn(groups, D, F, device=DEV)).bfloat16()
+    offs = off[: groups + 1]
+    results = []
+    for settled in (False, True, True, True):
+        act = torch.full((rows, F), float("nan"), device=DEV, dtype=torch.bfloat16)
+        y = torch.full((2, rows, D), float("nan"), device=DEV)
+        api.expert_sort(idx, off, pair, pos, E, st, extra, tile_rows, tl, nt)
+        api.gemm_stream(a, w_gu, act, st, offsets=offs, rows_hint=hint, mode=api.GEMM_SWIGLU, tiles=(tl, nt))
+        used = api.gemm_stream(act, w_dn, y, st, offsets=offs, rows_hint=hint, splits=2, mode=api.GEMM_PARTIALS, tiles=(tl, nt),
+                               offsets_settled=settled)
+        results.append(y[:used].sum(0))
+    torch.cuda.synchronize()
+    assert int(st) == 0 and not bool(torch.isnan(results[0]).any())
+    for r in results[1:]:
+        assert torch.equal(r, results[0])
+
+
 @pytest.mark.parametrize("kind, size", [("window", 100), ("chunk", 192), ("chunk", 80)])
 def test_attention_edges_of_windows_and_chunks(kind, size):
     """A key whose score would swamp all others sits exactly on the first position a query may see, and then
