@@ -52,7 +52,7 @@ class RoutedExperts(FeedForward):
     kernel_libraries_bf16 = ("gemm_stream",)
     needs_f32_input = True
     OVERLAP_MIN_ROWS = 512  # from this many rows on (prompt portions), the shared expert runs on a second stream beside the routed ones
-    FORK_MIN_ROWS = 3  # and in steps of few rows (decoding) from this many on; below, it rides as a group of the routed products
+    FORK_MIN_ROWS = 2  # and in steps of few rows (decoding) from this many on; below, it rides as a group of the routed products
 
     def __init__(self, w_router: torch.Tensor, we_gate_up: torch.Tensor, we_down: torch.Tensor, top_k: int,
                  shared: DenseSwiGLU | None = None):
@@ -87,10 +87,10 @@ class RoutedExperts(FeedForward):
 
     def placement(self, ctx: StepContext, n: int) -> tuple[bool, bool]:
         """Where the shared expert runs in a step of n rows: (on a second stream beside the routed experts, as one more
-        group of the routed experts' products).  One or two rows: as a group (two launches fewer; with so few blocks one
-        kernel streams better than two).  More rows: on a second stream, beside the sort, the gather and the routed
-        products: its weights stream while those small kernels would leave the memory idle (decode at batch 8: +3.7 %,
-        batch 64: +6.5 %; batch 1 would lose 4 %).  Prompt portions: the routed experts stream their weights once for
+        group of the routed experts' products).  One row: as a group (two launches fewer; with so few blocks one
+        kernel streams better than two).  More rows: on a second stream, beside the routed products: its weights stream
+        while the routed products' few blocks leave memory bandwidth unused, or their short predecessors leave it idle
+        (decode at batch 2: +7.5 %, batch 8: +3.7 %, batch 64: +6.5 %; batch 1 would lose 2 %).  Prompt portions: the routed experts stream their weights once for
         about a hundred rows each (bound by HBM), the shared expert's products are dense (bound by the tensor cores);
         side by side, the tails and the small kernels of either hide behind the other.  Between STREAM_MAX_ROWS and
         OVERLAP_MIN_ROWS: one after the other."""

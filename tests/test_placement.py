@@ -27,8 +27,8 @@ def test_where_the_shared_expert_runs():
 
     ffn, ws = _experts(True), object()
     assert ffn.merged
-    # one or two rows: a group of the routed experts' products; a few rows up to the streaming limit: a second stream
-    assert ffn.placement(_ctx(ws), 1) == (False, True) and ffn.placement(_ctx(ws), 2) == (False, True)
+    # one row: a group of the routed experts' products; a few rows up to the streaming limit: a second stream
+    assert ffn.FORK_MIN_ROWS == 2 and ffn.placement(_ctx(ws), 1) == (False, True)
     assert ffn.placement(_ctx(ws), ffn.FORK_MIN_ROWS) == (True, False) and ffn.placement(_ctx(ws), linear.STREAM_MAX_ROWS) == (True, False)
     # between the streaming limit and a prompt portion worth overlapping: one after the other; then beside again
     assert ffn.placement(_ctx(ws), linear.STREAM_MAX_ROWS + 1) == (False, False)

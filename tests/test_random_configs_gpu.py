@@ -39,7 +39,7 @@ def random_config(rng: random.Random, wide: bool = False) -> dict:
     if wide:
         # widths from 1024 on take the kernels that a decode step of the real sizes takes (a cluster of blocks per row
         # for the norms, the norm that also sorts and gathers); a shared expert of the experts' shape rides as a group
-        # of the experts' products when a step has one or two rows
+        # of the experts' products when a step has one row
         cfg["hidden_size"] = rng.choice([1024, 1032, 1280, 2048])
         cfg["intermediate_size"] = rng.choice([32, 64, 96, 128])
         if rng.random() < 0.6:
